@@ -1,0 +1,136 @@
+"""GEMM on the tcgen05 tensor cores (bf16 / fp16 in, fp32 accumulate in tensor memory).
+
+``gemm(a, b, ...)`` computes ``a @ b.T``-style products where each operand is
+given by its *logical* ``[rows, K]`` matrix: a row-major tensor is passed
+"K-major", a transposed view (``x.t()``) is passed "MN-major" — no copy is made
+in either case.  ``linear`` is the autograd function used by every Linear layer of
+this package on CUDA; on CPU (or for dtypes/shapes the kernel does not take) it
+falls back to ``torch.nn.functional.linear``.
+
+Kernel: ``csrc/gemm_sm100a.cu``.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+_EPI = {None: 0, "none": 0, "bias": 1, "gelu": 2}
+
+
+def _operand(t: torch.Tensor):
+    """Classify a 2-D/3-D operand [.., rows, K]: returns (tensor, mn_major, ld, batch_stride)."""
+    if t.stride(-1) == 1 and (t.shape[-2] == 1 or t.stride(-2) >= t.shape[-1]):
+        return t, 0, t.stride(-2) if t.shape[-2] > 1 else t.shape[-1], (t.stride(0) if t.dim() == 3 else 0)
+    if t.stride(-2) == 1 and t.stride(-1) >= t.shape[-2]:
+        return t, 1, t.stride(-1), (t.stride(0) if t.dim() == 3 else 0)
+    t = t.contiguous()
+    return t, 0, t.stride(-2), (t.stride(0) if t.dim() == 3 else 0)
+
+
+def supported(a: torch.Tensor, b: torch.Tensor) -> bool:
+    if not (a.is_cuda and b.is_cuda and _lib.has_cuda_kernels()):
+        return False
+    if a.dtype not in (torch.bfloat16, torch.float16) or a.dtype != b.dtype:
+        return False
+    return True
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+    epilogue: Optional[str] = None,
+    out: Optional[torch.Tensor] = None,
+    accumulate: bool = False,
+    aux: Optional[torch.Tensor] = None,
+    block_n: int = 0,
+) -> torch.Tensor:
+    """``out[.., M, N] = epilogue(a[.., M, K] @ b[.., N, K]^T (+ bias))`` on tcgen05.
+
+    ``a`` / ``b`` may be transposed views (MN-major).  ``aux`` (optional, same shape
+    as ``out``) receives the pre-activation ``acc + bias`` when ``epilogue="gelu"``.
+    """
+    assert a.dim() == b.dim() and a.dim() in (2, 3), "gemm takes 2-D or batched 3-D operands"
+    M, K = a.shape[-2], a.shape[-1]
+    N = b.shape[-2]
+    assert b.shape[-1] == K, f"K mismatch {a.shape} x {b.shape}"
+    batch = a.shape[0] if a.dim() == 3 else 1
+    a, a_mn, lda, sa = _operand(a)
+    b, b_mn, ldb, sb = _operand(b)
+    shape = (batch, M, N) if a.dim() == 3 else (M, N)
+    if out is None:
+        assert not accumulate
+        out = torch.empty(shape, dtype=a.dtype, device=a.device)
+    assert out.stride(-1) == 1
+    ldc = out.stride(-2) if M > 1 else N
+    sc = out.stride(0) if out.dim() == 3 else 0
+    lib = _lib.cuda_lib()
+    status = _lib.status_word(a.device)
+    rc = lib.oslo_gemm_tcgen05(
+        _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(aux),
+        ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(batch),
+        ctypes.c_longlong(lda), ctypes.c_longlong(ldb), ctypes.c_longlong(ldc),
+        ctypes.c_longlong(sa), ctypes.c_longlong(sb), ctypes.c_longlong(sc),
+        ctypes.c_int(a_mn), ctypes.c_int(b_mn), ctypes.c_int(1 if a.dtype == torch.bfloat16 else 0),
+        ctypes.c_int(_EPI[epilogue] if bias is not None or epilogue == "gelu" else 0),
+        ctypes.c_int(1 if accumulate else 0), ctypes.c_int(block_n), ctypes.c_int(_lib.num_sms()),
+        _lib.ptr(status), _lib.stream_ptr(),
+    )
+    if rc != 0:
+        raise RuntimeError(f"oslo_gemm_tcgen05 failed with code {rc} for shapes {tuple(a.shape)} x {tuple(b.shape)}")
+    return out
+
+
+def _aligned(*dims) -> bool:
+    return all(d % 8 == 0 for d in dims)
+
+
+class _LinearFn(torch.autograd.Function):
+    """y = x W^T (+ b); dX = dY W; dW = dY^T x; db = column sum — three tcgen05 GEMMs."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        x2 = x.reshape(-1, x.shape[-1])
+        y = gemm(x2, weight, bias=bias, epilogue="bias" if bias is not None else None)
+        ctx.save_for_backward(x2, weight)
+        ctx.has_bias = bias is not None
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, weight = ctx.saved_tensors
+        gy2 = gy.reshape(-1, gy.shape[-1])
+        if not gy2.is_contiguous():
+            gy2 = gy2.contiguous()
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            # dX[M, K] = dY[M, N] x (W^T)[K, N]^T : B operand is W viewed [K, N] -> MN-major
+            gx = gemm(gy2, weight.t()).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            # dW[N, K] = (dY^T)[N, M] x (x^T)[K, M]^T : both operands MN-major
+            gw = gemm(gy2.t(), x2.t())
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            gb = gy2.sum(dim=0)
+        return gx, gw, gb
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Drop-in for ``F.linear`` that runs the tcgen05 kernel on CUDA bf16/fp16 inputs."""
+    if supported(x, weight) and _aligned(x.shape[-1], weight.shape[0], x.numel() // x.shape[-1]):
+        if bias is not None and bias.dtype != x.dtype:
+            bias = bias.to(x.dtype)
+        return _LinearFn.apply(x, weight, bias)
+    return F.linear(x, weight, bias)
+
+
+def matmul_nt(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``a @ b.transpose(-1, -2)`` (no autograd) with tcgen05 when possible."""
+    if supported(a, b) and a.dim() in (2, 3):
+        return gemm(a, b)
+    return torch.matmul(a, b.transpose(-1, -2))
