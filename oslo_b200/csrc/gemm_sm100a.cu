@@ -35,6 +35,9 @@ constexpr int kGemmThreads = 192;
 
 struct GemmParams {
   int M, N, K, batch;
+  int batch_inner;    // batch index b = outer * batch_inner + inner; each part has its own stride in the maps
+  int causal;         // 0 none; 1 skip tiles entirely above the diagonal (n0 > m0 + 127);
+                      // 2 reduce only k <= m0 + 127 (lower-triangular A); 3 reduce only k >= m0 (upper-triangular A^T)
   int m_blocks, n_blocks;
   int epilogue;       // 0 none, 1 +bias, 2 gelu(+bias if given), 3 reserved
   int accumulate;     // 1: C = C_old + result
@@ -42,7 +45,8 @@ struct GemmParams {
   const void* bias;   // [N] in the operand dtype, or null
   void* c_ptr;        // plain pointer to C (used for accumulate)
   long long ldc;      // row stride of C in elements
-  long long stride_c; // batch stride of C in elements
+  long long stride_c; // inner batch stride of C in elements
+  long long stride_c_outer;  // outer batch stride of C in elements
   void* aux_ptr;      // optional second output: pre-activation (acc + bias), same layout as C
   int* status;
 };
@@ -71,6 +75,16 @@ OSLO_DEVINL void tile_coords(int tile, const GemmParams& p, int& b, int& mb, int
   const int r = t - g * group_size;
   mb = first_m + r % rows;
   nb = r / rows;
+}
+
+// k-block range [kb0, kb1) a tile has to reduce over, or skip = true when it has no work.
+OSLO_DEVINL void tile_k_range(const GemmParams& p, int m0, int n0, int num_kb, int& kb0, int& kb1, bool& skip) {
+  kb0 = 0;
+  kb1 = num_kb;
+  skip = false;
+  if (p.causal == 1) skip = n0 > m0 + kBlockM - 1;
+  else if (p.causal == 2) kb1 = min(num_kb, (m0 + kBlockM + kBlockK - 1) / kBlockK);
+  else if (p.causal == 3) kb0 = min(num_kb - 1, m0 / kBlockK);
 }
 
 template <int BLOCK_N, bool A_MN, bool B_MN>
@@ -132,7 +146,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         int b, mb, nb;
         tile_coords(tile, p, b, mb, nb);
         const int m0 = mb * kBlockM, n0 = nb * BLOCK_N;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int bi = b % p.batch_inner, bo = b / p.batch_inner;
+        int kb0, kb1;
+        bool skip;
+        tile_k_range(p, m0, n0, num_kb, kb0, kb1, skip);
+        if (skip) continue;
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
             ok = false;
             if (p.status) atomicCAS(p.status, kStatusOk, kStatusWaitTimeoutProducer);
@@ -144,15 +163,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const int k0 = kb * kBlockK;
           if (A_MN) {
 #pragma unroll
-            for (int c = 0; c < kBlockM / 64; ++c) tma_load_3d(sa + c * 8192, &tmA, &full_bar[stage], m0 + c * 64, k0, b);
+            for (int c = 0; c < kBlockM / 64; ++c) tma_load_4d(sa + c * 8192, &tmA, &full_bar[stage], m0 + c * 64, k0, bi, bo);
           } else {
-            tma_load_3d(sa, &tmA, &full_bar[stage], k0, m0, b);
+            tma_load_4d(sa, &tmA, &full_bar[stage], k0, m0, bi, bo);
           }
           if (B_MN) {
 #pragma unroll
-            for (int c = 0; c < BLOCK_N / 64; ++c) tma_load_3d(sb + c * 8192, &tmB, &full_bar[stage], n0 + c * 64, k0, b);
+            for (int c = 0; c < BLOCK_N / 64; ++c) tma_load_4d(sb + c * 8192, &tmB, &full_bar[stage], n0 + c * 64, k0, bi, bo);
           } else {
-            tma_load_3d(sb, &tmB, &full_bar[stage], k0, n0, b);
+            tma_load_4d(sb, &tmB, &full_bar[stage], k0, n0, bi, bo);
           }
           if (armed < kStages) ++armed;
           if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -180,10 +199,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int kb0 = 0, kb1 = num_kb;
+        if (p.causal) {
+          int b, mb, nb;
+          bool skip;
+          tile_coords(tile, p, b, mb, nb);
+          tile_k_range(p, mb * kBlockM, nb * BLOCK_N, num_kb, kb0, kb1, skip);
+          if (skip) continue;
+        }
         if (!mbar_wait_bounded(&tmem_empty[buf], acc_phase ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * BLOCK_N;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(stage_base + stage * Cfg::kStageBytes);
@@ -196,7 +223,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                                      : make_smem_desc_sw128(sa + k * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc_sw128(sb + k * 2048, 8192, 1024)
                                      : make_smem_desc_sw128(sb + k * 32, 16, 1024);
-            umma_f16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16(tmem_d, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -220,6 +247,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int b, mb, nb;
       tile_coords(tile, p, b, mb, nb);
       const int m0 = mb * kBlockM, n0 = nb * BLOCK_N;
+      const int bi = b % p.batch_inner, bo = b / p.batch_inner;
+      if (p.causal == 1 && n0 > m0 + kBlockM - 1) continue;
       if (!mbar_wait_bounded(&tmem_full[buf], acc_phase, abort_flag)) {
         ok = false;
         if (p.status && lane == 0) atomicCAS(p.status, kStatusOk, kStatusWaitTimeoutEpilogue);
@@ -272,8 +301,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
         if (p.accumulate && row < p.M) {
-          const uint16_t* cin = static_cast<const uint16_t*>(p.c_ptr) + static_cast<long long>(b) * p.stride_c +
-                                static_cast<long long>(row) * p.ldc + col0;
+          const uint16_t* cin = static_cast<const uint16_t*>(p.c_ptr) + static_cast<long long>(bi) * p.stride_c +
+                                static_cast<long long>(bo) * p.stride_c_outer + static_cast<long long>(row) * p.ldc + col0;
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             if (col0 + g * 8 < p.N) {
@@ -327,7 +356,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_3d(pass == 0 ? &tmAux : &tmC, sbuf_ptr, col0, m0 + q * 32, b);
+            tma_store_4d(pass == 0 ? &tmAux : &tmC, sbuf_ptr, col0, m0 + q * 32, bi, bo);
             tma_store_commit();
           }
           sbuf ^= 1;
@@ -365,16 +394,20 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 3-D map over a [batch, rows, cols] tensor (cols contiguous), 128-byte swizzle.
-static int make_map(CUtensorMap* map, const void* base, int is_bf16, long long cols, long long rows, long long batch,
-                    long long row_stride_elems, long long batch_stride_elems, int box_cols, int box_rows) {
+// 4-D map over a [batch_outer, batch_inner, rows, cols] tensor (cols contiguous), 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, int is_bf16, long long cols, long long rows, long long b_inner,
+                    long long b_outer, long long row_stride_elems, long long inner_stride_elems,
+                    long long outer_stride_elems, int box_cols, int box_rows) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -1;
-  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
-  cuuint64_t strides[2] = {(cuuint64_t)row_stride_elems * 2, (cuuint64_t)(batch > 1 ? batch_stride_elems : row_stride_elems * rows) * 2};
-  cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+  cuuint64_t dims[4] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)b_inner, (cuuint64_t)b_outer};
+  const long long dflt = row_stride_elems * rows;
+  cuuint64_t strides[3] = {(cuuint64_t)row_stride_elems * 2,
+                           (cuuint64_t)(b_inner > 1 ? inner_stride_elems : dflt) * 2,
+                           (cuuint64_t)(b_outer > 1 ? outer_stride_elems : dflt * b_inner) * 2};
+  cuuint32_t box[4] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -2;
@@ -407,16 +440,24 @@ static int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap&
 extern "C" int oslo_gemm_tcgen05(const void* A, const void* B, void* C, const void* bias, void* aux, int M, int N, int K,
                                  int batch, long long lda, long long ldb, long long ldc, long long stride_a,
                                  long long stride_b, long long stride_c, int a_mn, int b_mn, int is_bf16, int epilogue,
-                                 int accumulate, int block_n, int num_sms, int* status, void* stream_ptr) {
+                                 int accumulate, int block_n, int num_sms, int* status, void* stream_ptr,
+                                 int batch_outer, long long ostride_a, long long ostride_b, long long ostride_c,
+                                 int causal) {
   using namespace oslo;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
+  if (batch_outer <= 0) batch_outer = 1;
+  const int b_in = batch, b_out = batch_outer;
+  batch = b_in * b_out;
+  if (b_out > 1 && ((ostride_a % 8) || (ostride_b % 8) || (ostride_c % 8))) return -5;
+  if (causal && (M != N && causal == 1)) return -7;
   // TMA needs 16-byte aligned bases and strides
   auto bad = [](long long v) { return (v % 8) != 0; };
-  if (bad(lda) || bad(ldb) || bad(ldc) || (batch > 1 && (bad(stride_a) || bad(stride_b) || bad(stride_c))) ||
+  if (bad(lda) || bad(ldb) || bad(ldc) || (b_in > 1 && (bad(stride_a) || bad(stride_b) || bad(stride_c))) ||
       (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
       (reinterpret_cast<uintptr_t>(C) & 15) || (bias && (reinterpret_cast<uintptr_t>(bias) & 15)) || (N % 8) ||
       (a_mn && (M % 8)) || (!a_mn && (K % 8)) || (b_mn ? 0 : (K % 8)))
     return -5;
+  if (b_in == 1 && b_out == 1) batch = 1;
   if (block_n == 0) {
     const long long mb = (M + kBlockM - 1) / kBlockM;
     auto tiles = [&](int bn) { return (long long)batch * mb * ((N + bn - 1) / bn); };
@@ -427,24 +468,24 @@ extern "C" int oslo_gemm_tcgen05(const void* A, const void* B, void* C, const vo
     else if (N <= 128 && block_n > 128) block_n = 128;
   }
   GemmParams p;
-  p.M = M; p.N = N; p.K = K; p.batch = batch;
+  p.M = M; p.N = N; p.K = K; p.batch = batch; p.batch_inner = b_in; p.causal = causal; p.stride_c_outer = ostride_c;
   p.m_blocks = (M + kBlockM - 1) / kBlockM;
   p.n_blocks = (N + block_n - 1) / block_n;
   p.epilogue = epilogue; p.accumulate = accumulate; p.is_bf16 = is_bf16;
   p.bias = bias; p.c_ptr = C; p.ldc = ldc; p.stride_c = stride_c; p.aux_ptr = aux; p.status = status;
   CUtensorMap ta, tb, tc, taux;
   int rc;
-  if (a_mn) rc = make_map(&ta, A, is_bf16, M, K, batch, lda, stride_a, 64, kBlockK);
-  else      rc = make_map(&ta, A, is_bf16, K, M, batch, lda, stride_a, kBlockK, kBlockM);
+  if (a_mn) rc = make_map(&ta, A, is_bf16, M, K, b_in, b_out, lda, stride_a, ostride_a, 64, kBlockK);
+  else      rc = make_map(&ta, A, is_bf16, K, M, b_in, b_out, lda, stride_a, ostride_a, kBlockK, kBlockM);
   if (rc) return rc;
-  if (b_mn) rc = make_map(&tb, B, is_bf16, N, K, batch, ldb, stride_b, 64, kBlockK);
-  else      rc = make_map(&tb, B, is_bf16, K, N, batch, ldb, stride_b, kBlockK, block_n);
+  if (b_mn) rc = make_map(&tb, B, is_bf16, N, K, b_in, b_out, ldb, stride_b, ostride_b, 64, kBlockK);
+  else      rc = make_map(&tb, B, is_bf16, K, N, b_in, b_out, ldb, stride_b, ostride_b, kBlockK, block_n);
   if (rc) return rc;
-  rc = make_map(&tc, C, is_bf16, N, M, batch, ldc, stride_c, 64, 32);
+  rc = make_map(&tc, C, is_bf16, N, M, b_in, b_out, ldc, stride_c, ostride_c, 64, 32);
   if (rc) return rc;
   if (aux) {
     if (reinterpret_cast<uintptr_t>(aux) & 15) return -5;
-    rc = make_map(&taux, aux, is_bf16, N, M, batch, ldc, stride_c, 64, 32);
+    rc = make_map(&taux, aux, is_bf16, N, M, b_in, b_out, ldc, stride_c, ostride_c, 64, 32);
     if (rc) return rc;
   } else {
     taux = tc;

@@ -1,0 +1,147 @@
+"""GPT-NeoX style decoder (rotary on a fraction of the head dim, parallel attention + MLP residual).
+
+State-dict names follow Hugging Face ``GPTNeoXForCausalLM`` (``gpt_neox.layers.N.attention.query_key_value`` ...,
+``embed_out``); the fused QKV projection is laid out ``[heads, 3, head_dim]`` as there.  The model is written
+against :mod:`oslo_b200.nn` so every GEMM / norm / activation / softmax runs the sm_100a kernels on CUDA, and
+so the tensor-parallel wrapper can swap its linears for sharded ones by name.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+import oslo_b200.nn as onn
+from oslo_b200.nn import functional as OF
+
+from .config import GPTNeoXConfig
+from .modeling_utils import CausalLMOutput, PreTrainedModel
+
+
+def _sp_like(t, ref, module):
+    """Shard ``t`` (full batch) like ``ref`` when the model runs token-sharded between its linears."""
+    sp = getattr(module, "sequence_parallel_state", None)
+    if sp is None or t.shape[: ref.dim() - 1] == ref.shape[:-1]:
+        return t
+    return sp.shard(t)
+
+
+class GPTNeoXAttention(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.num_attention_heads = config.num_attention_heads
+        self.hidden_size = config.hidden_size
+        self.head_size = config.hidden_size // config.num_attention_heads
+        self.rotary_ndims = int(self.head_size * config.rotary_pct)
+        self.rotary_base = config.rotary_emb_base
+        self.max_positions = config.max_position_embeddings
+        self.query_key_value = onn.Linear(config.hidden_size, 3 * config.hidden_size)
+        self.dense = onn.Linear(config.hidden_size, config.hidden_size, skip_bias_add=True)
+        self._rope = None
+
+    def _tables(self, seq, device):
+        if self._rope is None or self._rope[0].shape[0] < seq or self._rope[0].device != device:
+            n = max(seq, self.max_positions)
+            self._rope = OF.rope_tables(n, self.rotary_ndims, self.rotary_base, device)
+        return self._rope
+
+    def forward(self, hidden_states, attention_mask=None):
+        qkv = self.query_key_value(hidden_states)  # [b, s, heads_local * 3 * hd]
+        b, s = qkv.shape[0], qkv.shape[1]
+        heads = qkv.shape[-1] // (3 * self.head_size)
+        qkv = qkv.view(b, s, heads, 3, self.head_size)
+        q, k, v = qkv[..., 0, :], qkv[..., 1, :], qkv[..., 2, :]
+        if self.rotary_ndims > 0:
+            cos, sin = self._tables(s, qkv.device)
+            q = OF.apply_rope(q, cos, sin, self.rotary_ndims, neox=True)
+            k = OF.apply_rope(k, cos, sin, self.rotary_ndims, neox=True)
+        ctx = OF.attention(q, k, v, causal=True, mask=attention_mask)
+        return self.dense(ctx)  # (out, bias)
+
+
+class GPTNeoXMLP(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.dense_h_to_4h = onn.Linear(config.hidden_size, config.intermediate_size, skip_bias_add=True)
+        self.dense_4h_to_h = onn.Linear(config.intermediate_size, config.hidden_size, skip_bias_add=True)
+
+    def forward(self, hidden_states):
+        h, bias = self.dense_h_to_4h(hidden_states)
+        h = OF.bias_gelu(h, bias)
+        return self.dense_4h_to_h(h)  # (out, bias)
+
+
+class GPTNeoXLayer(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.use_parallel_residual = config.use_parallel_residual
+        self.input_layernorm = onn.FusedLayerNorm(config.hidden_size, eps=config.layer_norm_eps)
+        self.post_attention_layernorm = onn.FusedLayerNorm(config.hidden_size, eps=config.layer_norm_eps)
+        self.attention = GPTNeoXAttention(config)
+        self.mlp = GPTNeoXMLP(config)
+        self.hidden_dropout = config.hidden_dropout
+
+    def forward(self, hidden_states, attention_mask=None):
+        attn, attn_bias = self.attention(self.input_layernorm(hidden_states), attention_mask)
+        p, tr = self.hidden_dropout, self.training
+        if self.use_parallel_residual:
+            mlp, mlp_bias = self.mlp(self.post_attention_layernorm(hidden_states))
+            x = OF.bias_dropout_add(attn, attn_bias, hidden_states, p, tr)
+            return OF.bias_dropout_add(mlp, mlp_bias, x, p, tr)
+        x = OF.bias_dropout_add(attn, attn_bias, hidden_states, p, tr)
+        mlp, mlp_bias = self.mlp(self.post_attention_layernorm(x))
+        return OF.bias_dropout_add(mlp, mlp_bias, x, p, tr)
+
+
+class GPTNeoXModel(PreTrainedModel):
+    config_class = GPTNeoXConfig
+
+    def __init__(self, config):
+        super().__init__(config)
+        self.embed_in = nn.Embedding(config.vocab_size, config.hidden_size)
+        self.layers = nn.ModuleList([GPTNeoXLayer(config) for _ in range(config.num_hidden_layers)])
+        self.final_layer_norm = onn.FusedLayerNorm(config.hidden_size, eps=config.layer_norm_eps)
+        self.gradient_checkpointing = False
+
+    def get_input_embeddings(self):
+        return self.embed_in
+
+    def forward(self, input_ids, attention_mask=None):
+        x = self.embed_in(input_ids)
+        for layer in self.layers:
+            if self.gradient_checkpointing and self.training:
+                x = torch.utils.checkpoint.checkpoint(layer, x, attention_mask, use_reentrant=False)
+            else:
+                x = layer(x, attention_mask)
+        return self.final_layer_norm(x)
+
+
+class GPTNeoXForCausalLM(PreTrainedModel):
+    config_class = GPTNeoXConfig
+    base_model_prefix = "gpt_neox"
+
+    def __init__(self, config):
+        super().__init__(config)
+        self.gpt_neox = GPTNeoXModel(config)
+        self.embed_out = onn.Linear(config.hidden_size, config.vocab_size, bias=False)
+        self.post_init()
+
+    def get_input_embeddings(self):
+        return self.gpt_neox.embed_in
+
+    def get_output_embeddings(self):
+        return self.embed_out
+
+    def gradient_checkpointing_enable(self):
+        self.gpt_neox.gradient_checkpointing = True
+
+    def forward(self, input_ids=None, attention_mask=None, labels=None, **kwargs):
+        hidden = self.gpt_neox(input_ids, attention_mask)
+        logits = self.embed_out(hidden)
+        loss = None
+        if labels is not None:
+            from .losses import causal_lm_loss
+
+            loss = causal_lm_loss(self, logits, labels)
+            logits = None if loss.consumed_logits else logits
+            loss = loss.value
+        return CausalLMOutput(loss=loss, logits=logits)

@@ -24,14 +24,27 @@ from oslo_b200.ops.gemm import linear as _linear
 
 
 class Linear(nn.Linear):
+    #: True when the weight is stored ``[in, out]`` (GPT-2 ``Conv1D`` layout); it is then used through
+    #: a transposed view, which the GEMM kernel reads as an MN-major operand without copying.
+    reversed = False
+
     def __init__(self, in_features, out_features, bias=True, dtype=None, skip_bias_add=False, device=None):
         super().__init__(in_features, out_features, bias=bias, device=device, dtype=dtype)
         self.skip_bias_add = skip_bias_add
 
+    @property
+    def _w(self):
+        return self.weight.t() if self.reversed else self.weight
+
     def forward(self, input: Tensor) -> Union[Tensor, Tuple[Tensor, Tensor]]:
         if self.skip_bias_add:
-            return _linear(input, self.weight), self.bias
-        return _linear(input, self.weight, self.bias)
+            return _linear(input, self._w), self.bias
+        return _linear(input, self._w, self.bias)
+
+
+def _sp_dim(module) -> int:
+    st = getattr(module, "sequence_parallel_state", None)
+    return st.dim if st is not None else 0
 
 
 class ColLinear1D(Linear):
@@ -68,18 +81,23 @@ class ColLinear1D(Linear):
 
         if self.sequence_parallel and self.world_size > 1:
             # input: token-sharded [..., T/tp, in]; gather over flattened tokens
-            lead = input.shape[:-1]
+            lead = list(input.shape[:-1])
             x2 = input.reshape(-1, input.shape[-1])
-            out = ops.ag_linear(x2, self.weight, self.parallel_context)
-            out = out.view(self.world_size * lead[0], *lead[1:], out.shape[-1]) if len(lead) > 1 else out
+            out = ops.ag_linear(x2, self._w, self.parallel_context)
+            if len(lead) > 1:
+                d = _sp_dim(self)
+                if d != 0 and any(n != 1 for n in lead[:d]):
+                    raise ValueError("sequence parallelism over dim 1 needs batch size 1 per rank")
+                lead[d] *= self.world_size
+                out = out.view(*lead, out.shape[-1])
             if self.bias is not None and not self.skip_bias_add:
                 out = out + self.bias
         else:
             x = ops.broadcast_tensor_1d(input, self.parallel_context)
             if self.bias is not None and not self.skip_bias_add:
-                out = _linear(x, self.weight, self.bias)
+                out = _linear(x, self._w, self.bias)
             else:
-                out = _linear(x, self.weight)
+                out = _linear(x, self._w)
         if self.bias is not None and self.skip_bias_add:
             return out, self.bias
         if self.gather_output:
@@ -125,13 +143,17 @@ class RowLinear1D(Linear):
         if not self.parallel_input:
             input = ops.scatter_tensor_1d(input, -1, self.parallel_context)
         if self.sequence_parallel and self.world_size > 1:
-            lead = input.shape[:-1]
+            lead = list(input.shape[:-1])
             x2 = input.reshape(-1, input.shape[-1])
-            out = ops.linear_rs(x2, self.weight, self.parallel_context)
+            out = ops.linear_rs(x2, self._w, self.parallel_context)
             if len(lead) > 1:
-                out = out.view(lead[0] // self.world_size, *lead[1:], out.shape[-1])
+                d = _sp_dim(self)
+                if d != 0 and any(n != 1 for n in lead[:d]):
+                    raise ValueError("sequence parallelism over dim 1 needs batch size 1 per rank")
+                lead[d] //= self.world_size
+                out = out.view(*lead, out.shape[-1])
         else:
-            out = _linear(input, self.weight)
+            out = _linear(input, self._w)
             out = ops.reduce_tensor_1d(out, self.parallel_context)
         if self.bias is not None:
             if self.skip_bias_add:

@@ -23,13 +23,22 @@ _EPI = {None: 0, "none": 0, "bias": 1, "gelu": 2}
 
 
 def _operand(t: torch.Tensor):
-    """Classify a 2-D/3-D operand [.., rows, K]: returns (tensor, mn_major, ld, batch_stride)."""
-    if t.stride(-1) == 1 and (t.shape[-2] == 1 or t.stride(-2) >= t.shape[-1]):
-        return t, 0, t.stride(-2) if t.shape[-2] > 1 else t.shape[-1], (t.stride(0) if t.dim() == 3 else 0)
-    if t.stride(-2) == 1 and t.stride(-1) >= t.shape[-2]:
-        return t, 1, t.stride(-1), (t.stride(0) if t.dim() == 3 else 0)
+    """Classify an operand ``[.., rows, K]``: returns (tensor, mn_major, ld, inner_stride, outer_stride)."""
+
+    def batch_strides(u):
+        if u.dim() == 2:
+            return 0, 0
+        if u.dim() == 3:
+            return u.stride(0), 0
+        return u.stride(1), u.stride(0)
+
+    rows, k = t.shape[-2], t.shape[-1]
+    if t.stride(-1) == 1 and (rows == 1 or t.stride(-2) >= k):
+        return (t, 0, t.stride(-2) if rows > 1 else k) + batch_strides(t)
+    if t.stride(-2) == 1 and (k == 1 or t.stride(-1) >= rows):
+        return (t, 1, t.stride(-1) if k > 1 else rows) + batch_strides(t)
     t = t.contiguous()
-    return t, 0, t.stride(-2), (t.stride(0) if t.dim() == 3 else 0)
+    return (t, 0, t.stride(-2)) + batch_strides(t)
 
 
 def supported(a: torch.Tensor, b: torch.Tensor) -> bool:
@@ -49,40 +58,53 @@ def gemm(
     accumulate: bool = False,
     aux: Optional[torch.Tensor] = None,
     block_n: int = 0,
+    causal: int = 0,
 ) -> torch.Tensor:
     """``out[.., M, N] = epilogue(a[.., M, K] @ b[.., N, K]^T (+ bias))`` on tcgen05.
 
-    ``a`` / ``b`` may be transposed views (MN-major).  ``aux`` (optional, same shape
-    as ``out``) receives the pre-activation ``acc + bias`` when ``epilogue="gelu"``.
+    Operands are 2-D, or 3-D / 4-D with one / two leading batch dims (any strides);
+    ``a`` / ``b`` may be transposed views (MN-major) — nothing is copied.  ``aux``
+    (optional, same layout as ``out``) receives the pre-activation ``acc + bias``
+    when ``epilogue="gelu"``.  ``causal`` selects triangular work skipping for
+    attention products (see ``csrc/gemm_sm100a.cu``).
     """
-    assert a.dim() == b.dim() and a.dim() in (2, 3), "gemm takes 2-D or batched 3-D operands"
+    assert a.dim() == b.dim() and a.dim() in (2, 3, 4), "gemm takes 2-D or batched 3-D / 4-D operands"
     M, K = a.shape[-2], a.shape[-1]
     N = b.shape[-2]
-    assert b.shape[-1] == K, f"K mismatch {a.shape} x {b.shape}"
-    batch = a.shape[0] if a.dim() == 3 else 1
-    a, a_mn, lda, sa = _operand(a)
-    b, b_mn, ldb, sb = _operand(b)
-    shape = (batch, M, N) if a.dim() == 3 else (M, N)
+    assert b.shape[-1] == K, f"K mismatch {tuple(a.shape)} x {tuple(b.shape)}"
+    nd = a.dim()
+    b_in = a.shape[-3] if nd >= 3 else 1
+    b_out = a.shape[0] if nd == 4 else 1
+    a, a_mn, lda, sa, osa = _operand(a)
+    b, b_mn, ldb, sb, osb = _operand(b)
     if out is None:
         assert not accumulate
-        out = torch.empty(shape, dtype=a.dtype, device=a.device)
-    assert out.stride(-1) == 1
+        out = torch.empty(tuple(a.shape[:-2]) + (M, N), dtype=a.dtype, device=a.device)
+    assert out.stride(-1) == 1 and out.dim() == nd
     ldc = out.stride(-2) if M > 1 else N
-    sc = out.stride(0) if out.dim() == 3 else 0
+    sc = out.stride(-3) if nd >= 3 else 0
+    osc = out.stride(0) if nd == 4 else 0
+    if aux is not None:
+        assert aux.stride() == out.stride()
     lib = _lib.cuda_lib()
     status = _lib.status_word(a.device)
+    use_epi = _EPI[epilogue] if (bias is not None or epilogue == "gelu") else 0
     rc = lib.oslo_gemm_tcgen05(
         _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(aux),
-        ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(batch),
+        ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(b_in),
         ctypes.c_longlong(lda), ctypes.c_longlong(ldb), ctypes.c_longlong(ldc),
         ctypes.c_longlong(sa), ctypes.c_longlong(sb), ctypes.c_longlong(sc),
         ctypes.c_int(a_mn), ctypes.c_int(b_mn), ctypes.c_int(1 if a.dtype == torch.bfloat16 else 0),
-        ctypes.c_int(_EPI[epilogue] if bias is not None or epilogue == "gelu" else 0),
-        ctypes.c_int(1 if accumulate else 0), ctypes.c_int(block_n), ctypes.c_int(_lib.num_sms()),
-        _lib.ptr(status), _lib.stream_ptr(),
+        ctypes.c_int(use_epi), ctypes.c_int(1 if accumulate else 0), ctypes.c_int(block_n),
+        ctypes.c_int(_lib.num_sms()), _lib.ptr(status), _lib.stream_ptr(),
+        ctypes.c_int(b_out), ctypes.c_longlong(osa), ctypes.c_longlong(osb), ctypes.c_longlong(osc),
+        ctypes.c_int(causal),
     )
     if rc != 0:
-        raise RuntimeError(f"oslo_gemm_tcgen05 failed with code {rc} for shapes {tuple(a.shape)} x {tuple(b.shape)}")
+        raise RuntimeError(
+            f"oslo_gemm_tcgen05 failed with code {rc} for {tuple(a.shape)} (strides {a.stride()}) x "
+            f"{tuple(b.shape)} (strides {b.stride()})"
+        )
     return out
 
 
@@ -131,6 +153,6 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
 
 def matmul_nt(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """``a @ b.transpose(-1, -2)`` (no autograd) with tcgen05 when possible."""
-    if supported(a, b) and a.dim() in (2, 3):
+    if supported(a, b) and a.dim() in (2, 3, 4) and a.dim() == b.dim():
         return gemm(a, b)
     return torch.matmul(a, b.transpose(-1, -2))

@@ -1,0 +1,3 @@
+from .tensor_parallel import TensorParallel
+
+__all__ = ["TensorParallel"]
