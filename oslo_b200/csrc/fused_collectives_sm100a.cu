@@ -1,0 +1,124 @@
+// Fused compute + collective entry points for 1-D tensor parallelism with sequence parallelism:
+//
+//   oslo_ag_gemm   C[T, N] = all_gather(x_shard)[T, K] x B[N, K]^T, also leaving the gathered x in local memory
+//   oslo_gemm_rs   out[T/tp, N] = reduce_scatter_rows( A[T, K] x B[N, K]^T )
+//
+// Both are ONE launch of the tcgen05 GEMM kernel in a fused mode (gemm_core.cuh):
+//   * all-gather: a few CTAs stream the peers' shards over NVLink into local memory with plain 16-byte loads
+//     while the remaining CTAs multiply, starting with the local shard and taking each remote shard as soon
+//     as its "copied" flag is up; TMA only ever reads local memory.
+//   * reduce-scatter: tiles are computed in destination order (next rank first, own rows last); the epilogue
+//     pushes each partial tile straight into the destination GPU's slot buffer with peer stores, the last
+//     tile per destination raises a flag there, and every CTA ends by summing the tp slots of its own rows.
+// All waits on peers are bounded (~2 s) and report through the status word instead of hanging.
+//
+// Replaces ColLinear1D / RowLinear1D = F.linear + a separate NCCL all-reduce in the reference
+// (oslo/torch/nn/modules/linear.py:73-160).
+#include "gemm_core.cuh"
+
+using namespace oslo;
+
+static int pick_block_n(int M, int N, int ctas) {
+  const long long mb = (M + kBlockM - 1) / kBlockM;
+  auto tiles = [&](int bn) { return mb * ((N + bn - 1) / bn); };
+  int bn = 256;
+  if (tiles(256) < ctas || N % 256 != 0) bn = 128;
+  if (N <= 64) bn = 64;
+  return bn;
+}
+
+#define OSLO_FUSED_LAUNCH(BN, MODE)                                                                       \
+  (b_mn ? launch<BN, false, true, MODE>(ta, tb, tc, taux, p, grid, stream, fp)                            \
+        : launch<BN, false, false, MODE>(ta, tb, tc, taux, p, grid, stream, fp))
+
+// peer_in / peer_ag_ready: host arrays of `tp` device pointers (entry [rank] is the local buffer).
+extern "C" int oslo_ag_gemm(void* const* peer_in, void* x_full, const void* B, void* C, const void* bias, int T, int N, int K,
+                            long long ldb, int b_mn, int is_bf16, int tp, int rank, int epoch, void* const* peer_ag_ready,
+                            int* chunk_flag, int* chunk_arrive, int copy_ctas, int num_sms, int* status, void* stream_ptr) {
+  if (tp > kMaxRanks || tp < 1 || T % tp) return -1;
+  const int Tl = T / tp;
+  if (Tl % kBlockM || N % 8 || K % 8 || ldb % 8) return -5;
+  bind_context_to_thread();
+  if (copy_ctas < 1) copy_ctas = 1;
+  if (copy_ctas > num_sms / 2) copy_ctas = num_sms / 2;
+  const int gemm_ctas_max = num_sms - copy_ctas;
+  const int block_n = pick_block_n(T, N, gemm_ctas_max);
+  GemmParams p{};
+  p.M = T; p.N = N; p.K = K; p.batch = 1; p.batch_inner = 1; p.causal = 0;
+  p.m_blocks = T / kBlockM;
+  p.n_blocks = (N + block_n - 1) / block_n;
+  p.epilogue = bias ? 1 : 0; p.accumulate = 0; p.is_bf16 = is_bf16;
+  p.bias = bias; p.c_ptr = C; p.ldc = N; p.stride_c = 0; p.stride_c_outer = 0; p.aux_ptr = nullptr; p.status = status;
+  FusedParams fp;
+  fp.tp = tp; fp.rank = rank; fp.shard_rows = Tl; fp.epoch = epoch; fp.copy_ctas = copy_ctas; fp.k_elems = K;
+  fp.tiles_per_shard = (Tl / kBlockM) * p.n_blocks;
+  for (int i = 0; i < tp; ++i) {
+    fp.peer_in[i] = peer_in[i];
+    fp.peer_ag_ready[i] = static_cast<int*>(peer_ag_ready[i]);
+  }
+  fp.x_full = x_full;
+  fp.ag_ready = static_cast<int*>(peer_ag_ready[rank]);
+  fp.chunk_flag = chunk_flag; fp.chunk_arrive = chunk_arrive; fp.status = status;
+  CUtensorMap ta, tb, tc, taux;
+  int rc = make_map(&ta, x_full, is_bf16, K, T, 1, 1, K, 0, 0, kBlockK, kBlockM);
+  if (rc) return rc;
+  rc = make_map(&taux, peer_in[rank], is_bf16, K, Tl, 1, 1, K, 0, 0, kBlockK, kBlockM);  // local shard, read in place
+  if (rc) return rc;
+  if (b_mn) rc = make_map(&tb, B, is_bf16, N, K, 1, 1, ldb, 0, 0, 64, kBlockK);
+  else      rc = make_map(&tb, B, is_bf16, K, N, 1, 1, ldb, 0, 0, kBlockK, block_n);
+  if (rc) return rc;
+  rc = make_map(&tc, C, is_bf16, N, T, 1, 1, N, 0, 0, 64, 32);
+  if (rc) return rc;
+  const long long total = (long long)p.m_blocks * p.n_blocks;
+  const int gemm_ctas = (int)(total < gemm_ctas_max ? total : gemm_ctas_max);
+  const int grid = copy_ctas + gemm_ctas;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  switch (block_n) {
+    case 256: return OSLO_FUSED_LAUNCH(256, kModeAllGather);
+    case 128: return OSLO_FUSED_LAUNCH(128, kModeAllGather);
+    default: return OSLO_FUSED_LAUNCH(64, kModeAllGather);
+  }
+}
+
+// peer_slots / peer_rs_flag: host arrays of `tp` device pointers.  A: [T, K] K-major (lda), out: [T/tp, N].
+extern "C" int oslo_gemm_rs(const void* A, long long lda, const void* B, long long ldb, int b_mn, void* out, const void* bias,
+                            int T, int N, int K, int is_bf16, int tp, int rank, int epoch, void* const* peer_slots,
+                            void* const* peer_rs_flag, int* tile_done, int num_sms, int* status, void* stream_ptr) {
+  if (tp > kMaxRanks || tp < 1 || T % tp) return -1;
+  const int Tl = T / tp;
+  if (Tl % kBlockM || N % 8 || K % 8 || lda % 8 || ldb % 8) return -5;
+  bind_context_to_thread();
+  const int block_n = pick_block_n(T, N, num_sms);
+  GemmParams p{};
+  p.M = T; p.N = N; p.K = K; p.batch = 1; p.batch_inner = 1; p.causal = 0;
+  p.m_blocks = T / kBlockM;
+  p.n_blocks = (N + block_n - 1) / block_n;
+  p.epilogue = 0; p.accumulate = 0; p.is_bf16 = is_bf16;
+  p.bias = nullptr; p.c_ptr = out; p.ldc = N; p.stride_c = 0; p.stride_c_outer = 0; p.aux_ptr = nullptr; p.status = status;
+  FusedParams fp;
+  fp.tp = tp; fp.rank = rank; fp.shard_rows = Tl; fp.epoch = epoch;
+  fp.tiles_per_shard = (Tl / kBlockM) * p.n_blocks;
+  for (int i = 0; i < tp; ++i) {
+    fp.peer_slots[i] = peer_slots[i];
+    fp.peer_rs_flag[i] = static_cast<int*>(peer_rs_flag[i]);
+  }
+  fp.rs_flag = static_cast<int*>(peer_rs_flag[rank]);
+  fp.tile_done = tile_done; fp.rs_out = out; fp.rs_bias = bias; fp.status = status;
+  CUtensorMap ta, tb, tc, taux;
+  int rc = make_map(&ta, A, is_bf16, K, T, 1, 1, lda, 0, 0, kBlockK, kBlockM);
+  if (rc) return rc;
+  if (b_mn) rc = make_map(&tb, B, is_bf16, N, K, 1, 1, ldb, 0, 0, 64, kBlockK);
+  else      rc = make_map(&tb, B, is_bf16, K, N, 1, 1, ldb, 0, 0, kBlockK, block_n);
+  if (rc) return rc;
+  rc = make_map(&tc, out, is_bf16, N, Tl, 1, 1, N, 0, 0, 64, 32);  // not stored through; kept valid for the prefetch
+  if (rc) return rc;
+  taux = tc;
+  const long long total = (long long)p.m_blocks * p.n_blocks;
+  const int grid = (int)(total < num_sms ? total : num_sms);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  switch (block_n) {
+    case 256: return OSLO_FUSED_LAUNCH(256, kModeReduceScatter);
+    case 128: return OSLO_FUSED_LAUNCH(128, kModeReduceScatter);
+    default: return OSLO_FUSED_LAUNCH(64, kModeReduceScatter);
+  }
+}

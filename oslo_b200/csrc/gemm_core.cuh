@@ -1,0 +1,687 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a (kernel template and host helpers).
+//
+//   C[b] = epilogue( A[b] x B[b]^T )        A: [M, K]   B: [N, K]   C: [M, N]
+//
+// Either operand may be "K-major" (reduction dim contiguous, as stored by
+// nn.Linear for x and W) or "MN-major" (the other dim contiguous), so forward
+// (x W^T), input-gradient (dY W) and weight-gradient (dY^T x) products all run on
+// the same kernel without a transposition pass.
+//
+// Structure of one CTA (192 threads, one CTA per SM, persistent over tiles):
+//   warp 0      TMA producer: cp.async.bulk.tensor loads into a ring of
+//               128-byte-swizzled shared-memory stages, completion on mbarriers;
+//   warp 1      MMA issuer: one elected thread issues tcgen05.mma (M=128, N=BLOCK_N,
+//               K=16) with the accumulator in tensor memory; two accumulator
+//               buffers so the epilogue of tile i overlaps the main loop of i+1;
+//   warps 2-5   epilogue: tcgen05.ld the accumulator (one TMEM lane quarter per
+//               warp), add bias / apply GELU / add the previous C, convert, stage
+//               in swizzled shared memory and write with TMA stores.
+//
+// All mbarrier waits are bounded; on a timeout the kernel records a status code,
+// drains, frees its tensor memory and returns.
+//
+// Replaces the cuBLAS calls behind F.linear / torch.matmul in the reference
+// (oslo/torch/nn/modules/linear.py:73-160 and every _ops.py Matmul_* function).
+#pragma once
+#include "common.cuh"
+#include <cstdio>
+#include <mutex>
+
+namespace oslo {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 64;   // 64 x 2 B = one 128-byte swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kGemmThreads = 192;
+
+struct GemmParams {
+  int M, N, K, batch;
+  int batch_inner;    // batch index b = outer * batch_inner + inner; each part has its own stride in the maps
+  int causal;         // 0 none; 1 skip tiles entirely above the diagonal (n0 > m0 + 127);
+                      // 2 reduce only k <= m0 + 127 (lower-triangular A); 3 reduce only k >= m0 (upper-triangular A^T)
+  int m_blocks, n_blocks;
+  int epilogue;       // 0 none, 1 +bias, 2 gelu(+bias if given), 3 reserved
+  int accumulate;     // 1: C = C_old + result
+  int is_bf16;        // 1 bf16, 0 fp16
+  const void* bias;   // [N] in the operand dtype, or null
+  void* c_ptr;        // plain pointer to C (used for accumulate)
+  long long ldc;      // row stride of C in elements
+  long long stride_c; // inner batch stride of C in elements
+  long long stride_c_outer;  // outer batch stride of C in elements
+  void* aux_ptr;      // optional second output: pre-activation (acc + bias), same layout as C
+  int* status;
+};
+
+template <int BLOCK_N>
+struct GemmCfg {
+  static constexpr int kStageA = kBlockM * kBlockK * 2;
+  static constexpr int kStageB = BLOCK_N * kBlockK * 2;
+  static constexpr int kStageBytes = kStageA + kStageB;
+  static constexpr int kStages = (BLOCK_N == 256) ? 4 : (BLOCK_N == 128 ? 6 : 8);
+  static constexpr int kStagingBytes = 4 * 2 * 4096;  // 4 epilogue warps x 2 buffers x (32 rows x 128 B)
+  static constexpr int kTmemCols = 2 * BLOCK_N;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+OSLO_DEVINL void tile_coords(int tile, const GemmParams& p, int& b, int& mb, int& nb) {
+  const int per_batch = p.m_blocks * p.n_blocks;
+  b = tile / per_batch;
+  int t = tile - b * per_batch;
+  // groups of 8 m-blocks sweep all n-blocks, m fastest: neighbouring CTAs share B tiles in L2
+  constexpr int kGroup = 8;
+  const int group_size = kGroup * p.n_blocks;
+  const int g = t / group_size;
+  const int first_m = g * kGroup;
+  const int rows = min(kGroup, p.m_blocks - first_m);
+  const int r = t - g * group_size;
+  mb = first_m + r % rows;
+  nb = r / rows;
+}
+
+
+// ------------------------------------------------------------------------------------------------
+// Fused collective modes.  Ranks exchange data through peer-mapped ("symmetric") buffers; flags hold
+// the epoch (a per-group call counter) of the last completed hand-off, so they never need clearing.
+constexpr int kModePlain = 0;
+constexpr int kModeAllGather = 1;      // A rows are gathered from all ranks while the GEMM runs
+constexpr int kModeReduceScatter = 2;  // C row blocks are pushed to their owner and summed there
+constexpr int kMaxRanks = 8;
+
+struct FusedParams {
+  int tp = 1, rank = 0;
+  int shard_rows = 0;       // rows of A (AG) / of C (RS) owned by one rank; a multiple of 128
+  int tiles_per_shard = 0;  // output tiles per shard
+  int epoch = 0;
+  int copy_ctas = 0;        // AG: CTAs [0, copy_ctas) copy, the others multiply
+  int k_elems = 0;          // AG: row length of A in elements
+  // all-gather
+  const void* peer_in[kMaxRanks] = {};  // every rank's symmetric input shard [shard_rows, K]
+  void* x_full = nullptr;               // local [tp * shard_rows, K]
+  int* ag_ready = nullptr;              // local [tp]: peer p's shard for `epoch` is in its buffer
+  int* peer_ag_ready[kMaxRanks] = {};   // the same array on every rank (to announce our shard)
+  int* chunk_flag = nullptr;            // local [tp]: shard s has been copied into x_full
+  int* chunk_arrive = nullptr;          // local [tp]: copy-CTA arrival counters
+  // reduce-scatter
+  void* peer_slots[kMaxRanks] = {};     // every rank's slot buffer [tp, shard_rows, N]
+  int* rs_flag = nullptr;               // local [tp]: source p has pushed all its partial tiles
+  int* peer_rs_flag[kMaxRanks] = {};
+  int* tile_done = nullptr;             // local [tp]: per-destination arrival counters
+  void* rs_out = nullptr;               // local [shard_rows, N]
+  const void* rs_bias = nullptr;        // optional [N]
+  int* status = nullptr;
+};
+
+OSLO_DEVINL int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+OSLO_DEVINL int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+OSLO_DEVINL void st_release_sys(int* p, int v) { asm volatile("st.release.sys.global.b32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+OSLO_DEVINL void st_release_gpu(int* p, int v) { asm volatile("st.release.gpu.global.b32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+OSLO_DEVINL void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+
+// Wait (bounded, ~2 s) until *flag >= target.  abort_flag may be null.
+OSLO_DEVINL bool flag_wait_bounded(const int* flag, int target, volatile int* abort_flag, bool sys_scope) {
+  if ((sys_scope ? ld_acquire_sys(flag) : ld_acquire_gpu(flag)) >= target) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t i = 1;; ++i) {
+    if ((sys_scope ? ld_acquire_sys(flag) : ld_acquire_gpu(flag)) >= target) return true;
+    if ((i & 0x3f) == 0) {
+      if (abort_flag && *abort_flag) return false;
+      if (global_timer_ns() - t0 > kWaitBudgetNs) break;
+    }
+    __nanosleep(64);
+  }
+  if (abort_flag) *abort_flag = 1;
+  return false;
+}
+
+// Output tiles in shard order: AG starts with the local shard (rank, rank+1, ...), RS ends with it
+// (rank+1, ..., rank), so remote traffic and compute overlap from the first tile on.
+template <int MODE>
+OSLO_DEVINL void fused_tile_coords(int tile, const GemmParams& p, const FusedParams& fp, int& b, int& mb, int& nb) {
+  b = 0;
+  const int i = tile / fp.tiles_per_shard;
+  const int t = tile - i * fp.tiles_per_shard;
+  const int shard = (fp.rank + i + (MODE == kModeReduceScatter ? 1 : 0)) % fp.tp;
+  const int blocks_per_shard = fp.shard_rows / kBlockM;
+  mb = shard * blocks_per_shard + t % blocks_per_shard;
+  nb = t / blocks_per_shard;
+}
+
+// AG copy role: announce our shard, then pull every shard (own first) into x_full and flag it.
+__device__ __noinline__ void ag_copy_role(const GemmParams& p, const FusedParams& fp) {
+  __shared__ int s_ok;
+  const int tid = threadIdx.x, nthreads = blockDim.x;
+  if (blockIdx.x == 0 && tid < fp.tp) {
+    __threadfence_system();
+    st_release_sys(fp.peer_ag_ready[tid] + fp.rank, fp.epoch);
+  }
+  const long long vec_per_shard = static_cast<long long>(fp.shard_rows) * fp.k_elems / 8;
+  const long long per_cta = (vec_per_shard + fp.copy_ctas - 1) / fp.copy_ctas;
+  const long long v0 = per_cta * blockIdx.x;
+  const long long v1 = v0 + per_cta < vec_per_shard ? v0 + per_cta : vec_per_shard;
+  for (int i = 0; i < fp.tp; ++i) {
+    const int s = (fp.rank + i) % fp.tp;
+    if (tid == 0) {
+      bool ok = true;
+      if (i > 0) ok = flag_wait_bounded(fp.ag_ready + s, fp.epoch, nullptr, true);
+      if (!ok && fp.status) atomicCAS(fp.status, kStatusOk, kStatusPeerFlagTimeout);
+      s_ok = ok ? 1 : 0;
+    }
+    __syncthreads();
+    if (!s_ok) return;  // the GEMM CTAs will time out on the chunk flag and report it
+    const uint4* src = static_cast<const uint4*>(fp.peer_in[s]);
+    uint4* dst = static_cast<uint4*>(fp.x_full) + static_cast<long long>(s) * vec_per_shard;
+    long long v = v0 + tid;
+    // 8 independent 16-byte loads in flight per thread hide the NVLink round trip
+    for (; v + 7LL * nthreads < v1; v += 8LL * nthreads) {
+      uint4 r[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) r[u] = src[v + static_cast<long long>(u) * nthreads];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) dst[v + static_cast<long long>(u) * nthreads] = r[u];
+    }
+    for (; v < v1; v += nthreads) dst[v] = src[v];
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence();
+      const int old = atomicAdd(fp.chunk_arrive + s, 1);
+      if (old == fp.copy_ctas - 1) {
+        fp.chunk_arrive[s] = 0;
+        __threadfence();
+        st_release_gpu(fp.chunk_flag + s, fp.epoch);
+      }
+    }
+  }
+}
+
+// RS reduce phase (all threads of all GEMM CTAs): wait for every source, then out = sum of the tp slots.
+__device__ __noinline__ void rs_reduce_phase(const GemmParams& p, const FusedParams& fp, int cta, int num_ctas,
+                                             volatile int* abort_flag) {
+  const int lane = threadIdx.x & 31;
+  bool ok = true;
+  if (lane < fp.tp) ok = flag_wait_bounded(fp.rs_flag + lane, fp.epoch, abort_flag, true);
+  ok = __all_sync(0xffffffffu, ok);
+  if (!ok) {
+    if (lane == 0 && fp.status) atomicCAS(fp.status, kStatusOk, kStatusPeerFlagTimeout);
+    return;
+  }
+  __threadfence_system();
+  const long long vecs = static_cast<long long>(fp.shard_rows) * p.N / 8;
+  const long long slot_vecs = vecs;
+  const uint4* slots = static_cast<const uint4*>(fp.peer_slots[fp.rank]);
+  uint4* out = static_cast<uint4*>(fp.rs_out);
+  const int nvec_row = p.N / 8;
+  for (long long v = static_cast<long long>(cta) * blockDim.x + threadIdx.x; v < vecs;
+       v += static_cast<long long>(num_ctas) * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    if (fp.rs_bias) {
+      const uint4 raw = __ldg(static_cast<const uint4*>(fp.rs_bias) + (v % nvec_row));
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (p.is_bf16) { acc[2 * j] = __uint_as_float(w[j] << 16); acc[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u); }
+        else { const __half2 h = *reinterpret_cast<const __half2*>(&w[j]); acc[2 * j] = __low2float(h); acc[2 * j + 1] = __high2float(h); }
+      }
+    }
+    for (int s = 0; s < fp.tp; ++s) {
+      const uint4 raw = slots[static_cast<long long>(s) * slot_vecs + v];
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (p.is_bf16) { acc[2 * j] += __uint_as_float(w[j] << 16); acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u); }
+        else { const __half2 h = *reinterpret_cast<const __half2*>(&w[j]); acc[2 * j] += __low2float(h); acc[2 * j + 1] += __high2float(h); }
+      }
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (p.is_bf16) { const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]); o[j] = *reinterpret_cast<const uint32_t*>(&h); }
+      else { const __half2 h = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]); o[j] = *reinterpret_cast<const uint32_t*>(&h); }
+    }
+    out[v] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// k-block range [kb0, kb1) a tile has to reduce over, or skip = true when it has no work.
+OSLO_DEVINL void tile_k_range(const GemmParams& p, int m0, int n0, int num_kb, int& kb0, int& kb1, bool& skip) {
+  kb0 = 0;
+  kb1 = num_kb;
+  skip = false;
+  if (p.causal == 1) skip = n0 > m0 + kBlockM - 1;
+  else if (p.causal == 2) kb1 = min(num_kb, (m0 + kBlockM + kBlockK - 1) / kBlockK);
+  else if (p.causal == 3) kb0 = min(num_kb - 1, m0 / kBlockK);
+}
+
+template <int BLOCK_N, bool A_MN, bool B_MN, int MODE>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux,
+                    const GemmParams p, const FusedParams fp) {
+  if constexpr (MODE == kModeAllGather) {
+    // the first fp.copy_ctas CTAs stream the peers' shards into local memory; the rest run the GEMM
+    if (static_cast<int>(blockIdx.x) < fp.copy_ctas) {
+      ag_copy_role(p, fp);
+      return;
+    }
+  }
+  const int cta = (MODE == kModeAllGather) ? static_cast<int>(blockIdx.x) - fp.copy_ctas : static_cast<int>(blockIdx.x);
+  const int num_ctas = (MODE == kModeAllGather) ? static_cast<int>(gridDim.x) - fp.copy_ctas : static_cast<int>(gridDim.x);
+  using Cfg = GemmCfg<BLOCK_N>;
+  constexpr int kStages = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stage_base = smem;
+  uint8_t* staging = smem + kStages * Cfg::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + Cfg::kStagingBytes);
+  uint64_t* full_bar = bars;                    // [kStages]
+  uint64_t* empty_bar = bars + kStages;         // [kStages]
+  uint64_t* tmem_full = bars + 2 * kStages;     // [2]
+  uint64_t* tmem_empty = bars + 2 * kStages + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.batch * p.m_blocks * p.n_blocks;
+  const int num_kb = (p.K + kBlockK - 1) / kBlockK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmC);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int armed = 0;  // stages armed since start (capped), used to drain on abort
+      int ready_shard = -1;
+      (void)ready_shard;
+      for (int tile = cta; tile < num_tiles && ok; tile += num_ctas) {
+        int b, mb, nb;
+        if constexpr (MODE == kModePlain) tile_coords(tile, p, b, mb, nb);
+        else fused_tile_coords<MODE>(tile, p, fp, b, mb, nb);
+        const int m0 = mb * kBlockM, n0 = nb * BLOCK_N;
+        const int bi = b % p.batch_inner, bo = b / p.batch_inner;
+        int kb0, kb1;
+        bool skip;
+        tile_k_range(p, m0, n0, num_kb, kb0, kb1, skip);
+        if (skip) continue;
+        bool a_local = false;
+        if constexpr (MODE == kModeAllGather) {
+          // rows of shard s become loadable once the copy CTAs have flagged the chunk; the own shard is read
+          // straight from the symmetric input buffer through its own tensor map
+          const int shard = m0 / fp.shard_rows;
+          a_local = shard == fp.rank;
+          if (!a_local && shard != ready_shard) {
+            if (!flag_wait_bounded(fp.chunk_flag + shard, fp.epoch, abort_flag, false)) {
+              ok = false;
+              if (p.status) atomicCAS(p.status, kStatusOk, kStatusPeerFlagTimeout);
+              break;
+            }
+            fence_proxy_async_global();
+            ready_shard = shard;
+          }
+        }
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
+            ok = false;
+            if (p.status) atomicCAS(p.status, kStatusOk, kStatusWaitTimeoutProducer);
+            break;
+          }
+          uint8_t* sa = stage_base + stage * Cfg::kStageBytes;
+          uint8_t* sb = sa + Cfg::kStageA;
+          mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          const int k0 = kb * kBlockK;
+          if (A_MN) {
+#pragma unroll
+            for (int c = 0; c < kBlockM / 64; ++c) tma_load_4d(sa + c * 8192, &tmA, &full_bar[stage], m0 + c * 64, k0, bi, bo);
+          } else {
+            if (MODE == kModeAllGather && a_local) tma_load_4d(sa, &tmAux, &full_bar[stage], k0, m0 - fp.rank * fp.shard_rows, bi, bo);
+            else tma_load_4d(sa, &tmA, &full_bar[stage], k0, m0, bi, bo);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int c = 0; c < BLOCK_N / 64; ++c) tma_load_4d(sb + c * 8192, &tmB, &full_bar[stage], n0 + c * 64, k0, bi, bo);
+          } else {
+            tma_load_4d(sb, &tmB, &full_bar[stage], k0, n0, bi, bo);
+          }
+          if (armed < kStages) ++armed;
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // leave no bulk copy in flight: every armed stage's full barrier must flip (bounded)
+        for (int s = 0; s < armed; ++s) {
+          int st = (stage - 1 - s + 2 * kStages) % kStages;
+          uint32_t ph = (st < stage) ? phase : (phase ^ 1);
+          for (uint32_t i = 0; i < (1u << 22); ++i)
+            if (mbar_try_wait(&full_bar[st], ph)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc_bf16 = make_idesc_f16(kBlockM, BLOCK_N, true, A_MN, B_MN);
+      constexpr uint32_t idesc_fp16 = make_idesc_f16(kBlockM, BLOCK_N, false, A_MN, B_MN);
+      const uint32_t idesc = p.is_bf16 ? idesc_bf16 : idesc_fp16;
+      int stage = 0;
+      uint32_t phase = 0;
+      int buf = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = cta; tile < num_tiles && ok; tile += num_ctas) {
+        int kb0 = 0, kb1 = num_kb;
+        if (p.causal) {
+          int b, mb, nb;
+          bool skip;
+          tile_coords(tile, p, b, mb, nb);
+          tile_k_range(p, mb * kBlockM, nb * BLOCK_N, num_kb, kb0, kb1, skip);
+          if (skip) continue;
+        }
+        if (!mbar_wait_bounded(&tmem_empty[buf], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BLOCK_N;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(stage_base + stage * Cfg::kStageBytes);
+          const uint32_t sb = sa + Cfg::kStageA;
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            // K-major: 16 elements = 32 bytes along the swizzled row; 8-row groups 1024 B apart.
+            // MN-major: 16 k-rows of 128 B = 2048 B; 64-wide MN chunks 8192 B apart.
+            const uint64_t da = A_MN ? make_smem_desc_sw128(sa + k * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(sa + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc_sw128(sb + k * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(sb + k * 32, 16, 1024);
+            umma_f16(tmem_d, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tmem_full[buf]);
+        buf ^= 1;
+        if (buf == 0) acc_phase ^= 1;
+      }
+      if (!ok && p.status) atomicCAS(p.status, kStatusOk, kStatusWaitTimeoutMma);
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    uint8_t* my_staging = staging + (warp - 2) * 2 * 4096;
+    int buf = 0;
+    uint32_t acc_phase = 0;
+    int sbuf = 0;
+    bool ok = true;
+    for (int tile = cta; tile < num_tiles && ok; tile += num_ctas) {
+      int b, mb, nb;
+      if constexpr (MODE == kModePlain) tile_coords(tile, p, b, mb, nb);
+      else fused_tile_coords<MODE>(tile, p, fp, b, mb, nb);
+      const int m0 = mb * kBlockM, n0 = nb * BLOCK_N;
+      const int bi = b % p.batch_inner, bo = b / p.batch_inner;
+      if (p.causal == 1 && n0 > m0 + kBlockM - 1) continue;
+      if (!mbar_wait_bounded(&tmem_full[buf], acc_phase, abort_flag)) {
+        ok = false;
+        if (p.status && lane == 0) atomicCAS(p.status, kStatusOk, kStatusWaitTimeoutEpilogue);
+        break;
+      }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BLOCK_N;
+#pragma unroll 1
+      for (int chunk = 0; chunk < BLOCK_N / 64; ++chunk) {
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32(taddr + chunk * 64, r0);
+        tmem_ld_32x32(taddr + chunk * 64 + 32, r1);
+        tmem_ld_wait();
+        if (chunk == BLOCK_N / 64 - 1) {
+          // accumulator fully read: hand the TMEM buffer back to the MMA warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+        }
+        const int col0 = n0 + chunk * 64;
+        if (col0 >= p.N) continue;  // warp-uniform
+        float v[64];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          v[i] = __uint_as_float(r0[i]);
+          v[32 + i] = __uint_as_float(r1[i]);
+        }
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            if (col0 + g * 8 < p.N) {
+              const uint4 raw = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.bias) + col0 + g * 8));
+              const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float lo, hi;
+                if (p.is_bf16) {
+                  lo = __uint_as_float(w[j] << 16);
+                  hi = __uint_as_float(w[j] & 0xffff0000u);
+                } else {
+                  const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+                  lo = __low2float(h);
+                  hi = __high2float(h);
+                }
+                v[g * 8 + 2 * j] += lo;
+                v[g * 8 + 2 * j + 1] += hi;
+              }
+            }
+          }
+        }
+        if (p.accumulate && row < p.M) {
+          const uint16_t* cin = static_cast<const uint16_t*>(p.c_ptr) + static_cast<long long>(bi) * p.stride_c +
+                                static_cast<long long>(bo) * p.stride_c_outer + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            if (col0 + g * 8 < p.N) {
+              const uint4 raw = *reinterpret_cast<const uint4*>(cin + g * 8);
+              const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float lo, hi;
+                if (p.is_bf16) {
+                  lo = __uint_as_float(w[j] << 16);
+                  hi = __uint_as_float(w[j] & 0xffff0000u);
+                } else {
+                  const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+                  lo = __low2float(h);
+                  hi = __high2float(h);
+                }
+                v[g * 8 + 2 * j] += lo;
+                v[g * 8 + 2 * j + 1] += hi;
+              }
+            }
+          }
+        }
+        const bool want_aux = (p.aux_ptr != nullptr);
+        // up to two stores per chunk: optional pre-activation (aux) then the final value
+        for (int pass = want_aux ? 0 : 1; pass < 2; ++pass) {
+          uint8_t* sbuf_ptr = my_staging + sbuf * 4096;
+          if (lane == 0) tma_store_wait_read<1>();  // the store issued two buffers ago has drained
+          __syncwarp();
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            uint32_t packed[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float a0 = v[g * 8 + 2 * j], a1 = v[g * 8 + 2 * j + 1];
+              if (pass == 1 && p.epilogue == 2) {
+                a0 = gelu_tanh(a0);
+                a1 = gelu_tanh(a1);
+              }
+              if (p.is_bf16) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(a0, a1);
+                packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+              } else {
+                const __half2 h = __floats2half2_rn(a0, a1);
+                packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+              }
+            }
+            // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
+            uint4* dst = reinterpret_cast<uint4*>(sbuf_ptr + lane * 128 + ((g ^ (lane & 7)) << 4));
+            *dst = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          }
+          if constexpr (MODE == kModeReduceScatter) {
+            // push the 32 x 64 block into slot [this rank] of the destination rank's buffer with plain
+            // 16-byte stores (coalesced: 8 lanes cover one 128-byte row segment)
+            __syncwarp();
+            const int dest = m0 / fp.shard_rows;
+            uint16_t* slot = static_cast<uint16_t*>(fp.peer_slots[dest]) +
+                             (static_cast<long long>(fp.rank) * fp.shard_rows + (m0 - dest * fp.shard_rows) + q * 32) * p.N;
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int r = it * 4 + (lane >> 3), c = lane & 7;
+              if (col0 + c * 8 < p.N) {
+                const uint4 val = *reinterpret_cast<const uint4*>(sbuf_ptr + r * 128 + ((c ^ (r & 7)) << 4));
+                *reinterpret_cast<uint4*>(slot + static_cast<long long>(r) * p.N + col0 + c * 8) = val;
+              }
+            }
+            __syncwarp();
+          } else {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_4d(pass == 0 ? &tmAux : &tmC, sbuf_ptr, col0, m0 + q * 32, bi, bo);
+              tma_store_commit();
+            }
+          }
+          sbuf ^= 1;
+        }
+      }
+      if constexpr (MODE == kModeReduceScatter) {
+        // this warp's quarter of the tile has landed at the destination: count it, the last one signals
+        const int dest = m0 / fp.shard_rows;
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const int need = fp.tiles_per_shard * 4;
+          const int old = atomicAdd(fp.tile_done + dest, 1);
+          if (old == need - 1) {
+            fp.tile_done[dest] = 0;
+            __threadfence_system();
+            st_release_sys(fp.peer_rs_flag[dest] + fp.rank, fp.epoch);
+          }
+        }
+      }
+      buf ^= 1;
+      if (buf == 0) acc_phase ^= 1;
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+
+  if constexpr (MODE == kModeReduceScatter) rs_reduce_phase(p, fp, cta, num_ctas, abort_flag);
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------- host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled is a driver call and needs a current context in the calling thread; worker threads
+// (e.g. the autograd engine's) may not have one yet.  Re-selecting the runtime's current device binds the
+// primary context to this thread.
+static inline void bind_context_to_thread() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaSetDevice(dev);
+}
+
+static inline EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// 4-D map over a [batch_outer, batch_inner, rows, cols] tensor (cols contiguous), 128-byte swizzle.
+static inline int make_map(CUtensorMap* map, const void* base, int is_bf16, long long cols, long long rows, long long b_inner,
+                    long long b_outer, long long row_stride_elems, long long inner_stride_elems,
+                    long long outer_stride_elems, int box_cols, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[4] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)b_inner, (cuuint64_t)b_outer};
+  const long long dflt = row_stride_elems * rows;
+  cuuint64_t strides[3] = {(cuuint64_t)row_stride_elems * 2,
+                           (cuuint64_t)(b_inner > 1 ? inner_stride_elems : dflt) * 2,
+                           (cuuint64_t)(b_outer > 1 ? outer_stride_elems : dflt * b_inner) * 2};
+  cuuint32_t box[4] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr,
+            "oslo_b200: cuTensorMapEncodeTiled failed (%d): base %p dims {%llu,%llu,%llu,%llu} strides {%llu,%llu,%llu} box {%u,%u}\n",
+            (int)r, base, (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2],
+            (unsigned long long)dims[3], (unsigned long long)strides[0], (unsigned long long)strides[1],
+            (unsigned long long)strides[2], box[0], box[1]);
+    return -2;
+  }
+  return 0;
+}
+
+template <int BLOCK_N, bool A_MN, bool B_MN, int MODE = kModePlain>
+static int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const CUtensorMap& aux,
+                  const GemmParams& p, int grid, cudaStream_t stream, const FusedParams& fp = FusedParams()) {
+  using Cfg = GemmCfg<BLOCK_N>;
+  auto kern = gemm_tcgen05_kernel<BLOCK_N, A_MN, B_MN, MODE>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return -3;
+    configured = true;
+  }
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(a, b, c, aux, p, fp);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace oslo
+

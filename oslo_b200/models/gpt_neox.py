@@ -48,13 +48,11 @@ class GPTNeoXAttention(nn.Module):
         qkv = self.query_key_value(hidden_states)  # [b, s, heads_local * 3 * hd]
         b, s = qkv.shape[0], qkv.shape[1]
         heads = qkv.shape[-1] // (3 * self.head_size)
-        qkv = qkv.view(b, s, heads, 3, self.head_size)
-        q, k, v = qkv[..., 0, :], qkv[..., 1, :], qkv[..., 2, :]
+        rope = None
         if self.rotary_ndims > 0:
             cos, sin = self._tables(s, qkv.device)
-            q = OF.apply_rope(q, cos, sin, self.rotary_ndims, neox=True)
-            k = OF.apply_rope(k, cos, sin, self.rotary_ndims, neox=True)
-        ctx = OF.attention(q, k, v, causal=True, mask=attention_mask)
+            rope = (cos, sin, self.rotary_ndims, True)
+        ctx = OF.qkv_attention(qkv, heads, self.head_size, layout="h3d", causal=True, rope=rope, mask=attention_mask)
         return self.dense(ctx)  # (out, bias)
 
 

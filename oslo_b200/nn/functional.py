@@ -10,7 +10,7 @@ from oslo_b200.ops.activation import (  # noqa: F401
     fused_gelu,
     swiglu,
 )
-from oslo_b200.ops.attention import attention  # noqa: F401
+from oslo_b200.ops.attention import attention, qkv_attention  # noqa: F401
 from oslo_b200.ops.norm import layer_norm as fused_layer_norm  # noqa: F401
 from oslo_b200.ops.norm import rms_norm as fused_rms_norm  # noqa: F401
 from oslo_b200.ops.softmax import apply_rope, rope_tables, scale_mask_softmax  # noqa: F401

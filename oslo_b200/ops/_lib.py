@@ -21,8 +21,40 @@ class NativeLibraryMissing(RuntimeError):
     pass
 
 
+#: number of native CUDA entry-point calls made by this process (each launches one or two kernels)
+native_calls = 0
+
+
+class _CountingLib:
+    """Proxy over the CDLL that counts calls, so benchmarks can report how many native launches a step made."""
+
+    def __init__(self, dll):
+        self._dll = dll
+        self._cache = {}
+
+    def __getattr__(self, name):
+        fn = self._cache.get(name)
+        if fn is None:
+            raw = getattr(self._dll, name)
+            if name.startswith("oslo_") and not name.endswith(("_parts", "_chunk", "_bytes")):
+
+                def fn(*args, _raw=raw):
+                    global native_calls
+                    native_calls += 1
+                    return _raw(*args)
+            else:
+                fn = raw
+            self._cache[name] = fn
+        return fn
+
+
 @lru_cache(maxsize=None)
-def cuda_lib() -> ctypes.CDLL:
+def cuda_lib():
+    return _CountingLib(_load_cuda_lib())
+
+
+@lru_cache(maxsize=None)
+def _load_cuda_lib() -> ctypes.CDLL:
     path = _LIB_DIR / "liboslo_b200_cuda.so"
     if not path.exists():
         if os.environ.get("OSLO_B200_AUTOBUILD", "1") == "1":

@@ -91,3 +91,105 @@ def attention(q, k, v, causal: bool = True, scale: Optional[float] = None, mask=
     if mask is None and supported(q, k) and s % 8 == 0 and hd % 8 == 0 and k.shape[1] == s:
         return _AttentionFn.apply(q, k, v, causal, float(scale))
     return attention_reference(q, k, v, causal, scale, mask)
+
+
+# ------------------------------------------------------------- fused-QKV entry point
+def _split_qkv(qkv5, layout):
+    """q, k, v views ``[b, s, heads, hd]`` of a fused projection viewed ``[b, s, heads, 3, hd]`` ("h3d", GPT-NeoX)
+    or ``[b, s, 3, heads, hd]`` ("3hd", GPT-2)."""
+    if layout == "h3d":
+        return qkv5[..., 0, :], qkv5[..., 1, :], qkv5[..., 2, :]
+    return qkv5[:, :, 0], qkv5[:, :, 1], qkv5[:, :, 2]
+
+
+class _QKVAttentionFn(torch.autograd.Function):
+    """Rotary embedding (optional) + attention on a fused QKV activation.
+
+    The rotation is applied in place on the projection output, and backward writes dQ / dK / dV straight into
+    one buffer with the layout of the input, so no gradient is ever re-assembled by slicing.
+    """
+
+    @staticmethod
+    def forward(ctx, qkv, heads, hd, layout, causal, scale, rope):
+        from .softmax import _rope_launch
+
+        b, s = qkv.shape[0], qkv.shape[1]
+        shape5 = (b, s, heads, 3, hd) if layout == "h3d" else (b, s, 3, heads, hd)
+        qkv5 = qkv.view(shape5)
+        q, k, v = _split_qkv(qkv5, layout)
+        if rope is not None:
+            cos, sin, rot, neox = rope
+            for t in (q, k):
+                _rope_launch(t.reshape(b * s, heads, hd) if t.is_contiguous() else _tok_view(t), cos, sin, rot, neox, None, False)
+            ctx.mark_dirty(qkv)
+        qh, kh, vh = (t.permute(0, 2, 1, 3) for t in (q, k, v))
+        p = torch.empty(b, heads, s, s, dtype=qkv.dtype, device=qkv.device)
+        gemm(qh, kh, out=p, causal=1 if causal else 0)
+        softmax_inplace_(p, scale, causal)
+        out = torch.empty(b, s, heads * hd, dtype=qkv.dtype, device=qkv.device)
+        gemm(p, vh.transpose(-1, -2), out=out.view(b, s, heads, hd).permute(0, 2, 1, 3), causal=2 if causal else 0)
+        ctx.save_for_backward(qkv, p)
+        ctx.meta = (heads, hd, layout, causal, scale, rope)
+        if rope is not None:
+            return out, qkv
+        return out, None
+
+    @staticmethod
+    def backward(ctx, go, _g_qkv):
+        from .softmax import _rope_launch
+
+        qkv, p = ctx.saved_tensors
+        heads, hd, layout, causal, scale, rope = ctx.meta
+        b, s = qkv.shape[0], qkv.shape[1]
+        shape5 = (b, s, heads, 3, hd) if layout == "h3d" else (b, s, 3, heads, hd)
+        q, k, v = _split_qkv(qkv.view(shape5), layout)
+        dqkv = torch.empty_like(qkv)
+        dq, dk, dv = _split_qkv(dqkv.view(shape5), layout)
+        goh = go.contiguous().view(b, s, heads, hd).permute(0, 2, 1, 3)
+        qh, kh, vh = (t.permute(0, 2, 1, 3) for t in (q, k, v))
+        gemm(p.transpose(-1, -2), goh.transpose(-1, -2), out=dv.permute(0, 2, 1, 3), causal=3 if causal else 0)
+        dp = torch.empty_like(p)
+        gemm(goh, vh, out=dp, causal=1 if causal else 0)
+        if causal:
+            _softmax_bwd_causal(dp, p, scale)
+        else:
+            softmax_backward_(dp, p, scale)
+        gemm(dp, kh.transpose(-1, -2), out=dq.permute(0, 2, 1, 3), causal=2 if causal else 0)
+        gemm(dp.transpose(-1, -2), qh.transpose(-1, -2), out=dk.permute(0, 2, 1, 3), causal=3 if causal else 0)
+        if rope is not None:
+            cos, sin, rot, neox = rope
+            for t in (dq, dk):
+                _rope_launch(_tok_view(t), cos, sin, rot, neox, None, True)
+        return dqkv, None, None, None, None, None, None
+
+
+def _tok_view(t):
+    """``[b, s, heads, hd]`` strided view -> ``[b*s, heads, hd]`` (token stride must be uniform across b)."""
+    b, s, heads, hd = t.shape
+    assert t.stride(0) == s * t.stride(1), "tokens must be uniformly strided"
+    return t.as_strided((b * s, heads, hd), (t.stride(1), t.stride(2), t.stride(3)), t.storage_offset())
+
+
+def qkv_attention(qkv, heads: int, head_dim: int, layout: str = "h3d", causal: bool = True, scale=None, rope=None,
+                  mask=None):
+    """Attention on a fused QKV projection ``[b, s, 3 * heads * head_dim]``; returns ``[b, s, heads * head_dim]``.
+
+    ``rope = (cos, sin, rot_dim, neox)`` applies rotary embedding to q and k first (positions 0..s-1).
+    """
+    from .softmax import apply_rope
+
+    b, s = qkv.shape[0], qkv.shape[1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+    if mask is None and qkv.is_cuda and _lib.has_cuda_kernels() and qkv.dtype in (torch.bfloat16, torch.float16) \
+            and s % 8 == 0 and head_dim % 8 == 0 and qkv.is_contiguous():
+        if rope is not None and qkv.requires_grad and qkv.is_leaf:
+            qkv = qkv.clone()
+        out, _ = _QKVAttentionFn.apply(qkv, heads, head_dim, layout, causal, float(scale), rope)
+        return out
+    shape5 = (b, s, heads, 3, head_dim) if layout == "h3d" else (b, s, 3, heads, head_dim)
+    q, k, v = _split_qkv(qkv.view(shape5), layout)
+    if rope is not None:
+        cos, sin, rot, neox = rope
+        q = apply_rope(q, cos, sin, rot, neox)
+        k = apply_rope(k, cos, sin, rot, neox)
+    return attention(q, k, v, causal, scale, mask)

@@ -118,11 +118,13 @@ class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias):
         x2 = x.reshape(-1, x.shape[-1])
-        y = gemm(x2, weight, bias=bias, epilogue="bias" if bias is not None else None)
+        # allocate the result in its final shape: returning a view made here would forbid in-place ops on it
+        y = torch.empty(*x.shape[:-1], weight.shape[0], dtype=x.dtype, device=x.device)
+        gemm(x2, weight, bias=bias, epilogue="bias" if bias is not None else None, out=y.view(-1, weight.shape[0]))
         ctx.save_for_backward(x2, weight)
         ctx.has_bias = bias is not None
         ctx.x_shape = x.shape
-        return y.view(*x.shape[:-1], weight.shape[0])
+        return y
 
     @staticmethod
     def backward(ctx, gy):
@@ -133,12 +135,15 @@ class _LinearFn(torch.autograd.Function):
         gx = gw = gb = None
         if ctx.needs_input_grad[0]:
             # dX[M, K] = dY[M, N] x (W^T)[K, N]^T : B operand is W viewed [K, N] -> MN-major
-            gx = gemm(gy2, weight.t()).view(ctx.x_shape)
+            gx = torch.empty(ctx.x_shape, dtype=gy2.dtype, device=gy2.device)
+            gemm(gy2, weight.t(), out=gx.view(-1, weight.shape[1]))
         if ctx.needs_input_grad[1]:
             # dW[N, K] = (dY^T)[N, M] x (x^T)[K, M]^T : both operands MN-major
             gw = gemm(gy2.t(), x2.t())
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            gb = gy2.sum(dim=0)
+            from .activation import colsum
+
+            gb = colsum(gy2)
         return gx, gw, gb
 
 

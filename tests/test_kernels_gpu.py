@@ -1,0 +1,290 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 reference (needs a B200)."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _rel(a, b):
+    return (a.float() - b.float()).abs().max().item() / (b.float().abs().max().item() + 1e-6)
+
+
+@pytest.fixture(autouse=True)
+def _status():
+    from oslo_b200.ops import _lib
+
+    yield
+    torch.cuda.synchronize()
+    _lib.check_status()
+
+
+@pytest.mark.parametrize("a_t,b_t", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("bn", [0, 64, 128, 256])
+def test_gemm_layouts(a_t, b_t, bn):
+    from oslo_b200.ops.gemm import gemm
+
+    torch.manual_seed(0)
+    M, N, K = 392, 520, 200
+    a = torch.randn((K, M) if a_t else (M, K), device=DEV, dtype=torch.bfloat16)
+    b = torch.randn((K, N) if b_t else (N, K), device=DEV, dtype=torch.bfloat16)
+    A, B = (a.t() if a_t else a), (b.t() if b_t else b)
+    y = gemm(A, B, block_n=bn)
+    ref = A.float() @ B.float().t()
+    assert _rel(y, ref) < 1e-2
+
+
+def test_gemm_epilogues_and_batch():
+    from oslo_b200.ops.gemm import gemm
+
+    torch.manual_seed(1)
+    a = torch.randn(512, 256, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(384, 256, device=DEV, dtype=torch.bfloat16)
+    bias = torch.randn(384, device=DEV, dtype=torch.bfloat16)
+    ref = a.float() @ b.float().t() + bias.float()
+    assert _rel(gemm(a, b, bias=bias, epilogue="bias"), ref) < 1e-2
+    aux = torch.empty(512, 384, device=DEV, dtype=torch.bfloat16)
+    y = gemm(a, b, bias=bias, epilogue="gelu", aux=aux)
+    assert _rel(y, F.gelu(ref, approximate="tanh")) < 1e-2
+    assert _rel(aux, ref) < 1e-2
+    c = torch.randn(512, 384, device=DEV, dtype=torch.bfloat16)
+    c0 = c.float().clone()
+    gemm(a, b, out=c, accumulate=True)
+    assert _rel(c, c0 + a.float() @ b.float().t()) < 1e-2
+    a4 = torch.randn(2, 3, 128, 64, device=DEV, dtype=torch.float16)
+    b4 = torch.randn(2, 3, 256, 64, device=DEV, dtype=torch.float16)
+    assert _rel(gemm(a4, b4), a4.float() @ b4.float().transpose(-1, -2)) < 1e-2
+
+
+def test_linear_autograd():
+    from oslo_b200.ops.gemm import linear
+
+    torch.manual_seed(2)
+    x = torch.randn(4, 96, 128, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = torch.randn(256, 128, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    b = torch.randn(256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = linear(x, w, b)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yr = F.linear(xr, wr, br)
+    yr.backward(g.float())
+    assert _rel(y, yr) < 1e-2 and _rel(x.grad, xr.grad) < 1e-2 and _rel(w.grad, wr.grad) < 1e-2
+    assert _rel(b.grad, br.grad) < 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("h", [256, 2048, 4096, 5120])
+@pytest.mark.parametrize("rms", [False, True])
+def test_norm(dtype, h, rms):
+    from oslo_b200.ops.norm import layer_norm, rms_norm, rms_norm_reference
+
+    torch.manual_seed(3)
+    x = torch.randn(37, 5, h, device=DEV, dtype=dtype, requires_grad=True)
+    w = (torch.randn(h, device=DEV) * 0.1 + 1).to(dtype).requires_grad_()
+    b = (torch.randn(h, device=DEV) * 0.1).to(dtype).requires_grad_()
+    g = torch.randn(37, 5, h, device=DEV, dtype=dtype)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    if rms:
+        y = rms_norm(x, h, w, 1e-6)
+        yr = rms_norm_reference(xr, wr, 1e-6)
+    else:
+        y = layer_norm(x, h, w, b, 1e-5)
+        yr = F.layer_norm(xr, (h,), wr, br, 1e-5)
+    y.backward(g)
+    yr.backward(g.float())
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert _rel(y, yr) < tol
+    assert _rel(x.grad, xr.grad) < tol
+    assert _rel(w.grad, wr.grad) < max(tol, 3e-2 if dtype != torch.float32 else tol)
+    if not rms:
+        assert _rel(b.grad, br.grad) < max(tol, 3e-2 if dtype != torch.float32 else tol)
+
+
+def test_norm_mixed_dtype():
+    from oslo_b200.ops.norm import layer_norm
+
+    x = torch.randn(64, 1024, device=DEV, dtype=torch.bfloat16)
+    w = torch.rand(1024, device=DEV) + 0.5
+    b = torch.randn(1024, device=DEV)
+    y = layer_norm(x, 1024, w, b, 1e-5)
+    assert y.dtype == torch.bfloat16
+    assert _rel(y, F.layer_norm(x.float(), (1024,), w, b, 1e-5)) < 1e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_bias_gelu_swiglu_dropout(dtype):
+    from oslo_b200.ops.activation import bias_dropout_add, bias_gelu, swiglu
+
+    torch.manual_seed(4)
+    x = torch.randn(33, 512, device=DEV, dtype=dtype, requires_grad=True)
+    bias = torch.randn(512, device=DEV, dtype=dtype, requires_grad=True)
+    g = torch.randn(33, 512, device=DEV, dtype=dtype)
+    y = bias_gelu(x, bias)
+    y.backward(g)
+    xr, br = x.detach().float().requires_grad_(), bias.detach().float().requires_grad_()
+    yr = F.gelu(xr + br, approximate="tanh")
+    yr.backward(g.float())
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    assert _rel(y, yr) < tol and _rel(x.grad, xr.grad) < tol and _rel(bias.grad, br.grad) < 3e-2
+
+    gu = torch.randn(17, 2 * 256, device=DEV, dtype=dtype, requires_grad=True)
+    gg = torch.randn(17, 256, device=DEV, dtype=dtype)
+    s = swiglu(gu)
+    s.backward(gg)
+    gur = gu.detach().float().requires_grad_()
+    sr = F.silu(gur[:, :256]) * gur[:, 256:]
+    sr.backward(gg.float())
+    assert _rel(s, sr) < tol and _rel(gu.grad, gur.grad) < tol
+
+    res = torch.randn(33, 512, device=DEV, dtype=dtype)
+    out = bias_dropout_add(x.detach(), bias.detach(), res, 0.0, True)
+    assert _rel(out, x.detach().float() + bias.detach().float() + res.float()) < tol
+    xd = torch.ones(64, 4096, device=DEV, dtype=dtype, requires_grad=True)
+    od = bias_dropout_add(xd, None, None, 0.25, True)
+    kept = (od != 0).float().mean().item()
+    assert abs(kept - 0.75) < 0.02
+    assert abs(od.float().mean().item() - 1.0) < 0.05
+    od.sum().backward()
+    assert torch.equal((xd.grad != 0), (od != 0))  # backward regenerates the same mask
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_softmax(causal):
+    from oslo_b200.ops.softmax import scale_mask_softmax, softmax_reference
+
+    torch.manual_seed(5)
+    x = torch.randn(2, 3, 64, 64, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    mask = None if causal else (torch.rand(2, 1, 1, 64, device=DEV) > 0.8).float() * -10000.0
+    y = scale_mask_softmax(x, 0.5, causal, mask)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    yr = softmax_reference(xr, 0.5, causal, mask)
+    yr.backward(g.float())
+    assert _rel(y, yr) < 1e-2 and _rel(x.grad, xr.grad) < 2e-2
+
+
+@pytest.mark.parametrize("neox", [True, False])
+def test_rope(neox):
+    from oslo_b200.ops.softmax import apply_rope, rope_reference, rope_tables
+
+    torch.manual_seed(6)
+    b, s, nh, hd, rot = 2, 32, 4, 64, 16
+    qkv = torch.randn(b, s, nh, 3, hd, device=DEV, dtype=torch.bfloat16)
+    cos, sin = rope_tables(s, rot, 10000.0, DEV)
+    q_ref = rope_reference(qkv[..., 0, :].clone(), cos, sin, rot, neox)
+    q = apply_rope(qkv[..., 0, :], cos, sin, rot, neox)  # in place on the strided view
+    assert _rel(q, q_ref) < 1e-2
+    back = apply_rope(q.clone().requires_grad_(), cos, sin, rot, neox)
+    back.backward(torch.ones_like(back))
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_attention(causal):
+    from oslo_b200.ops.attention import attention, attention_reference
+
+    torch.manual_seed(7)
+    b, s, nh, hd = 2, 384, 4, 64
+    qkv = (torch.randn(b, s, nh, 3, hd, device=DEV) * 0.5).to(torch.bfloat16).requires_grad_()
+    q, k, v = qkv[..., 0, :], qkv[..., 1, :], qkv[..., 2, :]
+    out = attention(q, k, v, causal=causal)
+    g = torch.randn_like(out)
+    out.backward(g)
+    qkv_r = qkv.detach().float().requires_grad_()
+    out_r = attention_reference(qkv_r[..., 0, :], qkv_r[..., 1, :], qkv_r[..., 2, :], causal=causal)
+    out_r.backward(g.float())
+    assert _rel(out, out_r) < 2e-2
+    assert _rel(qkv.grad, qkv_r.grad) < 3e-2
+
+
+def test_cross_entropy():
+    from oslo_b200.ops.loss import vocab_parallel_cross_entropy
+
+    torch.manual_seed(8)
+    rows, v = 50, 1000
+    logits = torch.randn(5, 10, v, device=DEV, dtype=torch.bfloat16)
+    tgt = torch.randint(0, 990, (5, 10), device=DEV)
+    tgt[0, :3] = -100
+    lr = logits.detach().float().requires_grad_()
+    lr_masked = lr.clone()
+    lr_masked[..., 990:] = float("-inf")
+    ref = F.cross_entropy(lr_masked.view(-1, v), tgt.view(-1), ignore_index=-100, reduction="none").view(5, 10)
+    ref.sum().backward()
+    x = logits.clone().requires_grad_()
+    loss = vocab_parallel_cross_entropy(x * 1.0, tgt, None, valid_vocab=990)
+    loss.sum().backward()
+    assert _rel(loss, ref) < 1e-3
+    assert _rel(x.grad, lr.grad) < 2e-2
+
+
+@pytest.mark.parametrize("dtype,master", [(torch.float32, False), (torch.bfloat16, True), (torch.float16, False)])
+def test_fused_adam(dtype, master):
+    from oslo_b200.optim import FusedAdam
+
+    torch.manual_seed(9)
+    shapes = [(300, 70), (17,), (4096, 33), (5,)]
+    ps = [torch.randn(s, device=DEV, dtype=dtype).requires_grad_() for s in shapes]
+    rs = [p.detach().float().clone().requires_grad_() for p in ps]
+    opt = FusedAdam(ps, lr=1e-2, weight_decay=0.1, master_weights=master)
+    ref = torch.optim.AdamW(rs, lr=1e-2, weight_decay=0.1)
+    for _ in range(5):
+        for p, r in zip(ps, rs):
+            g = torch.randn_like(r)
+            p.grad = g.to(dtype)
+            r.grad = g.to(dtype).float()
+        opt.step()
+        ref.step()
+    tol = 1e-5 if dtype == torch.float32 else (1e-2 if master else 3e-2)
+    for p, r in zip(ps, rs):
+        assert _rel(p, r) < tol
+    if master:
+        for p, r in zip(ps, rs):
+            assert _rel(opt.state[p]["master"], r) < 1e-5
+
+
+def test_neox_model_matches_reference_path():
+    """Whole model on the native kernels vs the same weights on the pure-torch CPU path."""
+    from oslo_b200.models.config import GPTNeoXConfig
+    from oslo_b200.models.gpt_neox import GPTNeoXForCausalLM
+
+    torch.manual_seed(10)
+    cfg = GPTNeoXConfig(vocab_size=512, hidden_size=128, num_hidden_layers=2, num_attention_heads=4,
+                        intermediate_size=512, max_position_embeddings=64)
+    cpu = GPTNeoXForCausalLM(cfg)
+    gpu = GPTNeoXForCausalLM(cfg)
+    gpu.load_state_dict(cpu.state_dict())
+    gpu = gpu.to(DEV, torch.bfloat16)
+    ids = torch.randint(0, 512, (2, 64))
+    l_cpu = cpu(input_ids=ids, labels=ids).loss
+    l_gpu = gpu(input_ids=ids.to(DEV), labels=ids.to(DEV)).loss
+    l_cpu.backward()
+    l_gpu.backward()
+    assert abs(l_cpu.item() - l_gpu.item()) < 3e-2
+    gc = dict(cpu.named_parameters())
+    for k, p in gpu.named_parameters():
+        assert _rel(p.grad, gc[k].grad) < 8e-2, k
+
+
+@pytest.mark.parametrize("layout", ["h3d", "3hd"])
+def test_qkv_attention_with_rope(layout):
+    from oslo_b200.ops.attention import qkv_attention
+    from oslo_b200.ops.softmax import rope_tables
+
+    torch.manual_seed(11)
+    b, s, nh, hd, rot = 2, 256, 4, 64, 16
+    base = (torch.randn(b, s, 3 * nh * hd, device=DEV) * 0.5).to(torch.bfloat16)
+    cos, sin = rope_tables(s, rot, 10000.0, DEV)
+    x = base.clone().requires_grad_()
+    out = qkv_attention(x * 1.0, nh, hd, layout=layout, causal=True, rope=(cos, sin, rot, True))
+    g = torch.randn_like(out)
+    out.backward(g)
+    xr = base.float().cpu().requires_grad_()
+    out_r = qkv_attention(xr * 1.0, nh, hd, layout=layout, causal=True, rope=(cos.cpu(), sin.cpu(), rot, True))
+    out_r.backward(g.float().cpu())
+    assert _rel(out.cpu(), out_r) < 2e-2
+    assert _rel(x.grad.cpu(), xr.grad) < 3e-2
