@@ -155,7 +155,7 @@ OSLO_DEVINL void fused_tile_coords(int tile, const GemmParams& p, const FusedPar
 }
 
 // AG copy role: announce our shard, then pull every shard (own first) into x_full and flag it.
-__device__ __noinline__ void ag_copy_role(const GemmParams& p, const FusedParams& fp) {
+static __device__ __noinline__ void ag_copy_role(const GemmParams& p, const FusedParams& fp) {
   __shared__ int s_ok;
   const int tid = threadIdx.x, nthreads = blockDim.x;
   if (blockIdx.x == 0 && tid < fp.tp) {
@@ -202,7 +202,7 @@ __device__ __noinline__ void ag_copy_role(const GemmParams& p, const FusedParams
 }
 
 // RS reduce phase (all threads of all GEMM CTAs): wait for every source, then out = sum of the tp slots.
-__device__ __noinline__ void rs_reduce_phase(const GemmParams& p, const FusedParams& fp, int cta, int num_ctas,
+static __device__ __noinline__ void rs_reduce_phase(const GemmParams& p, const FusedParams& fp, int cta, int num_ctas,
                                              volatile int* abort_flag) {
   const int lane = threadIdx.x & 31;
   bool ok = true;

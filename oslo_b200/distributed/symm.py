@@ -1,0 +1,221 @@
+"""Symmetric memory for a process group: one device allocation per rank, mapped into every peer (CUDA IPC).
+
+``enable(parallel_context, mode, max_tokens, max_features)`` builds a :class:`SymmetricWorkspace` for the
+group and registers it with :mod:`oslo_b200.ops.fused_collectives`, after which the sequence-parallel linears
+run as single fused kernels (``csrc/fused_collectives_sm100a.cu``).
+
+Workspace layout per rank (all offsets identical on every rank)::
+
+    [ flags 4 KiB | in[0] | in[1] | slots[0] | slots[1] ]
+
+* ``in[p]``     this rank's shard of the all-gather input for calls with parity ``p`` (``Tl x F`` elements);
+* ``slots[p]``  ``tp`` blocks of ``Tl x F``: block ``s`` receives rank ``s``'s partial rows of a reduce-scatter;
+* flags        ``ag_ready[tp]``, ``rs_flag[tp]``, ``barrier[tp]`` written by peers, holding call epochs.
+
+Double buffering by call parity is what makes the scheme free of write-after-read races without a trailing
+barrier: a rank can only be one call ahead of any peer, because each call needs data from every peer.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from oslo_b200.ops import _lib, fused_collectives
+
+_FLAG_BYTES = 4096
+
+
+class _RawCudaBuffer:
+    """Exposes a raw device pointer to torch through ``__cuda_array_interface__`` (zero copy)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class SymmetricWorkspace:
+    def __init__(self, pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 20):
+        self.pc, self.mode = pc, mode
+        self.tp = pc.get_world_size(mode)
+        self.rank = pc.get_local_rank(mode)
+        if self.tp > 8:
+            raise ValueError("fused collectives support groups of up to 8 ranks")
+        self.device = pc.device
+        self.dtype = dtype
+        self.copy_ctas = copy_ctas
+        self.max_tokens, self.max_features = max_tokens, max_features
+        esz = torch.empty((), dtype=dtype).element_size()
+        shard_elems = (max_tokens // self.tp) * max_features
+        self.in_bytes = (shard_elems * esz + 1023) // 1024 * 1024
+        self.slot_bytes = (max_tokens * max_features * esz + 1023) // 1024 * 1024
+        self.total = _FLAG_BYTES + 2 * self.in_bytes + 2 * self.slot_bytes
+        lib = _lib.cuda_lib()
+        base = ctypes.c_void_p()
+        rc = lib.oslo_symm_alloc(ctypes.c_ulonglong(self.total), ctypes.byref(base))
+        if rc:
+            raise RuntimeError(f"symmetric allocation of {self.total} bytes failed (cuda error {-rc})")
+        self.base = base.value
+        hbytes = lib.oslo_ipc_handle_bytes()
+        handle = (ctypes.c_ubyte * hbytes)()
+        rc = lib.oslo_ipc_get_handle(ctypes.c_void_p(self.base), handle)
+        if rc:
+            raise RuntimeError(f"cudaIpcGetMemHandle failed (cuda error {-rc})")
+        gathered: List[Optional[bytes]] = [None] * self.tp
+        dist.all_gather_object(gathered, bytes(handle), group=pc.get_cpu_group(mode))
+        self.peer_base: List[int] = []
+        for r, h in enumerate(gathered):
+            if r == self.rank:
+                self.peer_base.append(self.base)
+                continue
+            buf = (ctypes.c_ubyte * hbytes).from_buffer_copy(h)
+            out = ctypes.c_void_p()
+            rc = lib.oslo_ipc_open_handle(buf, ctypes.byref(out))
+            if rc:
+                raise RuntimeError(f"cudaIpcOpenMemHandle for peer {r} failed (cuda error {-rc})")
+            self.peer_base.append(out.value)
+        # local scratch counters (not shared): chunk_flag[tp], chunk_arrive[tp], tile_done[tp]
+        self.local = torch.zeros(64, dtype=torch.int32, device=self.device)
+        self.epoch = 0
+        self._local_bytes = torch.as_tensor(_RawCudaBuffer(self.base, self.total), device=self.device)
+        dist.barrier(group=pc.get_cpu_group(mode))
+        self.barrier()
+
+    # ------------------------------------------------------------ addressing
+    def _flag_ptrs(self, which: int):
+        # which: 0 ag_ready, 1 rs_flag, 2 barrier ; each 64 ints apart
+        return (ctypes.c_void_p * self.tp)(*[b + which * 256 for b in self.peer_base])
+
+    def _in_ptrs(self, parity: int):
+        off = _FLAG_BYTES + parity * self.in_bytes
+        return (ctypes.c_void_p * self.tp)(*[b + off for b in self.peer_base])
+
+    def _slot_ptrs(self, parity: int):
+        off = _FLAG_BYTES + 2 * self.in_bytes + parity * self.slot_bytes
+        return (ctypes.c_void_p * self.tp)(*[b + off for b in self.peer_base])
+
+    def _local_in(self, parity: int, rows: int, cols: int):
+        off = _FLAG_BYTES + parity * self.in_bytes
+        n = rows * cols * self._local_bytes.new_empty((), dtype=self.dtype).element_size()
+        return self._local_bytes[off : off + n].view(self.dtype).view(rows, cols)
+
+    def _local_ptr(self, idx: int) -> ctypes.c_void_p:
+        return ctypes.c_void_p(self.local.data_ptr() + idx * 4 * 16)
+
+    # ------------------------------------------------------------------ ops
+    def barrier(self):
+        """Device-side barrier over the group on the current stream (bounded wait)."""
+        self.epoch += 1
+        rc = _lib.cuda_lib().oslo_symm_barrier(
+            self._flag_ptrs(2), ctypes.c_void_p(self.base + 2 * 256), ctypes.c_int(self.rank), ctypes.c_int(self.tp),
+            ctypes.c_int(self.epoch), _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr())
+        if rc:
+            raise RuntimeError(f"oslo_symm_barrier failed ({rc})")
+
+    def supports(self, x: torch.Tensor, w: torch.Tensor) -> bool:
+        if x.dtype != self.dtype or w.dtype != self.dtype or x.dim() != 2 or w.dim() != 2:
+            return False
+        rows, k = x.shape
+        n = w.shape[0]
+        if k % 8 or n % 8:
+            return False
+        # x is either a token shard (ag) or the full token set (rs); both must tile into 128-row blocks per rank
+        return True
+
+    def _weight_operand(self, w):
+        if w.stride(-1) == 1:
+            return w, 0, w.stride(0)
+        if w.stride(0) == 1:
+            return w, 1, w.stride(1)
+        w = w.contiguous()
+        return w, 0, w.stride(0)
+
+    def ag_ok(self, x_shard, w) -> bool:
+        tl, k = x_shard.shape
+        return (self.supports(x_shard, w) and tl % 128 == 0 and tl * self.tp <= self.max_tokens
+                and k <= self.max_features and tl * k * x_shard.element_size() <= self.in_bytes)
+
+    def rs_ok(self, x, w) -> bool:
+        t, _ = x.shape
+        n = w.shape[0]
+        return (self.supports(x, w) and t % self.tp == 0 and (t // self.tp) % 128 == 0 and t <= self.max_tokens
+                and n <= self.max_features and t * n * x.element_size() <= self.slot_bytes)
+
+    def ag_gemm(self, x_shard: torch.Tensor, weight: torch.Tensor):
+        """Returns ``(all_gather(x_shard) @ weight^T, all_gather(x_shard))``."""
+        tl, k = x_shard.shape
+        t = tl * self.tp
+        n = weight.shape[0]
+        self.epoch += 1
+        parity = self.epoch & 1
+        self._local_in(parity, tl, k).copy_(x_shard)
+        x_full = torch.empty(t, k, dtype=x_shard.dtype, device=x_shard.device)
+        out = torch.empty(t, n, dtype=x_shard.dtype, device=x_shard.device)
+        w, b_mn, ldb = self._weight_operand(weight)
+        rc = _lib.cuda_lib().oslo_ag_gemm(
+            self._in_ptrs(parity), _lib.ptr(x_full), _lib.ptr(w), _lib.ptr(out), None, ctypes.c_int(t), ctypes.c_int(n),
+            ctypes.c_int(k), ctypes.c_longlong(ldb), ctypes.c_int(b_mn), ctypes.c_int(1 if self.dtype == torch.bfloat16 else 0),
+            ctypes.c_int(self.tp), ctypes.c_int(self.rank), ctypes.c_int(self.epoch), self._flag_ptrs(0),
+            self._local_ptr(0), self._local_ptr(1), ctypes.c_int(self.copy_ctas), ctypes.c_int(_lib.num_sms()),
+            _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr())
+        if rc:
+            raise RuntimeError(f"oslo_ag_gemm failed ({rc})")
+        return out, x_full
+
+    def gemm_rs(self, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None):
+        """Returns this rank's rows of ``reduce_scatter(x @ weight^T)``."""
+        t, k = x.shape
+        n = weight.shape[0]
+        tl = t // self.tp
+        if not x.is_contiguous():
+            x = x.contiguous()
+        self.epoch += 1
+        parity = self.epoch & 1
+        out = torch.empty(tl, n, dtype=x.dtype, device=x.device)
+        w, b_mn, ldb = self._weight_operand(weight)
+        rc = _lib.cuda_lib().oslo_gemm_rs(
+            _lib.ptr(x), ctypes.c_longlong(x.stride(0)), _lib.ptr(w), ctypes.c_longlong(ldb), ctypes.c_int(b_mn),
+            _lib.ptr(out), _lib.ptr(bias), ctypes.c_int(t), ctypes.c_int(n), ctypes.c_int(k),
+            ctypes.c_int(1 if self.dtype == torch.bfloat16 else 0), ctypes.c_int(self.tp), ctypes.c_int(self.rank),
+            ctypes.c_int(self.epoch), self._slot_ptrs(parity), self._flag_ptrs(1), self._local_ptr(2),
+            ctypes.c_int(_lib.num_sms()), _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr())
+        if rc:
+            raise RuntimeError(f"oslo_gemm_rs failed ({rc})")
+        return out
+
+
+class _Runtime:
+    """Adapter registered with :mod:`oslo_b200.ops.fused_collectives`."""
+
+    def __init__(self, ws: SymmetricWorkspace):
+        self.ws = ws
+
+    def supports(self, x, w):
+        if x.dim() != 2:
+            return False
+        # called with either a token shard (all-gather side) or full tokens (reduce-scatter side)
+        return self.ws.ag_ok(x, w) or self.ws.rs_ok(x, w)
+
+    def ag_gemm(self, x_shard, weight):
+        if not self.ws.ag_ok(x_shard, weight):
+            raise RuntimeError("ag_gemm: operands not supported by the fused kernel")
+        return self.ws.ag_gemm(x_shard, weight)
+
+    def gemm_rs(self, x, weight):
+        if not self.ws.rs_ok(x, weight):
+            raise RuntimeError("gemm_rs: operands not supported by the fused kernel")
+        return self.ws.gemm_rs(x, weight)
+
+
+def enable(pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 20) -> bool:
+    """Create the group's symmetric workspace and switch the sequence-parallel linears to the fused kernels."""
+    if not (torch.cuda.is_available() and pc.use_cuda) or pc.get_world_size(mode) == 1:
+        return False
+    ws = SymmetricWorkspace(pc, mode, max_tokens, max_features, dtype, copy_ctas)
+    fused_collectives.set_runtime(_Runtime(ws))
+    return True
+
+
+def disable():
+    fused_collectives.set_runtime(None)

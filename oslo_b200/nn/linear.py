@@ -201,8 +201,7 @@ class Linear2D(Linear):
                 return out, ops.gather_bias_2d(self.bias, pc)
             out = ops.add_bias_2d(out, self.bias, pc)
         if self.gather_output:
-            out = ops.all_gather_tensor_2d(out, -1, ParallelMode.TENSOR_2D_ROW, pc)
-            out = ops.all_gather_tensor_2d(out, 0, ParallelMode.TENSOR_2D_COL, pc)
+            out = ops.gather_output_2d(out, pc)
             if hasattr(self, "orig_num_classes"):
                 out = out[..., : self.orig_num_classes].contiguous()
         return out
@@ -246,8 +245,7 @@ class Linear2p5D(Linear):
                 return out, self.bias
             out = out + self.bias
         if self.gather_output:
-            out = ops.all_gather_tensor_2p5d(out, -1, ParallelMode.TENSOR_2P5D_ROW, pc)
-            out = ops.all_gather_tensor_2p5d(out, 0, ParallelMode.TENSOR_2P5D_COL, pc)
+            out = ops.gather_output_2p5d(out, pc)
             if hasattr(self, "orig_num_classes"):
                 out = out[..., : self.orig_num_classes].contiguous()
         return out

@@ -107,6 +107,10 @@ class _QKVAttentionFn(torch.autograd.Function):
 
     The rotation is applied in place on the projection output, and backward writes dQ / dK / dV straight into
     one buffer with the layout of the input, so no gradient is ever re-assembled by slicing.
+
+    The in-place rotation is deliberately not declared to autograd (``mark_dirty`` would force a second output
+    and forbid view inputs): the projection output has no other consumer, and the linear that produced it does
+    not keep it for its own backward.
     """
 
     @staticmethod
@@ -121,7 +125,6 @@ class _QKVAttentionFn(torch.autograd.Function):
             cos, sin, rot, neox = rope
             for t in (q, k):
                 _rope_launch(t.reshape(b * s, heads, hd) if t.is_contiguous() else _tok_view(t), cos, sin, rot, neox, None, False)
-            ctx.mark_dirty(qkv)
         qh, kh, vh = (t.permute(0, 2, 1, 3) for t in (q, k, v))
         p = torch.empty(b, heads, s, s, dtype=qkv.dtype, device=qkv.device)
         gemm(qh, kh, out=p, causal=1 if causal else 0)
@@ -130,12 +133,10 @@ class _QKVAttentionFn(torch.autograd.Function):
         gemm(p, vh.transpose(-1, -2), out=out.view(b, s, heads, hd).permute(0, 2, 1, 3), causal=2 if causal else 0)
         ctx.save_for_backward(qkv, p)
         ctx.meta = (heads, hd, layout, causal, scale, rope)
-        if rope is not None:
-            return out, qkv
-        return out, None
+        return out
 
     @staticmethod
-    def backward(ctx, go, _g_qkv):
+    def backward(ctx, go):
         from .softmax import _rope_launch
 
         qkv, p = ctx.saved_tensors
@@ -182,10 +183,9 @@ def qkv_attention(qkv, heads: int, head_dim: int, layout: str = "h3d", causal: b
     scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
     if mask is None and qkv.is_cuda and _lib.has_cuda_kernels() and qkv.dtype in (torch.bfloat16, torch.float16) \
             and s % 8 == 0 and head_dim % 8 == 0 and qkv.is_contiguous():
-        if rope is not None and qkv.requires_grad and qkv.is_leaf:
+        if rope is not None and qkv.is_leaf:
             qkv = qkv.clone()
-        out, _ = _QKVAttentionFn.apply(qkv, heads, head_dim, layout, causal, float(scale), rope)
-        return out
+        return _QKVAttentionFn.apply(qkv, heads, head_dim, layout, causal, float(scale), rope)
     shape5 = (b, s, heads, 3, head_dim) if layout == "h3d" else (b, s, 3, heads, head_dim)
     q, k, v = _split_qkv(qkv.view(shape5), layout)
     if rope is not None:

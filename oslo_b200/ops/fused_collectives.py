@@ -21,10 +21,15 @@ def runtime():
     return _runtime
 
 
-def available(x: torch.Tensor, w: torch.Tensor) -> bool:
+def available(x: torch.Tensor, w: torch.Tensor, kind: str = "any") -> bool:
+    """``kind``: "ag" (x is a token shard), "rs" (x holds all tokens) or "any"."""
     rt = _runtime
-    if rt is None or not x.is_cuda:
+    if rt is None or not x.is_cuda or x.dim() != 2:
         return False
+    if kind == "ag":
+        return rt.ws.ag_ok(x, w)
+    if kind == "rs":
+        return rt.ws.rs_ok(x, w)
     return rt.supports(x, w)
 
 

@@ -118,10 +118,10 @@ def gather_sequence_1d(x, dim, parallel_context):
 
 
 # ----------------------------------------------------------- sequence-parallel linears
-def _use_fused(x, weight) -> bool:
+def _use_fused(x, weight, kind) -> bool:
     from oslo_b200.ops import fused_collectives as fc
 
-    return fc.available(x, weight)
+    return fc.available(x, weight, kind)
 
 
 class _AGLinear(torch.autograd.Function):
@@ -130,7 +130,7 @@ class _AGLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, pc):
         ctx.pc = pc
-        if _use_fused(x, weight):
+        if _use_fused(x, weight, "ag"):
             from oslo_b200.ops import fused_collectives as fc
 
             y, x_full = fc.ag_gemm(x, weight, pc)
@@ -149,7 +149,7 @@ class _AGLinear(torch.autograd.Function):
         gy = gy.contiguous()
         gx = gw = None
         if ctx.needs_input_grad[0]:
-            if _use_fused(gy, weight):
+            if _use_fused(gy, weight.t(), "rs"):
                 from oslo_b200.ops import fused_collectives as fc
 
                 gx = fc.gemm_rs(gy, weight.t(), pc)
@@ -172,7 +172,7 @@ class _LinearRS(torch.autograd.Function):
     def forward(ctx, x, weight, pc):
         ctx.pc = pc
         ctx.save_for_backward(x, weight)
-        if _use_fused(x, weight):
+        if _use_fused(x, weight, "rs"):
             from oslo_b200.ops import fused_collectives as fc
 
             return fc.gemm_rs(x, weight, pc)
@@ -189,7 +189,7 @@ class _LinearRS(torch.autograd.Function):
         from oslo_b200.ops.gemm import matmul_nt
 
         gx = gw = None
-        if _use_fused(gy, weight):
+        if _use_fused(gy, weight.t(), "ag"):
             from oslo_b200.ops import fused_collectives as fc
 
             # dX = all_gather(dY) @ W ; the gathered dY is reused for dW

@@ -292,6 +292,42 @@ class TensorParallel(ParallelWrapper):
                 if m.__class__.__name__.endswith(("Attention", "MLP", "Layer", "Block", "Model")):
                     m.sequence_parallel_state = self.sp_state
 
+    # ------------------------------------------ replicated-parameter gradient sync
+    def _mark_replicated(self, p: nn.Parameter, modes):
+        """``p`` is held identically by every rank of ``modes`` but sees rank-specific data: sum its gradient over
+        those groups at the end of backward (one flattened all-reduce per distinct group list)."""
+        modes = tuple(modes)
+        if not hasattr(self, "_replicated"):
+            self._replicated = {}
+            self._rep_callback_queued = False
+        if any(p is q for q in self._replicated.get(modes, [])):
+            return
+        self._replicated.setdefault(modes, []).append(p)
+        p.register_post_accumulate_grad_hook(self._rep_hook)
+
+    def _rep_hook(self, p):
+        if not self._rep_callback_queued:
+            self._rep_callback_queued = True
+            torch.autograd.Variable._execution_engine.queue_callback(self._reduce_replicated_grads)
+
+    def _reduce_replicated_grads(self):
+        self._rep_callback_queued = False
+        pc = self.parallel_context
+        for modes, params in self._replicated.items():
+            grads = [p.grad for p in params if p.grad is not None]
+            by_dtype = {}
+            for g in grads:
+                by_dtype.setdefault(g.dtype, []).append(g)
+            for gs in by_dtype.values():
+                flat = torch.cat([g.reshape(-1) for g in gs])
+                for m in modes:
+                    comm.all_reduce(flat, parallel_context=pc, parallel_mode=m)
+                off = 0
+                for g in gs:
+                    n = g.numel()
+                    g.copy_(flat[off : off + n].view_as(g))
+                    off += n
+
     # ---------------------------------------- sequence-parallel gradient sync
     def _mark_sp(self, m: nn.Module):
         for p in m.parameters(recurse=False):

@@ -1,0 +1,113 @@
+"""Fused all-gather->GEMM and GEMM->reduce-scatter kernels vs the NCCL + matmul composition (needs >= 2 GPUs)."""
+import os
+
+import pytest
+import torch
+
+from dist_utils import run_dist
+
+pytestmark = pytest.mark.gpu
+
+
+def _n_gpus():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _worker(rank, world):
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch.distributed as dist
+
+    from oslo_b200 import ParallelContext, ParallelMode
+    from oslo_b200.distributed import comm, symm
+    from oslo_b200.ops import _lib, fused_collectives as fc
+
+    pc = ParallelContext.from_torch(tensor_parallel_size=world, tensor_parallel_mode=ParallelMode.TENSOR_1D,
+                                    backend="nccl", seed=0)
+    dev = pc.device
+    assert symm.enable(pc, ParallelMode.TENSOR_1D, max_tokens=4096, max_features=1024)
+    M1 = ParallelMode.TENSOR_1D
+    torch.manual_seed(100 + rank)
+
+    def rel(a, b):
+        return (a.float() - b.float()).abs().max().item() / (b.float().abs().max().item() + 1e-6)
+
+    for it, (T, K, N, b_t) in enumerate([(1024, 512, 384, False), (2048, 1024, 768, True), (1024, 256, 1024, False),
+                                          (4096, 1024, 256, True), (1024, 512, 384, False)]):
+        tl = T // world
+        # ---- all-gather -> GEMM
+        x = (torch.randn(tl, K, device=dev) * 0.5).to(torch.bfloat16)
+        w = (torch.randn(K, N, device=dev) * 0.1).to(torch.bfloat16) if b_t else (torch.randn(N, K, device=dev) * 0.1).to(torch.bfloat16)
+        W = w.t() if b_t else w
+        assert fc.available(x, W, "ag")
+        y, x_full = fc.ag_gemm(x, W, pc)
+        x_ref = comm.all_gather(x, dim=0, parallel_context=pc, parallel_mode=M1)
+        y_ref = x_ref.float() @ W.float().t()
+        torch.cuda.synchronize()
+        _lib.check_status()
+        assert torch.equal(x_full, x_ref), f"gathered activations differ (case {it})"
+        assert rel(y, y_ref) < 1e-2, (it, rel(y, y_ref))
+        # ---- GEMM -> reduce-scatter
+        xa = (torch.randn(T, K, device=dev) * 0.5).to(torch.bfloat16)
+        wn = (torch.randn(K, N, device=dev) * 0.1).to(torch.bfloat16) if b_t else (torch.randn(N, K, device=dev) * 0.1).to(torch.bfloat16)
+        WN = wn.t() if b_t else wn
+        assert fc.available(xa, WN, "rs")
+        out = fc.gemm_rs(xa, WN, pc)
+        part = (xa.float() @ WN.float().t())
+        ref = comm.reduce_scatter(part, dim=0, parallel_context=pc, parallel_mode=M1)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        assert rel(out, ref) < 2e-2, (it, rel(out, ref))
+    dist.barrier()
+    pc.destroy()
+
+
+@pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_fused_collectives_match_nccl():
+    run_dist(_worker, min(_n_gpus(), 4) if _n_gpus() != 3 else 2, timeout=600)
+
+
+def _model_worker(rank, world):
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import oslo_b200
+    from oslo_b200 import ParallelContext, ParallelMode
+    from oslo_b200.distributed import symm
+    from oslo_b200.models.config import GPTNeoXConfig
+    from oslo_b200.models.gpt_neox import GPTNeoXForCausalLM
+    from oslo_b200.ops import _lib
+    from oslo_b200.parallel import TensorParallel
+
+    pc = ParallelContext.from_torch(tensor_parallel_size=world, tensor_parallel_mode=ParallelMode.TENSOR_1D,
+                                    backend="nccl", seed=0)
+    dev = pc.device
+    cfg = GPTNeoXConfig(vocab_size=2048, hidden_size=512, num_hidden_layers=2, num_attention_heads=8,
+                        intermediate_size=2048, max_position_embeddings=256)
+    losses = {}
+    grads = {}
+    for fused in (False, True):
+        torch.manual_seed(3)
+        model = GPTNeoXForCausalLM(cfg).to(dev, torch.bfloat16)
+        wrapped = TensorParallel(model, pc, sequence_parallel=True)
+        oslo_b200.ready(wrapped, pc)
+        if fused:
+            assert symm.enable(pc, ParallelMode.TENSOR_1D, max_tokens=world * 2 * 256, max_features=512)
+        else:
+            symm.disable()
+        torch.manual_seed(4)
+        ids = torch.randint(0, 2048, (world * 2, 256), device=dev)
+        loss = wrapped(input_ids=ids, labels=ids).loss
+        loss.backward()
+        torch.cuda.synchronize()
+        _lib.check_status()
+        losses[fused] = loss.item()
+        grads[fused] = {k: p.grad.float().clone() for k, p in model.named_parameters()}
+    assert abs(losses[True] - losses[False]) < 2e-2, losses
+    for k in grads[True]:
+        a, b = grads[True][k], grads[False][k]
+        assert (a - b).abs().max().item() <= 5e-2 * (b.abs().max().item() + 1e-3), k
+    symm.disable()
+    pc.destroy()
+
+
+@pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_fused_model_step_matches_composition():
+    run_dist(_model_worker, 2, timeout=600)
