@@ -43,8 +43,9 @@ def causal_lm_loss(model, logits, labels, ignore_index: int = -100) -> LossResul
         fn.orig_vocab_size = orig_vocab
         return LossResult(fn(logits, targets), logits.is_cuda)
     if pc is not None and mode == ParallelMode.TENSOR_3D and pc.tensor_parallel_size > 1:
-        fn = onn.CrossEntropyLoss3D(parallel_context=pc, ignore_index=ignore_index)
-        return LossResult(fn(logits[..., :orig_vocab], targets), False)
+        # the 3-D head gathers full logits on every rank; the plain loss then runs replicated
+        flat = logits[..., :orig_vocab].reshape(-1, orig_vocab).float()
+        return LossResult(F.cross_entropy(flat, targets.reshape(-1), ignore_index=ignore_index), False)
     # unsharded vocabulary: same kernel path with a group of one
     fn = onn.VocabParallelCrossEntropyLoss1D(parallel_context=None, ignore_index=ignore_index)
     fn.orig_vocab_size = orig_vocab

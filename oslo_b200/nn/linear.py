@@ -195,7 +195,7 @@ class Linear2D(Linear):
         from oslo_b200.parallel.tensor_parallel import _ops_2d as ops
 
         pc = self.parallel_context
-        out = ops.matmul_abt_2d(input, self.weight, pc)
+        out = ops.matmul_abt_2d(input, self._w, pc)
         if self.bias is not None:
             if self.skip_bias_add:
                 return out, ops.gather_bias_2d(self.bias, pc)
@@ -239,7 +239,7 @@ class Linear2p5D(Linear):
         from oslo_b200.parallel.tensor_parallel import _ops_2p5d as ops
 
         pc = self.parallel_context
-        out = ops.matmul_abt_2p5d(input, self.weight, pc)
+        out = ops.matmul_abt_2p5d(input, self._w, pc)
         if self.bias is not None:
             if self.skip_bias_add:
                 return out, self.bias
@@ -282,9 +282,11 @@ class Linear3D(Linear):
         from oslo_b200.parallel.tensor_parallel import _ops_3d as ops
 
         pc = self.parallel_context
-        out = ops.linear_3d(input, self.weight, None if self.skip_bias_add else self.bias, pc)
+        out = ops.linear_3d(input, self._w, None if self.skip_bias_add else self.bias, pc)
         if self.bias is not None and self.skip_bias_add:
-            return out, self.bias
+            # the output's feature block is this rank's OUTPUT index after the final exchange, while the stored
+            # bias block follows the INPUT index: fetch the matching block from the exchange partner
+            return out, ops.transpose_3d(self.bias, pc)
         if self.gather_output:
             out = ops.gather_output_3d(out, pc)
             if hasattr(self, "orig_num_classes"):

@@ -29,14 +29,15 @@ class _AllReduceSum(torch.autograd.Function):
         return g, None, None
 
 
-def _mean_over_valid(loss, targets, ignore_index, pc=None, batch_mode=None):
-    """Mean of per-token losses over non-ignored tokens; with ``batch_mode`` the tokens are spread over that group."""
+def _mean_over_valid(loss, targets, ignore_index, pc=None, batch_modes=()):
+    """Mean of per-token losses over non-ignored tokens; the tokens are spread over the ``batch_modes`` groups."""
     valid = (targets != ignore_index)
     total = loss.sum()
     count = valid.sum().to(loss.dtype)
-    if pc is not None and batch_mode is not None and pc.get_world_size(batch_mode) > 1:
-        total = _AllReduceSum.apply(total, pc, batch_mode)
-        count = comm.all_reduce(count.clone(), parallel_context=pc, parallel_mode=batch_mode)
+    for mode in batch_modes:
+        if pc is not None and pc.get_world_size(mode) > 1:
+            total = _AllReduceSum.apply(total, pc, mode)
+            count = comm.all_reduce(count.clone(), parallel_context=pc, parallel_mode=mode)
     return total / count.clamp(min=1)
 
 
@@ -58,7 +59,7 @@ class VocabParallelCrossEntropyLoss1D(nn.Module):
 
 class _VocabParallelCrossEntropyLossND(nn.Module):
     vocab_mode: ParallelMode
-    batch_mode: ParallelMode
+    batch_modes = ()
 
     def __init__(self, reduce_mean=True, ignore_index=-100, parallel_context=None):
         super().__init__()
@@ -68,22 +69,23 @@ class _VocabParallelCrossEntropyLossND(nn.Module):
 
     def forward(self, logits, targets):
         pc = self.parallel_context
-        targets = comm.scatter(targets, dim=0, parallel_context=pc, parallel_mode=self.batch_mode)
+        for mode in self.batch_modes:
+            targets = comm.scatter(targets, dim=0, parallel_context=pc, parallel_mode=mode)
         valid_vocab = getattr(self, "orig_vocab_size", None)
         loss = vocab_parallel_cross_entropy(logits, targets, pc, self.vocab_mode, self.ignore_index, valid_vocab)
         if not self.reduce_mean:
             return loss
-        return _mean_over_valid(loss, targets, self.ignore_index, pc, self.batch_mode)
+        return _mean_over_valid(loss, targets, self.ignore_index, pc, self.batch_modes)
 
 
 class VocabParallelCrossEntropyLoss2D(_VocabParallelCrossEntropyLossND):
     vocab_mode = ParallelMode.TENSOR_2D_ROW
-    batch_mode = ParallelMode.TENSOR_2D_COL
+    batch_modes = (ParallelMode.TENSOR_2D_COL,)
 
 
 class VocabParallelCrossEntropyLoss2p5D(_VocabParallelCrossEntropyLossND):
     vocab_mode = ParallelMode.TENSOR_2P5D_ROW
-    batch_mode = ParallelMode.TENSOR_2P5D_COL
+    batch_modes = (ParallelMode.TENSOR_2P5D_DEP, ParallelMode.TENSOR_2P5D_COL)
 
 
 class _CrossEntropyLossND(nn.Module):
@@ -117,7 +119,7 @@ class CrossEntropyLoss2D(_CrossEntropyLossND):
 
 
 class CrossEntropyLoss2p5D(_CrossEntropyLossND):
-    batch_modes = (ParallelMode.TENSOR_2P5D_COL,)
+    batch_modes = (ParallelMode.TENSOR_2P5D_DEP, ParallelMode.TENSOR_2P5D_COL)
 
 
 class CrossEntropyLoss3D(_CrossEntropyLossND):

@@ -128,14 +128,15 @@ class _ShardedNormStats(torch.autograd.Function):
             stats = torch.cat([xf.sum(-1, keepdim=True), s2], dim=-1)
         stats = comm.all_reduce(stats.contiguous(), parallel_context=pc, parallel_mode=mode)
         ctx.save_for_backward(x)
-        ctx.rms = rms
+        ctx.rms, ctx.mode, ctx.pc = rms, mode, pc
         return stats
 
     @staticmethod
     def backward(ctx, g):
-        # d(sum x)/dx = 1, d(sum x^2)/dx = 2x; the all-reduce's adjoint is an all-reduce of g, but g is already
-        # identical on all ranks of the group (it comes from replicated math on the reduced stats).
+        # each rank's g is the sensitivity of ITS hidden shard to the shared statistics: sum them (the adjoint of
+        # an all-reduce whose result every rank consumes), then d(sum x)/dx = 1 and d(sum x^2)/dx = 2x
         (x,) = ctx.saved_tensors
+        g = comm.all_reduce(g.contiguous().clone(), parallel_context=ctx.pc, parallel_mode=ctx.mode)
         xf = x.float()
         if ctx.rms:
             gx = 2.0 * xf * g

@@ -144,9 +144,12 @@ def parallelize_nd(tp):
                 if v % feature_div == 0:
                     setattr(m, attr, v // feature_div)
 
+    marked = set()
+
     def sync(p, kind):
         modes = plan.replicated_sync(kind)
-        if modes:
+        if modes and id(p) not in marked:
+            marked.add(id(p))
             tp._mark_replicated(p, modes)
 
     def make_linear(child, name, w, b, gather_output):
@@ -250,3 +253,7 @@ def parallelize_nd(tp):
         new = make_linear(head, name, w, b, gather)
         new.orig_num_classes = head.orig_num_classes
         _set_child(module, name, new)
+    if mode == M.TENSOR_2P5D:
+        # every parameter is replicated along the depth dimension
+        for p in module.parameters():
+            sync(p, "weight")
