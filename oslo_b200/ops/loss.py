@@ -81,7 +81,12 @@ class _VPCEFn(torch.autograd.Function):
 
 
 class _VPCECudaFn(torch.autograd.Function):
-    """Writes d(loss)/d(logits) into the logits buffer during forward (the logits are consumed)."""
+    """Writes d(loss)/d(logits) into the logits buffer during forward (the logits are consumed).
+
+    The overwrite is not declared to autograd (``mark_dirty`` would add a second output, which autograd forbids
+    when the logits are a view, e.g. a reshaped linear output): the logits have no other consumer and the linear
+    that produced them does not keep them for its backward.
+    """
 
     @staticmethod
     def forward(ctx, logits, target, pc, mode, ignore_index, valid_vocab):
@@ -116,12 +121,10 @@ class _VPCECudaFn(torch.autograd.Function):
         if rc:
             raise RuntimeError(f"oslo_ce_loss_grad failed ({rc})")
         ctx.save_for_backward(logits)  # now holds softmax - onehot
-        ctx.mark_dirty(logits)
-        ctx.lead = target.shape
-        return loss.view(target.shape), logits
+        return loss.view(target.shape)
 
     @staticmethod
-    def backward(ctx, g, _unused):
+    def backward(ctx, g):
         (grad,) = ctx.saved_tensors
         g2 = g.reshape(-1, 1).to(grad.dtype)
         v = grad.shape[-1]
@@ -137,8 +140,7 @@ def vocab_parallel_cross_entropy(logits, target, parallel_context=None, parallel
     used afterwards) so no second vocabulary-sized buffer is ever allocated.
     """
     if logits.is_cuda and _lib.has_cuda_kernels() and logits.dtype in _DT and logits.is_contiguous():
-        if logits.requires_grad and logits.is_leaf:
+        if logits.is_leaf:
             logits = logits.clone()
-        loss, _ = _VPCECudaFn.apply(logits, target, parallel_context, parallel_mode, ignore_index, valid_vocab)
-        return loss
+        return _VPCECudaFn.apply(logits, target, parallel_context, parallel_mode, ignore_index, valid_vocab)
     return vocab_parallel_cross_entropy_reference(logits, target, parallel_context, parallel_mode, ignore_index, valid_vocab)

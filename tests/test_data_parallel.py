@@ -1,0 +1,89 @@
+"""DDP and ZeRO-1/2 on CPU / gloo (world 2): parameters after several steps equal single-process training on
+the full batch."""
+import copy
+
+import pytest
+import torch
+import torch.nn as nn
+
+from dist_utils import run_dist
+
+
+def _mlp(seed=0):
+    torch.manual_seed(seed)
+    return nn.Sequential(nn.Linear(16, 32), nn.GELU(), nn.Linear(32, 32), nn.LayerNorm(32), nn.Linear(32, 4))
+
+
+def _data(step, n=8):
+    g = torch.Generator().manual_seed(100 + step)
+    return torch.randn(n, 16, generator=g), torch.randn(n, 4, generator=g)
+
+
+def _reference(steps, lr=1e-2, clip=0.0):
+    model = _mlp()
+    opt = torch.optim.AdamW(model.parameters(), lr=lr)
+    for s in range(steps):
+        x, y = _data(s)
+        opt.zero_grad()
+        ((model(x) - y) ** 2).mean().backward()
+        if clip:
+            torch.nn.utils.clip_grad_norm_(model.parameters(), clip)
+        opt.step()
+    return model
+
+
+def _ddp_worker(rank, world):
+    import oslo_b200
+    from oslo_b200 import ParallelContext
+    from oslo_b200.parallel import DistributedDataParallel
+
+    pc = ParallelContext.from_torch(data_parallel_size=world, backend="gloo", seed=0)
+    model = _mlp()
+    wrapped = DistributedDataParallel(model, pc, model_wrapper_config=dict(bucket_cap_mb=0.001))
+    oslo_b200.ready(wrapped, pc)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-2)
+    for s in range(4):
+        x, y = _data(s)
+        xs, ys = x.chunk(world)[rank], y.chunk(world)[rank]
+        wrapped.zero_grad()
+        ((wrapped(xs) - ys) ** 2).mean().backward()
+        opt.step()
+    ref = _reference(4)
+    for p, r in zip(model.parameters(), ref.parameters()):
+        assert torch.allclose(p, r, rtol=1e-5, atol=1e-6), (p - r).abs().max()
+    pc.destroy()
+
+
+def test_ddp_matches_single_process():
+    run_dist(_ddp_worker, 2)
+
+
+def _zero_worker(rank, world, stage, overlap, clip):
+    from oslo_b200 import ParallelContext
+    from oslo_b200.parallel import ZeroRedundancyOptimizer
+
+    pc = ParallelContext.from_torch(data_parallel_size=world, backend="gloo", seed=0)
+    model = _mlp()
+    opt = ZeroRedundancyOptimizer(torch.optim.AdamW(model.parameters(), lr=1e-2), parallel_context=pc,
+                                  partition_grad=stage == 2, overlap_communication=overlap, clip_grad_norm=clip,
+                                  reduce_bucket_size=600)
+    for s in range(4):
+        x, y = _data(s)
+        xs, ys = x.chunk(world)[rank], y.chunk(world)[rank]
+        opt.zero_grad()
+        loss = ((model(xs) - ys) ** 2).mean()
+        opt.backward(loss)
+        opt.step()
+    ref = _reference(4, clip=clip)
+    for p, r in zip(model.parameters(), ref.parameters()):
+        assert torch.allclose(p, r, rtol=1e-5, atol=1e-6), (p - r).abs().max()
+    # optimizer state is sharded: this rank holds moments for 1/world of the (padded) parameters only
+    n_state = sum(v["exp_avg"].numel() for v in opt.state.values())
+    n_param = sum(p.numel() for p in model.parameters())
+    assert n_state < n_param
+    pc.destroy()
+
+
+@pytest.mark.parametrize("stage,overlap,clip", [(1, False, 0.0), (2, False, 0.0), (2, True, 0.0), (1, True, 0.05)])
+def test_zero_matches_single_process(stage, overlap, clip):
+    run_dist(_zero_worker, 2, stage, overlap, clip)
