@@ -491,3 +491,90 @@ extern "C" int oslo_colsum(const void* x, void* out, float* partial, long long r
                 (colsum_finish_kernel<__nv_bfloat16><<<fb, 256, 0, st>>>(partial, (__nv_bfloat16*)out, parts, H)));
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free column sum (declared in oslo_b200_noalloc.h).  Same kernels as oslo_colsum, but the
+// per-block partial sums go to a fixed array that is part of the library image instead of a buffer the
+// caller allocates.  See the header for who needs this and for the rules of use.
+#include "oslo_b200_noalloc.h"
+#include <cstdio>
+#include <mutex>
+
+namespace {
+constexpr long long kNoAllocScratchFloats = OSLO_COLSUM_NOALLOC_MAX_SCRATCH_FLOATS;
+// Lives in every GPU that loads the library until the process exits (8 MiB).
+static __device__ __align__(256) float g_colsum_noalloc_scratch[kNoAllocScratchFloats];
+
+constexpr int kMaxDevices = 64;
+struct NoAllocDeviceState {
+  float* scratch = nullptr;  // DEVICE address of g_colsum_noalloc_scratch on that device
+  int num_sms = 0;
+};
+NoAllocDeviceState g_noalloc_state[kMaxDevices];
+std::mutex g_noalloc_mutex;
+
+// One-time set-up for the current device.  In host code the array's name is only a handle for the
+// runtime, not an address a kernel can use, so the device address is looked up once and kept.
+int noalloc_setup(int dev, NoAllocDeviceState** out) {
+  if (dev < 0 || dev >= kMaxDevices) return OSLO_NOALLOC_ERR_DEVICE;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  NoAllocDeviceState& st = g_noalloc_state[dev];
+  if (st.scratch == nullptr) {
+    float* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_colsum_noalloc_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      fprintf(stderr, "oslo_colsum_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
+      return OSLO_NOALLOC_ERR_SETUP;
+    }
+    int sms = 0;
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess || sms <= 0) {
+      fprintf(stderr, "oslo_colsum_noalloc: cannot read the SM count: %s\n", cudaGetErrorString(e));
+      return OSLO_NOALLOC_ERR_SETUP;
+    }
+    st.num_sms = sms;
+    st.scratch = ptr;
+  }
+  *out = &st;
+  return 0;
+}
+}  // namespace
+
+extern "C" long long oslo_colsum_noalloc_max_scratch_floats() { return kNoAllocScratchFloats; }
+
+extern "C" int oslo_colsum_noalloc(const void* x, void* out, long long rows, int H, int dtype, void* stream) {
+  if (H <= 0 || rows < 0) return 0;
+  if (dtype < 0 || dtype > 2) return OSLO_NOALLOC_ERR_ARGUMENT;
+  const int P = dtype == 0 ? 4 : 8;
+  if (H % P) {
+    fprintf(stderr, "oslo_colsum_noalloc: H = %d must be a multiple of %d for this dtype\n", H, P);
+    return OSLO_NOALLOC_ERR_ARGUMENT;
+  }
+  if (static_cast<long long>(H) > kNoAllocScratchFloats) {
+    fprintf(stderr,
+            "oslo_colsum_noalloc: H = %d columns exceeds the built-in scratch of %lld floats; use oslo_colsum with a "
+            "caller-provided buffer instead\n", H, kNoAllocScratchFloats);
+    return OSLO_NOALLOC_ERR_TOO_LARGE;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return OSLO_NOALLOC_ERR_DEVICE;
+  NoAllocDeviceState* st = nullptr;
+  int rc = noalloc_setup(dev, &st);
+  if (rc) return rc;
+  // as many row partitions as oslo_colsum would use, capped so that parts * H fits the fixed array
+  long long parts = oslo_colsum_parts(rows, st->num_sms);
+  const long long fit = kNoAllocScratchFloats / H;
+  if (parts > fit) parts = fit;
+  if (parts < 1) parts = 1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* partial = st->scratch;  // every (part, column) cell used below is overwritten: nothing to clear
+  dim3 block(32, 8), grid((H / P + 31) / 32, static_cast<unsigned>(parts));
+  OSLO_BY_DTYPE((colsum_kernel<float><<<grid, block, 0, s>>>((const float*)x, partial, rows, H)),
+                (colsum_kernel<__half><<<grid, block, 0, s>>>((const __half*)x, partial, rows, H)),
+                (colsum_kernel<__nv_bfloat16><<<grid, block, 0, s>>>((const __nv_bfloat16*)x, partial, rows, H)));
+  const int fb = (H + 255) / 256;
+  OSLO_BY_DTYPE((colsum_finish_kernel<float><<<fb, 256, 0, s>>>(partial, (float*)out, (int)parts, H)),
+                (colsum_finish_kernel<__half><<<fb, 256, 0, s>>>(partial, (__half*)out, (int)parts, H)),
+                (colsum_finish_kernel<__nv_bfloat16><<<fb, 256, 0, s>>>(partial, (__nv_bfloat16*)out, (int)parts, H)));
+  return cudaGetLastError() == cudaSuccess ? 0 : OSLO_NOALLOC_ERR_LAUNCH;
+}
