@@ -464,6 +464,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll 1
       for (int chunk = 0; chunk < BLOCK_N / 64; ++chunk) {
         uint32_t r0[32], r1[32];
+        __syncwarp();  // tcgen05.ld is .sync.aligned: the warp must be converged (lane 0 branches above)
         tmem_ld_32x32(taddr + chunk * 64, r0);
         tmem_ld_32x32(taddr + chunk * 64 + 32, r1);
         tmem_ld_wait();
@@ -598,6 +599,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             st_release_sys(fp.peer_rs_flag[dest] + fp.rank, fp.epoch);
           }
         }
+        __syncwarp();
       }
       buf ^= 1;
       if (buf == 0) acc_phase ^= 1;
