@@ -1,4 +1,5 @@
 from .data_parallel import DistributedDataParallel, ShardingStrategy, ZeroRedundancyOptimizer
+from .expert_parallel import ExpertParallel
 from .tensor_parallel import TensorParallel
 
-__all__ = ["TensorParallel", "DistributedDataParallel", "ShardingStrategy", "ZeroRedundancyOptimizer"]
+__all__ = ["TensorParallel", "ExpertParallel", "DistributedDataParallel", "ShardingStrategy", "ZeroRedundancyOptimizer"]
