@@ -52,6 +52,12 @@ extern "C" int oslo_ag_gemm(void* const* peer_in, void* x_full, const void* B, v
   FusedParams fp;
   fp.tp = tp; fp.rank = rank; fp.shard_rows = Tl; fp.epoch = epoch; fp.copy_ctas = copy_ctas; fp.k_elems = K;
   fp.tiles_per_shard = (Tl / kBlockM) * p.n_blocks;
+  // copy granularity: about 1024 rows, at most 16 chunks per shard, always a multiple of 128 dividing Tl
+  int chunk_rows = Tl;
+  for (int cand = 1024; cand >= kBlockM; cand -= kBlockM) {
+    if (Tl % cand == 0 && (Tl / cand) * tp <= 64) { chunk_rows = cand; break; }
+  }
+  fp.chunk_rows = chunk_rows;
   for (int i = 0; i < tp; ++i) {
     fp.peer_in[i] = peer_in[i];
     fp.peer_ag_ready[i] = static_cast<int*>(peer_ag_ready[i]);

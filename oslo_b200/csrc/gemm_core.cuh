@@ -94,13 +94,14 @@ struct FusedParams {
   int epoch = 0;
   int copy_ctas = 0;        // AG: CTAs [0, copy_ctas) copy, the others multiply
   int k_elems = 0;          // AG: row length of A in elements
+  int chunk_rows = 0;       // AG: rows per copy chunk (a multiple of 128 dividing shard_rows); one flag per chunk
   // all-gather
   const void* peer_in[kMaxRanks] = {};  // every rank's symmetric input shard [shard_rows, K]
   void* x_full = nullptr;               // local [tp * shard_rows, K]
   int* ag_ready = nullptr;              // local [tp]: peer p's shard for `epoch` is in its buffer
   int* peer_ag_ready[kMaxRanks] = {};   // the same array on every rank (to announce our shard)
-  int* chunk_flag = nullptr;            // local [tp]: shard s has been copied into x_full
-  int* chunk_arrive = nullptr;          // local [tp]: copy-CTA arrival counters
+  int* chunk_flag = nullptr;            // local [tp * chunks_per_shard]: that chunk of x_full is complete
+  int* chunk_arrive = nullptr;          // local, same size: copy-CTA arrival counters
   // reduce-scatter
   void* peer_slots[kMaxRanks] = {};     // every rank's slot buffer [tp, shard_rows, N]
   int* rs_flag = nullptr;               // local [tp]: source p has pushed all its partial tiles
@@ -150,11 +151,23 @@ OSLO_DEVINL void fused_tile_coords(int tile, const GemmParams& p, const FusedPar
   const int t = tile - i * fp.tiles_per_shard;
   const int shard = (fp.rank + i + (MODE == kModeReduceScatter ? 1 : 0)) % fp.tp;
   const int blocks_per_shard = fp.shard_rows / kBlockM;
-  mb = shard * blocks_per_shard + t % blocks_per_shard;
-  nb = t / blocks_per_shard;
+  if (MODE == kModeAllGather) {
+    // walk chunk by chunk (the order the copy CTAs deliver them), all n-blocks of a chunk before the next chunk
+    const int blocks_per_chunk = fp.chunk_rows / kBlockM;
+    const int n_blocks = fp.tiles_per_shard / blocks_per_shard;
+    const int per_chunk = blocks_per_chunk * n_blocks;
+    const int c = t / per_chunk, r = t - c * per_chunk;
+    mb = shard * blocks_per_shard + c * blocks_per_chunk + r % blocks_per_chunk;
+    nb = r / blocks_per_chunk;
+  } else {
+    mb = shard * blocks_per_shard + t % blocks_per_shard;
+    nb = t / blocks_per_shard;
+  }
 }
 
-// AG copy role: announce our shard, then pull every shard (own first) into x_full and flag it.
+// AG copy role: announce our shard, then pull the other ranks' shards chunk by chunk (next rank first) into
+// x_full, flagging every chunk, and finally copy the own shard (the GEMM reads that one in place, x_full only needs
+// it for later use by the caller).
 static __device__ __noinline__ void ag_copy_role(const GemmParams& p, const FusedParams& fp) {
   __shared__ int s_ok;
   const int tid = threadIdx.x, nthreads = blockDim.x;
@@ -162,40 +175,44 @@ static __device__ __noinline__ void ag_copy_role(const GemmParams& p, const Fuse
     __threadfence_system();
     st_release_sys(fp.peer_ag_ready[tid] + fp.rank, fp.epoch);
   }
-  const long long vec_per_shard = static_cast<long long>(fp.shard_rows) * fp.k_elems / 8;
-  const long long per_cta = (vec_per_shard + fp.copy_ctas - 1) / fp.copy_ctas;
+  const int chunks_per_shard = fp.shard_rows / fp.chunk_rows;
+  const long long vec_per_chunk = static_cast<long long>(fp.chunk_rows) * fp.k_elems / 8;
+  const long long per_cta = (vec_per_chunk + fp.copy_ctas - 1) / fp.copy_ctas;
   const long long v0 = per_cta * blockIdx.x;
-  const long long v1 = v0 + per_cta < vec_per_shard ? v0 + per_cta : vec_per_shard;
-  for (int i = 0; i < fp.tp; ++i) {
-    const int s = (fp.rank + i) % fp.tp;
+  const long long v1 = v0 + per_cta < vec_per_chunk ? v0 + per_cta : vec_per_chunk;
+  for (int i = 1; i <= fp.tp; ++i) {
+    const int s = (fp.rank + i) % fp.tp;  // i == tp: the own shard, last
     if (tid == 0) {
       bool ok = true;
-      if (i > 0) ok = flag_wait_bounded(fp.ag_ready + s, fp.epoch, nullptr, true);
+      if (s != fp.rank) ok = flag_wait_bounded(fp.ag_ready + s, fp.epoch, nullptr, true);
       if (!ok && fp.status) atomicCAS(fp.status, kStatusOk, kStatusPeerFlagTimeout);
       s_ok = ok ? 1 : 0;
     }
     __syncthreads();
     if (!s_ok) return;  // the GEMM CTAs will time out on the chunk flag and report it
-    const uint4* src = static_cast<const uint4*>(fp.peer_in[s]);
-    uint4* dst = static_cast<uint4*>(fp.x_full) + static_cast<long long>(s) * vec_per_shard;
-    long long v = v0 + tid;
-    // 8 independent 16-byte loads in flight per thread hide the NVLink round trip
-    for (; v + 7LL * nthreads < v1; v += 8LL * nthreads) {
-      uint4 r[8];
+    for (int c = 0; c < chunks_per_shard; ++c) {
+      const int chunk = s * chunks_per_shard + c;
+      const uint4* src = static_cast<const uint4*>(fp.peer_in[s]) + static_cast<long long>(c) * vec_per_chunk;
+      uint4* dst = static_cast<uint4*>(fp.x_full) + static_cast<long long>(chunk) * vec_per_chunk;
+      long long v = v0 + tid;
+      // 8 independent 16-byte loads in flight per thread hide the NVLink round trip
+      for (; v + 7LL * nthreads < v1; v += 8LL * nthreads) {
+        uint4 r[8];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) r[u] = src[v + static_cast<long long>(u) * nthreads];
+        for (int u = 0; u < 8; ++u) r[u] = src[v + static_cast<long long>(u) * nthreads];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) dst[v + static_cast<long long>(u) * nthreads] = r[u];
-    }
-    for (; v < v1; v += nthreads) dst[v] = src[v];
-    __syncthreads();
-    if (tid == 0) {
-      __threadfence();
-      const int old = atomicAdd(fp.chunk_arrive + s, 1);
-      if (old == fp.copy_ctas - 1) {
-        fp.chunk_arrive[s] = 0;
+        for (int u = 0; u < 8; ++u) dst[v + static_cast<long long>(u) * nthreads] = r[u];
+      }
+      for (; v < v1; v += nthreads) dst[v] = src[v];
+      __syncthreads();
+      if (tid == 0) {
         __threadfence();
-        st_release_gpu(fp.chunk_flag + s, fp.epoch);
+        const int old = atomicAdd(fp.chunk_arrive + chunk, 1);
+        if (old == fp.copy_ctas - 1) {
+          fp.chunk_arrive[chunk] = 0;
+          __threadfence();
+          st_release_gpu(fp.chunk_flag + chunk, fp.epoch);
+        }
       }
     }
   }
@@ -342,15 +359,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           // rows of shard s become loadable once the copy CTAs have flagged the chunk; the own shard is read
           // straight from the symmetric input buffer through its own tensor map
           const int shard = m0 / fp.shard_rows;
+          const int chunk = m0 / fp.chunk_rows;
           a_local = shard == fp.rank;
-          if (!a_local && shard != ready_shard) {
-            if (!flag_wait_bounded(fp.chunk_flag + shard, fp.epoch, abort_flag, false)) {
+          if (!a_local && chunk != ready_shard) {
+            if (!flag_wait_bounded(fp.chunk_flag + chunk, fp.epoch, abort_flag, false)) {
               ok = false;
               if (p.status) atomicCAS(p.status, kStatusOk, kStatusPeerFlagTimeout);
               break;
             }
             fence_proxy_async_global();
-            ready_shard = shard;
+            ready_shard = chunk;
           }
         }
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -445,6 +463,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     int buf = 0;
     uint32_t acc_phase = 0;
     int sbuf = 0;
+    int rs_pending = 0;
+    (void)rs_pending;
     bool ok = true;
     for (int tile = cta; tile < num_tiles && ok; tile += num_ctas) {
       int b, mb, nb;
@@ -586,18 +606,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
       if constexpr (MODE == kModeReduceScatter) {
-        // this warp's quarter of the tile has landed at the destination: count it, the last one signals
+        // count this warp's finished quarter-tiles per destination; publish the count (after ONE system fence
+        // covering all of them) when the destination changes or the CTA runs out of tiles
         const int dest = m0 / fp.shard_rows;
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0) {
-          const int need = fp.tiles_per_shard * 4;
-          const int old = atomicAdd(fp.tile_done + dest, 1);
-          if (old == need - 1) {
-            fp.tile_done[dest] = 0;
-            __threadfence_system();
-            st_release_sys(fp.peer_rs_flag[dest] + fp.rank, fp.epoch);
+        const int next_tile = tile + num_ctas;
+        int next_dest = -1;
+        if (next_tile < num_tiles) {
+          int nb2, mb2, b2;
+          fused_tile_coords<MODE>(next_tile, p, fp, b2, mb2, nb2);
+          next_dest = mb2 * kBlockM / fp.shard_rows;
+        }
+        ++rs_pending;
+        if (next_dest != dest) {
+          __threadfence_system();
+          __syncwarp();
+          if (lane == 0) {
+            const int need = fp.tiles_per_shard * 4;
+            const int old = atomicAdd(fp.tile_done + dest, rs_pending);
+            if (old + rs_pending == need) {
+              fp.tile_done[dest] = 0;
+              __threadfence_system();
+              st_release_sys(fp.peer_rs_flag[dest] + fp.rank, fp.epoch);
+            }
           }
+          rs_pending = 0;
         }
         __syncwarp();
       }

@@ -75,8 +75,8 @@ class SymmetricWorkspace:
             if rc:
                 raise RuntimeError(f"cudaIpcOpenMemHandle for peer {r} failed (cuda error {-rc})")
             self.peer_base.append(out.value)
-        # local scratch counters (not shared): chunk_flag[tp], chunk_arrive[tp], tile_done[tp]
-        self.local = torch.zeros(64, dtype=torch.int32, device=self.device)
+        # local scratch counters (not shared): chunk_flag[64], chunk_arrive[64], tile_done[64]
+        self.local = torch.zeros(256, dtype=torch.int32, device=self.device)
         self.epoch = 0
         self._local_bytes = torch.as_tensor(_RawCudaBuffer(self.base, self.total), device=self.device)
         dist.barrier(group=pc.get_cpu_group(mode))
@@ -101,7 +101,8 @@ class SymmetricWorkspace:
         return self._local_bytes[off : off + n].view(self.dtype).view(rows, cols)
 
     def _local_ptr(self, idx: int) -> ctypes.c_void_p:
-        return ctypes.c_void_p(self.local.data_ptr() + idx * 4 * 16)
+        # three local int arrays of 64 entries: chunk flags, chunk arrival counters, per-destination tile counters
+        return ctypes.c_void_p(self.local.data_ptr() + idx * 4 * 64)
 
     # ------------------------------------------------------------------ ops
     def barrier(self):

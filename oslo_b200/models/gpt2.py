@@ -118,6 +118,41 @@ class GPT2LMHeadModel(PreTrainedModel):
     def gradient_checkpointing_enable(self):
         self.transformer.gradient_checkpointing = True
 
+    def pipeline_units(self):
+        from oslo_b200.parallel.pipeline_parallel.partitioner import PipeUnit
+
+        base = self.transformer
+
+        def embed(state):
+            ids = state["input_ids"]
+            pos = torch.arange(ids.shape[-1], device=ids.device).unsqueeze(0)
+            state["hidden"] = base.drop(base.wte(ids) + base.wpe(pos))
+            return state
+
+        def make_layer(block):
+            def run(state):
+                state["hidden"] = block(state["hidden"], state.get("attention_mask"))
+                return state
+
+            return run
+
+        def head(state):
+            logits = self.lm_head(base.ln_f(state["hidden"]))
+            state["logits"] = logits
+            if state.get("labels") is not None:
+                from .losses import causal_lm_loss
+
+                res = causal_lm_loss(self, logits, state["labels"])
+                state["loss"] = res.value
+                if res.consumed_logits:
+                    state["logits"] = None
+            return state
+
+        units = [PipeUnit("embed", [base.wte, base.wpe], embed)]
+        units += [PipeUnit(f"h.{i}", [b], make_layer(b)) for i, b in enumerate(base.h)]
+        units.append(PipeUnit("head", [base.ln_f, self.lm_head], head))
+        return units
+
     def forward(self, input_ids=None, attention_mask=None, position_ids=None, labels=None, **kwargs):
         hidden = self.transformer(input_ids, attention_mask, position_ids)
         logits = self.lm_head(hidden)

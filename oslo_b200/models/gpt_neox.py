@@ -132,6 +132,40 @@ class GPTNeoXForCausalLM(PreTrainedModel):
     def gradient_checkpointing_enable(self):
         self.gpt_neox.gradient_checkpointing = True
 
+    def pipeline_units(self):
+        """Embedding, one unit per layer, then final norm + head + loss."""
+        from oslo_b200.parallel.pipeline_parallel.partitioner import PipeUnit
+
+        base = self.gpt_neox
+
+        def embed(state):
+            state["hidden"] = base.embed_in(state["input_ids"])
+            return state
+
+        def make_layer(layer):
+            def run(state):
+                state["hidden"] = layer(state["hidden"], state.get("attention_mask"))
+                return state
+
+            return run
+
+        def head(state):
+            logits = self.embed_out(base.final_layer_norm(state["hidden"]))
+            state["logits"] = logits
+            if state.get("labels") is not None:
+                from .losses import causal_lm_loss
+
+                res = causal_lm_loss(self, logits, state["labels"])
+                state["loss"] = res.value
+                if res.consumed_logits:
+                    state["logits"] = None
+            return state
+
+        units = [PipeUnit("embed_in", [base.embed_in], embed)]
+        units += [PipeUnit(f"layers.{i}", [l], make_layer(l)) for i, l in enumerate(base.layers)]
+        units.append(PipeUnit("head", [base.final_layer_norm, self.embed_out], head))
+        return units
+
     def forward(self, input_ids=None, attention_mask=None, labels=None, **kwargs):
         hidden = self.gpt_neox(input_ids, attention_mask)
         logits = self.embed_out(hidden)

@@ -1,5 +1,7 @@
 from .data_parallel import DistributedDataParallel, ShardingStrategy, ZeroRedundancyOptimizer
 from .expert_parallel import ExpertParallel
+from .pipeline_parallel import PipelineParallel
 from .tensor_parallel import TensorParallel
 
-__all__ = ["TensorParallel", "ExpertParallel", "DistributedDataParallel", "ShardingStrategy", "ZeroRedundancyOptimizer"]
+__all__ = ["TensorParallel", "PipelineParallel", "ExpertParallel", "DistributedDataParallel", "ShardingStrategy",
+           "ZeroRedundancyOptimizer"]
