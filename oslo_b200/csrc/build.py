@@ -33,7 +33,8 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default",
     "--expt-relaxed-constexpr",
 ]
-CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-fopenmp", "-march=native", "-shared"]
+# no -march=native: SIMD bodies are selected at run time, so the library runs on any x86-64 host
+CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-fopenmp", "-shared"]
 
 
 def _nvcc() -> str:

@@ -7,9 +7,9 @@
 //   * all-gather: a few CTAs stream the peers' shards over NVLink into local memory with plain 16-byte loads
 //     while the remaining CTAs multiply, starting with the local shard and taking each remote shard as soon
 //     as its "copied" flag is up; TMA only ever reads local memory.
-//   * reduce-scatter: tiles are computed in destination order (next rank first, own rows last); the epilogue
-//     pushes each partial tile straight into the destination GPU's slot buffer with peer stores, the last
-//     tile per destination raises a flag there, and every CTA ends by summing the tp slots of its own rows.
+//   * reduce-scatter: tiles are computed in destination order (next rank first, own rows last) into a local
+//     partial-result buffer; finishing a chunk of rows raises a flag on the rank that owns those rows, where a few
+//     reducer CTAs pull the tp partial copies of the chunk (bulk loads over NVLink), sum them in fp32 and store.
 // All waits on peers are bounded (~2 s) and report through the status word instead of hanging.
 //
 // Replaces ColLinear1D / RowLinear1D = F.linear + a separate NCCL all-reduce in the reference
@@ -86,28 +86,38 @@ extern "C" int oslo_ag_gemm(void* const* peer_in, void* x_full, const void* B, v
   }
 }
 
-// peer_slots / peer_rs_flag: host arrays of `tp` device pointers.  A: [T, K] K-major (lda), out: [T/tp, N].
+// peer_partial / peer_rs_flag: host arrays of `tp` device pointers ([T, N] partial-result buffers and flag arrays of
+// tp * chunks_per_shard ints).  A: [T, K] K-major (lda), out: [T/tp, N].
 extern "C" int oslo_gemm_rs(const void* A, long long lda, const void* B, long long ldb, int b_mn, void* out, const void* bias,
-                            int T, int N, int K, int is_bf16, int tp, int rank, int epoch, void* const* peer_slots,
-                            void* const* peer_rs_flag, int* tile_done, int num_sms, int* status, void* stream_ptr) {
+                            int T, int N, int K, int is_bf16, int tp, int rank, int epoch, void* const* peer_partial,
+                            void* const* peer_rs_flag, int* tile_done, int reduce_ctas, int num_sms, int* status,
+                            void* stream_ptr) {
   if (tp > kMaxRanks || tp < 1 || T % tp) return -1;
   const int Tl = T / tp;
   if (Tl % kBlockM || N % 8 || K % 8 || lda % 8 || ldb % 8) return -5;
   bind_context_to_thread();
-  // 128-wide tiles only: the 256-wide instantiation of this mode raised an illegal-instruction error on B200
-  // (cause not yet found by reading), so it is not dispatched
-  const int block_n = pick_block_n(T, N, num_sms, 128);
+  if (reduce_ctas < 1) reduce_ctas = 1;
+  if (reduce_ctas > num_sms / 2) reduce_ctas = num_sms / 2;
+  const int gemm_ctas_max = num_sms - reduce_ctas;
+  const int block_n = pick_block_n(T, N, gemm_ctas_max, 256);
   GemmParams p{};
   p.M = T; p.N = N; p.K = K; p.batch = 1; p.batch_inner = 1; p.causal = 0;
   p.m_blocks = T / kBlockM;
   p.n_blocks = (N + block_n - 1) / block_n;
   p.epilogue = 0; p.accumulate = 0; p.is_bf16 = is_bf16;
-  p.bias = nullptr; p.c_ptr = out; p.ldc = N; p.stride_c = 0; p.stride_c_outer = 0; p.aux_ptr = nullptr; p.status = status;
+  p.bias = nullptr; p.c_ptr = peer_partial[rank]; p.ldc = N; p.stride_c = 0; p.stride_c_outer = 0; p.aux_ptr = nullptr;
+  p.status = status;
   FusedParams fp;
-  fp.tp = tp; fp.rank = rank; fp.shard_rows = Tl; fp.epoch = epoch;
+  fp.tp = tp; fp.rank = rank; fp.shard_rows = Tl; fp.epoch = epoch; fp.copy_ctas = reduce_ctas;
   fp.tiles_per_shard = (Tl / kBlockM) * p.n_blocks;
+  int chunk_rows = Tl;  // hand-off granularity: about 512 rows, at most 64 flags in total
+  for (int cand = 512; cand >= kBlockM; cand -= kBlockM) {
+    if (Tl % cand == 0 && (Tl / cand) * tp <= 64) { chunk_rows = cand; break; }
+  }
+  fp.chunk_rows = chunk_rows;
+  fp.tiles_per_chunk = (chunk_rows / kBlockM) * p.n_blocks;
   for (int i = 0; i < tp; ++i) {
-    fp.peer_slots[i] = peer_slots[i];
+    fp.peer_slots[i] = peer_partial[i];
     fp.peer_rs_flag[i] = static_cast<int*>(peer_rs_flag[i]);
   }
   fp.rs_flag = static_cast<int*>(peer_rs_flag[rank]);
@@ -118,13 +128,15 @@ extern "C" int oslo_gemm_rs(const void* A, long long lda, const void* B, long lo
   if (b_mn) rc = make_map(&tb, B, is_bf16, N, K, 1, 1, ldb, 0, 0, 64, kBlockK);
   else      rc = make_map(&tb, B, is_bf16, K, N, 1, 1, ldb, 0, 0, kBlockK, block_n);
   if (rc) return rc;
-  rc = make_map(&tc, out, is_bf16, N, Tl, 1, 1, N, 0, 0, 64, 32);  // not stored through; kept valid for the prefetch
+  rc = make_map(&tc, peer_partial[rank], is_bf16, N, T, 1, 1, N, 0, 0, 64, 32);  // partial results stay local
   if (rc) return rc;
   taux = tc;
   const long long total = (long long)p.m_blocks * p.n_blocks;
-  const int grid = (int)(total < num_sms ? total : num_sms);
+  const int gemm_ctas = (int)(total < gemm_ctas_max ? total : gemm_ctas_max);
+  const int grid = reduce_ctas + gemm_ctas;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   switch (block_n) {
+    case 256: return OSLO_FUSED_LAUNCH(256, kModeReduceScatter);
     case 128: return OSLO_FUSED_LAUNCH(128, kModeReduceScatter);
     default: return OSLO_FUSED_LAUNCH(64, kModeReduceScatter);
   }

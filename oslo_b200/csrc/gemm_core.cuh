@@ -84,17 +84,18 @@ OSLO_DEVINL void tile_coords(int tile, const GemmParams& p, int& b, int& mb, int
 // the epoch (a per-group call counter) of the last completed hand-off, so they never need clearing.
 constexpr int kModePlain = 0;
 constexpr int kModeAllGather = 1;      // A rows are gathered from all ranks while the GEMM runs
-constexpr int kModeReduceScatter = 2;  // C row blocks are pushed to their owner and summed there
+constexpr int kModeReduceScatter = 2;  // C row blocks are pulled by their owner, which sums the tp partial results
 constexpr int kMaxRanks = 8;
 
 struct FusedParams {
   int tp = 1, rank = 0;
   int shard_rows = 0;       // rows of A (AG) / of C (RS) owned by one rank; a multiple of 128
   int tiles_per_shard = 0;  // output tiles per shard
+  int tiles_per_chunk = 0;  // RS: output tiles per row chunk
   int epoch = 0;
   int copy_ctas = 0;        // AG: CTAs [0, copy_ctas) copy, the others multiply
   int k_elems = 0;          // AG: row length of A in elements
-  int chunk_rows = 0;       // AG: rows per copy chunk (a multiple of 128 dividing shard_rows); one flag per chunk
+  int chunk_rows = 0;       // rows per hand-off chunk (a multiple of 128 dividing shard_rows); one flag per chunk
   // all-gather
   const void* peer_in[kMaxRanks] = {};  // every rank's symmetric input shard [shard_rows, K]
   void* x_full = nullptr;               // local [tp * shard_rows, K]
@@ -103,10 +104,10 @@ struct FusedParams {
   int* chunk_flag = nullptr;            // local [tp * chunks_per_shard]: that chunk of x_full is complete
   int* chunk_arrive = nullptr;          // local, same size: copy-CTA arrival counters
   // reduce-scatter
-  void* peer_slots[kMaxRanks] = {};     // every rank's slot buffer [tp, shard_rows, N]
-  int* rs_flag = nullptr;               // local [tp]: source p has pushed all its partial tiles
+  void* peer_slots[kMaxRanks] = {};     // every rank's partial-result buffer [tp * shard_rows, N]
+  int* rs_flag = nullptr;               // local [tp * chunks_per_shard]: source p finished that chunk of our rows
   int* peer_rs_flag[kMaxRanks] = {};
-  int* tile_done = nullptr;             // local [tp]: per-destination arrival counters
+  int* tile_done = nullptr;             // local [tp * chunks_per_shard]: per-chunk arrival counters
   void* rs_out = nullptr;               // local [shard_rows, N]
   const void* rs_bias = nullptr;        // optional [N]
   int* status = nullptr;
@@ -151,64 +152,99 @@ OSLO_DEVINL void fused_tile_coords(int tile, const GemmParams& p, const FusedPar
   const int t = tile - i * fp.tiles_per_shard;
   const int shard = (fp.rank + i + (MODE == kModeReduceScatter ? 1 : 0)) % fp.tp;
   const int blocks_per_shard = fp.shard_rows / kBlockM;
-  if (MODE == kModeAllGather) {
-    // walk chunk by chunk (the order the copy CTAs deliver them), all n-blocks of a chunk before the next chunk
-    const int blocks_per_chunk = fp.chunk_rows / kBlockM;
-    const int n_blocks = fp.tiles_per_shard / blocks_per_shard;
-    const int per_chunk = blocks_per_chunk * n_blocks;
-    const int c = t / per_chunk, r = t - c * per_chunk;
-    mb = shard * blocks_per_shard + c * blocks_per_chunk + r % blocks_per_chunk;
-    nb = r / blocks_per_chunk;
-  } else {
-    mb = shard * blocks_per_shard + t % blocks_per_shard;
-    nb = t / blocks_per_shard;
-  }
+  // walk the shard chunk by chunk (the hand-off granularity of both modes): all n-blocks of a chunk before the next
+  // chunk, so chunks are consumed (all-gather) or completed (reduce-scatter) in order
+  const int blocks_per_chunk = fp.chunk_rows / kBlockM;
+  const int n_blocks = fp.tiles_per_shard / blocks_per_shard;
+  const int per_chunk = blocks_per_chunk * n_blocks;
+  const int c = t / per_chunk, r = t - c * per_chunk;
+  mb = shard * blocks_per_shard + c * blocks_per_chunk + r % blocks_per_chunk;
+  nb = r / blocks_per_chunk;
 }
 
-// AG copy role: announce our shard, then pull the other ranks' shards chunk by chunk (next rank first) into
-// x_full, flagging every chunk, and finally copy the own shard (the GEMM reads that one in place, x_full only needs
-// it for later use by the caller).
-static __device__ __noinline__ void ag_copy_role(const GemmParams& p, const FusedParams& fp) {
-  __shared__ int s_ok;
-  const int tid = threadIdx.x, nthreads = blockDim.x;
-  if (blockIdx.x == 0 && tid < fp.tp) {
+// Untiled bulk copies (TMA engine, no multicast): global -> shared with mbarrier completion, shared -> global in a
+// bulk group.  Addresses and sizes are multiples of 16 bytes.
+OSLO_DEVINL void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+OSLO_DEVINL void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+}
+
+constexpr int kCopyPiece = 32768;  // bytes per bulk copy
+constexpr int kCopyDepth = 6;      // pieces in flight per copy CTA (6 x 32 KiB of shared memory)
+
+// AG copy role.  ONE thread per copy CTA drives the TMA engine: it announces our shard, then streams the other
+// ranks' shards (next rank first, the own shard last) through a shared-memory ring into x_full, keeping
+// kCopyDepth - 1 peer loads in flight to cover the NVLink round trip, and raises a flag per chunk of rows once all
+// copy CTAs have stored their pieces of it.  The GEMM CTAs take a chunk as soon as its flag is up.
+static __device__ __noinline__ void ag_copy_role(const GemmParams& p, const FusedParams& fp, uint8_t* ring, uint64_t* bars) {
+  if (threadIdx.x != 0) return;
+  __shared__ int s_abort;
+  s_abort = 0;
+  for (int i = 0; i < kCopyDepth; ++i) mbar_init(&bars[i], 1);
+  fence_barrier_init();
+  if (blockIdx.x == 0) {
     __threadfence_system();
-    st_release_sys(fp.peer_ag_ready[tid] + fp.rank, fp.epoch);
+    for (int t = 0; t < fp.tp; ++t) st_release_sys(fp.peer_ag_ready[t] + fp.rank, fp.epoch);
   }
-  const int chunks_per_shard = fp.shard_rows / fp.chunk_rows;
-  const long long vec_per_chunk = static_cast<long long>(fp.chunk_rows) * fp.k_elems / 8;
-  const long long per_cta = (vec_per_chunk + fp.copy_ctas - 1) / fp.copy_ctas;
-  const long long v0 = per_cta * blockIdx.x;
-  const long long v1 = v0 + per_cta < vec_per_chunk ? v0 + per_cta : vec_per_chunk;
-  for (int i = 1; i <= fp.tp; ++i) {
-    const int s = (fp.rank + i) % fp.tp;  // i == tp: the own shard, last
-    if (tid == 0) {
-      bool ok = true;
-      if (s != fp.rank) ok = flag_wait_bounded(fp.ag_ready + s, fp.epoch, nullptr, true);
-      if (!ok && fp.status) atomicCAS(fp.status, kStatusOk, kStatusPeerFlagTimeout);
-      s_ok = ok ? 1 : 0;
-    }
-    __syncthreads();
-    if (!s_ok) return;  // the GEMM CTAs will time out on the chunk flag and report it
-    for (int c = 0; c < chunks_per_shard; ++c) {
-      const int chunk = s * chunks_per_shard + c;
-      const uint4* src = static_cast<const uint4*>(fp.peer_in[s]) + static_cast<long long>(c) * vec_per_chunk;
-      uint4* dst = static_cast<uint4*>(fp.x_full) + static_cast<long long>(chunk) * vec_per_chunk;
-      long long v = v0 + tid;
-      // 8 independent 16-byte loads in flight per thread hide the NVLink round trip
-      for (; v + 7LL * nthreads < v1; v += 8LL * nthreads) {
-        uint4 r[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) r[u] = src[v + static_cast<long long>(u) * nthreads];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) dst[v + static_cast<long long>(u) * nthreads] = r[u];
+  const int cps = fp.shard_rows / fp.chunk_rows;  // chunks per shard
+  const long long chunk_bytes = static_cast<long long>(fp.chunk_rows) * fp.k_elems * 2;
+  const int ppc = static_cast<int>((chunk_bytes + kCopyPiece - 1) / kCopyPiece);  // pieces per chunk
+  const long long total = static_cast<long long>(fp.tp) * cps * ppc;
+  const int owners = fp.copy_ctas < ppc ? fp.copy_ctas : ppc;
+  const long long my_count = (total - blockIdx.x + fp.copy_ctas - 1) / fp.copy_ctas;  // pieces g = b + j * copy_ctas
+  int ready_shard = fp.rank;
+  bool ok = true;
+  auto locate = [&](long long j, const uint8_t*& src, uint8_t*& dst, uint32_t& bytes, int& chunk, bool& last_of_chunk, int& shard) {
+    const long long g = blockIdx.x + j * fp.copy_ctas;
+    const long long o = g / ppc;                      // position of the chunk in copy order
+    const int piece = static_cast<int>(g - o * ppc);
+    const int i = static_cast<int>(o / cps) + 1, c = static_cast<int>(o % cps);
+    shard = (fp.rank + i) % fp.tp;
+    chunk = shard * cps + c;
+    const long long off = static_cast<long long>(piece) * kCopyPiece;
+    bytes = static_cast<uint32_t>(chunk_bytes - off < kCopyPiece ? chunk_bytes - off : kCopyPiece);
+    src = static_cast<const uint8_t*>(fp.peer_in[shard]) + static_cast<long long>(c) * chunk_bytes + off;
+    dst = static_cast<uint8_t*>(fp.x_full) + static_cast<long long>(chunk) * chunk_bytes + off;
+    last_of_chunk = (g + fp.copy_ctas) / ppc != o;    // our next piece (if any) belongs to a later chunk
+  };
+  for (long long n = 0; n < my_count + kCopyDepth - 1 && ok; ++n) {
+    if (n < my_count) {
+      const uint8_t* src; uint8_t* dst; uint32_t bytes; int chunk, shard; bool last;
+      locate(n, src, dst, bytes, chunk, last, shard);
+      if (shard != ready_shard) {
+        if (!flag_wait_bounded(fp.ag_ready + shard, fp.epoch, nullptr, true)) {
+          if (fp.status) atomicCAS(fp.status, kStatusOk, kStatusPeerFlagTimeout);
+          ok = false;
+          break;
+        }
+        ready_shard = shard;
       }
-      for (; v < v1; v += nthreads) dst[v] = src[v];
-      __syncthreads();
-      if (tid == 0) {
+      if (n >= kCopyDepth) tma_store_wait_read<0>();  // the store that last used this ring slot has drained it
+      uint64_t* bar = &bars[n % kCopyDepth];
+      mbar_arrive_expect_tx(bar, bytes);
+      bulk_load(ring + (n % kCopyDepth) * kCopyPiece, src, bytes, bar);
+    }
+    const long long m = n - (kCopyDepth - 1);
+    if (m >= 0 && m < my_count) {
+      const uint8_t* src; uint8_t* dst; uint32_t bytes; int chunk, shard; bool last;
+      locate(m, src, dst, bytes, chunk, last, shard);
+      if (!mbar_wait_bounded(&bars[m % kCopyDepth], static_cast<uint32_t>((m / kCopyDepth) & 1), &s_abort)) {
+        if (fp.status) atomicCAS(fp.status, kStatusOk, kStatusPeerFlagTimeout);
+        ok = false;
+        break;
+      }
+      bulk_store(dst, ring + (m % kCopyDepth) * kCopyPiece, bytes);
+      tma_store_commit();
+      if (last) {
+        tma_store_wait_all();  // our pieces of this chunk are in memory
+        fence_proxy_async_global();
         __threadfence();
         const int old = atomicAdd(fp.chunk_arrive + chunk, 1);
-        if (old == fp.copy_ctas - 1) {
+        if (old == owners - 1) {
           fp.chunk_arrive[chunk] = 0;
           __threadfence();
           st_release_gpu(fp.chunk_flag + chunk, fp.epoch);
@@ -216,56 +252,111 @@ static __device__ __noinline__ void ag_copy_role(const GemmParams& p, const Fuse
       }
     }
   }
+  tma_store_wait_all();
 }
 
-// RS reduce phase (all threads of all GEMM CTAs): wait for every source, then out = sum of the tp slots.
-static __device__ __noinline__ void rs_reduce_phase(const GemmParams& p, const FusedParams& fp, int cta, int num_ctas,
-                                             volatile int* abort_flag) {
-  const int lane = threadIdx.x & 31;
-  bool ok = true;
-  if (lane < fp.tp) ok = flag_wait_bounded(fp.rs_flag + lane, fp.epoch, abort_flag, true);
-  ok = __all_sync(0xffffffffu, ok);
-  if (!ok) {
-    if (lane == 0 && fp.status) atomicCAS(fp.status, kStatusOk, kStatusPeerFlagTimeout);
-    return;
+constexpr int kReducePiece = 16384;  // bytes per bulk load of the reducer CTAs
+constexpr int kReduceSlots = 12;     // ring slots (12 x 16 KiB); one "set" = tp slots, one per source rank
+
+// RS reducer role (whole CTA): this rank's rows [rank * shard_rows, +shard_rows) of the tp partial results are one
+// contiguous block of shard_rows * N elements in every rank's partial buffer.  It is cut into 16 KiB pieces; for
+// each piece the CTA pulls the tp copies (bulk loads, the remote ones over NVLink) into a shared-memory ring — as
+// soon as the producing rank has flagged that row chunk complete — sums them in fp32 and stores the result.
+static __device__ __noinline__ void rs_reduce_role(const GemmParams& p, const FusedParams& fp, uint8_t* ring, uint64_t* bars) {
+  __shared__ int s_abort;
+  __shared__ int s_ok;
+  const int tid = threadIdx.x;
+  const int tp = fp.tp;
+  const int depth = kReduceSlots / tp;  // sets in flight (>= 1 for tp <= 12)
+  if (tid == 0) {
+    s_abort = 0;
+    s_ok = 1;
+    for (int i = 0; i < depth; ++i) mbar_init(&bars[i], 1);
+    fence_barrier_init();
   }
-  __threadfence_system();
-  const long long vecs = static_cast<long long>(fp.shard_rows) * p.N / 8;
-  const long long slot_vecs = vecs;
-  const uint4* slots = static_cast<const uint4*>(fp.peer_slots[fp.rank]);
-  uint4* out = static_cast<uint4*>(fp.rs_out);
-  const int nvec_row = p.N / 8;
-  for (long long v = static_cast<long long>(cta) * blockDim.x + threadIdx.x; v < vecs;
-       v += static_cast<long long>(num_ctas) * blockDim.x) {
-    float acc[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    if (fp.rs_bias) {
-      const uint4 raw = __ldg(static_cast<const uint4*>(fp.rs_bias) + (v % nvec_row));
-      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (p.is_bf16) { acc[2 * j] = __uint_as_float(w[j] << 16); acc[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u); }
-        else { const __half2 h = *reinterpret_cast<const __half2*>(&w[j]); acc[2 * j] = __low2float(h); acc[2 * j + 1] = __high2float(h); }
-      }
+  __syncthreads();
+  const long long block_bytes = static_cast<long long>(fp.shard_rows) * p.N * 2;
+  const long long pieces = (block_bytes + kReducePiece - 1) / kReducePiece;
+  const long long my_count = (pieces - blockIdx.x + fp.copy_ctas - 1) / fp.copy_ctas;
+  const long long row_bytes = static_cast<long long>(p.N) * 2;
+  const int cps = fp.shard_rows / fp.chunk_rows;
+  const long long base_off = static_cast<long long>(fp.rank) * block_bytes;
+  auto piece_of = [&](long long j, long long& off, uint32_t& bytes) {
+    off = (blockIdx.x + j * fp.copy_ctas) * static_cast<long long>(kReducePiece);
+    bytes = static_cast<uint32_t>(block_bytes - off < kReducePiece ? block_bytes - off : kReducePiece);
+  };
+  int ready_upto = -1;  // chunks [0, ready_upto] of our rows are known complete on every source (thread 0 only)
+  auto issue = [&](long long j) {  // thread 0 only
+    long long off; uint32_t bytes;
+    piece_of(j, off, bytes);
+    const int c1 = static_cast<int>((off + bytes - 1) / row_bytes) / fp.chunk_rows;
+    if (c1 > ready_upto) {
+      for (int c = ready_upto + 1; c <= c1; ++c)
+        for (int src = 0; src < tp; ++src)
+          if (!flag_wait_bounded(fp.rs_flag + src * cps + c, fp.epoch, &s_abort, true)) return false;
+      ready_upto = c1;
+      fence_proxy_async_global();
     }
-    for (int s = 0; s < fp.tp; ++s) {
-      const uint4 raw = slots[static_cast<long long>(s) * slot_vecs + v];
-      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (p.is_bf16) { acc[2 * j] += __uint_as_float(w[j] << 16); acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u); }
-        else { const __half2 h = *reinterpret_cast<const __half2*>(&w[j]); acc[2 * j] += __low2float(h); acc[2 * j + 1] += __high2float(h); }
-      }
-    }
-    uint32_t o[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      if (p.is_bf16) { const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]); o[j] = *reinterpret_cast<const uint32_t*>(&h); }
-      else { const __half2 h = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]); o[j] = *reinterpret_cast<const uint32_t*>(&h); }
-    }
-    out[v] = make_uint4(o[0], o[1], o[2], o[3]);
+    const int set = static_cast<int>(j % depth);
+    mbar_arrive_expect_tx(&bars[set], bytes * tp);
+    for (int src = 0; src < tp; ++src)
+      bulk_load(ring + (set * tp + src) * kReducePiece, static_cast<const uint8_t*>(fp.peer_slots[src]) + base_off + off, bytes,
+                &bars[set]);
+    return true;
+  };
+  if (tid == 0) {
+    for (long long j = 0; j < depth && j < my_count; ++j)
+      if (!issue(j)) { s_ok = 0; break; }
   }
+  __syncthreads();
+  for (long long j = 0; j < my_count; ++j) {
+    if (!s_ok) break;
+    long long off; uint32_t bytes;
+    piece_of(j, off, bytes);
+    const int set = static_cast<int>(j % depth);
+    if (!mbar_wait_bounded(&bars[set], static_cast<uint32_t>((j / depth) & 1), &s_abort)) break;
+    const uint4* slots = reinterpret_cast<const uint4*>(ring + static_cast<long long>(set) * tp * kReducePiece);
+    uint4* out = reinterpret_cast<uint4*>(static_cast<uint8_t*>(fp.rs_out) + off);
+    const int nvec = bytes / 16;
+    for (int v = tid; v < nvec; v += blockDim.x) {
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      if (fp.rs_bias) {
+        const long long col = ((off / 2) + static_cast<long long>(v) * 8) % p.N;
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(fp.rs_bias) + col));
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (p.is_bf16) { acc[2 * e] = __uint_as_float(w[e] << 16); acc[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u); }
+          else { const __half2 h = *reinterpret_cast<const __half2*>(&w[e]); acc[2 * e] = __low2float(h); acc[2 * e + 1] = __high2float(h); }
+        }
+      }
+      for (int src = 0; src < tp; ++src) {
+        const uint4 raw = slots[src * (kReducePiece / 16) + v];
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (p.is_bf16) { acc[2 * e] += __uint_as_float(w[e] << 16); acc[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u); }
+          else { const __half2 h = *reinterpret_cast<const __half2*>(&w[e]); acc[2 * e] += __low2float(h); acc[2 * e + 1] += __high2float(h); }
+        }
+      }
+      uint32_t o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (p.is_bf16) { const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]); o[e] = *reinterpret_cast<const uint32_t*>(&h); }
+        else { const __half2 h = __floats2half2_rn(acc[2 * e], acc[2 * e + 1]); o[e] = *reinterpret_cast<const uint32_t*>(&h); }
+      }
+      out[v] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    __syncthreads();  // every thread is done with this set's slots
+    if (tid == 0 && j + depth < my_count) {
+      fence_proxy_async_smem();
+      if (!issue(j + depth)) s_ok = 0;
+    }
+    __syncthreads();
+  }
+  if (tid == 0 && (!s_ok || s_abort) && fp.status) atomicCAS(fp.status, kStatusOk, kStatusPeerFlagTimeout);
 }
 
 // k-block range [kb0, kb1) a tile has to reduce over, or skip = true when it has no work.
@@ -286,12 +377,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if constexpr (MODE == kModeAllGather) {
     // the first fp.copy_ctas CTAs stream the peers' shards into local memory; the rest run the GEMM
     if (static_cast<int>(blockIdx.x) < fp.copy_ctas) {
-      ag_copy_role(p, fp);
+      extern __shared__ uint8_t copy_smem_raw[];
+      uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(copy_smem_raw) + 1023) & ~uintptr_t(1023));
+      ag_copy_role(p, fp, ring, reinterpret_cast<uint64_t*>(ring + kCopyDepth * kCopyPiece));
       return;
     }
   }
-  const int cta = (MODE == kModeAllGather) ? static_cast<int>(blockIdx.x) - fp.copy_ctas : static_cast<int>(blockIdx.x);
-  const int num_ctas = (MODE == kModeAllGather) ? static_cast<int>(gridDim.x) - fp.copy_ctas : static_cast<int>(gridDim.x);
+  if constexpr (MODE == kModeReduceScatter) {
+    // the first fp.copy_ctas CTAs pull and sum this rank's rows of every rank's partial result
+    if (static_cast<int>(blockIdx.x) < fp.copy_ctas) {
+      extern __shared__ uint8_t red_smem_raw[];
+      uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(red_smem_raw) + 1023) & ~uintptr_t(1023));
+      rs_reduce_role(p, fp, ring, reinterpret_cast<uint64_t*>(ring + kReduceSlots * kReducePiece));
+      return;
+    }
+  }
+  const int cta = (MODE != kModePlain) ? static_cast<int>(blockIdx.x) - fp.copy_ctas : static_cast<int>(blockIdx.x);
+  const int num_ctas = (MODE != kModePlain) ? static_cast<int>(gridDim.x) - fp.copy_ctas : static_cast<int>(gridDim.x);
   using Cfg = GemmCfg<BLOCK_N>;
   constexpr int kStages = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -578,55 +680,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             uint4* dst = reinterpret_cast<uint4*>(sbuf_ptr + lane * 128 + ((g ^ (lane & 7)) << 4));
             *dst = make_uint4(packed[0], packed[1], packed[2], packed[3]);
           }
-          if constexpr (MODE == kModeReduceScatter) {
-            // push the 32 x 64 block into slot [this rank] of the destination rank's buffer with plain
-            // 16-byte stores (coalesced: 8 lanes cover one 128-byte row segment)
-            __syncwarp();
-            const int dest = m0 / fp.shard_rows;
-            uint16_t* slot = static_cast<uint16_t*>(fp.peer_slots[dest]) +
-                             (static_cast<long long>(fp.rank) * fp.shard_rows + (m0 - dest * fp.shard_rows) + q * 32) * p.N;
-#pragma unroll
-            for (int it = 0; it < 8; ++it) {
-              const int r = it * 4 + (lane >> 3), c = lane & 7;
-              if (col0 + c * 8 < p.N) {
-                const uint4 val = *reinterpret_cast<const uint4*>(sbuf_ptr + r * 128 + ((c ^ (r & 7)) << 4));
-                *reinterpret_cast<uint4*>(slot + static_cast<long long>(r) * p.N + col0 + c * 8) = val;
-              }
-            }
-            __syncwarp();
-          } else {
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_4d(pass == 0 ? &tmAux : &tmC, sbuf_ptr, col0, m0 + q * 32, bi, bo);
-              tma_store_commit();
-            }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_4d(pass == 0 ? &tmAux : &tmC, sbuf_ptr, col0, m0 + q * 32, bi, bo);
+            tma_store_commit();
           }
           sbuf ^= 1;
         }
       }
       if constexpr (MODE == kModeReduceScatter) {
-        // count this warp's finished quarter-tiles per destination; publish the count (after ONE system fence
-        // covering all of them) when the destination changes or the CTA runs out of tiles
-        const int dest = m0 / fp.shard_rows;
+        // The partial tile went to the LOCAL partial-result buffer.  Count this warp's finished quarter-tiles per
+        // row chunk and publish the count when the warp moves on to another chunk (or runs out of tiles): wait for
+        // its TMA stores to be complete, then one atomic; the warp that completes a chunk raises the flag on the
+        // rank that owns those rows, whose reducer CTAs then pull the chunk over NVLink.
+        const int chunk = m0 / fp.chunk_rows;
         const int next_tile = tile + num_ctas;
-        int next_dest = -1;
+        int next_chunk = -1;
         if (next_tile < num_tiles) {
           int nb2, mb2, b2;
           fused_tile_coords<MODE>(next_tile, p, fp, b2, mb2, nb2);
-          next_dest = mb2 * kBlockM / fp.shard_rows;
+          next_chunk = mb2 * kBlockM / fp.chunk_rows;
         }
         ++rs_pending;
-        if (next_dest != dest) {
-          __threadfence_system();
-          __syncwarp();
+        if (next_chunk != chunk) {
           if (lane == 0) {
-            const int need = fp.tiles_per_shard * 4;
-            const int old = atomicAdd(fp.tile_done + dest, rs_pending);
+            tma_store_wait_all();
+            fence_proxy_async_global();
+            __threadfence_system();
+            const int need = fp.tiles_per_chunk * 4;
+            const int old = atomicAdd(fp.tile_done + chunk, rs_pending);
             if (old + rs_pending == need) {
-              fp.tile_done[dest] = 0;
+              fp.tile_done[chunk] = 0;
               __threadfence_system();
-              st_release_sys(fp.peer_rs_flag[dest] + fp.rank, fp.epoch);
+              const int dest = m0 / fp.shard_rows;
+              const int cps = fp.shard_rows / fp.chunk_rows;
+              st_release_sys(fp.peer_rs_flag[dest] + fp.rank * cps + (chunk - dest * cps), fp.epoch);
             }
           }
           rs_pending = 0;
@@ -638,8 +727,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     if (lane == 0) tma_store_wait_all();
   }
-
-  if constexpr (MODE == kModeReduceScatter) rs_reduce_phase(p, fp, cta, num_ctas, abort_flag);
 
   tc_fence_before();
   __syncthreads();

@@ -9,7 +9,7 @@ Workspace layout per rank (all offsets identical on every rank)::
     [ flags 4 KiB | in[0] | in[1] | slots[0] | slots[1] ]
 
 * ``in[p]``     this rank's shard of the all-gather input for calls with parity ``p`` (``Tl x F`` elements);
-* ``slots[p]``  ``tp`` blocks of ``Tl x F``: block ``s`` receives rank ``s``'s partial rows of a reduce-scatter;
+* ``slots[p]``  this rank's partial result ``[T, F]`` of a reduce-scatter; rank ``r`` pulls rows ``[r*Tl, (r+1)*Tl)`` of it;
 * flags        ``ag_ready[tp]``, ``rs_flag[tp]``, ``barrier[tp]`` written by peers, holding call epochs.
 
 Double buffering by call parity is what makes the scheme free of write-after-read races without a trailing
@@ -36,7 +36,7 @@ class _RawCudaBuffer:
 
 
 class SymmetricWorkspace:
-    def __init__(self, pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 20):
+    def __init__(self, pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 16):
         self.pc, self.mode = pc, mode
         self.tp = pc.get_world_size(mode)
         self.rank = pc.get_local_rank(mode)
@@ -180,7 +180,8 @@ class SymmetricWorkspace:
             _lib.ptr(out), _lib.ptr(bias), ctypes.c_int(t), ctypes.c_int(n), ctypes.c_int(k),
             ctypes.c_int(1 if self.dtype == torch.bfloat16 else 0), ctypes.c_int(self.tp), ctypes.c_int(self.rank),
             ctypes.c_int(self.epoch), self._slot_ptrs(parity), self._flag_ptrs(1), self._local_ptr(2),
-            ctypes.c_int(_lib.num_sms()), _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr())
+            ctypes.c_int(self.copy_ctas), ctypes.c_int(_lib.num_sms()), _lib.ptr(_lib.status_word(self.device)),
+            _lib.stream_ptr())
         if rc:
             raise RuntimeError(f"oslo_gemm_rs failed ({rc})")
         return out
@@ -209,7 +210,7 @@ class _Runtime:
         return self.ws.gemm_rs(x, weight)
 
 
-def enable(pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 20) -> bool:
+def enable(pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 16) -> bool:
     """Create the group's symmetric workspace and switch the sequence-parallel linears to the fused kernels."""
     if not (torch.cuda.is_available() and pc.use_cuda) or pc.get_world_size(mode) == 1:
         return False

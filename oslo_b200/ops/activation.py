@@ -193,3 +193,41 @@ def bias_dropout_add(x, bias=None, residual=None, p: float = 0.0, training: bool
 
 def fused_bias_dropout(x, bias, p, training, inplace=False):
     return bias_dropout_add(x, bias, None, p, training)
+
+
+class _SwiGLU2Fn(torch.autograd.Function):
+    """``silu(gate) * up`` for two separate tensors (Llama's gate_proj / up_proj outputs)."""
+
+    @staticmethod
+    def forward(ctx, gate, up):
+        g, u = gate.contiguous(), up.contiguous()
+        f = g.shape[-1]
+        rows = g.numel() // f
+        y = torch.empty_like(g)
+        rc = _lib.cuda_lib().oslo_swiglu_forward(
+            _lib.ptr(g), _lib.ptr(u), _lib.ptr(y), ctypes.c_longlong(rows), ctypes.c_int(f), ctypes.c_longlong(f),
+            ctypes.c_int(_DT[g.dtype]), ctypes.c_int(_lib.num_sms()), _lib.stream_ptr())
+        if rc:
+            raise RuntimeError(f"oslo_swiglu_forward failed ({rc})")
+        ctx.save_for_backward(g, u)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        g, u = ctx.saved_tensors
+        f = g.shape[-1]
+        rows = g.numel() // f
+        gy = gy.contiguous()
+        dg, du = torch.empty_like(g), torch.empty_like(u)
+        rc = _lib.cuda_lib().oslo_swiglu_backward(
+            _lib.ptr(gy), _lib.ptr(g), _lib.ptr(u), _lib.ptr(dg), _lib.ptr(du), ctypes.c_longlong(rows), ctypes.c_int(f),
+            ctypes.c_longlong(f), ctypes.c_int(_DT[g.dtype]), ctypes.c_int(_lib.num_sms()), _lib.stream_ptr())
+        if rc:
+            raise RuntimeError(f"oslo_swiglu_backward failed ({rc})")
+        return dg, du
+
+
+def swiglu2(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    if _cuda_ok(gate) and gate.dtype == up.dtype:
+        return _SwiGLU2Fn.apply(gate, up)
+    return F.silu(gate) * up
