@@ -1,0 +1,92 @@
+"""Activation checkpointing (gradients equal the plain run, RNG replay), topology tables, P2P objects, logger."""
+import pytest
+import torch
+import torch.nn as nn
+
+from dist_utils import run_dist
+
+
+def test_checkpoint_function_matches_plain_backward_with_dropout():
+    from oslo_b200.utils.checkpoint import CheckpointFunction, CheckpointPartitioner
+
+    torch.manual_seed(0)
+    layer = nn.Sequential(nn.Linear(16, 32), nn.GELU(), nn.Dropout(0.3), nn.Linear(32, 16))
+    x = torch.randn(4, 16, requires_grad=True)
+    torch.manual_seed(5)
+    y = layer(x)
+    y.sum().backward()
+    ref_gx = x.grad.clone()
+    ref_gw = layer[0].weight.grad.clone()
+    layer.zero_grad()
+    x.grad = None
+    torch.manual_seed(5)
+    y2 = CheckpointFunction.apply(layer, CheckpointPartitioner(), x)
+    torch.randn(3)  # disturb the RNG between forward and backward: the recomputation must replay the saved state
+    y2.sum().backward()
+    assert torch.allclose(y, y2) and torch.allclose(x.grad, ref_gx) and torch.allclose(layer[0].weight.grad, ref_gw)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8, 16])
+def test_topology_groups_partition_the_world(world):
+    from oslo_b200.distributed import ParallelMode, Topology
+
+    for tp, mode, depth in [(1, ParallelMode.TENSOR_1D, None), (2, ParallelMode.TENSOR_1D, None), (4, ParallelMode.TENSOR_2D, None),
+                            (8, ParallelMode.TENSOR_2P5D, 2), (8, ParallelMode.TENSOR_3D, None)]:
+        if world % tp:
+            continue
+        for pp in (1, 2):
+            if (world // tp) % pp:
+                continue
+            dp = world // tp // pp
+            topo = Topology(world, dp, pp, tp, 1, 1, mode, depth).validate()
+            for m in topo.active_modes():
+                groups = topo.groups(m)
+                flat = sorted(r for g in groups for r in g)
+                assert flat == list(range(world)), (m, groups)
+                assert len({len(g) for g in groups}) == 1
+
+
+def test_topology_reference_formulas():
+    from oslo_b200.distributed import ParallelMode as M, Topology
+
+    t = Topology(8, 2, 2, 2, 1, 1, M.TENSOR_1D).validate()
+    assert t.groups(M.DATA) == [[0, 4], [1, 5], [2, 6], [3, 7]]
+    assert t.groups(M.TENSOR) == [[0, 1], [2, 3], [4, 5], [6, 7]]
+    assert t.groups(M.PIPELINE) == [[0, 2], [1, 3], [4, 6], [5, 7]]
+    assert t.groups(M.MODEL) == [[0, 1, 2, 3], [4, 5, 6, 7]]
+    t2 = Topology(4, 1, 1, 4, 1, 1, M.TENSOR_2D).validate()
+    assert t2.groups(M.TENSOR_2D_ROW) == [[0, 1], [2, 3]] and t2.groups(M.TENSOR_2D_COL) == [[0, 2], [1, 3]]
+    t3 = Topology(8, 1, 1, 8, 1, 1, M.TENSOR_3D).validate()
+    assert t3.groups(M.TENSOR_3D_WEIGHT)[0] == [0, 1] and t3.groups(M.TENSOR_3D_INPUT)[0] == [0, 2]
+    assert t3.groups(M.TENSOR_3D_OUTPUT)[0] == [0, 4]
+    t25 = Topology(8, 1, 1, 8, 1, 1, M.TENSOR_2P5D, 2).validate()
+    assert t25.groups(M.TENSOR_2P5D_DEP)[0] == [0, 4] and t25.groups(M.TENSOR_2P5D_XZ)[0] == [0, 2, 4, 6]
+    ov = Topology(8, 8, 1, 1, 1, 8, M.TENSOR_1D, None, True).validate()
+    assert ov.groups(M.EXPERT) == [list(range(8))]
+    with pytest.raises(ValueError):
+        Topology(8, 1, 1, 2, 2, 1, M.TENSOR_1D).validate()
+    with pytest.raises(ValueError):
+        Topology(6, 1, 1, 6, 1, 1, M.TENSOR_2D).validate()
+
+
+def _p2p_worker(rank, world):
+    from oslo_b200 import ParallelContext
+    from oslo_b200.distributed import comm
+
+    pc = ParallelContext.from_torch(data_parallel_size=world, backend="gloo")
+    obj = {"a": [1, 2.5, "x", None, True], "t": torch.arange(6).view(2, 3).float(), "n": (torch.Size([2, 3]), {3, 4}),
+           "g": torch.ones(2, requires_grad=True)}
+    if rank == 0:
+        comm.send(obj, 0, 1, parallel_context=pc)
+    else:
+        got = comm.recv(0, 1, parallel_context=pc)
+        assert got["a"] == obj["a"] and torch.equal(got["t"], obj["t"]) and got["n"] == obj["n"]
+        assert got["g"].requires_grad
+    x = torch.full((2, 3), float(rank))
+    g = comm.all_gather(x, dim=1, parallel_context=pc, parallel_mode=pc.topology and __import__("oslo_b200").ParallelMode.DATA)
+    assert g.shape == (2, 3 * world) and g[0, 3].item() == 1.0
+    pc.destroy()
+
+
+def test_object_p2p_and_gather_dim():
+    run_dist(_p2p_worker, 2)
