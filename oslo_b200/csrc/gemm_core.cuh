@@ -255,19 +255,22 @@ static __device__ __noinline__ void ag_copy_role(const GemmParams& p, const Fuse
   tma_store_wait_all();
 }
 
-constexpr int kReducePiece = 16384;  // bytes per bulk load of the reducer CTAs
-constexpr int kReduceSlots = 12;     // ring slots (12 x 16 KiB); one "set" = tp slots, one per source rank
+constexpr int kReduceRing = 196608;  // bytes of shared memory used as the reducers' landing ring
+constexpr int kReduceMaxSets = 12;
 
 // RS reducer role (whole CTA): this rank's rows [rank * shard_rows, +shard_rows) of the tp partial results are one
-// contiguous block of shard_rows * N elements in every rank's partial buffer.  It is cut into 16 KiB pieces; for
-// each piece the CTA pulls the tp copies (bulk loads, the remote ones over NVLink) into a shared-memory ring — as
-// soon as the producing rank has flagged that row chunk complete — sums them in fp32 and stores the result.
+// contiguous block of shard_rows * N elements in every rank's partial buffer.  It is cut into pieces (32 KiB, or
+// 16 KiB for groups of more than 4); for each piece the CTA pulls the tp - 1 REMOTE copies with bulk loads over NVLink
+// into a shared-memory ring — as soon as the producing ranks have flagged that row chunk complete — keeping as many
+// piece-sets in flight as the ring holds, adds the local copy read straight from memory, sums in fp32 and stores.
 static __device__ __noinline__ void rs_reduce_role(const GemmParams& p, const FusedParams& fp, uint8_t* ring, uint64_t* bars) {
   __shared__ int s_abort;
   __shared__ int s_ok;
   const int tid = threadIdx.x;
-  const int tp = fp.tp;
-  const int depth = kReduceSlots / tp;  // sets in flight (>= 1 for tp <= 12)
+  const int tp = fp.tp, remote = tp - 1;
+  const int piece = remote > 3 ? 16384 : 32768;
+  int depth = kReduceRing / (piece * remote);  // piece-sets in flight
+  if (depth > kReduceMaxSets) depth = kReduceMaxSets;
   if (tid == 0) {
     s_abort = 0;
     s_ok = 1;
@@ -276,14 +279,15 @@ static __device__ __noinline__ void rs_reduce_role(const GemmParams& p, const Fu
   }
   __syncthreads();
   const long long block_bytes = static_cast<long long>(fp.shard_rows) * p.N * 2;
-  const long long pieces = (block_bytes + kReducePiece - 1) / kReducePiece;
+  const long long pieces = (block_bytes + piece - 1) / piece;
   const long long my_count = (pieces - blockIdx.x + fp.copy_ctas - 1) / fp.copy_ctas;
   const long long row_bytes = static_cast<long long>(p.N) * 2;
   const int cps = fp.shard_rows / fp.chunk_rows;
   const long long base_off = static_cast<long long>(fp.rank) * block_bytes;
+  const uint8_t* local_src = static_cast<const uint8_t*>(fp.peer_slots[fp.rank]) + base_off;
   auto piece_of = [&](long long j, long long& off, uint32_t& bytes) {
-    off = (blockIdx.x + j * fp.copy_ctas) * static_cast<long long>(kReducePiece);
-    bytes = static_cast<uint32_t>(block_bytes - off < kReducePiece ? block_bytes - off : kReducePiece);
+    off = (blockIdx.x + j * fp.copy_ctas) * static_cast<long long>(piece);
+    bytes = static_cast<uint32_t>(block_bytes - off < piece ? block_bytes - off : piece);
   };
   int ready_upto = -1;  // chunks [0, ready_upto] of our rows are known complete on every source (thread 0 only)
   auto issue = [&](long long j) {  // thread 0 only
@@ -298,10 +302,14 @@ static __device__ __noinline__ void rs_reduce_role(const GemmParams& p, const Fu
       fence_proxy_async_global();
     }
     const int set = static_cast<int>(j % depth);
-    mbar_arrive_expect_tx(&bars[set], bytes * tp);
-    for (int src = 0; src < tp; ++src)
-      bulk_load(ring + (set * tp + src) * kReducePiece, static_cast<const uint8_t*>(fp.peer_slots[src]) + base_off + off, bytes,
-                &bars[set]);
+    mbar_arrive_expect_tx(&bars[set], bytes * remote);
+    int slot = 0;
+    for (int src = 0; src < tp; ++src) {
+      if (src == fp.rank) continue;
+      bulk_load(ring + (static_cast<long long>(set) * remote + slot) * piece,
+                static_cast<const uint8_t*>(fp.peer_slots[src]) + base_off + off, bytes, &bars[set]);
+      ++slot;
+    }
     return true;
   };
   if (tid == 0) {
@@ -315,16 +323,14 @@ static __device__ __noinline__ void rs_reduce_role(const GemmParams& p, const Fu
     piece_of(j, off, bytes);
     const int set = static_cast<int>(j % depth);
     if (!mbar_wait_bounded(&bars[set], static_cast<uint32_t>((j / depth) & 1), &s_abort)) break;
-    const uint4* slots = reinterpret_cast<const uint4*>(ring + static_cast<long long>(set) * tp * kReducePiece);
+    const uint4* slots = reinterpret_cast<const uint4*>(ring + static_cast<long long>(set) * remote * piece);
+    const uint4* mine = reinterpret_cast<const uint4*>(local_src + off);
     uint4* out = reinterpret_cast<uint4*>(static_cast<uint8_t*>(fp.rs_out) + off);
-    const int nvec = bytes / 16;
+    const int nvec = bytes / 16, slot_vecs = piece / 16;
     for (int v = tid; v < nvec; v += blockDim.x) {
       float acc[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-      if (fp.rs_bias) {
-        const long long col = ((off / 2) + static_cast<long long>(v) * 8) % p.N;
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(fp.rs_bias) + col));
+      {
+        const uint4 raw = mine[v];
         const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -332,8 +338,18 @@ static __device__ __noinline__ void rs_reduce_role(const GemmParams& p, const Fu
           else { const __half2 h = *reinterpret_cast<const __half2*>(&w[e]); acc[2 * e] = __low2float(h); acc[2 * e + 1] = __high2float(h); }
         }
       }
-      for (int src = 0; src < tp; ++src) {
-        const uint4 raw = slots[src * (kReducePiece / 16) + v];
+      if (fp.rs_bias) {
+        const long long col = ((off / 2) + static_cast<long long>(v) * 8) % p.N;
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(fp.rs_bias) + col));
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (p.is_bf16) { acc[2 * e] += __uint_as_float(w[e] << 16); acc[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u); }
+          else { const __half2 h = *reinterpret_cast<const __half2*>(&w[e]); acc[2 * e] += __low2float(h); acc[2 * e + 1] += __high2float(h); }
+        }
+      }
+      for (int src = 0; src < remote; ++src) {
+        const uint4 raw = slots[src * slot_vecs + v];
         const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -388,7 +404,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (static_cast<int>(blockIdx.x) < fp.copy_ctas) {
       extern __shared__ uint8_t red_smem_raw[];
       uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(red_smem_raw) + 1023) & ~uintptr_t(1023));
-      rs_reduce_role(p, fp, ring, reinterpret_cast<uint64_t*>(ring + kReduceSlots * kReducePiece));
+      rs_reduce_role(p, fp, ring, reinterpret_cast<uint64_t*>(ring + kReduceRing));
       return;
     }
   }

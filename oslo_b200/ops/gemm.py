@@ -86,6 +86,10 @@ def gemm(
     osc = out.stride(0) if nd == 4 else 0
     if aux is not None:
         assert aux.stride() == out.stride()
+    from oslo_b200.transformers import profiler as _prof
+
+    if _prof._ACTIVE is not None:
+        _prof.report_gemm_flops(M, N, K, b_in * b_out)
     lib = _lib.cuda_lib()
     status = _lib.status_word(a.device)
     use_epi = _EPI[epilogue] if (bias is not None or epilogue == "gelu") else 0

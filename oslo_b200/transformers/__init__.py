@@ -1,0 +1,6 @@
+from .oslo_init import OsloTrainerConfig, init_oslo_features
+from .profiler import FlopsProfiler, get_model_profile
+from .trainer import Trainer
+from .training_args import TrainingArguments
+
+__all__ = ["Trainer", "TrainingArguments", "OsloTrainerConfig", "init_oslo_features", "FlopsProfiler", "get_model_profile"]

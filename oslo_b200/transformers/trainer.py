@@ -1,0 +1,389 @@
+"""``Trainer``: training / evaluation loop over the parallel wrappers.
+
+Covers what the reference trainer does (oslo/transformers/trainer.py:91-1871) in a compact form: distributed samplers
+over the DATA group, gradient accumulation (``no_sync`` on DDP), clipping, LR schedules, logging history, evaluation,
+checkpoints (per-rank model shards through ``save_pretrained``, ``optimizer.pt``, ``scheduler.pt``,
+``trainer_state.json``, per-rank ``rng_state_{rank}.pth``), resume (skips the batches already seen), best-model tracking,
+one-step FLOPs profiling, and the pipeline generator protocol.
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+import random
+import shutil
+import time
+from typing import Callable, Dict, List, Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+from torch.utils.data import DataLoader, Dataset
+from torch.utils.data.distributed import DistributedSampler
+
+import oslo_b200
+from oslo_b200.distributed import ParallelMode
+from oslo_b200.utils.logging import get_dist_logger
+
+from .training_args import TrainingArguments
+
+
+def _scheduler(optimizer, kind: str, warmup: int, total: int):
+    def lr_lambda(step):
+        if warmup and step < warmup:
+            return (step + 1) / warmup
+        if kind == "constant":
+            return 1.0
+        frac = (step - warmup) / max(1, total - warmup)
+        if kind == "cosine":
+            return 0.5 * (1.0 + math.cos(math.pi * min(1.0, frac)))
+        return max(0.0, 1.0 - frac)  # linear
+
+    return torch.optim.lr_scheduler.LambdaLR(optimizer, lr_lambda)
+
+
+class TrainerState:
+    def __init__(self):
+        self.global_step = 0
+        self.epoch = 0.0
+        self.log_history: List[dict] = []
+        self.best_metric = None
+        self.best_model_checkpoint = None
+
+    def to_json(self):
+        return json.dumps(self.__dict__, indent=2)
+
+
+class Trainer:
+    def __init__(self, model, args: TrainingArguments, train_dataset: Optional[Dataset] = None,
+                 eval_dataset: Optional[Dataset] = None, data_collator: Optional[Callable] = None,
+                 optimizers=(None, None), compute_metrics: Optional[Callable] = None, callbacks=None):
+        self.args = args
+        self.pc = args.parallel_context
+        self.logger = get_dist_logger("oslo_b200.trainer")
+        self.train_dataset, self.eval_dataset = train_dataset, eval_dataset
+        self.data_collator = data_collator
+        self.compute_metrics = compute_metrics
+        self.callbacks = callbacks or []
+        self.state = TrainerState()
+        self.base_model = model
+        if args.dtype != torch.float32:
+            model.to(args.dtype)
+        self.model = model
+        self.zero = None
+        if self.pc is not None:
+            from .oslo_init import apply_wrappers
+
+            self.model = apply_wrappers(model, self.pc, args.wrapper_recipes or [])
+            cfg = args.oslo_config
+            dp = cfg.data_parallelism if cfg else None
+            stage = (dp or {}).get("zero_stage", 0)
+            if self.pc.data_parallel_size > 1 and stage == 0:
+                from oslo_b200.parallel import DistributedDataParallel
+
+                self.model = DistributedDataParallel(model if self.model is model else self.model, self.pc) \
+                    if self.model is model else self._ddp_over(self.model)
+            oslo_b200.ready(self.model, self.pc)
+            if cfg and cfg.activation_checkpointing:
+                from oslo_b200.utils.checkpoint import ActivationCheckpointing
+
+                ac = cfg.activation_checkpointing
+                ActivationCheckpointing(model, self.pc, ac.get("partitioned", False), ac.get("contiguous", False), ac.get("cpu", False))
+        elif torch.cuda.is_available():
+            model.to("cuda")
+        self.optimizer, self.lr_scheduler = optimizers
+        self.is_pipeline = self.pc is not None and self.pc.pipeline_parallel_size > 1
+        self.profiler = None
+
+    def _ddp_over(self, wrapped):
+        from oslo_b200.parallel.data_parallel import _DistributedDataParallel
+
+        _DistributedDataParallel(self.base_model, self.pc)  # registers itself on the base module
+        return wrapped
+
+    # ------------------------------------------------------------------ setup
+    @property
+    def device(self):
+        return self.pc.device if self.pc is not None else next(self.base_model.parameters()).device
+
+    def _dp(self):
+        if self.pc is None:
+            return 1, 0
+        return self.pc.get_world_size(ParallelMode.DATA), self.pc.get_local_rank(ParallelMode.DATA)
+
+    def get_train_dataloader(self) -> DataLoader:
+        world, rank = self._dp()
+        sampler = DistributedSampler(self.train_dataset, num_replicas=world, rank=rank, shuffle=True, seed=self.args.seed,
+                                     drop_last=self.args.dataloader_drop_last)
+        return DataLoader(self.train_dataset, batch_size=self.args.per_device_train_batch_size, sampler=sampler,
+                          collate_fn=self.data_collator, drop_last=self.args.dataloader_drop_last,
+                          num_workers=self.args.dataloader_num_workers, pin_memory=torch.cuda.is_available())
+
+    def get_eval_dataloader(self, dataset=None) -> DataLoader:
+        dataset = dataset or self.eval_dataset
+        world, rank = self._dp()
+        sampler = DistributedSampler(dataset, num_replicas=world, rank=rank, shuffle=False)
+        return DataLoader(dataset, batch_size=self.args.per_device_eval_batch_size, sampler=sampler,
+                          collate_fn=self.data_collator)
+
+    def create_optimizer(self):
+        if self.optimizer is not None:
+            return self.optimizer
+        from oslo_b200 import optim
+
+        a = self.args
+        params = [p for p in self.base_model.parameters() if p.requires_grad and p.numel() > 0]
+        kind = a.optim.lower()
+        if kind in ("adam", "adamw"):
+            opt = optim.FusedAdam(params, lr=a.learning_rate, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
+                                  weight_decay=a.weight_decay, master_weights=a.dtype != torch.float32)
+        elif kind == "lamb":
+            opt = optim.FusedLamb(params, lr=a.learning_rate, weight_decay=a.weight_decay, max_grad_norm=a.max_grad_norm)
+        elif kind == "sgd":
+            opt = optim.FusedSGD(params, lr=a.learning_rate, weight_decay=a.weight_decay)
+        elif kind == "adagrad":
+            opt = optim.FusedAdagrad(params, lr=a.learning_rate, weight_decay=a.weight_decay)
+        elif kind == "novograd":
+            opt = optim.FusedNovoGrad(params, lr=a.learning_rate, weight_decay=a.weight_decay)
+        else:
+            raise ValueError(f"unknown optimizer {a.optim}")
+        cfg = a.oslo_config
+        dp = (cfg.data_parallelism if cfg else None) or {}
+        if self.pc is not None and dp.get("zero_stage", 0) in (1, 2):
+            from oslo_b200.parallel import ZeroRedundancyOptimizer
+
+            inner = torch.optim.AdamW(params, lr=a.learning_rate, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
+                                      weight_decay=a.weight_decay)
+            self.zero = opt = ZeroRedundancyOptimizer(inner, parallel_context=self.pc, partition_grad=dp["zero_stage"] == 2,
+                                                      clip_grad_norm=a.max_grad_norm, **(dp.get("params") or {}))
+        self.optimizer = opt
+        return opt
+
+    # ------------------------------------------------------------- train loop
+    def _move(self, batch: Dict[str, torch.Tensor]):
+        return {k: (v.to(self.device, non_blocking=True) if torch.is_tensor(v) else v) for k, v in batch.items()}
+
+    def training_step(self, batch) -> torch.Tensor:
+        batch = self._move(batch)
+        accum = self.args.gradient_accumulation_steps
+        if self.is_pipeline:
+            total = torch.zeros((), device=self.device)
+            for _, out in self.model(**batch):
+                if torch.is_tensor(out.loss):
+                    (out.loss / accum).backward()
+                    total += out.loss.detach()
+            return total
+        loss = self.model(**batch).loss / accum
+        if self.zero is not None:
+            self.zero.backward(loss)
+        else:
+            loss.backward()
+        return loss.detach() * accum
+
+    def _clip(self):
+        if self.zero is not None or not self.args.max_grad_norm:
+            return
+        params = [p for p in self.base_model.parameters() if p.grad is not None]
+        if params:
+            torch.nn.utils.clip_grad_norm_(params, self.args.max_grad_norm)
+
+    def train(self, resume_from_checkpoint: Optional[str] = None):
+        a = self.args
+        loader = self.get_train_dataloader()
+        steps_per_epoch = max(1, len(loader) // a.gradient_accumulation_steps)
+        max_steps = a.max_steps if a.max_steps > 0 else int(math.ceil(a.num_train_epochs * steps_per_epoch))
+        opt = self.create_optimizer()
+        inner = opt.optim if self.zero is not None else opt
+        if self.lr_scheduler is None:
+            warm = a.warmup_steps or int(a.warmup_ratio * max_steps)
+            self.lr_scheduler = _scheduler(inner, a.lr_scheduler_type, warm, max_steps)
+        resume = resume_from_checkpoint or a.resume_from_checkpoint
+        skip_batches = 0
+        if resume:
+            skip_batches = self._load_checkpoint(resume) * a.gradient_accumulation_steps
+        self.base_model.train()
+        t0 = time.time()
+        tokens = 0
+        running, epoch = 0.0, int(self.state.epoch)
+        done = False
+        while not done:
+            if hasattr(loader.sampler, "set_epoch"):
+                loader.sampler.set_epoch(epoch)
+            for i, batch in enumerate(loader):
+                if skip_batches > 0:
+                    skip_batches -= 1
+                    continue
+                sync_now = (i + 1) % a.gradient_accumulation_steps == 0
+                profile = a.flops_profiler and self.state.global_step == a.flops_profiler_step and self._rank() == 0
+                if profile:
+                    from .profiler import FlopsProfiler
+
+                    self.profiler = FlopsProfiler(self.base_model)
+                    self.profiler.start_profile()
+                ctx = self.model.no_sync() if (not sync_now and hasattr(self.model, "no_sync")) else _null()
+                with ctx:
+                    running += float(self.training_step(batch))
+                if profile:
+                    self.profiler.stop_profile()
+                    self.profiler.print_model_profile(output_file=a.flops_profiler_output_path)
+                if "input_ids" in batch:
+                    tokens += batch["input_ids"].numel()
+                if not sync_now:
+                    continue
+                self._clip()
+                opt.step()
+                self.lr_scheduler.step()
+                if self.zero is not None:
+                    opt.zero_grad()
+                elif hasattr(self.model, "zero_grad") and hasattr(self.model, "flats"):
+                    self.model.zero_grad()
+                else:
+                    opt.zero_grad()
+                self.state.global_step += 1
+                self.state.epoch = epoch + (i + 1) / len(loader)
+                if a.logging_steps and self.state.global_step % a.logging_steps == 0:
+                    n = a.logging_steps * a.gradient_accumulation_steps
+                    self.log({"loss": self._mean_over_dp(running / n), "learning_rate": self.lr_scheduler.get_last_lr()[0],
+                              "epoch": round(self.state.epoch, 3), "step": self.state.global_step})
+                    running = 0.0
+                if a.eval_steps and self.eval_dataset is not None and self.state.global_step % a.eval_steps == 0:
+                    self._track_best(self.evaluate())
+                    self.base_model.train()
+                if a.save_steps and self.state.global_step % a.save_steps == 0:
+                    self.save_checkpoint()
+                if self.state.global_step >= max_steps:
+                    done = True
+                    break
+            epoch += 1
+        elapsed = time.time() - t0
+        dp_world, _ = self._dp()
+        metrics = {"train_runtime": elapsed, "train_steps_per_second": self.state.global_step / max(elapsed, 1e-9),
+                   "train_tokens_per_second": tokens * dp_world / max(elapsed, 1e-9)}
+        self.log(metrics)
+        return metrics
+
+    def _rank(self):
+        return self.pc.get_global_rank() if self.pc is not None else 0
+
+    def _mean_over_dp(self, value: float) -> float:
+        if self.pc is None or self.pc.data_parallel_size == 1:
+            return value
+        t = torch.tensor([value], device=self.device)
+        dist.all_reduce(t, group=self.pc.get_group(ParallelMode.DATA))
+        return float(t) / self.pc.data_parallel_size
+
+    def log(self, logs: dict):
+        self.state.log_history.append(dict(logs))
+        self.logger.info(json.dumps(logs), ranks=[0])
+        for cb in self.callbacks:
+            if hasattr(cb, "on_log"):
+                cb.on_log(self.args, self.state, logs)
+
+    # ------------------------------------------------------------- evaluation
+    @torch.no_grad()
+    def evaluate(self, eval_dataset=None) -> Dict[str, float]:
+        self.base_model.eval()
+        losses = []
+        for batch in self.get_eval_dataloader(eval_dataset):
+            batch = self._move(batch)
+            if self.is_pipeline:
+                total = None
+                for _, out in self.model(**batch):
+                    if torch.is_tensor(out.loss):
+                        total = out.loss if total is None else total + out.loss
+                if total is not None:
+                    losses.append(float(total))
+            else:
+                losses.append(float(self.model(**batch).loss))
+        loss = self._mean_over_dp(sum(losses) / max(1, len(losses)))
+        metrics = {"eval_loss": loss, "eval_ppl": math.exp(min(loss, 50.0))}
+        if self.compute_metrics:
+            metrics.update(self.compute_metrics(metrics))
+        self.log(metrics)
+        return metrics
+
+    predict = evaluate
+
+    def _track_best(self, metrics):
+        key = self.args.metric_for_best_model or "eval_loss"
+        if key not in metrics:
+            return
+        v = metrics[key]
+        better = self.state.best_metric is None or (v > self.state.best_metric if self.args.greater_is_better else v < self.state.best_metric)
+        if better:
+            self.state.best_metric = v
+            self.state.best_model_checkpoint = self.save_checkpoint()
+
+    # ------------------------------------------------------------ checkpoints
+    def save_checkpoint(self) -> str:
+        a = self.args
+        out = os.path.join(a.output_dir, f"checkpoint-{self.state.global_step}")
+        os.makedirs(out, exist_ok=True)
+        if hasattr(self.model, "save_pretrained") and self.pc is not None:
+            self.model.save_pretrained(out)
+        elif self._rank() == 0:
+            self.base_model.save_pretrained(out) if hasattr(self.base_model, "save_pretrained") else torch.save(
+                self.base_model.state_dict(), os.path.join(out, "pytorch_model.bin"))
+        rank = self._rank()
+        torch.save(self.optimizer.state_dict(), os.path.join(out, f"optimizer_{rank}.pt" if self.pc is not None else "optimizer.pt"))
+        rng = {"python": random.getstate(), "numpy": np.random.get_state(), "cpu": torch.get_rng_state()}
+        if torch.cuda.is_available():
+            rng["cuda"] = torch.cuda.get_rng_state()
+        torch.save(rng, os.path.join(out, f"rng_state_{rank}.pth"))
+        if rank == 0:
+            torch.save(self.lr_scheduler.state_dict(), os.path.join(out, "scheduler.pt"))
+            with open(os.path.join(out, "trainer_state.json"), "w") as f:
+                f.write(self.state.to_json())
+            torch.save(self.args.__dict__.get("oslo_config_path_or_dict"), os.path.join(out, "training_args.bin"))
+            self._rotate()
+        if dist.is_initialized():
+            dist.barrier()
+        return out
+
+    def _rotate(self):
+        limit = self.args.save_total_limit
+        if not limit:
+            return
+        ckpts = sorted((d for d in os.listdir(self.args.output_dir) if d.startswith("checkpoint-")), key=lambda d: int(d.split("-")[1]))
+        for d in ckpts[:-limit]:
+            full = os.path.join(self.args.output_dir, d)
+            if full != self.state.best_model_checkpoint:
+                shutil.rmtree(full, ignore_errors=True)
+
+    def _load_checkpoint(self, path: str) -> int:
+        """Restores model shards, optimizer, scheduler, RNG and trainer state; returns the steps already done."""
+        rank = self._rank()
+        if self.pc is not None and hasattr(self.model, "from_parallelized"):
+            self.model.from_parallelized(path)
+        else:
+            self.base_model.load_state_dict(torch.load(os.path.join(path, "pytorch_model.bin"), map_location="cpu"))
+        opt_file = os.path.join(path, f"optimizer_{rank}.pt" if self.pc is not None else "optimizer.pt")
+        if os.path.exists(opt_file):
+            self.optimizer.load_state_dict(torch.load(opt_file, map_location="cpu"))
+        sched = os.path.join(path, "scheduler.pt")
+        if os.path.exists(sched):
+            self.lr_scheduler.load_state_dict(torch.load(sched))
+        rng_file = os.path.join(path, f"rng_state_{rank}.pth")
+        if os.path.exists(rng_file):
+            rng = torch.load(rng_file, weights_only=False)
+            random.setstate(rng["python"])
+            np.random.set_state(rng["numpy"])
+            torch.set_rng_state(rng["cpu"])
+            if "cuda" in rng and torch.cuda.is_available():
+                torch.cuda.set_rng_state(rng["cuda"])
+        with open(os.path.join(path, "trainer_state.json")) as f:
+            saved = json.load(f)
+        self.state.global_step = saved["global_step"]
+        self.state.epoch = saved["epoch"]
+        self.state.log_history = saved["log_history"]
+        self.state.best_metric = saved.get("best_metric")
+        return self.state.global_step
+
+
+class _null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False

@@ -1,0 +1,66 @@
+"""``TrainingArguments``: the knobs of :class:`oslo_b200.transformers.Trainer`.
+
+A compact counterpart of the reference's Hugging-Face-style dataclass (oslo/transformers/training_args.py): the fields
+the trainer acts on, plus ``oslo_config_path_or_dict`` whose parsing builds the ``ParallelContext`` and the wrapper
+recipes in ``__post_init__`` exactly once.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Optional, Union
+
+
+@dataclass
+class TrainingArguments:
+    output_dir: str = "output"
+    oslo_config_path_or_dict: Union[str, dict, None] = None
+    do_train: bool = True
+    do_eval: bool = False
+    per_device_train_batch_size: int = 8
+    per_device_eval_batch_size: int = 8
+    gradient_accumulation_steps: int = 1
+    learning_rate: float = 5e-5
+    weight_decay: float = 0.0
+    adam_beta1: float = 0.9
+    adam_beta2: float = 0.999
+    adam_epsilon: float = 1e-8
+    max_grad_norm: float = 1.0
+    num_train_epochs: float = 1.0
+    max_steps: int = -1
+    lr_scheduler_type: str = "linear"
+    warmup_ratio: float = 0.0
+    warmup_steps: int = 0
+    logging_steps: int = 10
+    save_steps: int = 0
+    save_total_limit: Optional[int] = None
+    eval_steps: int = 0
+    seed: int = 42
+    bf16: bool = False
+    fp16: bool = False
+    dataloader_drop_last: bool = True
+    dataloader_num_workers: int = 0
+    optim: str = "adam"  # adam | adamw | lamb | sgd | adagrad | novograd | cpu_adam
+    resume_from_checkpoint: Optional[str] = None
+    metric_for_best_model: Optional[str] = None
+    greater_is_better: bool = False
+    flops_profiler: bool = False
+    flops_profiler_step: int = 1
+    flops_profiler_output_path: Optional[str] = None
+    parallel_context: Any = field(default=None, repr=False)
+    wrapper_recipes: Any = field(default=None, repr=False)
+    oslo_config: Any = field(default=None, repr=False)
+
+    def __post_init__(self):
+        if self.bf16 and self.fp16:
+            raise ValueError("choose one of bf16 / fp16")
+        if self.oslo_config_path_or_dict is not None and self.parallel_context is None:
+            from .oslo_init import OsloTrainerConfig, init_oslo_features
+
+            self.oslo_config = OsloTrainerConfig(self.oslo_config_path_or_dict)
+            self.parallel_context, self.wrapper_recipes = init_oslo_features(self.oslo_config)
+
+    @property
+    def dtype(self):
+        import torch
+
+        return torch.bfloat16 if self.bf16 else (torch.float16 if self.fp16 else torch.float32)
