@@ -113,6 +113,8 @@ def main():
     ap.add_argument("--model", default="neox-1.3b", choices=sorted(CONFIGS))
     ap.add_argument("--no-sequence-parallel", action="store_true")
     ap.add_argument("--no-fused-collectives", action="store_true")
+    ap.add_argument("--profiler-range", action="store_true",
+                    help="bracket the device-timed steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -160,7 +162,7 @@ def main():
             from oslo_b200.distributed import symm
 
             fused = symm.enable(pc, ParallelMode.TENSOR_1D, max_tokens=B * S,
-                                max_features=max(mcfg.hidden_size, mcfg.intermediate_size // world * 1))
+                                max_features=max(mcfg.hidden_size, mcfg.intermediate_size // world * 1), model=model)
         except Exception as e:  # the NCCL composition still runs
             if rank == 0:
                 print(f"[bench] fused collectives unavailable: {e}", file=sys.stderr)
@@ -207,7 +209,11 @@ def main():
     sampler = ClockSampler(torch.cuda.current_device())
     sampler.start()
     calls0 = _lib.native_calls
+    if args.profiler_range:
+        torch.cuda.profiler.start()
     ms, _, loss_val = timed(args.steps, e2e=False)
+    if args.profiler_range:
+        torch.cuda.profiler.stop()
     calls = _lib.native_calls - calls0
     ms_e2e, wall_e2e, loss_e2e = timed(args.steps, e2e=True)
     clocks = sampler.stop()

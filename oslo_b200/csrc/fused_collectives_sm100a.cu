@@ -7,9 +7,11 @@
 //   * all-gather: a few CTAs stream the peers' shards over NVLink into local memory with plain 16-byte loads
 //     while the remaining CTAs multiply, starting with the local shard and taking each remote shard as soon
 //     as its "copied" flag is up; TMA only ever reads local memory.
-//   * reduce-scatter: tiles are computed in destination order (next rank first, own rows last) into a local
-//     partial-result buffer; finishing a chunk of rows raises a flag on the rank that owns those rows, where a few
-//     reducer CTAs pull the tp partial copies of the chunk (bulk loads over NVLink), sum them in fp32 and store.
+//   * reduce-scatter: tiles are computed in destination order (next rank first, own rows last).  The epilogue of a
+//     tile of another rank's rows TMA-stores the partial tile straight into slot [this rank] of the OWNER's slot
+//     buffer (a plain bulk tensor store to peer memory) and flags each finished chunk of rows there; the epilogue of
+//     a tile of our own rows adds the other ranks' partial rows (already in our slot buffer) to the accumulator and
+//     stores the final result, so no separate reduction pass exists.
 // All waits on peers are bounded (~2 s) and report through the status word instead of hanging.
 //
 // Replaces ColLinear1D / RowLinear1D = F.linear + a separate NCCL all-reduce in the reference
@@ -28,8 +30,8 @@ static int pick_block_n(int M, int N, int ctas, int max_bn) {
 }
 
 #define OSLO_FUSED_LAUNCH(BN, MODE)                                                                       \
-  (b_mn ? launch<BN, false, true, MODE>(ta, tb, tc, taux, p, grid, stream, fp)                            \
-        : launch<BN, false, false, MODE>(ta, tb, tc, taux, p, grid, stream, fp))
+  (b_mn ? launch<BN, false, true, MODE>(ta, tb, tc, taux, p, grid, stream, fp, peer_maps_ptr)             \
+        : launch<BN, false, false, MODE>(ta, tb, tc, taux, p, grid, stream, fp, peer_maps_ptr))
 
 // peer_in / peer_ag_ready: host arrays of `tp` device pointers (entry [rank] is the local buffer).
 extern "C" int oslo_ag_gemm(void* const* peer_in, void* x_full, const void* B, void* C, const void* bias, int T, int N, int K,
@@ -79,6 +81,7 @@ extern "C" int oslo_ag_gemm(void* const* peer_in, void* x_full, const void* B, v
   const int gemm_ctas = (int)(total < gemm_ctas_max ? total : gemm_ctas_max);
   const int grid = copy_ctas + gemm_ctas;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  const PeerMaps* peer_maps_ptr = nullptr;
   switch (block_n) {
     case 256: return OSLO_FUSED_LAUNCH(256, kModeAllGather);
     case 128: return OSLO_FUSED_LAUNCH(128, kModeAllGather);
@@ -86,26 +89,25 @@ extern "C" int oslo_ag_gemm(void* const* peer_in, void* x_full, const void* B, v
   }
 }
 
-// peer_partial / peer_rs_flag: host arrays of `tp` device pointers ([T, N] partial-result buffers and flag arrays of
+// peer_partial / peer_rs_flag: host arrays of `tp` device pointers (slot buffers [tp, T/tp, N] and flag arrays of
 // tp * chunks_per_shard ints).  A: [T, K] K-major (lda), out: [T/tp, N].
 extern "C" int oslo_gemm_rs(const void* A, long long lda, const void* B, long long ldb, int b_mn, void* out, const void* bias,
                             int T, int N, int K, int is_bf16, int tp, int rank, int epoch, void* const* peer_partial,
                             void* const* peer_rs_flag, int* tile_done, int reduce_ctas, int num_sms, int* status,
-                            void* stream_ptr) {
+                            void* stream_ptr, unsigned long long* debug_times) {
   if (tp > kMaxRanks || tp < 1 || T % tp) return -1;
   const int Tl = T / tp;
   if (Tl % kBlockM || N % 8 || K % 8 || lda % 8 || ldb % 8) return -5;
   bind_context_to_thread();
-  if (reduce_ctas < 1) reduce_ctas = 1;
-  if (reduce_ctas > num_sms / 2) reduce_ctas = num_sms / 2;
-  const int gemm_ctas_max = num_sms - reduce_ctas;
+  reduce_ctas = 0;  // the reduction is folded into the epilogue of the tiles of our own rows
+  const int gemm_ctas_max = num_sms;
   const int block_n = pick_block_n(T, N, gemm_ctas_max, 256);
   GemmParams p{};
   p.M = T; p.N = N; p.K = K; p.batch = 1; p.batch_inner = 1; p.causal = 0;
   p.m_blocks = T / kBlockM;
   p.n_blocks = (N + block_n - 1) / block_n;
-  p.epilogue = 0; p.accumulate = 0; p.is_bf16 = is_bf16;
-  p.bias = nullptr; p.c_ptr = peer_partial[rank]; p.ldc = N; p.stride_c = 0; p.stride_c_outer = 0; p.aux_ptr = nullptr;
+  p.epilogue = bias ? 1 : 0; p.accumulate = 0; p.is_bf16 = is_bf16;
+  p.bias = bias; p.c_ptr = out; p.ldc = N; p.stride_c = 0; p.stride_c_outer = 0; p.aux_ptr = nullptr;
   p.status = status;
   FusedParams fp;
   fp.tp = tp; fp.rank = rank; fp.shard_rows = Tl; fp.epoch = epoch; fp.copy_ctas = reduce_ctas;
@@ -121,14 +123,21 @@ extern "C" int oslo_gemm_rs(const void* A, long long lda, const void* B, long lo
     fp.peer_rs_flag[i] = static_cast<int*>(peer_rs_flag[i]);
   }
   fp.rs_flag = static_cast<int*>(peer_rs_flag[rank]);
-  fp.tile_done = tile_done; fp.rs_out = out; fp.rs_bias = bias; fp.status = status;
+  fp.tile_done = tile_done; fp.rs_out = out; fp.rs_bias = bias; fp.status = status; fp.debug_times = debug_times;
   CUtensorMap ta, tb, tc, taux;
   int rc = make_map(&ta, A, is_bf16, K, T, 1, 1, lda, 0, 0, kBlockK, kBlockM);
   if (rc) return rc;
   if (b_mn) rc = make_map(&tb, B, is_bf16, N, K, 1, 1, ldb, 0, 0, 64, kBlockK);
   else      rc = make_map(&tb, B, is_bf16, K, N, 1, 1, ldb, 0, 0, kBlockK, block_n);
   if (rc) return rc;
-  rc = make_map(&tc, peer_partial[rank], is_bf16, N, T, 1, 1, N, 0, 0, 64, 32);  // partial results stay local
+  // one store map per destination: rank d's slot buffer viewed [tp * Tl, N]; our rows go to slot [rank]
+  PeerMaps maps;
+  for (int d = 0; d < kMaxRanks; ++d) {
+    rc = make_map(&maps.m[d], peer_partial[d < tp ? d : rank], is_bf16, N, T, 1, 1, N, 0, 0, 64, 32);
+    if (rc) return rc;
+  }
+  const PeerMaps* peer_maps_ptr = &maps;
+  rc = make_map(&tc, out, is_bf16, N, Tl, 1, 1, N, 0, 0, 64, 32);  // final rows of this rank
   if (rc) return rc;
   taux = tc;
   const long long total = (long long)p.m_blocks * p.n_blocks;

@@ -84,7 +84,7 @@ OSLO_DEVINL void tile_coords(int tile, const GemmParams& p, int& b, int& mb, int
 // the epoch (a per-group call counter) of the last completed hand-off, so they never need clearing.
 constexpr int kModePlain = 0;
 constexpr int kModeAllGather = 1;      // A rows are gathered from all ranks while the GEMM runs
-constexpr int kModeReduceScatter = 2;  // C row blocks are pulled by their owner, which sums the tp partial results
+constexpr int kModeReduceScatter = 2;  // partial row blocks are TMA-stored to their owner; the owner's own tiles add them in
 constexpr int kMaxRanks = 8;
 
 struct FusedParams {
@@ -104,13 +104,19 @@ struct FusedParams {
   int* chunk_flag = nullptr;            // local [tp * chunks_per_shard]: that chunk of x_full is complete
   int* chunk_arrive = nullptr;          // local, same size: copy-CTA arrival counters
   // reduce-scatter
-  void* peer_slots[kMaxRanks] = {};     // every rank's partial-result buffer [tp * shard_rows, N]
+  void* peer_slots[kMaxRanks] = {};     // every rank's slot buffer [tp, shard_rows, N] (slot s = rows from rank s)
   int* rs_flag = nullptr;               // local [tp * chunks_per_shard]: source p finished that chunk of our rows
   int* peer_rs_flag[kMaxRanks] = {};
   int* tile_done = nullptr;             // local [tp * chunks_per_shard]: per-chunk arrival counters
   void* rs_out = nullptr;               // local [shard_rows, N]
   const void* rs_bias = nullptr;        // optional [N]
   int* status = nullptr;
+  unsigned long long* debug_times = nullptr;  // optional [8]: globaltimer stamps for tuning (null in normal use)
+};
+
+// Tensor maps over every rank's slot buffer (reduce-scatter mode: the epilogue TMA-stores straight into the owner).
+struct PeerMaps {
+  CUtensorMap m[kMaxRanks];
 };
 
 OSLO_DEVINL int ld_acquire_sys(const int* p) {
@@ -255,126 +261,6 @@ static __device__ __noinline__ void ag_copy_role(const GemmParams& p, const Fuse
   tma_store_wait_all();
 }
 
-constexpr int kReduceRing = 196608;  // bytes of shared memory used as the reducers' landing ring
-constexpr int kReduceMaxSets = 12;
-
-// RS reducer role (whole CTA): this rank's rows [rank * shard_rows, +shard_rows) of the tp partial results are one
-// contiguous block of shard_rows * N elements in every rank's partial buffer.  It is cut into pieces (32 KiB, or
-// 16 KiB for groups of more than 4); for each piece the CTA pulls the tp - 1 REMOTE copies with bulk loads over NVLink
-// into a shared-memory ring — as soon as the producing ranks have flagged that row chunk complete — keeping as many
-// piece-sets in flight as the ring holds, adds the local copy read straight from memory, sums in fp32 and stores.
-static __device__ __noinline__ void rs_reduce_role(const GemmParams& p, const FusedParams& fp, uint8_t* ring, uint64_t* bars) {
-  __shared__ int s_abort;
-  __shared__ int s_ok;
-  const int tid = threadIdx.x;
-  const int tp = fp.tp, remote = tp - 1;
-  const int piece = remote > 3 ? 16384 : 32768;
-  int depth = kReduceRing / (piece * remote);  // piece-sets in flight
-  if (depth > kReduceMaxSets) depth = kReduceMaxSets;
-  if (tid == 0) {
-    s_abort = 0;
-    s_ok = 1;
-    for (int i = 0; i < depth; ++i) mbar_init(&bars[i], 1);
-    fence_barrier_init();
-  }
-  __syncthreads();
-  const long long block_bytes = static_cast<long long>(fp.shard_rows) * p.N * 2;
-  const long long pieces = (block_bytes + piece - 1) / piece;
-  const long long my_count = (pieces - blockIdx.x + fp.copy_ctas - 1) / fp.copy_ctas;
-  const long long row_bytes = static_cast<long long>(p.N) * 2;
-  const int cps = fp.shard_rows / fp.chunk_rows;
-  const long long base_off = static_cast<long long>(fp.rank) * block_bytes;
-  const uint8_t* local_src = static_cast<const uint8_t*>(fp.peer_slots[fp.rank]) + base_off;
-  auto piece_of = [&](long long j, long long& off, uint32_t& bytes) {
-    off = (blockIdx.x + j * fp.copy_ctas) * static_cast<long long>(piece);
-    bytes = static_cast<uint32_t>(block_bytes - off < piece ? block_bytes - off : piece);
-  };
-  int ready_upto = -1;  // chunks [0, ready_upto] of our rows are known complete on every source (thread 0 only)
-  auto issue = [&](long long j) {  // thread 0 only
-    long long off; uint32_t bytes;
-    piece_of(j, off, bytes);
-    const int c1 = static_cast<int>((off + bytes - 1) / row_bytes) / fp.chunk_rows;
-    if (c1 > ready_upto) {
-      for (int c = ready_upto + 1; c <= c1; ++c)
-        for (int src = 0; src < tp; ++src)
-          if (!flag_wait_bounded(fp.rs_flag + src * cps + c, fp.epoch, &s_abort, true)) return false;
-      ready_upto = c1;
-      fence_proxy_async_global();
-    }
-    const int set = static_cast<int>(j % depth);
-    mbar_arrive_expect_tx(&bars[set], bytes * remote);
-    int slot = 0;
-    for (int src = 0; src < tp; ++src) {
-      if (src == fp.rank) continue;
-      bulk_load(ring + (static_cast<long long>(set) * remote + slot) * piece,
-                static_cast<const uint8_t*>(fp.peer_slots[src]) + base_off + off, bytes, &bars[set]);
-      ++slot;
-    }
-    return true;
-  };
-  if (tid == 0) {
-    for (long long j = 0; j < depth && j < my_count; ++j)
-      if (!issue(j)) { s_ok = 0; break; }
-  }
-  __syncthreads();
-  for (long long j = 0; j < my_count; ++j) {
-    if (!s_ok) break;
-    long long off; uint32_t bytes;
-    piece_of(j, off, bytes);
-    const int set = static_cast<int>(j % depth);
-    if (!mbar_wait_bounded(&bars[set], static_cast<uint32_t>((j / depth) & 1), &s_abort)) break;
-    const uint4* slots = reinterpret_cast<const uint4*>(ring + static_cast<long long>(set) * remote * piece);
-    const uint4* mine = reinterpret_cast<const uint4*>(local_src + off);
-    uint4* out = reinterpret_cast<uint4*>(static_cast<uint8_t*>(fp.rs_out) + off);
-    const int nvec = bytes / 16, slot_vecs = piece / 16;
-    for (int v = tid; v < nvec; v += blockDim.x) {
-      float acc[8];
-      {
-        const uint4 raw = mine[v];
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          if (p.is_bf16) { acc[2 * e] = __uint_as_float(w[e] << 16); acc[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u); }
-          else { const __half2 h = *reinterpret_cast<const __half2*>(&w[e]); acc[2 * e] = __low2float(h); acc[2 * e + 1] = __high2float(h); }
-        }
-      }
-      if (fp.rs_bias) {
-        const long long col = ((off / 2) + static_cast<long long>(v) * 8) % p.N;
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(fp.rs_bias) + col));
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          if (p.is_bf16) { acc[2 * e] += __uint_as_float(w[e] << 16); acc[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u); }
-          else { const __half2 h = *reinterpret_cast<const __half2*>(&w[e]); acc[2 * e] += __low2float(h); acc[2 * e + 1] += __high2float(h); }
-        }
-      }
-      for (int src = 0; src < remote; ++src) {
-        const uint4 raw = slots[src * slot_vecs + v];
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          if (p.is_bf16) { acc[2 * e] += __uint_as_float(w[e] << 16); acc[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u); }
-          else { const __half2 h = *reinterpret_cast<const __half2*>(&w[e]); acc[2 * e] += __low2float(h); acc[2 * e + 1] += __high2float(h); }
-        }
-      }
-      uint32_t o[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        if (p.is_bf16) { const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]); o[e] = *reinterpret_cast<const uint32_t*>(&h); }
-        else { const __half2 h = __floats2half2_rn(acc[2 * e], acc[2 * e + 1]); o[e] = *reinterpret_cast<const uint32_t*>(&h); }
-      }
-      out[v] = make_uint4(o[0], o[1], o[2], o[3]);
-    }
-    __syncthreads();  // every thread is done with this set's slots
-    if (tid == 0 && j + depth < my_count) {
-      fence_proxy_async_smem();
-      if (!issue(j + depth)) s_ok = 0;
-    }
-    __syncthreads();
-  }
-  if (tid == 0 && (!s_ok || s_abort) && fp.status) atomicCAS(fp.status, kStatusOk, kStatusPeerFlagTimeout);
-}
-
 // k-block range [kb0, kb1) a tile has to reduce over, or skip = true when it has no work.
 OSLO_DEVINL void tile_k_range(const GemmParams& p, int m0, int n0, int num_kb, int& kb0, int& kb1, bool& skip) {
   kb0 = 0;
@@ -389,22 +275,13 @@ template <int BLOCK_N, bool A_MN, bool B_MN, int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux,
-                    const GemmParams p, const FusedParams fp) {
+                    const GemmParams p, const FusedParams fp, const __grid_constant__ PeerMaps peer_maps) {
   if constexpr (MODE == kModeAllGather) {
     // the first fp.copy_ctas CTAs stream the peers' shards into local memory; the rest run the GEMM
     if (static_cast<int>(blockIdx.x) < fp.copy_ctas) {
       extern __shared__ uint8_t copy_smem_raw[];
       uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(copy_smem_raw) + 1023) & ~uintptr_t(1023));
       ag_copy_role(p, fp, ring, reinterpret_cast<uint64_t*>(ring + kCopyDepth * kCopyPiece));
-      return;
-    }
-  }
-  if constexpr (MODE == kModeReduceScatter) {
-    // the first fp.copy_ctas CTAs pull and sum this rank's rows of every rank's partial result
-    if (static_cast<int>(blockIdx.x) < fp.copy_ctas) {
-      extern __shared__ uint8_t red_smem_raw[];
-      uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(red_smem_raw) + 1023) & ~uintptr_t(1023));
-      rs_reduce_role(p, fp, ring, reinterpret_cast<uint64_t*>(ring + kReduceRing));
       return;
     }
   }
@@ -584,6 +461,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     int rs_pending = 0;
     (void)rs_pending;
     bool ok = true;
+    if (MODE != kModePlain && fp.debug_times && cta == 0 && warp == 2 && lane == 0) fp.debug_times[4] = global_timer_ns();
     for (int tile = cta; tile < num_tiles && ok; tile += num_ctas) {
       int b, mb, nb;
       if constexpr (MODE == kModePlain) tile_coords(tile, p, b, mb, nb);
@@ -599,6 +477,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BLOCK_N;
+      bool rs_own = false;
+      if constexpr (MODE == kModeReduceScatter) {
+        // tiles of OUR rows finish the reduction themselves: the other ranks' partial rows must have landed in our
+        // slot buffer (they compute our rows first, so this normally does not wait)
+        rs_own = (m0 / fp.shard_rows) == fp.rank;
+        if (rs_own) {
+          const int cps = fp.shard_rows / fp.chunk_rows;
+          const int c = (m0 - fp.rank * fp.shard_rows) / fp.chunk_rows;
+          bool got = true;
+          if (lane < fp.tp && lane != fp.rank) got = flag_wait_bounded(fp.rs_flag + lane * cps + c, fp.epoch, abort_flag, true);
+          got = __all_sync(0xffffffffu, got);
+          if (!got) {
+            ok = false;
+            if (p.status && lane == 0) atomicCAS(p.status, kStatusOk, kStatusPeerFlagTimeout);
+          }
+        }
+      }
 #pragma unroll 1
       for (int chunk = 0; chunk < BLOCK_N / 64; ++chunk) {
         uint32_t r0[32], r1[32];
@@ -620,7 +515,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           v[i] = __uint_as_float(r0[i]);
           v[32 + i] = __uint_as_float(r1[i]);
         }
-        if (p.bias != nullptr) {
+        if (p.bias != nullptr && (MODE != kModeReduceScatter || rs_own)) {  // RS: the bias is added once, by the owner
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             if (col0 + g * 8 < p.N) {
@@ -668,6 +563,37 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
           }
         }
+        if constexpr (MODE == kModeReduceScatter) {
+          if (rs_own && ok) {
+            const long long r_local = static_cast<long long>(m0 - fp.rank * fp.shard_rows + q * 32 + lane);
+            for (int src = 0; src < fp.tp; ++src) {
+              if (src == fp.rank) continue;
+              const uint16_t* sp = static_cast<const uint16_t*>(fp.peer_slots[fp.rank]) +
+                                   (static_cast<long long>(src) * fp.shard_rows + r_local) * p.N + col0;
+#pragma unroll
+              for (int g = 0; g < 8; ++g) {
+                if (col0 + g * 8 < p.N) {
+                  const uint4 raw = *reinterpret_cast<const uint4*>(sp + g * 8);
+                  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    float lo, hi;
+                    if (p.is_bf16) {
+                      lo = __uint_as_float(w[j] << 16);
+                      hi = __uint_as_float(w[j] & 0xffff0000u);
+                    } else {
+                      const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+                      lo = __low2float(h);
+                      hi = __high2float(h);
+                    }
+                    v[g * 8 + 2 * j] += lo;
+                    v[g * 8 + 2 * j + 1] += hi;
+                  }
+                }
+              }
+            }
+          }
+        }
         const bool want_aux = (p.aux_ptr != nullptr);
         // up to two stores per chunk: optional pre-activation (aux) then the final value
         for (int pass = want_aux ? 0 : 1; pass < 2; ++pass) {
@@ -699,17 +625,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_4d(pass == 0 ? &tmAux : &tmC, sbuf_ptr, col0, m0 + q * 32, bi, bo);
+            if constexpr (MODE == kModeReduceScatter) {
+              // slot [this rank] of the rank that owns these rows (a peer-mapped buffer; plain bulk store, no multicast)
+              const int dest = m0 / fp.shard_rows;
+              if (rs_own) tma_store_4d(&tmC, sbuf_ptr, col0, m0 - fp.rank * fp.shard_rows + q * 32, 0, 0);  // final rows
+              else tma_store_4d(&peer_maps.m[dest], sbuf_ptr, col0, fp.rank * fp.shard_rows + (m0 - dest * fp.shard_rows) + q * 32, 0, 0);
+            } else {
+              tma_store_4d(pass == 0 ? &tmAux : &tmC, sbuf_ptr, col0, m0 + q * 32, bi, bo);
+            }
             tma_store_commit();
           }
           sbuf ^= 1;
         }
       }
       if constexpr (MODE == kModeReduceScatter) {
-        // The partial tile went to the LOCAL partial-result buffer.  Count this warp's finished quarter-tiles per
-        // row chunk and publish the count when the warp moves on to another chunk (or runs out of tiles): wait for
-        // its TMA stores to be complete, then one atomic; the warp that completes a chunk raises the flag on the
-        // rank that owns those rows, whose reducer CTAs then pull the chunk over NVLink.
+        // The partial tile went into the owner's slot buffer.  Count this warp's finished quarter-tiles per row chunk
+        // and publish the count when the warp moves on to another chunk (or runs out of tiles): wait for its TMA
+        // stores to be complete, then one atomic; the warp that completes a chunk raises the flag on the owner,
+        // whose reducer CTAs then sum the tp slots of that chunk out of their local memory.
         const int chunk = m0 / fp.chunk_rows;
         const int next_tile = tile + num_ctas;
         int next_chunk = -1;
@@ -718,8 +651,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           fused_tile_coords<MODE>(next_tile, p, fp, b2, mb2, nb2);
           next_chunk = mb2 * kBlockM / fp.chunk_rows;
         }
-        ++rs_pending;
-        if (next_chunk != chunk) {
+        if (!rs_own) ++rs_pending;
+        if (next_chunk != chunk && rs_pending > 0) {
           if (lane == 0) {
             tma_store_wait_all();
             fence_proxy_async_global();
@@ -742,6 +675,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (buf == 0) acc_phase ^= 1;
     }
     if (lane == 0) tma_store_wait_all();
+    if (MODE != kModePlain && fp.debug_times && cta == 0 && warp == 2 && lane == 0) fp.debug_times[5] = global_timer_ns();
   }
 
   tc_fence_before();
@@ -807,7 +741,8 @@ static inline int make_map(CUtensorMap* map, const void* base, int is_bf16, long
 
 template <int BLOCK_N, bool A_MN, bool B_MN, int MODE = kModePlain>
 static int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const CUtensorMap& aux,
-                  const GemmParams& p, int grid, cudaStream_t stream, const FusedParams& fp = FusedParams()) {
+                  const GemmParams& p, int grid, cudaStream_t stream, const FusedParams& fp = FusedParams(),
+                  const PeerMaps* peer_maps = nullptr) {
   using Cfg = GemmCfg<BLOCK_N>;
   auto kern = gemm_tcgen05_kernel<BLOCK_N, A_MN, B_MN, MODE>;
   static bool configured = false;
@@ -816,7 +751,10 @@ static int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap&
     if (e != cudaSuccess) return -3;
     configured = true;
   }
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(a, b, c, aux, p, fp);
+  PeerMaps pm;
+  if (peer_maps) pm = *peer_maps;
+  else for (int i = 0; i < kMaxRanks; ++i) pm.m[i] = c;
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(a, b, c, aux, p, fp, pm);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -9,7 +9,7 @@ Workspace layout per rank (all offsets identical on every rank)::
     [ flags 4 KiB | in[0] | in[1] | slots[0] | slots[1] ]
 
 * ``in[p]``     this rank's shard of the all-gather input for calls with parity ``p`` (``Tl x F`` elements);
-* ``slots[p]``  this rank's partial result ``[T, F]`` of a reduce-scatter; rank ``r`` pulls rows ``[r*Tl, (r+1)*Tl)`` of it;
+* ``slots[p]``  ``tp`` blocks of ``Tl x F``: block ``s`` receives rank ``s``'s partial rows of a reduce-scatter;
 * flags        ``ag_ready[tp]``, ``rs_flag[tp]``, ``barrier[tp]`` written by peers, holding call epochs.
 
 Double buffering by call parity is what makes the scheme free of write-after-read races without a trailing
@@ -35,8 +35,118 @@ class _RawCudaBuffer:
         self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
 
 
+class SymmetricBuffer:
+    """``nbytes`` of device memory on every rank of a group, each rank's block mapped into all the others.
+
+    ``local`` is a ``uint8`` tensor over this rank's block; ``peer_ptrs[r]`` the address of rank ``r``'s block in this
+    process.  The first 1 KiB holds flags used by :meth:`barrier` (a bounded device-side barrier on the current
+    stream); ``payload_offset`` is where user data starts.
+    """
+
+    payload_offset = 1024
+
+    def __init__(self, pc, mode, nbytes: int):
+        self.pc, self.mode = pc, mode
+        self.world = pc.get_world_size(mode)
+        self.rank = pc.get_local_rank(mode)
+        if self.world > 8:
+            raise ValueError("symmetric buffers support groups of up to 8 ranks")
+        self.device = pc.device
+        self.nbytes = (nbytes + self.payload_offset + 1023) // 1024 * 1024
+        lib = _lib.cuda_lib()
+        base = ctypes.c_void_p()
+        rc = lib.oslo_symm_alloc(ctypes.c_ulonglong(self.nbytes), ctypes.byref(base))
+        if rc:
+            raise RuntimeError(f"symmetric allocation of {self.nbytes} bytes failed (cuda error {-rc})")
+        self.base = base.value
+        hbytes = lib.oslo_ipc_handle_bytes()
+        handle = (ctypes.c_ubyte * hbytes)()
+        rc = lib.oslo_ipc_get_handle(ctypes.c_void_p(self.base), handle)
+        if rc:
+            raise RuntimeError(f"cudaIpcGetMemHandle failed (cuda error {-rc})")
+        gathered: List[Optional[bytes]] = [None] * self.world
+        dist.all_gather_object(gathered, bytes(handle), group=pc.get_cpu_group(mode))
+        self.peer_ptrs: List[int] = []
+        for r, h in enumerate(gathered):
+            if r == self.rank:
+                self.peer_ptrs.append(self.base)
+                continue
+            buf = (ctypes.c_ubyte * hbytes).from_buffer_copy(h)
+            out = ctypes.c_void_p()
+            rc = lib.oslo_ipc_open_handle(buf, ctypes.byref(out))
+            if rc:
+                raise RuntimeError(f"cudaIpcOpenMemHandle for peer {r} failed (cuda error {-rc})")
+            self.peer_ptrs.append(out.value)
+        self.local = torch.as_tensor(_RawCudaBuffer(self.base, self.nbytes), device=self.device)
+        self.epoch = 0
+        dist.barrier(group=pc.get_cpu_group(mode))
+
+    def payload(self, offset: int, nbytes: int, dtype, shape=None) -> torch.Tensor:
+        t = self.local[self.payload_offset + offset : self.payload_offset + offset + nbytes].view(dtype)
+        return t.view(shape) if shape is not None else t
+
+    def peer_array(self, offset: int = 0):
+        """ctypes array of every rank's address of ``payload + offset``."""
+        return (ctypes.c_void_p * self.world)(*[b + self.payload_offset + offset for b in self.peer_ptrs])
+
+    def barrier(self):
+        self.epoch += 1
+        flags = (ctypes.c_void_p * self.world)(*self.peer_ptrs)
+        rc = _lib.cuda_lib().oslo_symm_barrier(flags, ctypes.c_void_p(self.base), ctypes.c_int(self.rank), ctypes.c_int(self.world),
+                                               ctypes.c_int(self.epoch), _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr())
+        if rc:
+            raise RuntimeError(f"oslo_symm_barrier failed ({rc})")
+
+
+_group_buffers = {}
+
+
+def group_buffer(pc, mode, key: str, nbytes: int) -> "SymmetricBuffer":
+    """A cached :class:`SymmetricBuffer` per (context, mode, key); grown (re-created) when a larger size is asked for.
+    Collective over the group."""
+    k = (id(pc), mode, key)
+    buf = _group_buffers.get(k)
+    if buf is None or buf.nbytes < nbytes + SymmetricBuffer.payload_offset:
+        buf = _group_buffers[k] = SymmetricBuffer(pc, mode, nbytes)
+    return buf
+
+
+def rehome_parameter(pc, mode, param: torch.nn.Parameter) -> "SymmetricBuffer":
+    """Move a parameter's storage into symmetric memory (its shard becomes readable by every rank of the group).
+    The Parameter object is kept, so tied weights stay tied.  Collective over the group."""
+    nbytes = param.numel() * param.element_size()
+    buf = SymmetricBuffer(pc, mode, nbytes)
+    view = buf.payload(0, nbytes, param.dtype, tuple(param.shape))
+    view.copy_(param.data)
+    param.data = view
+    param.oslo_symm = buf
+    return buf
+
+
+def rehome_vocab_embeddings(model, pc, mode) -> int:
+    """Put every ``VocabParallelEmbedding1D`` table of ``model`` into symmetric memory so its lookups read the owning
+    rank directly; returns how many were moved."""
+    from oslo_b200.nn.embedding import VocabParallelEmbedding1D
+
+    n = 0
+    for m in model.modules():
+        if isinstance(m, VocabParallelEmbedding1D) and m.weight.is_cuda and not hasattr(m.weight, "oslo_symm"):
+            if (m.weight.shape[1] * m.weight.element_size()) % 16 == 0:
+                rehome_parameter(pc, mode, m.weight)
+                n += 1
+    return n
+
+
+_fused_small_ops = False
+
+
+def small_ops_enabled() -> bool:
+    """True once :func:`enable` ran: the loss / embedding / optimizer paths may use peer memory too."""
+    return _fused_small_ops
+
+
 class SymmetricWorkspace:
-    def __init__(self, pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 16):
+    def __init__(self, pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 24):
         self.pc, self.mode = pc, mode
         self.tp = pc.get_world_size(mode)
         self.rank = pc.get_local_rank(mode)
@@ -78,6 +188,7 @@ class SymmetricWorkspace:
         # local scratch counters (not shared): chunk_flag[64], chunk_arrive[64], tile_done[64]
         self.local = torch.zeros(256, dtype=torch.int32, device=self.device)
         self.epoch = 0
+        self.debug_times = None  # set to a uint64[8] device tensor to collect in-kernel time stamps
         self._local_bytes = torch.as_tensor(_RawCudaBuffer(self.base, self.total), device=self.device)
         dist.barrier(group=pc.get_cpu_group(mode))
         self.barrier()
@@ -181,7 +292,7 @@ class SymmetricWorkspace:
             ctypes.c_int(1 if self.dtype == torch.bfloat16 else 0), ctypes.c_int(self.tp), ctypes.c_int(self.rank),
             ctypes.c_int(self.epoch), self._slot_ptrs(parity), self._flag_ptrs(1), self._local_ptr(2),
             ctypes.c_int(self.copy_ctas), ctypes.c_int(_lib.num_sms()), _lib.ptr(_lib.status_word(self.device)),
-            _lib.stream_ptr())
+            _lib.stream_ptr(), _lib.ptr(self.debug_times))
         if rc:
             raise RuntimeError(f"oslo_gemm_rs failed ({rc})")
         return out
@@ -210,14 +321,21 @@ class _Runtime:
         return self.ws.gemm_rs(x, weight)
 
 
-def enable(pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 16) -> bool:
-    """Create the group's symmetric workspace and switch the sequence-parallel linears to the fused kernels."""
+def enable(pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 24, model=None) -> bool:
+    """Create the group's symmetric workspace and switch the sequence-parallel linears to the fused kernels.
+    With ``model`` given, its vocab-parallel embedding tables are moved to symmetric memory as well."""
     if not (torch.cuda.is_available() and pc.use_cuda) or pc.get_world_size(mode) == 1:
         return False
+    if model is not None:
+        rehome_vocab_embeddings(model, pc, mode)
+    global _fused_small_ops
     ws = SymmetricWorkspace(pc, mode, max_tokens, max_features, dtype, copy_ctas)
     fused_collectives.set_runtime(_Runtime(ws))
+    _fused_small_ops = True
     return True
 
 
 def disable():
+    global _fused_small_ops
     fused_collectives.set_runtime(None)
+    _fused_small_ops = False

@@ -47,3 +47,4 @@ from .loss import (
     VocabParallelCrossEntropyLoss2D,
     VocabParallelCrossEntropyLoss2p5D,
 )
+from .ngram_repeat_block import FusedNoRepeatNGramLogitsProcessor, NGramRepeatBlock, fused_no_repeat_ngram_logits_processor

@@ -71,6 +71,16 @@ class VocabParallelEmbedding1D(nn.Embedding):
 
         if self.world_size == 1:
             return F.embedding(input, self.weight)
+        sbuf = getattr(self.weight, "oslo_symm", None)
+        if sbuf is not None and self.sequence_parallel and input.is_cuda:
+            # the table is readable by every rank: look up this rank's token shard straight from the owners
+            from oslo_b200.distributed import comm
+            from oslo_b200.ops.embedding import embedding_pull
+
+            st = getattr(self, "sequence_parallel_state", None)
+            d = st.dim if st is not None else 0
+            ids = comm.scatter(input, dim=d, parallel_context=self.parallel_context, parallel_mode=ParallelMode.TENSOR_1D)
+            return embedding_pull(ids, self.weight, sbuf, self.parallel_context, ParallelMode.TENSOR_1D)
         out = _masked_lookup(input, self.weight, self.vocab_start_index, self.vocab_end_index)
         if self.sequence_parallel:
             st = getattr(self, "sequence_parallel_state", None)

@@ -105,7 +105,20 @@ class _VPCECudaFn(torch.autograd.Function):
                                ctypes.c_int(_DT[x.dtype]), ctypes.c_int(nsm), _lib.stream_ptr())
         if rc:
             raise RuntimeError(f"oslo_ce_stats failed ({rc})")
-        if world > 1:
+        from oslo_b200.distributed import symm
+
+        if world > 1 and symm.small_ops_enabled() and world <= 8:
+            # ONE exchange without a collective call: the triples are written to symmetric memory, a device-side
+            # barrier orders them, and the second kernel reads every peer's triples straight over NVLink
+            nbytes = rows * 3 * 4
+            buf = symm.group_buffer(pc, mode, "ce_stats", 2 * nbytes)
+            parity = (buf.epoch + 1) & 1
+            buf.payload(parity * nbytes, nbytes, torch.float32, (rows, 3)).copy_(stats)
+            buf.barrier()
+            base = buf.payload_offset + parity * nbytes
+            ptrs = [b + base for b in buf.peer_ptrs]
+            gathered = stats
+        elif world > 1:
             gathered = torch.empty(world, rows, 3, dtype=torch.float32, device=x.device)
             dist.all_gather_into_tensor(gathered.view(-1), stats.view(-1), group=group)
             ptrs = [gathered[r].data_ptr() for r in range(world)]

@@ -25,7 +25,17 @@ class Slot:
 class FlatBuffer:
     """One contiguous buffer holding the given parameters (same dtype/device), padded to ``pad_to`` elements."""
 
-    def __init__(self, params: Sequence[torch.nn.Parameter], pad_to: int = 1, with_grads: bool = True, flatten_params: bool = True):
+    @staticmethod
+    def layout_numel(params: Sequence[torch.nn.Parameter], pad_to: int = 1) -> int:
+        """Elements the flat buffer will have for these parameters (to size externally provided storage)."""
+        off = 0
+        for p in params:
+            off += (p.numel() + ALIGN - 1) // ALIGN * ALIGN
+        total = (off + pad_to - 1) // pad_to * pad_to if pad_to > 1 else off
+        return max(total, pad_to)
+
+    def __init__(self, params: Sequence[torch.nn.Parameter], pad_to: int = 1, with_grads: bool = True, flatten_params: bool = True,
+                 param_storage: torch.Tensor = None, grad_storage: torch.Tensor = None):
         self.dtype = params[0].dtype
         self.device = params[0].device
         self.slots: List[Slot] = []
@@ -37,12 +47,17 @@ class FlatBuffer:
         self.numel = max(total, pad_to)
         self.param = None
         if flatten_params:
-            self.param = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
+            self.param = param_storage if param_storage is not None else torch.zeros(self.numel, dtype=self.dtype, device=self.device)
+            assert self.param.numel() == self.numel and self.param.dtype == self.dtype
             for s in self.slots:
                 view = self.param[s.offset : s.offset + s.numel].view(s.param.shape)
                 view.copy_(s.param.data)
                 s.param.data = view
-        self.grad = torch.zeros(self.numel, dtype=self.dtype, device=self.device) if with_grads else None
+        if with_grads:
+            self.grad = grad_storage if grad_storage is not None else torch.zeros(self.numel, dtype=self.dtype, device=self.device)
+            self.grad.zero_()
+        else:
+            self.grad = None
         if with_grads:
             self.attach_grads()
 

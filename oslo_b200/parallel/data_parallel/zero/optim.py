@@ -55,7 +55,7 @@ class ZeroRedundancyOptimizer:
                  reduce_bucket_size: int = 64 * 1024 * 1024, communication_dtype: Optional[torch.dtype] = None,
                  overlap_communication: bool = False, partition_grad: bool = False, cpu_offload: bool = False,
                  forced_dtype: Optional[torch.dtype] = None, initial_scale: float = 1.0, growth_interval: int = 1000,
-                 data_parallel_mode: ParallelMode = ParallelMode.DATA):
+                 data_parallel_mode: ParallelMode = ParallelMode.DATA, fused: Optional[bool] = None):
         from oslo_b200.distributed import ParallelContext
 
         self.optim = optimizer
@@ -73,6 +73,14 @@ class ZeroRedundancyOptimizer:
         self.growth_interval, self._good_steps = growth_interval, 0
         self._groups: List[List[_Group]] = []
         self._callback_queued = False
+        # fused path: flat buffers in symmetric memory and the whole step as one peer-memory kernel
+        if fused is None:
+            from oslo_b200.distributed import symm
+
+            fused = symm.small_ops_enabled()
+        inner_ok = type(optimizer).__name__ in ("Adam", "AdamW", "FusedAdam")
+        self.fused = bool(fused and self.pc.use_cuda and self.world > 1 and self.world <= 8 and inner_ok and not cpu_offload)
+        self._fused_state = {}
         self._param_to_bucket: Dict[int, tuple] = {}
         for pg in self.optim.param_groups:
             params = [p for p in pg["params"] if p.requires_grad]
@@ -84,7 +92,19 @@ class ZeroRedundancyOptimizer:
                 by_dtype.setdefault((p.dtype, p.device), []).append(p)
             groups = []
             for (dtype, device), ps in by_dtype.items():
-                flat = FlatBuffer(ps, pad_to=self.world * 128, with_grads=True, flatten_params=True)
+                use_fused = self.fused and dtype in (torch.bfloat16, torch.float16)
+                if use_fused:
+                    from oslo_b200.distributed import symm
+
+                    numel = FlatBuffer.layout_numel(ps, self.world * 128)
+                    nbytes = numel * 2
+                    sbuf = symm.SymmetricBuffer(self.pc, self.mode, 2 * nbytes)
+                    flat = FlatBuffer(ps, pad_to=self.world * 128, with_grads=True, flatten_params=True,
+                                      param_storage=sbuf.payload(0, nbytes, dtype), grad_storage=sbuf.payload(nbytes, nbytes, dtype))
+                    reduce_bucket_size = numel  # one bucket: this rank's shard is one contiguous range
+                    flat.symm, flat.symm_nbytes = sbuf, nbytes
+                else:
+                    flat = FlatBuffer(ps, pad_to=self.world * 128, with_grads=True, flatten_params=True)
                 master_dev = torch.device("cpu") if cpu_offload else device
                 g = _Group(flat, self.world, self.rank, reduce_bucket_size, master_dev)
                 groups.append(g)
@@ -196,8 +216,52 @@ class ZeroRedundancyOptimizer:
         norm = sq.sqrt().item()
         return norm, not math.isfinite(norm)
 
+    def _fused_step_group(self, g: _Group, pg: dict, step_no: int):
+        """reduce-scatter + AdamW + all-gather for one flat buffer as one kernel (``csrc/zero_sm100a.cu``)."""
+        import ctypes
+
+        from oslo_b200.ops import _lib
+
+        flat, sbuf = g.flat, g.flat.symm
+        st = self._fused_state.get(id(g))
+        if st is None:
+            st = self._fused_state[id(g)] = dict(m=torch.zeros_like(g.master.data), v=torch.zeros_like(g.master.data))
+        (s0, e0) = g.shard_ranges[0]
+        b1, b2 = pg.get("betas", (0.9, 0.999))
+        lib = _lib.cuda_lib()
+        grads, params = sbuf.peer_array(flat.symm_nbytes), sbuf.peer_array(0)
+        common = [ctypes.c_longlong(s0), ctypes.c_longlong(e0 - s0), ctypes.c_int(self.world),
+                  ctypes.c_int(1 if flat.dtype == torch.bfloat16 else 0), ctypes.c_float(pg["lr"]), ctypes.c_float(b1),
+                  ctypes.c_float(b2), ctypes.c_float(pg.get("eps", 1e-8)), ctypes.c_float(pg.get("weight_decay", 0.0)),
+                  ctypes.c_float(1 - b1**step_no), ctypes.c_float(1 - b2**step_no),
+                  ctypes.c_float(1.0 / (self.world * self.loss_scale)),
+                  ctypes.c_int(0 if type(self.optim).__name__ == "Adam" else 1)]
+        sbuf.barrier()  # every rank's gradients are final
+        coef = None
+        if self.clip_grad_norm > 0:
+            sq = torch.zeros(1, dtype=torch.float32, device=flat.device)
+            rc = lib.oslo_zero_step(grads, params, _lib.ptr(g.master.data), _lib.ptr(st["m"]), _lib.ptr(st["v"]), *common,
+                                    ctypes.c_int(0), None, _lib.ptr(sq), ctypes.c_int(_lib.num_sms()), _lib.stream_ptr())
+            if rc:
+                raise RuntimeError(f"oslo_zero_step (norm) failed ({rc})")
+            dist.all_reduce(sq, group=self.group)
+            coef = (self.clip_grad_norm / (sq.sqrt() + 1e-6)).clamp(max=1.0)
+            self.last_grad_norm = sq.sqrt()
+        rc = lib.oslo_zero_step(grads, params, _lib.ptr(g.master.data), _lib.ptr(st["m"]), _lib.ptr(st["v"]), *common,
+                                ctypes.c_int(1), _lib.ptr(coef), None, ctypes.c_int(_lib.num_sms()), _lib.stream_ptr())
+        if rc:
+            raise RuntimeError(f"oslo_zero_step failed ({rc})")
+        sbuf.barrier()  # every rank's parameters have landed everywhere
+
     @torch.no_grad()
     def step(self, closure=None):
+        if self.fused and all(hasattr(g.flat, "symm") for g in self._all_groups()):
+            self._step_count = getattr(self, "_step_count", 0) + 1
+            for groups, pg in zip(self._groups, self.optim.param_groups):
+                for g in groups:
+                    self._fused_step_group(g, pg, self._step_count)
+            self._reset_pending()
+            return None
         self._finish_reduction()
         self._grad_shards_to_master()
         norm, overflow = self._global_norm_and_overflow()

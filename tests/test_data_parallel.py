@@ -87,3 +87,44 @@ def _zero_worker(rank, world, stage, overlap, clip):
 @pytest.mark.parametrize("stage,overlap,clip", [(1, False, 0.0), (2, False, 0.0), (2, True, 0.0), (1, True, 0.05)])
 def test_zero_matches_single_process(stage, overlap, clip):
     run_dist(_zero_worker, 2, stage, overlap, clip)
+
+
+def _hetero_worker(rank, world, policy):
+    import oslo_b200
+    from oslo_b200 import ParallelContext
+    from oslo_b200.parallel import DistributedDataParallel, ShardingStrategy
+
+    pc = ParallelContext.from_torch(data_parallel_size=world, backend="gloo", seed=0)
+    model = _mlp()
+    inner = torch.optim.AdamW(model.parameters(), lr=1e-2)
+    wrapped, opt = DistributedDataParallel(model, pc, model_wrapper_config=dict(placement_policy=policy, chunk_size_mb=0.004),
+                                           sharding_strategy=ShardingStrategy.HETERO_SHARD, optimizer=inner)
+    oslo_b200.ready(wrapped, pc)
+    assert len(wrapped.manager.chunks) > 1
+    # between steps every rank holds only shards
+    assert all(p.numel() == 0 for p in model.parameters())
+    for s in range(4):
+        x, y = _data(s)
+        xs, ys = x.chunk(world)[rank], y.chunk(world)[rank]
+        opt.zero_grad()
+        loss = ((wrapped(xs) - ys) ** 2).mean()
+        opt.backward(loss)
+        opt.step()
+    ref = _reference(4)
+    sd = wrapped.state_dict()
+    for (n, r) in ref.named_parameters():
+        assert torch.allclose(sd[n], r, rtol=1e-5, atol=1e-6), (n, (sd[n] - r).abs().max())
+    pc.destroy()
+
+
+@pytest.mark.parametrize("policy", ["cuda", "cpu"])
+def test_hetero_zero3_matches_single_process(policy):
+    run_dist(_hetero_worker, 2, policy)
+
+
+def test_chunk_size_search_reduces_waste():
+    from oslo_b200.parallel.data_parallel.zero.hetero import search_chunk_size
+
+    numels = [300_000] * 7 + [1000] * 20
+    size = search_chunk_size(numels, world=2, min_mb=0.5, max_mb=8, elem_bytes=2)
+    assert size % 2048 == 0 and size >= 300_000

@@ -111,3 +111,46 @@ def _model_worker(rank, world):
 @pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
 def test_fused_model_step_matches_composition():
     run_dist(_model_worker, 2, timeout=600)
+
+
+def _zero_worker(rank, world):
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch.nn as nn
+
+    from oslo_b200 import ParallelContext, ParallelMode
+    from oslo_b200.distributed import symm
+    from oslo_b200.ops import _lib
+    from oslo_b200.parallel import ZeroRedundancyOptimizer
+
+    pc = ParallelContext.from_torch(data_parallel_size=world, backend="nccl", seed=0)
+    dev = pc.device
+
+    def make():
+        torch.manual_seed(0)
+        return nn.Sequential(nn.Linear(256, 512), nn.GELU(), nn.Linear(512, 512), nn.LayerNorm(512), nn.Linear(512, 64)).to(dev, torch.bfloat16)
+
+    results = {}
+    for fused in (False, True):
+        model = make()
+        opt = ZeroRedundancyOptimizer(torch.optim.AdamW(model.parameters(), lr=1e-2, weight_decay=0.1), parallel_context=pc,
+                                      partition_grad=True, fused=fused, clip_grad_norm=1.0 if fused else 1.0)
+        assert opt.fused == fused
+        for s in range(3):
+            g = torch.Generator().manual_seed(10 + s)
+            x = torch.randn(8 * world, 256, generator=g).to(dev, torch.bfloat16).chunk(world)[rank]
+            y = torch.randn(8 * world, 64, generator=g).to(dev, torch.bfloat16).chunk(world)[rank]
+            opt.zero_grad()
+            loss = ((model(x) - y).float() ** 2).mean()
+            opt.backward(loss)
+            opt.step()
+        torch.cuda.synchronize()
+        _lib.check_status()
+        results[fused] = [p.detach().float().clone() for p in model.parameters()]
+    for a, b in zip(results[True], results[False]):
+        assert (a - b).abs().max().item() <= 2e-2 * (b.abs().max().item() + 1e-3)
+    pc.destroy()
+
+
+@pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_fused_zero_step_matches_collective_path():
+    run_dist(_zero_worker, 2, timeout=600)

@@ -288,3 +288,87 @@ def test_qkv_attention_with_rope(layout):
     out_r.backward(g.float().cpu())
     assert _rel(out.cpu(), out_r) < 2e-2
     assert _rel(x.grad.cpu(), xr.grad) < 3e-2
+
+
+def test_moe_kernels_match_torch_paths():
+    from oslo_b200.ops import moe
+
+    torch.manual_seed(12)
+    S, E, K, H, C = 300, 8, 2, 128, 96
+    idx = torch.stack([torch.randint(0, E, (S,)), torch.randint(0, E, (S,))], 1).to(torch.int32)
+    pos_g, cnt_g = moe.positions(idx.to(DEV), E)
+    pos_c, cnt_c = moe.positions(idx, E)
+    assert torch.equal(pos_g.cpu(), pos_c) and torch.equal(cnt_g.cpu(), cnt_c)
+    slot = torch.where(pos_c < C, idx * C + pos_c, torch.full_like(pos_c, -1))
+    x = torch.randn(S, H)
+    w = torch.rand(S, K)
+    xg = x.to(DEV, torch.bfloat16).requires_grad_()
+    wg = w.to(DEV).requires_grad_()
+    xr = x.to(torch.bfloat16).float().requires_grad_()
+    wr = w.clone().requires_grad_()
+    yg = moe.combine(moe.dispatch(xg, slot.to(DEV), E * C) * 1.5, wg, slot.to(DEV))
+    yr = moe.combine(moe.dispatch(xr, slot, E * C) * 1.5, wr, slot)
+    g = torch.randn(S, H)
+    yg.backward(g.to(DEV, torch.bfloat16))
+    yr.backward(g.to(torch.bfloat16).float())
+    assert _rel(yg.cpu(), yr) < 2e-2
+    assert _rel(xg.grad.cpu(), xr.grad) < 2e-2
+    assert _rel(wg.grad.cpu(), wr.grad) < 3e-2
+
+
+@pytest.mark.parametrize("name", ["sgd", "adagrad", "lamb", "novograd"])
+def test_fused_optimizers_cuda_match_cpu_paths(name):
+    from oslo_b200 import optim
+
+    make = {"sgd": lambda ps: optim.FusedSGD(ps, lr=1e-2, momentum=0.9, weight_decay=0.01),
+            "adagrad": lambda ps: optim.FusedAdagrad(ps, lr=1e-2, weight_decay=0.01),
+            "lamb": lambda ps: optim.FusedLamb(ps, lr=1e-2, weight_decay=0.01),
+            "novograd": lambda ps: optim.FusedNovoGrad(ps, lr=1e-2, weight_decay=0.01)}[name]
+    torch.manual_seed(13)
+    shapes = [(257, 33), (19,), (1024, 40)]
+    cpu = [torch.randn(s).requires_grad_() for s in shapes]
+    gpu = [p.detach().to(DEV).requires_grad_() for p in cpu]
+    oc, og = make(cpu), make(gpu)
+    for step in range(4):
+        for a, b in zip(cpu, gpu):
+            g = torch.randn_like(a)
+            a.grad, b.grad = g, g.to(DEV)
+        oc.step()
+        og.step()
+    for a, b in zip(cpu, gpu):
+        assert _rel(b.cpu(), a) < 1e-4, name
+
+
+def test_ngram_repeat_block_kernel():
+    from oslo_b200.nn.ngram_repeat_block import NGramRepeatBlock, ngram_repeat_block_reference
+
+    torch.manual_seed(14)
+    rows, length, vocab, n = 12, 40, 50, 3
+    tok = torch.randint(0, 6, (rows, length))
+    lp = torch.randn(rows, vocab)
+    ref = ngram_repeat_block_reference(tok, lp.clone(), 29, n)
+    out = NGramRepeatBlock()(tok.to(DEV), lp.clone().to(DEV), rows, 29, 1, n)
+    assert torch.equal(torch.isinf(out.cpu()), torch.isinf(ref))
+
+
+def test_llama_and_gpt2_models_run_on_native_kernels():
+    from oslo_b200.models import GPT2Config, GPT2LMHeadModel, LlamaConfig, LlamaForCausalLM
+
+    torch.manual_seed(15)
+    ids = torch.randint(0, 512, (2, 64))
+    for cls, cfg in [(LlamaForCausalLM, LlamaConfig(vocab_size=512, hidden_size=128, intermediate_size=352, num_hidden_layers=2,
+                                                    num_attention_heads=4, max_position_embeddings=64)),
+                     (GPT2LMHeadModel, GPT2Config(vocab_size=512, n_positions=64, n_embd=128, n_layer=2, n_head=4, resid_pdrop=0.0,
+                                                  embd_pdrop=0.0, attn_pdrop=0.0))]:
+        cpu = cls(cfg)
+        gpu = cls(cfg)
+        gpu.load_state_dict(cpu.state_dict())
+        gpu = gpu.to(DEV, torch.bfloat16)
+        lc = cpu(input_ids=ids, labels=ids).loss
+        lg = gpu(input_ids=ids.to(DEV), labels=ids.to(DEV)).loss
+        lc.backward()
+        lg.backward()
+        assert abs(lc.item() - lg.item()) < 5e-2, cls.__name__
+        gc = dict(cpu.named_parameters())
+        for k, p in gpu.named_parameters():
+            assert _rel(p.grad.cpu(), gc[k].grad) < 0.1, (cls.__name__, k)
