@@ -113,6 +113,7 @@ def main():
     ap.add_argument("--model", default="neox-1.3b", choices=sorted(CONFIGS))
     ap.add_argument("--no-sequence-parallel", action="store_true")
     ap.add_argument("--no-fused-collectives", action="store_true")
+    ap.add_argument("--no-cuda-graph", action="store_true", help="launch every kernel from the host instead of replaying a captured step")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the device-timed steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     args = ap.parse_args()
@@ -166,7 +167,7 @@ def main():
         except Exception as e:  # the NCCL composition still runs
             if rank == 0:
                 print(f"[bench] fused collectives unavailable: {e}", file=sys.stderr)
-    opt = FusedAdam(model.parameters(), lr=1e-4, weight_decay=0.01, master_weights=True)
+    opt = FusedAdam(model.parameters(), lr=1e-4, weight_decay=0.01, master_weights=True, capturable=True)
 
     gen = torch.Generator().manual_seed(99)
     host_ids = [torch.randint(0, mcfg.vocab_size, (B, S), generator=gen).pin_memory() for _ in range(4)]
@@ -206,6 +207,40 @@ def main():
     torch.cuda.synchronize()
     _lib.check_status()
 
+    graphed = None
+    if not args.no_cuda_graph and not args.profiler_range:
+        from oslo_b200.ops import fused_collectives
+        from oslo_b200.utils.cuda_graph import try_graphed_step
+
+        rt = fused_collectives.runtime()
+        mark = {"epoch": 0}
+
+        def eager(ids):
+            mark["epoch"] = rt.ws.epoch if rt is not None else 0
+            mark["calls0"] = _lib.native_calls
+            out = step(ids).detach()
+            mark["calls"] = _lib.native_calls - mark["calls0"]
+            return out
+
+        def pad():
+            if rt is not None:
+                rt.ws.pad_to_even(mark["epoch"])
+
+        def failed(e):
+            if rank == 0:
+                print(f"[bench] CUDA-graph capture unavailable, running eagerly: {e}", file=sys.stderr)
+
+        graphed = try_graphed_step(eager, [dev_ids[0]], warmup=2, before_capture_end=pad, on_failure=failed)
+        ok = torch.tensor([1 if graphed is not None else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() == 0:
+            graphed = None
+        if graphed is not None:
+            eager_step = step
+
+            def step(ids):  # noqa: F811 - same contract as the eager step
+                return graphed(ids)
+
     sampler = ClockSampler(torch.cuda.current_device())
     sampler.start()
     calls0 = _lib.native_calls
@@ -215,6 +250,9 @@ def main():
     if args.profiler_range:
         torch.cuda.profiler.stop()
     calls = _lib.native_calls - calls0
+    if graphed is not None:
+        # the captured step holds that many launches of this repository's kernels; each replay runs all of them
+        calls = mark.get("calls", 0) * args.steps
     ms_e2e, wall_e2e, loss_e2e = timed(args.steps, e2e=True)
     clocks = sampler.stop()
     _lib.check_status()
@@ -252,6 +290,7 @@ def main():
                 "seq_len": S,
                 "parallelism": f"tp{world}" + ("+sp" if sp else ""),
                 "fused_collectives": bool(fused),
+                "cuda_graph": graphed is not None,
                 "optimizer": "AdamW, fp32 master weights and moments",
                 "l2_policy": "inputs larger than L2: every step streams > 126 MB of weights and activations",
             },

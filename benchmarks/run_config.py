@@ -42,7 +42,7 @@ def build(args, world):
     name = args.config
     small = args.scale_down
     if name == "llama-2d-pp2":
-        tp = 4 if world >= 8 else (4 if world == 4 else 1)
+        tp = args.tp or (4 if world >= 4 else 1)
         pp = world // tp
         pc = ParallelContext.from_torch(tensor_parallel_size=tp, pipeline_parallel_size=pp,
                                         tensor_parallel_mode=ParallelMode.TENSOR_2D, backend="nccl", seed=7)
@@ -109,6 +109,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--scale-down", action="store_true")
     ap.add_argument("--fused-zero", action="store_true")
+    ap.add_argument("--tp", type=int, default=0, help="override the tensor-parallel size of llama-2d-pp2 (smoke runs)")
     args = ap.parse_args()
     world = int(os.environ["WORLD_SIZE"])
     pc, model, wrapped, opts, cfg, batch, seq = build(args, world)

@@ -36,7 +36,8 @@ static int pick_block_n(int M, int N, int ctas, int max_bn) {
 // peer_in / peer_ag_ready: host arrays of `tp` device pointers (entry [rank] is the local buffer).
 extern "C" int oslo_ag_gemm(void* const* peer_in, void* x_full, const void* B, void* C, const void* bias, int T, int N, int K,
                             long long ldb, int b_mn, int is_bf16, int tp, int rank, int epoch, void* const* peer_ag_ready,
-                            int* chunk_flag, int* chunk_arrive, int copy_ctas, int num_sms, int* status, void* stream_ptr) {
+                            int* chunk_flag, int* chunk_arrive, int copy_ctas, int num_sms, int* status, void* stream_ptr,
+                            const int* epoch_ptr) {
   if (tp > kMaxRanks || tp < 1 || T % tp) return -1;
   const int Tl = T / tp;
   if (Tl % kBlockM || N % 8 || K % 8 || ldb % 8) return -5;
@@ -66,7 +67,7 @@ extern "C" int oslo_ag_gemm(void* const* peer_in, void* x_full, const void* B, v
   }
   fp.x_full = x_full;
   fp.ag_ready = static_cast<int*>(peer_ag_ready[rank]);
-  fp.chunk_flag = chunk_flag; fp.chunk_arrive = chunk_arrive; fp.status = status;
+  fp.chunk_flag = chunk_flag; fp.chunk_arrive = chunk_arrive; fp.status = status; fp.epoch_ptr = epoch_ptr;
   CUtensorMap ta, tb, tc, taux;
   int rc = make_map(&ta, x_full, is_bf16, K, T, 1, 1, K, 0, 0, kBlockK, kBlockM);
   if (rc) return rc;
@@ -94,7 +95,7 @@ extern "C" int oslo_ag_gemm(void* const* peer_in, void* x_full, const void* B, v
 extern "C" int oslo_gemm_rs(const void* A, long long lda, const void* B, long long ldb, int b_mn, void* out, const void* bias,
                             int T, int N, int K, int is_bf16, int tp, int rank, int epoch, void* const* peer_partial,
                             void* const* peer_rs_flag, int* tile_done, int reduce_ctas, int num_sms, int* status,
-                            void* stream_ptr, unsigned long long* debug_times) {
+                            void* stream_ptr, unsigned long long* debug_times, const int* epoch_ptr) {
   if (tp > kMaxRanks || tp < 1 || T % tp) return -1;
   const int Tl = T / tp;
   if (Tl % kBlockM || N % 8 || K % 8 || lda % 8 || ldb % 8) return -5;
@@ -123,7 +124,7 @@ extern "C" int oslo_gemm_rs(const void* A, long long lda, const void* B, long lo
     fp.peer_rs_flag[i] = static_cast<int*>(peer_rs_flag[i]);
   }
   fp.rs_flag = static_cast<int*>(peer_rs_flag[rank]);
-  fp.tile_done = tile_done; fp.rs_out = out; fp.rs_bias = bias; fp.status = status; fp.debug_times = debug_times;
+  fp.tile_done = tile_done; fp.rs_out = out; fp.rs_bias = bias; fp.status = status; fp.debug_times = debug_times; fp.epoch_ptr = epoch_ptr;
   CUtensorMap ta, tb, tc, taux;
   int rc = make_map(&ta, A, is_bf16, K, T, 1, 1, lda, 0, 0, kBlockK, kBlockM);
   if (rc) return rc;

@@ -93,6 +93,7 @@ struct FusedParams {
   int tiles_per_shard = 0;  // output tiles per shard
   int tiles_per_chunk = 0;  // RS: output tiles per row chunk
   int epoch = 0;
+  const int* epoch_ptr = nullptr;  // when set, the epoch is read from device memory (CUDA-graph replays advance it)
   int copy_ctas = 0;        // AG: CTAs [0, copy_ctas) copy, the others multiply
   int k_elems = 0;          // AG: row length of A in elements
   int chunk_rows = 0;       // rows per hand-off chunk (a multiple of 128 dividing shard_rows); one flag per chunk
@@ -275,7 +276,9 @@ template <int BLOCK_N, bool A_MN, bool B_MN, int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux,
-                    const GemmParams p, const FusedParams fp, const __grid_constant__ PeerMaps peer_maps) {
+                    const GemmParams p, const FusedParams fp_in, const __grid_constant__ PeerMaps peer_maps) {
+  FusedParams fp = fp_in;
+  if (MODE != kModePlain && fp.epoch_ptr) fp.epoch = *fp.epoch_ptr;
   if constexpr (MODE == kModeAllGather) {
     // the first fp.copy_ctas CTAs stream the peers' shards into local memory; the rest run the GEMM
     if (static_cast<int>(blockIdx.x) < fp.copy_ctas) {

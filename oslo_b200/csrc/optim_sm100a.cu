@@ -37,6 +37,8 @@ struct AdamArgs {
   float lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale;
   int adamw;           // 1: decoupled weight decay, 0: L2 added to the gradient
   const float* inv_scale;  // optional device scalar multiplied into the gradient (GradScaler)
+  const int* step_ptr;     // optional device step counter: bias corrections are then computed in the kernel, so a
+                           // captured launch stays correct when replayed from a CUDA graph
 };
 
 // ptr: 0 = param (TP), 1 = grad (TG), 2 = exp_avg (f32), 3 = exp_avg_sq (f32), 4 = master (f32, optional)
@@ -54,7 +56,12 @@ __global__ void __launch_bounds__(kMTThreads) mt_adam_kernel(const MTRecord* __r
   float* v = static_cast<float*>(rec.ptr[3]);
   float* master = static_cast<float*>(rec.ptr[4]);
   const float gs = a.grad_scale * (a.inv_scale ? *a.inv_scale : 1.0f);
-  const float inv_bc1 = 1.0f / a.bc1, inv_bc2 = 1.0f / a.bc2;
+  float inv_bc1 = 1.0f / a.bc1, inv_bc2 = 1.0f / a.bc2;
+  if (a.step_ptr) {
+    const float t = static_cast<float>(*a.step_ptr);
+    inv_bc1 = 1.0f / (1.0f - powf(a.beta1, t));
+    inv_bc2 = 1.0f / (1.0f - powf(a.beta2, t));
+  }
   for (long long i = start + threadIdx.x; i < end; i += kMTThreads) {
     float pv = master ? master[i] : ldf<TP>(p, i);
     float gv = ldf<TG>(g, i) * gs;
@@ -298,10 +305,10 @@ extern "C" int oslo_mt_record_bytes() { return (int)sizeof(MTRecord); }
 
 extern "C" int oslo_mt_adam(const void* table, const void* block_map, int nblocks, float lr, float beta1, float beta2, float eps,
                             float weight_decay, float bc1, float bc2, float grad_scale, int adamw, const float* inv_scale,
-                            const int* noop, int pdtype, int gdtype, void* stream) {
+                            const int* noop, int pdtype, int gdtype, void* stream, const int* step_ptr) {
   if (nblocks <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
-  AdamArgs a{lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale, adamw, inv_scale};
+  AdamArgs a{lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale, adamw, inv_scale, step_ptr};
   OSLO_PG_DISPATCH(mt_adam_kernel, (const MTRecord*)table, (const int2*)block_map, a, noop);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

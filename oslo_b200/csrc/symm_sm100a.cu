@@ -57,8 +57,10 @@ struct PeerFlagPtrs {
 
 // Every rank stores `epoch` into slot [rank] of every peer's flag array, then waits (bounded) until its own
 // array holds `epoch` from everyone.  One block of 32 threads.
-__global__ void symm_barrier_kernel(PeerFlagPtrs peers, int* local_flags, int rank, int tp, int epoch, int* status) {
+__global__ void symm_barrier_kernel(PeerFlagPtrs peers, int* local_flags, int rank, int tp, int epoch, int* status,
+                                    const int* epoch_ptr) {
   const int t = threadIdx.x;
+  if (epoch_ptr) epoch = *epoch_ptr;  // device-resident epoch: the same launch can be replayed from a CUDA graph
   bool ok = true;
   if (t < tp) {
     __threadfence_system();
@@ -70,10 +72,10 @@ __global__ void symm_barrier_kernel(PeerFlagPtrs peers, int* local_flags, int ra
 }
 
 extern "C" int oslo_symm_barrier(void* const* peer_flags, int* local_flags, int rank, int tp, int epoch, int* status,
-                                 void* stream) {
+                                 void* stream, const int* epoch_ptr) {
   if (tp > kMaxRanks) return -1;
   PeerFlagPtrs pf;
   for (int i = 0; i < kMaxRanks; ++i) pf.p[i] = i < tp ? static_cast<int*>(peer_flags[i]) : nullptr;
-  symm_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pf, local_flags, rank, tp, epoch, status);
+  symm_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pf, local_flags, rank, tp, epoch, status, epoch_ptr);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -79,6 +79,7 @@ class SymmetricBuffer:
             self.peer_ptrs.append(out.value)
         self.local = torch.as_tensor(_RawCudaBuffer(self.base, self.nbytes), device=self.device)
         self.epoch = 0
+        self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=self.device)  # what the kernels actually read
         dist.barrier(group=pc.get_cpu_group(mode))
 
     def payload(self, offset: int, nbytes: int, dtype, shape=None) -> torch.Tensor:
@@ -91,9 +92,11 @@ class SymmetricBuffer:
 
     def barrier(self):
         self.epoch += 1
+        self.epoch_dev.add_(1)  # a stream-ordered (and graph-capturable) increment
         flags = (ctypes.c_void_p * self.world)(*self.peer_ptrs)
         rc = _lib.cuda_lib().oslo_symm_barrier(flags, ctypes.c_void_p(self.base), ctypes.c_int(self.rank), ctypes.c_int(self.world),
-                                               ctypes.c_int(self.epoch), _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr())
+                                               ctypes.c_int(self.epoch), _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr(),
+                                               _lib.ptr(self.epoch_dev))
         if rc:
             raise RuntimeError(f"oslo_symm_barrier failed ({rc})")
 
@@ -188,6 +191,7 @@ class SymmetricWorkspace:
         # local scratch counters (not shared): chunk_flag[64], chunk_arrive[64], tile_done[64]
         self.local = torch.zeros(256, dtype=torch.int32, device=self.device)
         self.epoch = 0
+        self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=self.device)  # what the kernels actually read
         self.debug_times = None  # set to a uint64[8] device tensor to collect in-kernel time stamps
         self._local_bytes = torch.as_tensor(_RawCudaBuffer(self.base, self.total), device=self.device)
         dist.barrier(group=pc.get_cpu_group(mode))
@@ -216,12 +220,26 @@ class SymmetricWorkspace:
         return ctypes.c_void_p(self.local.data_ptr() + idx * 4 * 64)
 
     # ------------------------------------------------------------------ ops
+    def _next_epoch(self) -> int:
+        """Advance the call counter on the host (for buffer parity) and on the device (the value kernels compare flags
+        with).  The device increment is an ordinary stream operation, so a captured step replays correctly as long as
+        the number of fused calls per replay is even (parity then repeats); see ``pad_to_even``."""
+        self.epoch += 1
+        self.epoch_dev.add_(1)
+        return self.epoch
+
+    def pad_to_even(self, calls_before: int):
+        """Call at the end of a step that will be captured in a CUDA graph: if the step made an odd number of fused
+        calls, spend one barrier so every replay starts on the same buffer parity."""
+        if (self.epoch - calls_before) % 2:
+            self.barrier()
+
     def barrier(self):
         """Device-side barrier over the group on the current stream (bounded wait)."""
-        self.epoch += 1
+        self._next_epoch()
         rc = _lib.cuda_lib().oslo_symm_barrier(
             self._flag_ptrs(2), ctypes.c_void_p(self.base + 2 * 256), ctypes.c_int(self.rank), ctypes.c_int(self.tp),
-            ctypes.c_int(self.epoch), _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr())
+            ctypes.c_int(self.epoch), _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr(), _lib.ptr(self.epoch_dev))
         if rc:
             raise RuntimeError(f"oslo_symm_barrier failed ({rc})")
 
@@ -259,7 +277,7 @@ class SymmetricWorkspace:
         tl, k = x_shard.shape
         t = tl * self.tp
         n = weight.shape[0]
-        self.epoch += 1
+        self._next_epoch()
         parity = self.epoch & 1
         self._local_in(parity, tl, k).copy_(x_shard)
         x_full = torch.empty(t, k, dtype=x_shard.dtype, device=x_shard.device)
@@ -270,7 +288,7 @@ class SymmetricWorkspace:
             ctypes.c_int(k), ctypes.c_longlong(ldb), ctypes.c_int(b_mn), ctypes.c_int(1 if self.dtype == torch.bfloat16 else 0),
             ctypes.c_int(self.tp), ctypes.c_int(self.rank), ctypes.c_int(self.epoch), self._flag_ptrs(0),
             self._local_ptr(0), self._local_ptr(1), ctypes.c_int(self.copy_ctas), ctypes.c_int(_lib.num_sms()),
-            _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr())
+            _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr(), _lib.ptr(self.epoch_dev))
         if rc:
             raise RuntimeError(f"oslo_ag_gemm failed ({rc})")
         return out, x_full
@@ -282,7 +300,7 @@ class SymmetricWorkspace:
         tl = t // self.tp
         if not x.is_contiguous():
             x = x.contiguous()
-        self.epoch += 1
+        self._next_epoch()
         parity = self.epoch & 1
         out = torch.empty(tl, n, dtype=x.dtype, device=x.device)
         w, b_mn, ldb = self._weight_operand(weight)
@@ -292,7 +310,7 @@ class SymmetricWorkspace:
             ctypes.c_int(1 if self.dtype == torch.bfloat16 else 0), ctypes.c_int(self.tp), ctypes.c_int(self.rank),
             ctypes.c_int(self.epoch), self._slot_ptrs(parity), self._flag_ptrs(1), self._local_ptr(2),
             ctypes.c_int(self.copy_ctas), ctypes.c_int(_lib.num_sms()), _lib.ptr(_lib.status_word(self.device)),
-            _lib.stream_ptr(), _lib.ptr(self.debug_times))
+            _lib.stream_ptr(), _lib.ptr(self.debug_times), _lib.ptr(self.epoch_dev))
         if rc:
             raise RuntimeError(f"oslo_gemm_rs failed ({rc})")
         return out

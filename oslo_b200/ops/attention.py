@@ -93,6 +93,31 @@ def attention(q, k, v, causal: bool = True, scale: Optional[float] = None, mask=
     return attention_reference(q, k, v, causal, scale, mask)
 
 
+# ------------------------------------------------------------------ fused forward
+def flash_supported(q, k, v) -> bool:
+    b, s, nh, hd = q.shape
+    return (supported(q, k) and hd in (64, 128) and s % 128 == 0 and k.shape == q.shape and v.shape == q.shape
+            and q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1)
+
+
+def flash_attention_forward(q, k, v, causal: bool, scale: float):
+    """Fused attention forward (``csrc/attention_sm100a.cu``): returns ``(out [b, s, heads*hd], lse [b, heads, s])``.
+    q, k, v are ``[b, s, heads, hd]`` views (any token / head / batch strides, unit stride on ``hd``)."""
+    import ctypes
+
+    b, s, nh, hd = q.shape
+    out = torch.empty(b, s, nh, hd, dtype=q.dtype, device=q.device)
+    lse = torch.empty(b, nh, s, dtype=torch.float32, device=q.device)
+    st = lambda t: (ctypes.c_longlong(t.stride(1)), ctypes.c_longlong(t.stride(2)), ctypes.c_longlong(t.stride(0)))
+    rc = _lib.cuda_lib().oslo_attention_forward(
+        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse), ctypes.c_int(b), ctypes.c_int(s), ctypes.c_int(nh),
+        ctypes.c_int(hd), *st(q), *st(k), *st(v), *st(out), ctypes.c_float(scale), ctypes.c_int(1 if causal else 0),
+        ctypes.c_int(1 if q.dtype == torch.bfloat16 else 0), _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr())
+    if rc:
+        raise RuntimeError(f"oslo_attention_forward failed ({rc})")
+    return out.view(b, s, nh * hd), lse
+
+
 # ------------------------------------------------------------- fused-QKV entry point
 def _split_qkv(qkv5, layout):
     """q, k, v views ``[b, s, heads, hd]`` of a fused projection viewed ``[b, s, heads, 3, hd]`` ("h3d", GPT-NeoX)

@@ -111,13 +111,12 @@ class _VPCECudaFn(torch.autograd.Function):
             # ONE exchange without a collective call: the triples are written to symmetric memory, a device-side
             # barrier orders them, and the second kernel reads every peer's triples straight over NVLink
             nbytes = rows * 3 * 4
-            buf = symm.group_buffer(pc, mode, "ce_stats", 2 * nbytes)
-            parity = (buf.epoch + 1) & 1
-            buf.payload(parity * nbytes, nbytes, torch.float32, (rows, 3)).copy_(stats)
-            buf.barrier()
-            base = buf.payload_offset + parity * nbytes
-            ptrs = [b + base for b in buf.peer_ptrs]
+            buf = symm.group_buffer(pc, mode, "ce_stats", nbytes)
+            buf.payload(0, nbytes, torch.float32, (rows, 3)).copy_(stats)
+            buf.barrier()  # everybody's triples are in place
+            ptrs = [b + buf.payload_offset for b in buf.peer_ptrs]
             gathered = stats
+            ce_buf = buf
         elif world > 1:
             gathered = torch.empty(world, rows, 3, dtype=torch.float32, device=x.device)
             dist.all_gather_into_tensor(gathered.view(-1), stats.view(-1), group=group)
@@ -133,6 +132,8 @@ class _VPCECudaFn(torch.autograd.Function):
                                    ctypes.c_int(1), ctypes.c_int(_DT[x.dtype]), ctypes.c_int(nsm), _lib.stream_ptr())
         if rc:
             raise RuntimeError(f"oslo_ce_loss_grad failed ({rc})")
+        if world > 1 and "ce_buf" in locals():
+            ce_buf.barrier()  # everybody has read them: the buffer may be overwritten by the next call
         ctx.save_for_backward(logits)  # now holds softmax - onehot
         return loss.view(target.shape)
 

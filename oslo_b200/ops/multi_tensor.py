@@ -53,8 +53,15 @@ class TensorTable:
             recs.append(row)
             for c in range((numel + self.chunk - 1) // self.chunk):
                 bmap.append((i, c))
-        self.table = torch.tensor(recs, dtype=torch.int64).to(self.device, non_blocking=False)
-        self.block_map = torch.tensor(bmap, dtype=torch.int32).reshape(-1, 2).to(self.device)
+        # staged through pinned memory with async copies: legal while a CUDA graph is being captured (the pinned
+        # tensors are kept alive because a replay reads them again)
+        host_table = torch.tensor(recs, dtype=torch.int64)
+        host_map = torch.tensor(bmap, dtype=torch.int32).reshape(-1, 2)
+        if torch.cuda.is_available():
+            host_table, host_map = host_table.pin_memory(), host_map.pin_memory()
+        self._host = (host_table, host_map)
+        self.table = host_table.to(self.device, non_blocking=True)
+        self.block_map = host_map.to(self.device, non_blocking=True)
         self.nblocks = len(bmap)
         self.columns = columns  # keep tensors alive
 

@@ -23,7 +23,7 @@ _DT = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 
 class FusedAdam(torch.optim.Optimizer):
     def __init__(self, params, lr=1e-3, bias_correction=True, betas=(0.9, 0.999), eps=1e-8, adam_w_mode=True,
-                 weight_decay=0.0, amsgrad=False, set_grad_none=True, master_weights=False):
+                 weight_decay=0.0, amsgrad=False, set_grad_none=True, master_weights=False, capturable=False):
         if amsgrad:
             raise RuntimeError("FusedAdam does not support the AMSGrad variant")
         defaults = dict(lr=lr, bias_correction=bias_correction, betas=betas, eps=eps, weight_decay=weight_decay)
@@ -31,6 +31,10 @@ class FusedAdam(torch.optim.Optimizer):
         self.adam_w_mode = 1 if adam_w_mode else 0
         self.set_grad_none = set_grad_none
         self.master_weights = master_weights
+        #: keep the step count on the device and compute bias corrections in the kernel, so ``step()`` can be captured
+        #: in a CUDA graph and replayed
+        self.capturable = capturable
+        self._step_dev = {}
         self._tables: Dict[tuple, TensorTable] = {}
 
     def zero_grad(self, set_to_none: bool = None):
@@ -56,6 +60,12 @@ class FusedAdam(torch.optim.Optimizer):
             b1, b2 = group["betas"]
             bc1 = 1 - b1**step if group["bias_correction"] else 1.0
             bc2 = 1 - b2**step if group["bias_correction"] else 1.0
+            if self.capturable:
+                first = next((p for p in group["params"] if p.is_cuda), None)
+                if first is not None:
+                    if gi not in self._step_dev:
+                        self._step_dev[gi] = torch.zeros(1, dtype=torch.int32, device=first.device)
+                    self._step_dev[gi].add_(1)
             buckets: Dict[tuple, List[torch.Tensor]] = {}
             for p in group["params"]:
                 if p.grad is None:
@@ -91,7 +101,8 @@ class FusedAdam(torch.optim.Optimizer):
             ctypes.c_float(group["lr"]), ctypes.c_float(b1), ctypes.c_float(b2), ctypes.c_float(group["eps"]),
             ctypes.c_float(group["weight_decay"]), ctypes.c_float(bc1), ctypes.c_float(bc2),
             ctypes.c_float(grad_scale), ctypes.c_int(self.adam_w_mode), _lib.ptr(inv_scale), _lib.ptr(noop_flag),
-            ctypes.c_int(_DT[pdt]), ctypes.c_int(_DT[gdt]), _lib.stream_ptr())
+            ctypes.c_int(_DT[pdt]), ctypes.c_int(_DT[gdt]), _lib.stream_ptr(),
+            _lib.ptr(self._step_dev.get(gi)) if self.capturable and group["bias_correction"] else None)
         if rc:
             raise RuntimeError(f"oslo_mt_adam failed ({rc})")
 

@@ -372,3 +372,22 @@ def test_llama_and_gpt2_models_run_on_native_kernels():
         gc = dict(cpu.named_parameters())
         for k, p in gpu.named_parameters():
             assert _rel(p.grad.cpu(), gc[k].grad) < 0.1, (cls.__name__, k)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("hd", [64, 128])
+def test_flash_attention_forward(causal, hd):
+    from oslo_b200.ops.attention import attention_reference, flash_attention_forward
+
+    torch.manual_seed(16)
+    b, s, nh = 2, 512, 3
+    qkv = (torch.randn(b, s, nh, 3, hd, device=DEV) * 0.7).to(torch.bfloat16)
+    q, k, v = qkv[..., 0, :], qkv[..., 1, :], qkv[..., 2, :]
+    scale = 1.0 / math.sqrt(hd)
+    out, lse = flash_attention_forward(q, k, v, causal, scale)
+    ref = attention_reference(q.float(), k.float(), v.float(), causal=causal, scale=scale)
+    assert _rel(out, ref) < 2e-2
+    scores = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) * scale
+    if causal:
+        scores = scores.masked_fill(~torch.ones(s, s, dtype=torch.bool, device=DEV).tril(), float("-inf"))
+    assert _rel(lse, torch.logsumexp(scores, dim=-1)) < 1e-3
