@@ -88,6 +88,8 @@ def attention(q, k, v, causal: bool = True, scale: Optional[float] = None, mask=
     """Multi-head attention.  q, k, v: ``[b, s, heads, head_dim]``; returns ``[b, s, heads*head_dim]``."""
     b, s, nh, hd = q.shape
     scale = scale if scale is not None else 1.0 / math.sqrt(hd)
+    if mask is None and flash_supported(q, k, v):
+        return _FlashAttentionFn.apply(q, k, v, causal, float(scale))
     if mask is None and supported(q, k) and s % 8 == 0 and hd % 8 == 0 and k.shape[1] == s:
         return _AttentionFn.apply(q, k, v, causal, float(scale))
     return attention_reference(q, k, v, causal, scale, mask)
@@ -116,6 +118,47 @@ def flash_attention_forward(q, k, v, causal: bool, scale: float):
     if rc:
         raise RuntimeError(f"oslo_attention_forward failed ({rc})")
     return out.view(b, s, nh * hd), lse
+
+
+def flash_attention_backward(q, k, v, out, d_out, lse, dq, dk, dv, causal: bool, scale: float):
+    """Fused attention backward (``csrc/attention_bwd_sm100a.cu``).  All tensors ``[b, s, heads, hd]`` views; ``dq, dk, dv``
+    are written (they may be slices of one fused buffer)."""
+    import ctypes
+
+    b, s, nh, hd = q.shape
+    delta = torch.empty(b, nh, s, dtype=torch.float32, device=q.device)
+    strides = []
+    for t in (q, k, v, out, d_out, dq, dk, dv):
+        assert t.stride(-1) == 1
+        strides += [t.stride(1), t.stride(2), t.stride(0)]
+    arr = (ctypes.c_longlong * len(strides))(*strides)
+    rc = _lib.cuda_lib().oslo_attention_backward(
+        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(d_out), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv),
+        _lib.ptr(lse), _lib.ptr(delta), ctypes.c_int(b), ctypes.c_int(s), ctypes.c_int(nh), ctypes.c_int(hd), arr,
+        ctypes.c_float(scale), ctypes.c_int(1 if causal else 0), ctypes.c_int(1 if q.dtype == torch.bfloat16 else 0),
+        _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr())
+    if rc:
+        raise RuntimeError(f"oslo_attention_backward failed ({rc})")
+
+
+class _FlashAttentionFn(torch.autograd.Function):
+    """Fused forward + backward on separate q, k, v tensors."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale):
+        out, lse = flash_attention_forward(q, k, v, causal, scale)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.causal, ctx.scale = causal, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, go):
+        q, k, v, out, lse = ctx.saved_tensors
+        b, s, nh, hd = q.shape
+        dqkv = torch.empty(3, b, s, nh, hd, dtype=q.dtype, device=q.device)
+        flash_attention_backward(q, k, v, out.view(b, s, nh, hd), go.contiguous().view(b, s, nh, hd), lse, dqkv[0], dqkv[1],
+                                 dqkv[2], ctx.causal, ctx.scale)
+        return dqkv[0], dqkv[1], dqkv[2], None, None
 
 
 # ------------------------------------------------------------- fused-QKV entry point
@@ -150,13 +193,20 @@ class _QKVAttentionFn(torch.autograd.Function):
             cos, sin, rot, neox = rope
             for t in (q, k):
                 _rope_launch(t.reshape(b * s, heads, hd) if t.is_contiguous() else _tok_view(t), cos, sin, rot, neox, None, False)
-        qh, kh, vh = (t.permute(0, 2, 1, 3) for t in (q, k, v))
-        p = torch.empty(b, heads, s, s, dtype=qkv.dtype, device=qkv.device)
-        gemm(qh, kh, out=p, causal=1 if causal else 0)
-        softmax_inplace_(p, scale, causal)
-        out = torch.empty(b, s, heads * hd, dtype=qkv.dtype, device=qkv.device)
-        gemm(p, vh.transpose(-1, -2), out=out.view(b, s, heads, hd).permute(0, 2, 1, 3), causal=2 if causal else 0)
-        ctx.save_for_backward(qkv, p)
+        if flash_supported(q, k, v):
+            # fused kernel: scores never leave the SM; only the row log-sum-exp is kept for backward
+            out, lse = flash_attention_forward(q, k, v, causal, scale)
+            ctx.save_for_backward(qkv, lse, out)
+            ctx.flash = True
+        else:
+            qh, kh, vh = (t.permute(0, 2, 1, 3) for t in (q, k, v))
+            p = torch.empty(b, heads, s, s, dtype=qkv.dtype, device=qkv.device)
+            gemm(qh, kh, out=p, causal=1 if causal else 0)
+            softmax_inplace_(p, scale, causal)
+            out = torch.empty(b, s, heads * hd, dtype=qkv.dtype, device=qkv.device)
+            gemm(p, vh.transpose(-1, -2), out=out.view(b, s, heads, hd).permute(0, 2, 1, 3), causal=2 if causal else 0)
+            ctx.save_for_backward(qkv, p)
+            ctx.flash = False
         ctx.meta = (heads, hd, layout, causal, scale, rope)
         return out
 
@@ -164,11 +214,24 @@ class _QKVAttentionFn(torch.autograd.Function):
     def backward(ctx, go):
         from .softmax import _rope_launch
 
-        qkv, p = ctx.saved_tensors
         heads, hd, layout, causal, scale, rope = ctx.meta
+        if ctx.flash:
+            qkv, lse, out_saved = ctx.saved_tensors
+        else:
+            qkv, p = ctx.saved_tensors
         b, s = qkv.shape[0], qkv.shape[1]
         shape5 = (b, s, heads, 3, hd) if layout == "h3d" else (b, s, 3, heads, hd)
         q, k, v = _split_qkv(qkv.view(shape5), layout)
+        if ctx.flash:
+            dqkv = torch.empty_like(qkv)
+            dq, dk, dv = _split_qkv(dqkv.view(shape5), layout)
+            flash_attention_backward(q, k, v, out_saved.view(b, s, heads, hd), go.contiguous().view(b, s, heads, hd), lse, dq, dk,
+                                     dv, causal, scale)
+            if rope is not None:
+                cos, sin, rot, neox = rope
+                for t in (dq, dk):
+                    _rope_launch(_tok_view(t), cos, sin, rot, neox, None, True)
+            return dqkv, None, None, None, None, None, None
         dqkv = torch.empty_like(qkv)
         dq, dk, dv = _split_qkv(dqkv.view(shape5), layout)
         goh = go.contiguous().view(b, s, heads, hd).permute(0, 2, 1, 3)

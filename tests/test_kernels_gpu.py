@@ -185,6 +185,25 @@ def test_rope(neox):
 
 
 @pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("hd", [64, 128])
+def test_flash_attention_backward(causal, hd):
+    from oslo_b200.ops.attention import attention, attention_reference
+
+    torch.manual_seed(17)
+    b, s, nh = 2, 512, 2
+    qkv = (torch.randn(b, s, nh, 3, hd, device=DEV) * 0.6).to(torch.bfloat16).requires_grad_()
+    out = attention(qkv[..., 0, :], qkv[..., 1, :], qkv[..., 2, :], causal=causal)
+    g = torch.randn_like(out)
+    out.backward(g)
+    ref_in = qkv.detach().float().requires_grad_()
+    ref = attention_reference(ref_in[..., 0, :], ref_in[..., 1, :], ref_in[..., 2, :], causal=causal)
+    ref.backward(g.float())
+    assert _rel(out, ref) < 2e-2
+    for i, name in enumerate("qkv"):
+        assert _rel(qkv.grad[..., i, :], ref_in.grad[..., i, :]) < 4e-2, name
+
+
+@pytest.mark.parametrize("causal", [True, False])
 def test_attention(causal):
     from oslo_b200.ops.attention import attention, attention_reference
 
