@@ -161,6 +161,89 @@ __global__ void moe_dispatch_bwd_kernel(const T* __restrict__ dbuf, const int* _
   }
 }
 
+// ---- peer-memory variants: the all-to-all of the expert buffers is done by the gather / scatter itself ----
+// Expert buffers live in symmetric memory on their owner, laid out [local expert][source rank][C]; slot = expert * C +
+// position as above.  `pull`: y[s] = sum_k w[s,k] * buffer_of_owner[row]  (combine forward; dispatch backward with w = 1).
+struct SrcPtrs {
+  const void* p[8];
+};
+OSLO_DEVINL size_t peer_row(int sl, int C, int experts_per_rank, int ep_size, int src_rank, int& owner) {
+  const int e = sl / C, c = sl - e * C;
+  owner = e / experts_per_rank;
+  const int le = e - owner * experts_per_rank;
+  return (static_cast<size_t>(le) * ep_size + src_rank) * C + c;
+}
+
+template <typename T>
+__global__ void moe_pull_kernel(SrcPtrs src, const float* __restrict__ w, const int* __restrict__ slot, T* __restrict__ y, int S,
+                                int K, int H, int ep_size, int my_rank, int experts_per_rank, int C) {
+  const int s = blockIdx.x;
+  for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < K; ++k) {
+      const int sl = slot[s * K + k];
+      if (sl < 0) continue;
+      int owner;
+      const size_t row = peer_row(sl, C, experts_per_rank, ep_size, my_rank, owner);
+      const float wk = w ? w[s * K + k] : 1.0f;
+      const uint4 raw = *reinterpret_cast<const uint4*>(static_cast<const T*>(src.p[owner]) + row * H + c);
+      const T* v = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += wk * static_cast<float>(v[j]);
+    }
+    T o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = static_cast<T>(acc[j]);
+    *reinterpret_cast<uint4*>(y + static_cast<size_t>(s) * H + c) = *reinterpret_cast<const uint4*>(o);
+  }
+}
+
+// `push scaled` (combine backward): grad_buffer_of_owner[row] = w[s,k] * dy[s]  and  dw[s,k] = <dy[s], buffer_of_owner[row]>.
+template <typename T>
+__global__ void moe_push_scaled_kernel(const T* __restrict__ dy, DestPtrs gdst, SrcPtrs xsrc, const float* __restrict__ w,
+                                       const int* __restrict__ slot, float* __restrict__ dw, int S, int K, int H, int ep_size,
+                                       int my_rank, int experts_per_rank, int C) {
+  __shared__ float red[32];
+  const int s = blockIdx.x;
+  for (int k = 0; k < K; ++k) {
+    const int sl = slot[s * K + k];
+    if (sl < 0) {
+      if (threadIdx.x == 0) dw[s * K + k] = 0.f;
+      continue;
+    }
+    int owner;
+    const size_t row = peer_row(sl, C, experts_per_rank, ep_size, my_rank, owner);
+    const float wk = w[s * K + k];
+    const T* xr = static_cast<const T*>(xsrc.p[owner]) + row * H;
+    T* gr = static_cast<T*>(gdst.p[owner]) + row * H;
+    float dot = 0.f;
+    for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+      const uint4 graw = *reinterpret_cast<const uint4*>(dy + static_cast<size_t>(s) * H + c);
+      const uint4 xraw = *reinterpret_cast<const uint4*>(xr + c);
+      const T* g = reinterpret_cast<const T*>(&graw);
+      const T* x = reinterpret_cast<const T*>(&xraw);
+      T o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float gv = static_cast<float>(g[j]);
+        dot += gv * static_cast<float>(x[j]);
+        o[j] = static_cast<T>(wk * gv);
+      }
+      *reinterpret_cast<uint4*>(gr + c) = *reinterpret_cast<const uint4*>(o);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = dot;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int i = 0; i < (blockDim.x + 31) / 32; ++i) t += red[i];
+      dw[s * K + k] = t;
+    }
+  }
+}
+
 }  // namespace oslo
 
 using namespace oslo;
@@ -210,5 +293,37 @@ extern "C" int oslo_moe_dispatch_backward(const void* dbuf, const int* slot, voi
                                           void* stream) {
   if (S <= 0) return 0;
   OSLO_MOE_DTYPE((moe_dispatch_bwd_kernel<T><<<S, 256, 0, (cudaStream_t)stream>>>((const T*)dbuf, slot, (T*)dx, S, K, H)));
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// 16-bit types only (rows are moved as 16-byte packets of 8 elements); src_ptrs: host array of ep_size device pointers.
+extern "C" int oslo_moe_pull(void* const* src_ptrs, int ep_size, const float* w, const int* slot, void* y, int S, int K, int H,
+                             int my_rank, int experts_per_rank, int C, int dtype, void* stream) {
+  if (S <= 0) return 0;
+  if (H % 8 || ep_size > 8 || dtype == 0) return -1;
+  SrcPtrs sp;
+  for (int i = 0; i < 8; ++i) sp.p[i] = i < ep_size ? src_ptrs[i] : nullptr;
+  if (dtype == 1)
+    moe_pull_kernel<__half><<<S, 128, 0, (cudaStream_t)stream>>>(sp, w, slot, (__half*)y, S, K, H, ep_size, my_rank, experts_per_rank, C);
+  else
+    moe_pull_kernel<__nv_bfloat16><<<S, 128, 0, (cudaStream_t)stream>>>(sp, w, slot, (__nv_bfloat16*)y, S, K, H, ep_size, my_rank, experts_per_rank, C);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int oslo_moe_push_scaled(const void* dy, void* const* grad_dst_ptrs, void* const* x_src_ptrs, int ep_size, const float* w,
+                                    const int* slot, float* dw, int S, int K, int H, int my_rank, int experts_per_rank, int C,
+                                    int dtype, void* stream) {
+  if (S <= 0) return 0;
+  if (H % 8 || ep_size > 8 || dtype == 0) return -1;
+  DestPtrs d;
+  SrcPtrs sp;
+  for (int i = 0; i < 8; ++i) {
+    d.p[i] = i < ep_size ? grad_dst_ptrs[i] : nullptr;
+    sp.p[i] = i < ep_size ? x_src_ptrs[i] : nullptr;
+  }
+  if (dtype == 1)
+    moe_push_scaled_kernel<__half><<<S, 128, 0, (cudaStream_t)stream>>>((const __half*)dy, d, sp, w, slot, dw, S, K, H, ep_size, my_rank, experts_per_rank, C);
+  else
+    moe_push_scaled_kernel<__nv_bfloat16><<<S, 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)dy, d, sp, w, slot, dw, S, K, H, ep_size, my_rank, experts_per_rank, C);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -41,8 +41,10 @@ class _EmbedPull(torch.autograd.Function):
         all_g = comm.all_gather(g2, dim=0, parallel_context=pc, parallel_mode=mode)
         local = all_ids - rank * v_local
         mine = (local >= 0) & (local < v_local)
+        # masked scatter-add without boolean indexing (which would synchronise with the host and cannot be captured
+        # in a CUDA graph): rows of other ranks' vocabulary add zeros to row 0
         gw = torch.zeros(v_local, h, dtype=torch.float32, device=g.device)
-        gw.index_add_(0, local[mine], all_g[mine].float())
+        gw.index_add_(0, local.clamp(0, v_local - 1), all_g.float() * mine.unsqueeze(1))
         return None, gw.to(dtype), None, None, None
 
 

@@ -198,8 +198,15 @@ class ExpertParallelFrontBlock(nn.Module):
         l_aux, slot, weight, C = self.gate(tokens)
         link.l_aux, link.slot, link.weight, link.capacity = l_aux, slot, weight, C
         E = self.ep_size * self.num_local_experts
-        buf = moe_ops.dispatch(tokens, slot, E * C)
-        buf = _all_to_all_experts(buf, self.ep_size, self.num_local_experts, C, self.parallel_context)
+        from . import fused
+
+        link.fused = fused.available(tokens, self.ep_size)
+        if link.fused:
+            # the dispatch kernel stores every token row straight into its expert's buffer on the owning GPU
+            buf = fused.PeerDispatch.apply(tokens, slot, self.parallel_context, self.ep_size, self.num_local_experts, C)
+        else:
+            buf = moe_ops.dispatch(tokens, slot, E * C)
+            buf = _all_to_all_experts(buf, self.ep_size, self.num_local_experts, C, self.parallel_context)
         out = self.experts(buf)
         if self.residual is not None:
             link.residual_in = tokens
@@ -217,6 +224,13 @@ class ExpertParallelBehindBlock(nn.Module):
     def forward(self, x):  # x: [E_local, ep * C, ffn]
         link = self.link
         out = self.experts(x)
+        if getattr(link, "fused", False):
+            from . import fused
+
+            y = fused.PeerCombine.apply(out, link.weight, link.slot, self.parallel_context, self.ep_size, self.num_local_experts,
+                                        link.capacity)
+            y = y.view(*link.in_shape[:-1], y.shape[-1])
+            return (y, None) if self.skip_bias_add else y
         out = _all_to_all_experts(out, self.ep_size, self.num_local_experts, link.capacity, self.parallel_context, inverse=True)
         y = moe_ops.combine(out.reshape(-1, out.shape[-1]), link.weight.to(out.dtype), link.slot)
         y = y.view(*link.in_shape[:-1], y.shape[-1])

@@ -154,3 +154,44 @@ def _zero_worker(rank, world):
 @pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
 def test_fused_zero_step_matches_collective_path():
     run_dist(_zero_worker, 2, timeout=600)
+
+
+def _moe_worker(rank, world):
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import oslo_b200
+    from oslo_b200 import ParallelContext, ParallelMode
+    from oslo_b200.distributed import symm
+    from oslo_b200.models import MoEGPTConfig, MoEGPTLMHeadModel
+    from oslo_b200.ops import _lib
+    from oslo_b200.parallel import ExpertParallel
+
+    pc = ParallelContext.from_torch(expert_parallel_size=world, backend="nccl", seed=0)
+    dev = pc.device
+    cfg = MoEGPTConfig(vocab_size=512, n_positions=64, n_embd=128, n_layer=2, n_head=4, resid_pdrop=0.0, embd_pdrop=0.0,
+                       attn_pdrop=0.0, num_experts=4, moe_every=2, top_k=2)
+    res = {}
+    for fused in (False, True):
+        torch.manual_seed(0)
+        model = MoEGPTLMHeadModel(cfg).to(dev, torch.bfloat16)
+        wrapped = ExpertParallel(model, pc, num_dec_experts={1: 4}, top_k=2, capacity_factor_train=2.0, use_rts=False)
+        oslo_b200.ready(wrapped, pc)
+        wrapped.eval()
+        symm._fused_small_ops = fused
+        torch.manual_seed(5 + rank)
+        ids = torch.randint(0, 512, (2, 64), device=dev)
+        loss = wrapped(input_ids=ids, labels=ids).loss
+        loss.backward()
+        torch.cuda.synchronize()
+        _lib.check_status()
+        res[fused] = (loss.item(), {k: p.grad.float().clone() for k, p in model.named_parameters() if p.grad is not None})
+    symm._fused_small_ops = False
+    assert abs(res[True][0] - res[False][0]) < 2e-2, (res[True][0], res[False][0])
+    for k, g in res[False][1].items():
+        a = res[True][1][k]
+        assert (a - g).abs().max().item() <= 6e-2 * (g.abs().max().item() + 1e-3), k
+    pc.destroy()
+
+
+@pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_moe_peer_dispatch_combine_matches_all_to_all():
+    run_dist(_moe_worker, 2, timeout=600)
