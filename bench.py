@@ -311,8 +311,17 @@ def main():
             "gpu_launches": calls,
             "loss": loss_val,
         }
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
     dist.barrier()
+    torch.cuda.synchronize()
+    if graphed is not None:
+        # a captured step holds NCCL work; tearing communicators down underneath a live graph can block, so drop the
+        # graph first and leave without the communicator destructors (the result line is already out)
+        graphed.graph = None
+        graphed = None
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     pc.destroy()
     return 0
 
