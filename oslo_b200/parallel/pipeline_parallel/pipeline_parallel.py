@@ -158,6 +158,11 @@ class PipelineParallel(ParallelWrapper):
         prev_rank = pc.get_prev_global_rank(ParallelMode.PIPELINE)
         next_rank = pc.get_next_global_rank(ParallelMode.PIPELINE)
         micro = self._split_kwargs(kwargs)
+        if pc.tensor_parallel_size > 1 and pc.tensor_parallel_mode != ParallelMode.TENSOR_1D:
+            # the stage functions bypass TensorParallel.forward, so the N-D input split happens here, per micro-batch
+            from oslo_b200.parallel.tensor_parallel._wrapper_nd import scatter_batch_inputs
+
+            micro = [scatter_batch_inputs(self.module, (), kw, pc)[1] for kw in micro]
         warmup = min(P - 1 - s, M)
         inputs: Dict[int, Optional[torch.Tensor]] = {}
         outputs: Dict[int, torch.Tensor] = {}

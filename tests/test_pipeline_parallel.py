@@ -70,3 +70,40 @@ def _worker(rank, world, micro):
 @pytest.mark.parametrize("world,micro", [(2, 2), (2, 4), (4, 4)])
 def test_pipeline_matches_unsplit_model(world, micro):
     run_dist(_worker, world, micro)
+
+
+def _llama(seed=0):
+    from oslo_b200.models import LlamaConfig, LlamaForCausalLM
+
+    torch.manual_seed(seed)
+    return LlamaForCausalLM(LlamaConfig(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=4,
+                                        num_attention_heads=4, max_position_embeddings=32))
+
+
+def _pp_tp2d_worker(rank, world):
+    import oslo_b200
+    from oslo_b200 import ParallelContext, ParallelMode
+    from oslo_b200.parallel import PipelineParallel, TensorParallel
+
+    pc = ParallelContext.from_torch(tensor_parallel_size=4, pipeline_parallel_size=2, tensor_parallel_mode=ParallelMode.TENSOR_2D,
+                                    backend="gloo", seed=0)
+    ref = _llama()
+    model = _llama()
+    TensorParallel(model, pc)
+    wrapped = PipelineParallel(model, pc, num_micro_batches=2)
+    oslo_b200.ready(wrapped, pc)
+    torch.manual_seed(3)
+    ids = torch.randint(0, 128, (8, 16))
+    ref_loss = sum(ref(input_ids=c, labels=c).loss.item() for c in ids.chunk(2)) / 2
+    total = 0.0
+    for _, out in wrapped(input_ids=ids, labels=ids):
+        out.loss.backward()
+        if wrapped.stage == 1:
+            total += out.loss.item()
+    if wrapped.stage == 1:
+        assert abs(total - ref_loss) < 1e-4, (total, ref_loss)
+    pc.destroy()
+
+
+def test_pipeline_with_2d_tensor_parallel():
+    run_dist(_pp_tp2d_worker, 8, timeout=900)
