@@ -30,6 +30,39 @@ def _build(kind):
         return GPTNeoXForCausalLM(GPTNeoXConfig(vocab_size=100, hidden_size=32, num_hidden_layers=2, num_attention_heads=4,
                                                 intermediate_size=64, max_position_embeddings=32, hidden_dropout=0.0,
                                                 attention_dropout=0.0)).eval()
+    if kind == "roberta":
+        from transformers import RobertaConfig, RobertaForMaskedLM
+
+        return RobertaForMaskedLM(RobertaConfig(vocab_size=100, hidden_size=32, num_hidden_layers=2, num_attention_heads=4,
+                                                intermediate_size=64, max_position_embeddings=40, hidden_dropout_prob=0.0,
+                                                attention_probs_dropout_prob=0.0)).eval()
+    if kind == "distilbert":
+        from transformers import DistilBertConfig, DistilBertForMaskedLM
+
+        return DistilBertForMaskedLM(DistilBertConfig(vocab_size=100, dim=32, n_layers=2, n_heads=4, hidden_dim=64,
+                                                      max_position_embeddings=32, dropout=0.0, attention_dropout=0.0)).eval()
+    if kind == "electra":
+        from transformers import ElectraConfig, ElectraForMaskedLM
+
+        return ElectraForMaskedLM(ElectraConfig(vocab_size=100, embedding_size=32, hidden_size=32, num_hidden_layers=2,
+                                                num_attention_heads=4, intermediate_size=64, max_position_embeddings=32,
+                                                hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)).eval()
+    if kind == "albert":
+        from transformers import AlbertConfig, AlbertForMaskedLM
+
+        return AlbertForMaskedLM(AlbertConfig(vocab_size=100, embedding_size=16, hidden_size=32, num_hidden_layers=2,
+                                              num_attention_heads=4, intermediate_size=64, max_position_embeddings=32,
+                                              hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)).eval()
+    if kind == "llama":
+        from transformers import LlamaConfig, LlamaForCausalLM
+
+        return LlamaForCausalLM(LlamaConfig(vocab_size=100, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                                            num_attention_heads=4, max_position_embeddings=32)).eval()
+    if kind == "opt":
+        from transformers import OPTConfig, OPTForCausalLM
+
+        return OPTForCausalLM(OPTConfig(vocab_size=100, hidden_size=32, ffn_dim=64, num_hidden_layers=2, num_attention_heads=4,
+                                        max_position_embeddings=32, word_embed_proj_dim=32, dropout=0.0)).eval()
     raise KeyError(kind)
 
 
@@ -61,7 +94,7 @@ def _worker(rank, world, kind, tmp):
     pc.destroy()
 
 
-@pytest.mark.parametrize("kind", ["gpt2", "bert", "gpt_neox"])
+@pytest.mark.parametrize("kind", ["gpt2", "bert", "gpt_neox", "roberta", "distilbert", "electra", "albert", "llama", "opt"])
 def test_hf_model_tensor_parallel_1d(kind):
     with tempfile.TemporaryDirectory() as tmp:
         run_dist(_worker, 2, kind, tmp, timeout=600)
