@@ -5,9 +5,9 @@
 //
 //   warp 0     TMA producer: Q tile once, then K tiles (pass 1), then K and V tiles (pass 2), 2-stage rings
 //   warp 1     MMA issuer: S = Q K_j^T into one of two TMEM buffers; O += P_j V_j into a third
-//   warps 2-5  softmax: one thread per query row.  Pass 1 keeps the running row max and row sum (online, scalars only);
-//              pass 2 recomputes S, writes P = exp2(S - max) as bf16 into shared memory in the swizzled operand layout
-//              the MMA reads, and finally scales O by 1 / sum, stages it and stores it with TMA.
+//   warps 2-5  softmax: one thread per query row.  Pass 1 finds the row max (no exponentials); pass 2 recomputes S,
+//              writes P = exp2(S - max) as bf16 into shared memory in the swizzled operand layout the MMA reads while
+//              summing the row, and finally scales O by 1 / sum, stages it and stores it with TMA.
 //
 // Two passes over K trade one extra Q K^T product (tensor cores are idle most of the time here: the exponentials are
 // the bottleneck) for never having to rescale the O accumulator in tensor memory.  The row log-sum-exp is written for
@@ -187,13 +187,13 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     int sb = 0;
     uint32_t sph = 0, peph = 0;
     bool ok = true;
-    // pass 1: running max / sum
+    // pass 1: row maximum only (the row sum is accumulated in pass 2 from the very exponentials written to P, so the
+    // exponential unit is used once per score, not twice)
     for (int j = 0; j < nkv && ok; ++j) {
       if (!mbar_wait_bounded(&s_full[sb], sph, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const bool diag = p.causal && j == qb;
       float bm = -INFINITY;
-      float vals[4][32];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t r[32];
@@ -202,23 +202,14 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float t = __uint_as_float(r[i]) * p.scale_log2;
-          if (diag && c * 32 + i > row) t = -INFINITY;
-          vals[c][i] = t;
-          bm = fmaxf(bm, t);
+          const float t = __uint_as_float(r[i]);
+          if (!(diag && c * 32 + i > row)) bm = fmaxf(bm, t);
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[sb]);
-      const float mn = fmaxf(m, bm);
-      float sum = 0.f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-#pragma unroll
-        for (int i = 0; i < 32; ++i) sum += exp2f(vals[c][i] - mn);
-      l = l * exp2f(m - mn) + sum;
-      m = mn;
+      m = fmaxf(m, bm * p.scale_log2);
       if (++sb == 2) { sb = 0; sph ^= 1; }
     }
     // pass 2: P tiles
@@ -243,6 +234,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             float a1 = exp2f(__uint_as_float(r[i0 + 1]) * p.scale_log2 - m);
             if (diag && c * 32 + i0 > row) a0 = 0.f;
             if (diag && c * 32 + i0 + 1 > row) a1 = 0.f;
+            l += a0 + a1;
             if (p.is_bf16) { const __nv_bfloat162 hh = __floats2bfloat162_rn(a0, a1); packed[e] = *reinterpret_cast<const uint32_t*>(&hh); }
             else { const __half2 hh = __floats2half2_rn(a0, a1); packed[e] = *reinterpret_cast<const uint32_t*>(&hh); }
           }
