@@ -35,12 +35,12 @@ CONFIGS = {
 
 
 def reference_arm(args):
-    """The unmodified reference cannot be imported on this stack; say why in one line and exit 0."""
-    why = ("reference oslo-core 3.0.0 installed with --no-deps into baseline/_ref, but `import oslo` fails on the "
-           "GPU box: its import-time JIT build of oslo_ngram_repeat_block does not compile against torch 2.11 "
-           "headers (kaiming_uniform_ kFanIn enum error, -gencode compute_100), and anytree is absent")
-    print(json.dumps({"impl": "reference", "unavailable": why}))
-    return 0
+    """Run the unmodified reference package from ``baseline/_ref`` (see ``baseline/reference_arm.py``); if that attempt
+    fails, the line carries the traceback of this very attempt."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm as arm
+
+    return arm.run(args, CONFIGS, model_flops_per_token, ClockSampler)
 
 
 class ClockSampler(threading.Thread):
@@ -314,15 +314,24 @@ def main():
         print(json.dumps(out), flush=True)
     dist.barrier()
     torch.cuda.synchronize()
+    # orderly teardown: the captured step holds NCCL work, so the graph goes first, then the device drains, then the
+    # communicators are destroyed.  A timer ends the process only if a communicator destructor blocks.
+    guard = threading.Timer(90.0, lambda: os._exit(0))
+    guard.daemon = True
+    guard.start()
     if graphed is not None:
-        # a captured step holds NCCL work; tearing communicators down underneath a live graph can block, so drop the
-        # graph first and leave without the communicator destructors (the result line is already out)
-        graphed.graph = None
+        step = eager_step
+        graphed.graph.reset()
+        graphed.static_outputs = None
         graphed = None
-        sys.stdout.flush()
-        sys.stderr.flush()
-        os._exit(0)
+        import gc
+
+        gc.collect()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
     pc.destroy()
+    guard.cancel()
     return 0
 
 
