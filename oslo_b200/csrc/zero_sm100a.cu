@@ -9,7 +9,12 @@
 // barrier before (gradients final everywhere) and after (parameters landed everywhere) brackets the kernel.
 //
 // mode 0: only the squared norm of the reduced shard is accumulated (for global-norm clipping);
-// mode 1: update, with an optional device scalar multiplying the gradient (the clip coefficient).
+// mode 1: pull + update + push, with an optional device scalar multiplying the gradient (the clip coefficient);
+// mode 2: pull once, keep the reduced, scaled fp32 gradients of the shard in `reduced` and accumulate their squared norm
+//         (launched per bucket while backward is still running);
+// mode 3: update from `reduced` (no second pull) with the clip coefficient, then push.
+// A clip coefficient that is not finite (the global norm overflowed) makes modes 1 and 3 return without touching
+// parameters or moments: the step is skipped on every rank, with no host round trip.
 //
 // Replaces the reference's bucket reduce + per-owner broadcasts + separate optimizer kernels
 // (oslo/torch/nn/parallel/data_parallel/zero/optim/optim.py:354-634).
@@ -27,6 +32,7 @@ struct ZeroArgs {
   int adamw, mode, world, is_bf16;
   const float* clip_coef;  // optional device scalar
   float* sumsq_out;        // optional: += sum of squares of the reduced, scaled shard
+  float* reduced;          // modes 2 / 3: fp32 reduced gradients of this shard
 };
 
 OSLO_DEVINL void unpack8(const uint4& raw, bool bf16, float* f) {
@@ -54,22 +60,32 @@ __global__ void __launch_bounds__(256) zero_step_kernel(ZeroPeers peers, float* 
   __shared__ float red[8];
   const long long nvec = shard_len / 8;
   const bool bf16 = a.is_bf16 != 0;
-  const float gs = a.grad_scale * ((a.mode == 1 && a.clip_coef) ? *a.clip_coef : 1.0f);
+  const bool updating = a.mode == 1 || a.mode == 3;
+  const float coef = (updating && a.clip_coef) ? *a.clip_coef : 1.0f;
+  if (updating && !(fabsf(coef) <= 3.0e38f)) return;  // NaN or infinity: skip this step
+  const float gs = a.mode == 3 ? coef : a.grad_scale * coef;
   float local_sq = 0.f;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
     const long long e0 = shard_start + i * 8;
-    uint4 raw[8];
-#pragma unroll
-    for (int r = 0; r < 8; ++r)
-      if (r < a.world) raw[r] = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(peers.grad[r]) + e0);
+    const long long off = i * 8;
     float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (a.mode == 3) {
+      const float4 lo = *reinterpret_cast<const float4*>(a.reduced + off);
+      const float4 hi = *reinterpret_cast<const float4*>(a.reduced + off + 4);
+      g[0] = lo.x; g[1] = lo.y; g[2] = lo.z; g[3] = lo.w; g[4] = hi.x; g[5] = hi.y; g[6] = hi.z; g[7] = hi.w;
+    } else {
+      uint4 raw[8];
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
-      if (r < a.world) {
-        float f[8];
-        unpack8(raw[r], bf16, f);
+      for (int r = 0; r < 8; ++r)
+        if (r < a.world) raw[r] = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(peers.grad[r]) + e0);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) g[j] += f[j];
+      for (int r = 0; r < 8; ++r) {
+        if (r < a.world) {
+          float f[8];
+          unpack8(raw[r], bf16, f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) g[j] += f[j];
+        }
       }
     }
 #pragma unroll
@@ -78,8 +94,12 @@ __global__ void __launch_bounds__(256) zero_step_kernel(ZeroPeers peers, float* 
       local_sq += g[j] * g[j];
     }
     if (a.mode == 0) continue;
+    if (a.mode == 2) {
+      *reinterpret_cast<float4*>(a.reduced + off) = make_float4(g[0], g[1], g[2], g[3]);
+      *reinterpret_cast<float4*>(a.reduced + off + 4) = make_float4(g[4], g[5], g[6], g[7]);
+      continue;
+    }
     float pnew[8];
-    const long long off = i * 8;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       float pv = master[off + j];
@@ -120,16 +140,18 @@ __global__ void __launch_bounds__(256) zero_step_kernel(ZeroPeers peers, float* 
 extern "C" int oslo_zero_step(void* const* peer_grads, void* const* peer_params, float* master, float* m, float* v,
                               long long shard_start, long long shard_len, int world, int is_bf16, float lr, float beta1,
                               float beta2, float eps, float weight_decay, float bc1, float bc2, float grad_scale, int adamw,
-                              int mode, const float* clip_coef, float* sumsq_out, int num_sms, void* stream) {
+                              int mode, const float* clip_coef, float* sumsq_out, int num_sms, void* stream,
+                              float* reduced) {
   using namespace oslo;
   if (shard_len <= 0) return 0;
   if (world > 8 || shard_start % 8 || shard_len % 8) return -1;
+  if ((mode == 2 || mode == 3) && (reduced == nullptr || (reinterpret_cast<uintptr_t>(reduced) & 15))) return -1;
   ZeroPeers peers;
   for (int i = 0; i < 8; ++i) {
     peers.grad[i] = i < world ? peer_grads[i] : nullptr;
     peers.param[i] = i < world ? peer_params[i] : nullptr;
   }
-  ZeroArgs a{lr, beta1, beta2, eps, weight_decay, 1.f / bc1, 1.f / sqrtf(bc2), grad_scale, adamw, mode, world, is_bf16, clip_coef, sumsq_out};
+  ZeroArgs a{lr, beta1, beta2, eps, weight_decay, 1.f / bc1, 1.f / sqrtf(bc2), grad_scale, adamw, mode, world, is_bf16, clip_coef, sumsq_out, reduced};
   long long blocks = (shard_len / 8 + 255) / 256;
   const long long cap = (long long)num_sms * 8;
   if (blocks > cap) blocks = cap;

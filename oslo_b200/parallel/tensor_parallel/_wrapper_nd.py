@@ -142,6 +142,7 @@ def parallelize_nd(tp):
             if hasattr(m, attr) and isinstance(getattr(m, attr), int) and m is not module:
                 v = getattr(m, attr)
                 if v % feature_div == 0:
+                    tp._divided_attrs.append((m, attr, v))  # rolled back by deparallelize()
                     setattr(m, attr, v // feature_div)
 
     marked = set()

@@ -99,6 +99,7 @@ class TensorParallel(ParallelWrapper):
         self.sp_state = SequenceParallelState(self.parallel_context) if sequence_parallel else None
         self._sp_params = []
         self._sp_callback_queued = False
+        self._divided_attrs = []  # (module, attribute, value before the division by the tensor-parallel size)
         add_wrapper(module, ParallelMode.TENSOR, self)
 
     # ------------------------------------------------------------------ forward
@@ -210,6 +211,7 @@ class TensorParallel(ParallelWrapper):
                 if hasattr(m, attr) and isinstance(getattr(m, attr), int) and not isinstance(m, type(module)):
                     v = getattr(m, attr)
                     if v % tp == 0:
+                        self._divided_attrs.append((m, attr, v))  # rolled back by deparallelize()
                         setattr(m, attr, v // tp)
 
         for name, child in list(module.named_modules()):
@@ -391,6 +393,22 @@ class TensorParallel(ParallelWrapper):
             _set_child(module, name, _restore_plain(child, full))
         if hasattr(module, "orig_vocab_size"):
             module.padded_vocab_size = module.orig_vocab_size
+        # per-module arguments that were divided by the tensor-parallel size (head counts, split sizes, ...) get their
+        # original values back (the reference's _rollback_mp_arguments, .../_1d/_wrapper.py)
+        for m, attr, value in reversed(self._divided_attrs):
+            setattr(m, attr, value)
+        self._divided_attrs = []
+        # gradient-sync bookkeeping refers to parameters that no longer exist
+        self._sp_params = []
+        self._sp_callback_queued = False
+        if hasattr(self, "_replicated"):
+            self._replicated = {}
+            self._rep_callback_queued = False
+        for m in module.modules():
+            if getattr(m, "sequence_parallel_state", None) is not None:
+                m.sequence_parallel_state = None
+        self.sp_state = None
+        self.sequence_parallel = False
         self._parallelized = False
 
 

@@ -222,7 +222,8 @@ class Trainer:
                     self.profiler = FlopsProfiler(self.base_model)
                     self.profiler.start_profile()
                 ctx = self.model.no_sync() if (not sync_now and hasattr(self.model, "no_sync")) else _null()
-                with ctx:
+                zctx = self.zero.no_sync() if (not sync_now and self.zero is not None) else _null()
+                with ctx, zctx:
                     running += float(self.training_step(batch))
                 if profile:
                     self.profiler.stop_profile()
@@ -360,7 +361,9 @@ class Trainer:
             self.base_model.load_state_dict(torch.load(os.path.join(path, "pytorch_model.bin"), map_location="cpu"))
         opt_file = os.path.join(path, f"optimizer_{rank}.pt" if self.pc is not None else "optimizer.pt")
         if os.path.exists(opt_file):
-            self.optimizer.load_state_dict(torch.load(opt_file, map_location="cpu"))
+            self.optimizer.load_state_dict(torch.load(opt_file, map_location="cpu", weights_only=False))
+        elif self.zero is not None:
+            self.zero.resync_master()  # the fp32 master shards must follow the weights that were just loaded
         sched = os.path.join(path, "scheduler.pt")
         if os.path.exists(sched):
             self.lr_scheduler.load_state_dict(torch.load(sched))

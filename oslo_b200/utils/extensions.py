@@ -69,7 +69,11 @@ def _merged_state_dict(model, pc):
     cache = {}
     for key, p in base.state_dict(keep_vars=True).items():
         spec = getattr(p, "oslo_shard", None)
-        if spec is not None:
+        if getattr(p, "oslo_pipeline_released", False):
+            # another pipeline stage owns this tensor (every rank of this tensor-parallel group released it, so skipping
+            # the merge keeps the collective order identical inside the group); the pipeline hook below fills it in
+            out[key] = p.detach().cpu()
+        elif spec is not None:
             if id(p) not in cache:
                 cache[id(p)] = merge(p.data, spec, pc).cpu()
             out[key] = cache[id(p)]
