@@ -114,6 +114,9 @@ def main():
     ap.add_argument("--no-sequence-parallel", action="store_true")
     ap.add_argument("--no-fused-collectives", action="store_true")
     ap.add_argument("--no-cuda-graph", action="store_true", help="launch every kernel from the host instead of replaying a captured step")
+    ap.add_argument("--kernel-table", default=None, metavar="FILE",
+                    help="after the timed runs, trace two eager steps with torch.profiler on rank 0 and write the per-kernel "
+                         "device-time table to FILE (a diagnosis aid: times taken under the profiler are never reported)")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the device-timed steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     args = ap.parse_args()
@@ -314,6 +317,24 @@ def main():
         print(json.dumps(out), flush=True)
     dist.barrier()
     torch.cuda.synchronize()
+    if args.kernel_table:
+        from torch.profiler import ProfilerActivity, profile
+
+        run = eager_step if graphed is not None else step
+        acts = [ProfilerActivity.CUDA] if rank == 0 else []
+        if rank == 0:
+            with profile(activities=acts) as prof:
+                for i in range(2):
+                    run(dev_ids[i % len(dev_ids)])
+                torch.cuda.synchronize()
+            with open(args.kernel_table, "w") as f:
+                f.write(f"# two eager steps, rank 0 of {world}; device time per kernel under torch.profiler (shares, not absolutes)\n")
+                f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=40, max_name_column_width=90))
+        else:
+            for i in range(2):
+                run(dev_ids[i % len(dev_ids)])
+            torch.cuda.synchronize()
+        dist.barrier()
     # orderly teardown: the captured step holds NCCL work, so the graph goes first, then the device drains, then the
     # communicators are destroyed.  A timer ends the process only if a communicator destructor blocks.
     guard = threading.Timer(90.0, lambda: os._exit(0))

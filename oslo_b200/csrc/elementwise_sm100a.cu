@@ -550,6 +550,11 @@ extern "C" int oslo_colsum_noalloc(const void* x, void* out, long long rows, int
     fprintf(stderr, "oslo_colsum_noalloc: H = %d must be a multiple of %d for this dtype\n", H, P);
     return OSLO_NOALLOC_ERR_ARGUMENT;
   }
+  // the kernels read x and write out with 16-byte vectors: refuse a misaligned pointer here, before any launch
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) || x == nullptr || out == nullptr) {
+    fprintf(stderr, "oslo_colsum_noalloc: x (%p) and out (%p) must be non-null and 16-byte aligned\n", x, out);
+    return OSLO_NOALLOC_ERR_ARGUMENT;
+  }
   if (static_cast<long long>(H) > kNoAllocScratchFloats) {
     fprintf(stderr,
             "oslo_colsum_noalloc: H = %d columns exceeds the built-in scratch of %lld floats; use oslo_colsum with a "

@@ -91,14 +91,15 @@ extern "C" int oslo_ag_gemm(void* const* peer_in, void* x_full, const void* B, v
 }
 
 // peer_partial / peer_rs_flag: host arrays of `tp` device pointers (slot buffers [tp, T/tp, N] and flag arrays of
-// tp * chunks_per_shard ints).  A: [T, K] K-major (lda), out: [T/tp, N].
+// tp * chunks_per_shard ints).  A: [T, K] K-major (lda), out: [T/tp, N].  addend: optional local [T, N] (see below).
 extern "C" int oslo_gemm_rs(const void* A, long long lda, const void* B, long long ldb, int b_mn, void* out, const void* bias,
                             int T, int N, int K, int is_bf16, int tp, int rank, int epoch, void* const* peer_partial,
                             void* const* peer_rs_flag, int* tile_done, int reduce_ctas, int num_sms, int* status,
-                            void* stream_ptr, unsigned long long* debug_times, const int* epoch_ptr) {
+                            void* stream_ptr, unsigned long long* debug_times, const int* epoch_ptr, const void* addend) {
   if (tp > kMaxRanks || tp < 1 || T % tp) return -1;
   const int Tl = T / tp;
   if (Tl % kBlockM || N % 8 || K % 8 || lda % 8 || ldb % 8) return -5;
+  if (addend && (reinterpret_cast<uintptr_t>(addend) & 15)) return -5;
   bind_context_to_thread();
   reduce_ctas = 0;  // the reduction is folded into the epilogue of the tiles of our own rows
   const int gemm_ctas_max = num_sms;
@@ -107,8 +108,12 @@ extern "C" int oslo_gemm_rs(const void* A, long long lda, const void* B, long lo
   p.M = T; p.N = N; p.K = K; p.batch = 1; p.batch_inner = 1; p.causal = 0;
   p.m_blocks = T / kBlockM;
   p.n_blocks = (N + block_n - 1) / block_n;
-  p.epilogue = bias ? 1 : 0; p.accumulate = 0; p.is_bf16 = is_bf16;
-  p.bias = bias; p.c_ptr = out; p.ldc = N; p.stride_c = 0; p.stride_c_outer = 0; p.aux_ptr = nullptr;
+  p.epilogue = bias ? 1 : 0; p.is_bf16 = is_bf16;
+  // `addend`: a local, contiguous [T, N] partial product of this rank that is summed into every tile before it leaves
+  // (two row-parallel products that feed one reduce-scatter cross NVLink once)
+  p.accumulate = addend ? 1 : 0;
+  p.bias = bias; p.c_ptr = addend ? const_cast<void*>(addend) : out; p.ldc = N; p.stride_c = 0; p.stride_c_outer = 0;
+  p.aux_ptr = nullptr;
   p.status = status;
   FusedParams fp;
   fp.tp = tp; fp.rank = rank; fp.shard_rows = Tl; fp.epoch = epoch; fp.copy_ctas = reduce_ctas;

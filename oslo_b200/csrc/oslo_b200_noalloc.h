@@ -18,7 +18,8 @@
 //   * Limit: H (the number of columns) must not exceed OSLO_COLSUM_NOALLOC_MAX_SCRATCH_FLOATS; larger inputs are
 //     refused with OSLO_NOALLOC_ERR_TOO_LARGE and a message on stderr.  When parts x H would not fit, fewer row
 //     partitions are used, which only costs speed.  H must be a multiple of 4 (fp32) or 8 (fp16 / bf16), and
-//     x and out must be 16-byte aligned, as for oslo_colsum.
+//     x and out must be 16-byte aligned, as for oslo_colsum; a misaligned or null pointer is refused with
+//     OSLO_NOALLOC_ERR_ARGUMENT before anything is launched.
 //   * First call on a device: the first call made while a given device is current looks up the device address
 //     of the array and the SM count for that device and remembers them.  Make that first call outside any
 //     stream capture; later calls on the device only launch kernels.
@@ -32,7 +33,7 @@
 
 #define OSLO_COLSUM_NOALLOC_MAX_SCRATCH_FLOATS (1LL << 21)
 
-#define OSLO_NOALLOC_ERR_ARGUMENT (-1)   /* bad dtype code or H not a multiple of the vector width */
+#define OSLO_NOALLOC_ERR_ARGUMENT (-1)   /* bad dtype code, H not a multiple of the vector width, or x / out null or not 16-byte aligned */
 #define OSLO_NOALLOC_ERR_LAUNCH (-2)     /* a kernel launch failed */
 #define OSLO_NOALLOC_ERR_TOO_LARGE (-10) /* H exceeds the built-in scratch */
 #define OSLO_NOALLOC_ERR_SETUP (-11)     /* the one-time look-up of the scratch address failed */

@@ -272,8 +272,8 @@ class SymmetricWorkspace:
         return (self.supports(x, w) and t % self.tp == 0 and (t // self.tp) % 128 == 0 and t <= self.max_tokens
                 and n <= self.max_features and t * n * x.element_size() <= self.slot_bytes)
 
-    def ag_gemm(self, x_shard: torch.Tensor, weight: torch.Tensor):
-        """Returns ``(all_gather(x_shard) @ weight^T, all_gather(x_shard))``."""
+    def ag_gemm(self, x_shard: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None):
+        """Returns ``(all_gather(x_shard) @ weight^T (+ bias, added in the epilogue), all_gather(x_shard))``."""
         tl, k = x_shard.shape
         t = tl * self.tp
         n = weight.shape[0]
@@ -283,8 +283,12 @@ class SymmetricWorkspace:
         x_full = torch.empty(t, k, dtype=x_shard.dtype, device=x_shard.device)
         out = torch.empty(t, n, dtype=x_shard.dtype, device=x_shard.device)
         w, b_mn, ldb = self._weight_operand(weight)
+        if bias is not None:
+            if bias.shape != (n,):
+                raise ValueError("ag_gemm: bias must be [N]")
+            bias = bias.to(x_shard.dtype).contiguous()
         rc = _lib.cuda_lib().oslo_ag_gemm(
-            self._in_ptrs(parity), _lib.ptr(x_full), _lib.ptr(w), _lib.ptr(out), None, ctypes.c_int(t), ctypes.c_int(n),
+            self._in_ptrs(parity), _lib.ptr(x_full), _lib.ptr(w), _lib.ptr(out), _lib.ptr(bias), ctypes.c_int(t), ctypes.c_int(n),
             ctypes.c_int(k), ctypes.c_longlong(ldb), ctypes.c_int(b_mn), ctypes.c_int(1 if self.dtype == torch.bfloat16 else 0),
             ctypes.c_int(self.tp), ctypes.c_int(self.rank), ctypes.c_int(self.epoch), self._flag_ptrs(0),
             self._local_ptr(0), self._local_ptr(1), ctypes.c_int(self.copy_ctas), ctypes.c_int(_lib.num_sms()),
@@ -293,8 +297,10 @@ class SymmetricWorkspace:
             raise RuntimeError(f"oslo_ag_gemm failed ({rc})")
         return out, x_full
 
-    def gemm_rs(self, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None):
-        """Returns this rank's rows of ``reduce_scatter(x @ weight^T)``."""
+    def gemm_rs(self, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                addend: Optional[torch.Tensor] = None):
+        """Returns this rank's rows of ``reduce_scatter(x @ weight^T + addend)``; ``addend`` is an optional local
+        ``[T, N]`` partial product that rides along in the same reduce-scatter."""
         t, k = x.shape
         n = weight.shape[0]
         tl = t // self.tp
@@ -304,13 +310,17 @@ class SymmetricWorkspace:
         parity = self.epoch & 1
         out = torch.empty(tl, n, dtype=x.dtype, device=x.device)
         w, b_mn, ldb = self._weight_operand(weight)
+        if addend is not None:
+            if addend.shape != (t, n) or addend.dtype != x.dtype:
+                raise ValueError("gemm_rs: addend must be [T, N] in the operand dtype")
+            addend = addend.contiguous()
         rc = _lib.cuda_lib().oslo_gemm_rs(
             _lib.ptr(x), ctypes.c_longlong(x.stride(0)), _lib.ptr(w), ctypes.c_longlong(ldb), ctypes.c_int(b_mn),
             _lib.ptr(out), _lib.ptr(bias), ctypes.c_int(t), ctypes.c_int(n), ctypes.c_int(k),
             ctypes.c_int(1 if self.dtype == torch.bfloat16 else 0), ctypes.c_int(self.tp), ctypes.c_int(self.rank),
             ctypes.c_int(self.epoch), self._slot_ptrs(parity), self._flag_ptrs(1), self._local_ptr(2),
             ctypes.c_int(self.copy_ctas), ctypes.c_int(_lib.num_sms()), _lib.ptr(_lib.status_word(self.device)),
-            _lib.stream_ptr(), _lib.ptr(self.debug_times), _lib.ptr(self.epoch_dev))
+            _lib.stream_ptr(), _lib.ptr(self.debug_times), _lib.ptr(self.epoch_dev), _lib.ptr(addend))
         if rc:
             raise RuntimeError(f"oslo_gemm_rs failed ({rc})")
         return out
@@ -328,15 +338,15 @@ class _Runtime:
         # called with either a token shard (all-gather side) or full tokens (reduce-scatter side)
         return self.ws.ag_ok(x, w) or self.ws.rs_ok(x, w)
 
-    def ag_gemm(self, x_shard, weight):
+    def ag_gemm(self, x_shard, weight, bias=None):
         if not self.ws.ag_ok(x_shard, weight):
             raise RuntimeError("ag_gemm: operands not supported by the fused kernel")
-        return self.ws.ag_gemm(x_shard, weight)
+        return self.ws.ag_gemm(x_shard, weight, bias)
 
-    def gemm_rs(self, x, weight):
+    def gemm_rs(self, x, weight, addend=None):
         if not self.ws.rs_ok(x, weight):
             raise RuntimeError("gemm_rs: operands not supported by the fused kernel")
-        return self.ws.gemm_rs(x, weight)
+        return self.ws.gemm_rs(x, weight, addend=addend)
 
 
 def enable(pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 24, model=None) -> bool:

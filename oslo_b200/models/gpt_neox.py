@@ -46,14 +46,17 @@ class GPTNeoXAttention(nn.Module):
 
     def forward(self, hidden_states, attention_mask=None):
         qkv = self.query_key_value(hidden_states)  # [b, s, heads_local * 3 * hd]
+        return self.dense(self.core(qkv, attention_mask))  # (out, bias)
+
+    def core(self, qkv, attention_mask=None):
+        """Rotary embedding + causal attention on an already projected ``[b, s, heads_local * 3 * hd]`` tensor."""
         b, s = qkv.shape[0], qkv.shape[1]
         heads = qkv.shape[-1] // (3 * self.head_size)
         rope = None
         if self.rotary_ndims > 0:
             cos, sin = self._tables(s, qkv.device)
             rope = (cos, sin, self.rotary_ndims, True)
-        ctx = OF.qkv_attention(qkv, heads, self.head_size, layout="h3d", causal=True, rope=rope, mask=attention_mask)
-        return self.dense(ctx)  # (out, bias)
+        return OF.qkv_attention(qkv, heads, self.head_size, layout="h3d", causal=True, rope=rope, mask=attention_mask)
 
 
 class GPTNeoXMLP(nn.Module):
@@ -63,8 +66,14 @@ class GPTNeoXMLP(nn.Module):
         self.dense_4h_to_h = onn.Linear(config.intermediate_size, config.hidden_size, skip_bias_add=True)
 
     def forward(self, hidden_states):
-        h, bias = self.dense_h_to_4h(hidden_states)
-        h = OF.bias_gelu(h, bias)
+        up = self.dense_h_to_4h
+        if type(up) is onn.Linear and not up.reversed:
+            from oslo_b200.ops.gemm import linear_gelu
+
+            h = linear_gelu(hidden_states, up.weight, up.bias)  # bias + GELU in the GEMM epilogue
+        else:
+            h, bias = up(hidden_states)
+            h = OF.bias_gelu(h, bias)
         return self.dense_4h_to_h(h)  # (out, bias)
 
 
@@ -78,7 +87,59 @@ class GPTNeoXLayer(nn.Module):
         self.mlp = GPTNeoXMLP(config)
         self.hidden_dropout = config.hidden_dropout
 
+    def _paired_ok(self) -> bool:
+        """Sequence-parallel 1-D layers with a parallel residual and no active dropout: the two column linears share
+        one all-gather and the two row linears one reduce-scatter."""
+        qkv = self.attention.query_key_value
+        return (self.use_parallel_residual and getattr(qkv, "sequence_parallel", False)
+                and getattr(qkv, "world_size", 1) > 1 and not (self.training and self.hidden_dropout > 0)
+                and getattr(self.mlp.dense_4h_to_h, "sequence_parallel", False)
+                and self.input_layernorm.elementwise_affine and not qkv.reversed)
+
+    def _forward_paired(self, x, attention_mask):
+        """Parallel-residual block with HALF the NVLink traffic of four independent sequence-parallel linears.
+
+        Both LayerNorms normalise the same ``x``; they differ only in their affine parameters, which are folded into
+        the weights that consume them (``W (g * xhat + b) = (W diag(g)) xhat + W b``).  So the normalised shard
+        ``xhat`` is all-gathered ONCE and feeds both column linears, and the attention and MLP row products are summed
+        locally before ONE reduce-scatter.  Backward mirrors this: one all-gather of ``dY`` serves both row linears
+        and ``d xhat`` of both column linears leaves in one reduce-scatter.  The folds are ordinary autograd ops on
+        the (small, sharded) weights, so gradients of the LayerNorm parameters need no special handling."""
+        from oslo_b200.ops.norm import layer_norm
+        from oslo_b200.parallel.tensor_parallel import _ops_1d as ops
+
+        att, mlp = self.attention, self.mlp
+        ln1, ln2 = self.input_layernorm, self.post_attention_layernorm
+        qkv_l, h4h = att.query_key_value, mlp.dense_h_to_4h
+        pc, tp = qkv_l.parallel_context, qkv_l.world_size
+        lead = list(x.shape[:-1])
+        hidden = x.shape[-1]
+        xhat = layer_norm(x, (hidden,), None, None, ln1.eps).reshape(-1, hidden)
+        w1 = qkv_l.weight * ln1.weight.to(qkv_l.weight.dtype)
+        b1 = torch.mv(qkv_l.weight, ln1.bias.to(qkv_l.weight.dtype))
+        if qkv_l.bias is not None:
+            b1 = b1 + qkv_l.bias
+        w2 = h4h.weight * ln2.weight.to(h4h.weight.dtype)
+        b2 = torch.mv(h4h.weight, ln2.bias.to(h4h.weight.dtype))
+        if h4h.bias is not None:
+            b2 = b2 + h4h.bias
+        qkv, h = ops.ag_linear_pair(xhat, w1, w2, pc, b1, b2, gelu2=True)
+        d = att.query_key_value.sequence_parallel_state.dim if getattr(att.query_key_value, "sequence_parallel_state", None) else 0
+        full = list(lead)
+        full[d] *= tp
+        qkv = qkv.view(*full, qkv.shape[-1])
+        ctx = att.core(qkv, attention_mask)
+        out = ops.linear_pair_rs(ctx.reshape(-1, ctx.shape[-1]), att.dense.weight, h, mlp.dense_4h_to_h.weight, pc)
+        out = out.view(*lead, hidden)
+        bias = None
+        for b in (att.dense.bias, mlp.dense_4h_to_h.bias):
+            if b is not None:
+                bias = b if bias is None else bias + b
+        return OF.bias_dropout_add(out, bias, x, 0.0, False)
+
     def forward(self, hidden_states, attention_mask=None):
+        if self._paired_ok():
+            return self._forward_paired(hidden_states, attention_mask)
         attn, attn_bias = self.attention(self.input_layernorm(hidden_states), attention_mask)
         p, tr = self.hidden_dropout, self.training
         if self.use_parallel_residual:

@@ -83,15 +83,14 @@ class ColLinear1D(Linear):
             # input: token-sharded [..., T/tp, in]; gather over flattened tokens
             lead = list(input.shape[:-1])
             x2 = input.reshape(-1, input.shape[-1])
-            out = ops.ag_linear(x2, self._w, self.parallel_context)
+            fuse_bias = self.bias is not None and not self.skip_bias_add
+            out = ops.ag_linear(x2, self._w, self.parallel_context, self.bias if fuse_bias else None)
             if len(lead) > 1:
                 d = _sp_dim(self)
                 if d != 0 and any(n != 1 for n in lead[:d]):
                     raise ValueError("sequence parallelism over dim 1 needs batch size 1 per rank")
                 lead[d] *= self.world_size
                 out = out.view(*lead, out.shape[-1])
-            if self.bias is not None and not self.skip_bias_add:
-                out = out + self.bias
         else:
             x = ops.broadcast_tensor_1d(input, self.parallel_context)
             if self.bias is not None and not self.skip_bias_add:

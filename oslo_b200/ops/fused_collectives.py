@@ -33,11 +33,11 @@ def available(x: torch.Tensor, w: torch.Tensor, kind: str = "any") -> bool:
     return rt.supports(x, w)
 
 
-def ag_gemm(x_shard, weight, pc):
-    """``(all_gather(x_shard) @ weight^T, all_gather(x_shard))`` in one kernel."""
-    return _runtime.ag_gemm(x_shard, weight)
+def ag_gemm(x_shard, weight, pc, bias=None):
+    """``(all_gather(x_shard) @ weight^T (+ bias), all_gather(x_shard))`` in one kernel."""
+    return _runtime.ag_gemm(x_shard, weight, bias)
 
 
-def gemm_rs(x, weight, pc):
-    """``reduce_scatter(x @ weight^T)`` over the token dim in one kernel."""
-    return _runtime.gemm_rs(x, weight)
+def gemm_rs(x, weight, pc, addend=None):
+    """``reduce_scatter(x @ weight^T + addend)`` over the token dim in one kernel (``addend``: optional local [T, N])."""
+    return _runtime.gemm_rs(x, weight, addend=addend)

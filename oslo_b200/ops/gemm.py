@@ -160,6 +160,73 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     return F.linear(x, weight, bias)
 
 
+def gelu_backward(gy: torch.Tensor, pre: torch.Tensor) -> torch.Tensor:
+    """``gy * gelu_tanh'(pre)`` (no autograd): one pass of the bias-GELU backward kernel, or torch elsewhere."""
+    from . import activation as act
+
+    if act._cuda_ok(pre) and gy.dtype == pre.dtype:
+        gy = gy.contiguous()
+        dx = torch.empty_like(pre)
+        rc = _lib.cuda_lib().oslo_bias_gelu_backward(
+            _lib.ptr(gy), _lib.ptr(pre), None, _lib.ptr(dx), ctypes.c_longlong(pre.numel()), ctypes.c_int(pre.shape[-1]),
+            ctypes.c_int(act._DT[pre.dtype]), ctypes.c_int(_lib.num_sms()), _lib.stream_ptr())
+        if rc:
+            raise RuntimeError(f"oslo_bias_gelu_backward failed ({rc})")
+        return dx
+    with torch.enable_grad():
+        p = pre.detach().float().requires_grad_(True)
+        y = F.gelu(p, approximate="tanh")
+    (g,) = torch.autograd.grad(y, p, gy.float())
+    return g.to(pre.dtype)
+
+
+def gemm_bias_gelu(x2: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]):
+    """``(gelu_tanh(x2 W^T + b), x2 W^T + b)`` (no autograd): on tcgen05 both come out of ONE GEMM, whose epilogue writes
+    the pre-activation as a second output and applies the GELU before the first."""
+    if supported(x2, weight) and _aligned(x2.shape[-1], weight.shape[0], x2.shape[0]) and (bias is None or bias.dtype == x2.dtype):
+        pre = torch.empty(x2.shape[0], weight.shape[0], dtype=x2.dtype, device=x2.device)
+        h = gemm(x2, weight, bias=bias, epilogue="gelu", aux=pre)
+        return h, pre
+    pre = F.linear(x2, weight, bias)
+    return F.gelu(pre, approximate="tanh"), pre
+
+
+class _LinearGeluFn(torch.autograd.Function):
+    """y = gelu_tanh(x W^T + b) with the bias and the activation in the GEMM epilogue; backward: one GELU-derivative
+    pass, a column sum, and the two gradient GEMMs."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        x2 = x.reshape(-1, x.shape[-1])
+        h, pre = gemm_bias_gelu(x2, weight, bias)
+        ctx.save_for_backward(x2, weight, pre)
+        ctx.has_bias = bias is not None
+        ctx.x_shape = x.shape
+        return h.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, weight, pre = ctx.saved_tensors
+        dpre = gelu_backward(gy.reshape(-1, gy.shape[-1]), pre)
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gx = matmul_nt(dpre, weight.t()).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            gw = matmul_nt(dpre.t(), x2.t())
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            from .activation import colsum
+
+            gb = colsum(dpre)
+        return gx, gw, gb
+
+
+def linear_gelu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``gelu_tanh(F.linear(x, weight, bias))`` as one fused GEMM on CUDA bf16/fp16."""
+    if bias is not None and bias.dtype != x.dtype:
+        bias = bias.to(x.dtype)
+    return _LinearGeluFn.apply(x, weight, bias)
+
+
 def matmul_nt(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """``a @ b.transpose(-1, -2)`` (no autograd) with tcgen05 when possible."""
     if supported(a, b) and a.dim() in (2, 3, 4) and a.dim() == b.dim():

@@ -13,6 +13,11 @@ stages it is a placeholder whose ``backward()`` does nothing — those stages ru
 generator when the gradients arrive, following 1F1B: stage ``s`` of ``P`` does ``min(P-1-s, M)`` warm-up forwards, then
 alternates one forward and one backward, then drains.
 
+Overlap: the receive of micro-batch ``i + 1``'s activation is posted (``irecv``) as soon as micro-batch ``i``'s has
+arrived, i.e. before the stage computes ``i``, so the transfer runs under the compute.  Gradients travel on a second
+communicator over the same ranks: point-to-point operations between one pair of ranks execute in issue order on one
+stream, and an early-posted activation receive must never sit in front of a gradient send to the same neighbour.
+
 A model provides its decomposition through ``pipeline_units()`` (a list of :class:`PipeUnit`); ``nn.Sequential`` works
 out of the box.  Parameters used by units on several stages (tied embeddings) are kept on each of them and their
 gradients are summed at the end of the batch.
@@ -68,6 +73,8 @@ class PipelineParallel(ParallelWrapper):
         self._shared: List[nn.Parameter] = []
         self._meta_cache: Dict[str, tuple] = {}
         self.partition: List[range] = []
+        self._tree = None  # set when the stages come from cutting the module tree
+        self._grad_group = None  # second communicator over the pipeline ranks, for the backward direction
         add_wrapper(module, ParallelMode.PIPELINE, self)
 
     # ------------------------------------------------------------ parallelize
@@ -76,10 +83,28 @@ class PipelineParallel(ParallelWrapper):
             return self.module.pipeline_units()
         if isinstance(self.module, nn.Sequential):
             return sequential_units(self.module)
-        raise TypeError(f"{type(self.module).__name__} must define pipeline_units() (or be an nn.Sequential)")
+        # any other model: cut its module tree (embeddings / list of blocks / head), see tree_stage.py
+        from .tree_stage import TreeStage
+
+        self._tree = TreeStage(self.module)
+        return self._tree.units()
+
+    def _make_grad_group(self):
+        """One more process group per pipeline group (collective over the whole job: every rank walks every list)."""
+        pc = self.parallel_context
+        if self.pp_size == 1 or not dist.is_initialized():
+            return
+        mine = sorted(pc.get_ranks_in_group(ParallelMode.PIPELINE))
+        every = [None] * dist.get_world_size()
+        dist.all_gather_object(every, mine)
+        for ranks in sorted({tuple(r) for r in every}):
+            g = dist.new_group(list(ranks))
+            if tuple(mine) == ranks:
+                self._grad_group = g
 
     @torch.no_grad()
     def parallelize(self):
+        self._make_grad_group()
         self.units = self._get_units()
         self.partition = ModelPartitioner(self.units, self.pp_size, self.memory_computation_balance).partition()
         mine = self.partition[self.stage]
@@ -100,6 +125,8 @@ class PipelineParallel(ParallelWrapper):
                 p.data = torch.empty(0, dtype=p.dtype, device=p.device)  # not ours: release the storage
                 p.requires_grad_(False)
                 p.oslo_pipeline_released = True
+        if self._tree is not None:
+            self._tree.install(mine, len(self.units), self.stage, self.pp_size)
 
     # ---------------------------------------------------------------- helpers
     def _split_kwargs(self, kwargs) -> List[dict]:
@@ -117,9 +144,14 @@ class PipelineParallel(ParallelWrapper):
                     out[i][k] = v
         return out
 
+    def _p2p_group(self, tag: str):
+        if tag == "grad" and self._grad_group is not None:
+            return self._grad_group
+        return self.parallel_context.get_group(ParallelMode.PIPELINE)
+
     def _send(self, t: torch.Tensor, dst: int, tag: str):
         pc = self.parallel_context
-        group = pc.get_group(ParallelMode.PIPELINE)
+        group = self._p2p_group(tag)
         t = t.contiguous()
         key = ("send", tag)  # shape / dtype travel once per direction and tag, then only payloads
         if self._meta_cache.get(key) != (tuple(t.shape), t.dtype):
@@ -129,18 +161,25 @@ class PipelineParallel(ParallelWrapper):
             self._meta_cache[key] = (tuple(t.shape), t.dtype)
         return dist.isend(t, dst=dst, group=group)
 
-    def _recv(self, src: int, tag: str) -> torch.Tensor:
+    def _post_recv(self, src: int, tag: str):
+        """Post a non-blocking receive; returns ``(work, tensor)``.  The first receive of a tag learns shape and dtype
+        from the sender (one object message), later ones reuse them."""
         pc = self.parallel_context
-        group = pc.get_group(ParallelMode.PIPELINE)
         key = ("recv", tag)
         if key not in self._meta_cache:
             self._meta_cache[key] = P2P().recv(src, pc.get_global_rank(), pc, ParallelMode.PIPELINE)
         shape, dtype = self._meta_cache[key]
         t = torch.empty(shape, dtype=dtype, device=pc.device)
-        dist.recv(t, src=src, group=group)
+        return dist.irecv(t, src=src, group=self._p2p_group(tag)), t
+
+    def _recv(self, src: int, tag: str) -> torch.Tensor:
+        work, t = self._post_recv(src, tag)
+        work.wait()
         return t
 
     def _run_stage(self, state: dict) -> dict:
+        if self._tree is not None:
+            return self._tree.run(state)
         for u in self.my_units:
             state = u.fn(state)
         return state
@@ -169,10 +208,15 @@ class PipelineParallel(ParallelWrapper):
         pending = []
         self._meta_cache = {}  # shapes may change between calls (last partial batch, eval): re-announce them
 
+        posted = {}  # micro-batch index -> (work, tensor) of an activation receive already in flight
+
         def forward_mb(i):
             state = dict(micro[i])
             if not first:
-                h = self._recv(prev_rank, "act")
+                work, h = posted.pop(i) if i in posted else self._post_recv(prev_rank, "act")
+                work.wait()
+                if i + 1 < M:
+                    posted[i + 1] = self._post_recv(prev_rank, "act")  # runs under this micro-batch's compute
                 h.requires_grad_(torch.is_grad_enabled() and h.is_floating_point())
                 inputs[i] = h
                 state["hidden"] = h
@@ -279,3 +323,5 @@ class PipelineParallel(ParallelWrapper):
                 p.data = merged[k].to(self.parallel_context.device)
                 p.requires_grad_(True)
                 p.oslo_pipeline_released = False
+        if self._tree is not None:
+            self._tree.uninstall()

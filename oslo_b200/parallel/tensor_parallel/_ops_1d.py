@@ -128,17 +128,20 @@ class _AGLinear(torch.autograd.Function):
     """y_full = all_gather(x_shard, dim 0) @ W^T.  x_shard: [T/tp, K] (tokens flattened)."""
 
     @staticmethod
-    def forward(ctx, x, weight, pc):
+    def forward(ctx, x, weight, pc, bias=None):
         ctx.pc = pc
+        ctx.has_bias = bias is not None
         if _use_fused(x, weight, "ag"):
             from oslo_b200.ops import fused_collectives as fc
 
-            y, x_full = fc.ag_gemm(x, weight, pc)
+            y, x_full = fc.ag_gemm(x, weight, pc, bias=bias)  # the bias is added in the GEMM epilogue
         else:
             from oslo_b200.ops.gemm import matmul_nt
 
             x_full = comm.all_gather(x, dim=0, parallel_context=pc, parallel_mode=_MODE)
             y = matmul_nt(x_full, weight)
+            if bias is not None:
+                y = y + bias
         ctx.save_for_backward(x_full, weight)
         return y
 
@@ -162,7 +165,12 @@ class _AGLinear(torch.autograd.Function):
             from oslo_b200.ops.gemm import matmul_nt
 
             gw = matmul_nt(gy.t(), x_full.t())
-        return gx, gw, None
+        gb = None
+        if ctx.has_bias and ctx.needs_input_grad[3]:
+            from oslo_b200.ops.activation import colsum
+
+            gb = colsum(gy)
+        return gx, gw, None, gb
 
 
 class _LinearRS(torch.autograd.Function):
@@ -202,11 +210,121 @@ class _LinearRS(torch.autograd.Function):
         return gx, gw, None
 
 
-def ag_linear(x, weight, parallel_context):
-    """Sequence-parallel column linear on flattened tokens ``[T/tp, K] -> [T, N/tp]``."""
-    return _AGLinear.apply(x, weight, parallel_context)
+def ag_linear(x, weight, parallel_context, bias=None):
+    """Sequence-parallel column linear on flattened tokens ``[T/tp, K] -> [T, N/tp]`` (``bias``: ``[N/tp]``, optional)."""
+    return _AGLinear.apply(x, weight, parallel_context, bias)
 
 
 def linear_rs(x, weight, parallel_context):
     """Sequence-parallel row linear on flattened tokens ``[T, K/tp] -> [T/tp, N]``."""
     return _LinearRS.apply(x, weight, parallel_context)
+
+
+# ------------------------------------------- paired linears: two products, one collective
+class _AGLinearPair(torch.autograd.Function):
+    """``(y1, y2) = (X W1^T, X W2^T)`` with ``X = all_gather(x_shard)``: two column-parallel linears that read the same
+    token-sharded input share ONE all-gather forward and ONE reduce-scatter backward
+    (``dx = reduce_scatter(dY1 W1 + dY2 W2)``, the first product riding along as the fused kernel's addend)."""
+
+    @staticmethod
+    def forward(ctx, x, w1, w2, pc, b1=None, b2=None, gelu2=False):
+        from oslo_b200.ops.gemm import gemm_bias_gelu, matmul_nt
+
+        ctx.pc = pc
+        ctx.has_b1, ctx.has_b2, ctx.gelu2 = b1 is not None, b2 is not None, gelu2
+        if _use_fused(x, w1, "ag"):
+            from oslo_b200.ops import fused_collectives as fc
+
+            y1, x_full = fc.ag_gemm(x, w1, pc, bias=b1)
+        else:
+            x_full = comm.all_gather(x, dim=0, parallel_context=pc, parallel_mode=_MODE)
+            y1 = matmul_nt(x_full, w1)
+            if b1 is not None:
+                y1 = y1 + b1
+        pre2 = None
+        if gelu2:
+            y2, pre2 = gemm_bias_gelu(x_full, w2, b2)  # bias + GELU in the epilogue, pre-activation kept for backward
+        else:
+            y2 = matmul_nt(x_full, w2)
+            if b2 is not None:
+                y2 = y2 + b2
+        ctx.save_for_backward(x_full, w1, w2, pre2)
+        return y1, y2
+
+    @staticmethod
+    def backward(ctx, g1, g2):
+        from oslo_b200.ops.activation import colsum
+        from oslo_b200.ops.gemm import gelu_backward, matmul_nt
+
+        x_full, w1, w2, pre2 = ctx.saved_tensors
+        pc = ctx.pc
+        g1, g2 = g1.contiguous(), g2.contiguous()
+        if ctx.gelu2:
+            g2 = gelu_backward(g2, pre2)
+        gx = gw1 = gw2 = None
+        if ctx.needs_input_grad[0]:
+            part = matmul_nt(g1, w1.t())  # local [T, K]
+            if _use_fused(g2, w2.t(), "rs"):
+                from oslo_b200.ops import fused_collectives as fc
+
+                gx = fc.gemm_rs(g2, w2.t(), pc, addend=part)
+            else:
+                part = part + matmul_nt(g2, w2.t())
+                gx = comm.reduce_scatter(part, dim=0, parallel_context=pc, parallel_mode=_MODE)
+        if ctx.needs_input_grad[1]:
+            gw1 = matmul_nt(g1.t(), x_full.t())
+        if ctx.needs_input_grad[2]:
+            gw2 = matmul_nt(g2.t(), x_full.t())
+        gb1 = colsum(g1) if (ctx.has_b1 and ctx.needs_input_grad[4]) else None
+        gb2 = colsum(g2) if (ctx.has_b2 and ctx.needs_input_grad[5]) else None
+        return gx, gw1, gw2, None, gb1, gb2, None
+
+
+class _LinearPairRS(torch.autograd.Function):
+    """``y_shard = reduce_scatter(X1 W1^T + X2 W2^T)``: two row-parallel linears whose outputs are summed right after
+    (attention output and MLP output of a parallel-residual block) share ONE reduce-scatter forward and ONE all-gather
+    of ``dY`` backward."""
+
+    @staticmethod
+    def forward(ctx, x1, w1, x2, w2, pc):
+        from oslo_b200.ops.gemm import matmul_nt
+
+        ctx.pc = pc
+        ctx.save_for_backward(x1, w1, x2, w2)
+        part = matmul_nt(x1, w1)  # local [T, N]
+        if _use_fused(x2, w2, "rs"):
+            from oslo_b200.ops import fused_collectives as fc
+
+            return fc.gemm_rs(x2, w2, pc, addend=part)
+        part = part + matmul_nt(x2, w2)
+        return comm.reduce_scatter(part, dim=0, parallel_context=pc, parallel_mode=_MODE)
+
+    @staticmethod
+    def backward(ctx, gy):
+        from oslo_b200.ops.gemm import matmul_nt
+
+        x1, w1, x2, w2 = ctx.saved_tensors
+        pc = ctx.pc
+        gy = gy.contiguous()
+        if _use_fused(gy, w2.t(), "ag"):
+            from oslo_b200.ops import fused_collectives as fc
+
+            gx2, gy_full = fc.ag_gemm(gy, w2.t(), pc)
+        else:
+            gy_full = comm.all_gather(gy, dim=0, parallel_context=pc, parallel_mode=_MODE)
+            gx2 = matmul_nt(gy_full, w2.t())
+        gx1 = matmul_nt(gy_full, w1.t()) if ctx.needs_input_grad[0] else None
+        gw1 = matmul_nt(gy_full.t(), x1.t()) if ctx.needs_input_grad[1] else None
+        gw2 = matmul_nt(gy_full.t(), x2.t()) if ctx.needs_input_grad[3] else None
+        return gx1, gw1, gx2, gw2, None
+
+
+def ag_linear_pair(x, w1, w2, parallel_context, b1=None, b2=None, gelu2=False):
+    """Two sequence-parallel column linears on the same input: ``[T/tp, K] -> ([T, N1/tp] (+ b1), [T, N2/tp] (+ b2))``;
+    ``gelu2`` applies the tanh GELU to the second output inside its GEMM epilogue."""
+    return _AGLinearPair.apply(x, w1, w2, parallel_context, b1, b2, gelu2)
+
+
+def linear_pair_rs(x1, w1, x2, w2, parallel_context):
+    """Two sequence-parallel row linears summed: ``([T, K1/tp], [T, K2/tp]) -> [T/tp, N]``."""
+    return _LinearPairRS.apply(x1, w1, x2, w2, parallel_context)

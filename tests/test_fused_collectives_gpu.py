@@ -57,13 +57,26 @@ def _worker(rank, world):
         torch.cuda.synchronize()
         _lib.check_status()
         assert rel(out, ref) < 2e-2, (it, rel(out, ref))
+        # ---- the same with a local [T, N] addend riding along (two row products, one reduce-scatter)
+        add = (torch.randn(T, N, device=dev) * 0.5).to(torch.bfloat16)
+        out2 = fc.gemm_rs(xa, WN, pc, addend=add)
+        ref2 = comm.reduce_scatter(part + add.float(), dim=0, parallel_context=pc, parallel_mode=M1)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        assert rel(out2, ref2) < 2e-2, (it, rel(out2, ref2))
     dist.barrier()
     pc.destroy()
 
 
+def _world_sizes():
+    """Every power of two up to the number of visible GPUs (2, 4, 8): the 8-rank case runs wherever 8 GPUs are."""
+    return [w for w in (2, 4, 8) if w <= _n_gpus()] or [2]
+
+
 @pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
-def test_fused_collectives_match_nccl():
-    run_dist(_worker, min(_n_gpus(), 4) if _n_gpus() != 3 else 2, timeout=600)
+@pytest.mark.parametrize("world", _world_sizes())
+def test_fused_collectives_match_nccl(world):
+    run_dist(_worker, world, timeout=600)
 
 
 def _model_worker(rank, world):
@@ -113,7 +126,7 @@ def test_fused_model_step_matches_composition():
     run_dist(_model_worker, 2, timeout=600)
 
 
-def _zero_worker(rank, world):
+def _zero_worker(rank, world, clip):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     import torch.nn as nn
 
@@ -130,11 +143,14 @@ def _zero_worker(rank, world):
         return nn.Sequential(nn.Linear(256, 512), nn.GELU(), nn.Linear(512, 512), nn.LayerNorm(512), nn.Linear(512, 64)).to(dev, torch.bfloat16)
 
     results = {}
-    for fused in (False, True):
+    for fused in (False, True, "overlap"):
         model = make()
         opt = ZeroRedundancyOptimizer(torch.optim.AdamW(model.parameters(), lr=1e-2, weight_decay=0.1), parallel_context=pc,
-                                      partition_grad=True, fused=fused, clip_grad_norm=1.0 if fused else 1.0)
-        assert opt.fused == fused
+                                      partition_grad=True, fused=bool(fused), clip_grad_norm=clip,
+                                      overlap_communication=fused == "overlap", reduce_bucket_size=64 * 1024)
+        assert opt.fused == bool(fused)
+        if fused:
+            assert sum(len(g.buckets) for g in opt._all_groups()) > 2  # several per-bucket kernels
         for s in range(3):
             g = torch.Generator().manual_seed(10 + s)
             x = torch.randn(8 * world, 256, generator=g).to(dev, torch.bfloat16).chunk(world)[rank]
@@ -146,14 +162,20 @@ def _zero_worker(rank, world):
         torch.cuda.synchronize()
         _lib.check_status()
         results[fused] = [p.detach().float().clone() for p in model.parameters()]
-    for a, b in zip(results[True], results[False]):
-        assert (a - b).abs().max().item() <= 2e-2 * (b.abs().max().item() + 1e-3)
+    bad = []
+    for key in (True, "overlap"):
+        for i, (a, b) in enumerate(zip(results[key], results[False])):
+            err, tol = (a - b).abs().max().item(), 2e-2 * (b.abs().max().item() + 1e-3)
+            if err > tol:
+                bad.append((key, i, tuple(a.shape), err, tol, ((a - b).abs() > tol).float().mean().item()))
+    assert not bad, bad
     pc.destroy()
 
 
 @pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
-def test_fused_zero_step_matches_collective_path():
-    run_dist(_zero_worker, 2, timeout=600)
+@pytest.mark.parametrize("clip", [1.0, 0.0])
+def test_fused_zero_step_matches_collective_path(clip):
+    run_dist(_zero_worker, 2, clip, timeout=600)
 
 
 def _moe_worker(rank, world):

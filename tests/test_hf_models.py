@@ -98,3 +98,44 @@ def _worker(rank, world, kind, tmp):
 def test_hf_model_tensor_parallel_1d(kind):
     with tempfile.TemporaryDirectory() as tmp:
         run_dist(_worker, 2, kind, tmp, timeout=600)
+
+
+def _pp_worker(rank, world, kind):
+    """Stock Hugging Face model, no ``pipeline_units()``: the module tree is cut into two stages."""
+    import oslo_b200
+    from oslo_b200 import ParallelContext
+    from oslo_b200.parallel import PipelineParallel
+
+    pc = ParallelContext.from_torch(pipeline_parallel_size=world, backend="gloo", seed=0)
+    ref = _build(kind).train()
+    model = _build(kind).train()
+    wrapped = PipelineParallel(model, pc, num_micro_batches=2)
+    oslo_b200.ready(wrapped, pc)
+    assert wrapped._tree is not None
+    released = [n for n, p in model.named_parameters() if getattr(p, "oslo_pipeline_released", False)]
+    assert released, "every stage still holds the whole model"
+    ids = torch.randint(0, 100, (4, 12), generator=torch.Generator().manual_seed(1))
+    ref_loss = sum(ref(input_ids=c, labels=c).loss for c in ids.chunk(2)) / 2
+    ref_loss.backward()
+    total = 0.0
+    for _, out in wrapped(input_ids=ids, labels=ids):
+        out.loss.backward()
+        if wrapped.stage == world - 1:
+            total += out.loss.item()
+    if wrapped.stage == world - 1:
+        assert abs(total - ref_loss.item()) < 1e-4, (total, ref_loss.item())
+    ref_grads = dict(ref.named_parameters())
+    checked = 0
+    for n, p in model.named_parameters():
+        if getattr(p, "oslo_pipeline_released", False) or p.grad is None:
+            continue
+        g = ref_grads[n].grad
+        assert torch.allclose(p.grad, g, rtol=1e-3, atol=1e-5), (n, (p.grad - g).abs().max().item())
+        checked += 1
+    assert checked > 5
+    pc.destroy()
+
+
+@pytest.mark.parametrize("kind", ["gpt2", "gpt_neox"])
+def test_hf_model_pipeline_parallel_from_module_tree(kind):
+    run_dist(_pp_worker, 2, kind, timeout=600)

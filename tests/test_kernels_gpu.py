@@ -410,3 +410,98 @@ def test_flash_attention_forward(causal, hd):
     if causal:
         scores = scores.masked_fill(~torch.ones(s, s, dtype=torch.bool, device=DEV).tril(), float("-inf"))
     assert _rel(lse, torch.logsumexp(scores, dim=-1)) < 1e-3
+
+
+def _close(a, b, rtol, atol):
+    """Per-element check ``|a - b| <= atol + rtol * |b|`` (a single large element cannot hide errors elsewhere);
+    returns the fraction of elements outside the bound and the worst excess, for the assertion message."""
+    a, b = a.float(), b.float()
+    excess = (a - b).abs() - (atol + rtol * b.abs())
+    return (excess > 0).float().mean().item(), excess.max().item()
+
+
+@pytest.mark.parametrize("a_t,b_t", [(False, False), (False, True), (True, True)])
+def test_gemm_production_shape(a_t, b_t):
+    """4096 x 3072 x 2048: 32 k-blocks (the 4-8 stage ring wraps and flips phase several times) and 384 / 768 tiles on
+    148 persistent CTAs (each CTA runs 3-6 tiles, so both TMEM accumulator buffers and their phases are reused)."""
+    from oslo_b200.ops.gemm import gemm
+
+    torch.manual_seed(40)
+    M, N, K = 4096, 3072, 2048
+    a = (torch.randn((K, M) if a_t else (M, K), device=DEV) * 0.5).to(torch.bfloat16)
+    b = (torch.randn((K, N) if b_t else (N, K), device=DEV) * 0.5).to(torch.bfloat16)
+    A, B = (a.t() if a_t else a), (b.t() if b_t else b)
+    ref = A.float() @ B.float().t()
+    for bn in (0, 128):
+        y = gemm(A, B, block_n=bn)
+        # bf16 output rounding is 2^-9 relative; the fp32 accumulation error over K = 2048 is far below the atol
+        frac, worst = _close(y, ref, rtol=1e-2, atol=0.05)
+        assert frac == 0.0, (bn, frac, worst)
+
+
+@pytest.mark.parametrize("mode", [1, 2, 3])
+def test_gemm_causal_modes_at_seq_2048(mode):
+    """The three triangular work-skipping modes of the attention products at the sequence length the benchmark uses."""
+    from oslo_b200.ops.gemm import gemm
+
+    torch.manual_seed(41)
+    s, hd = 2048, 128
+    tril = torch.ones(s, s, device=DEV).tril()
+    if mode == 1:  # scores = Q K^T, tiles above the diagonal skipped: compare the lower triangle only
+        q = (torch.randn(2, s, hd, device=DEV) * 0.5).to(torch.bfloat16)
+        k = (torch.randn(2, s, hd, device=DEV) * 0.5).to(torch.bfloat16)
+        y = gemm(q, k, causal=1)
+        ref = q.float() @ k.float().transpose(-1, -2)
+        keep = tril.bool()  # skipped tiles are never written (they may hold anything, NaN included)
+        frac, worst = _close(torch.where(keep, y.float(), torch.zeros_like(ref)), ref * tril, rtol=1e-2, atol=0.05)
+    elif mode == 2:  # out = P V with lower-triangular P: reduce only over k <= row
+        p = ((torch.rand(2, s, s, device=DEV) * tril) / 32).to(torch.bfloat16)
+        v = (torch.randn(2, s, hd, device=DEV) * 0.5).to(torch.bfloat16)
+        y = gemm(p, v.transpose(-1, -2), causal=2)
+        ref = p.float() @ v.float()
+        frac, worst = _close(y, ref, rtol=1e-2, atol=0.05)
+    else:  # dV = P^T dO with P^T upper-triangular: reduce only over k >= row
+        p = ((torch.rand(2, s, s, device=DEV) * tril) / 32).to(torch.bfloat16)
+        do = (torch.randn(2, s, hd, device=DEV) * 0.5).to(torch.bfloat16)
+        y = gemm(p.transpose(-1, -2), do.transpose(-1, -2), causal=3)
+        ref = p.float().transpose(-1, -2) @ do.float()
+        frac, worst = _close(y, ref, rtol=1e-2, atol=0.05)
+    assert frac == 0.0, (mode, frac, worst)
+
+
+def test_linear_gelu_fused_epilogue():
+    from oslo_b200.ops.gemm import linear_gelu
+
+    torch.manual_seed(42)
+    x = (torch.randn(2, 512, 256, device=DEV) * 0.5).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(1024, 256, device=DEV) * 0.1).to(torch.bfloat16).requires_grad_()
+    b = (torch.randn(1024, device=DEV) * 0.1).to(torch.bfloat16).requires_grad_()
+    y = linear_gelu(x, w, b)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yr = F.gelu(F.linear(xr, wr, br), approximate="tanh")
+    yr.backward(g.float())
+    for got, want, name in ((y, yr, "y"), (x.grad, xr.grad, "dx"), (w.grad, wr.grad, "dw"), (b.grad, br.grad, "db")):
+        frac, worst = _close(got, want, rtol=2e-2, atol=0.03 * want.abs().max().item())
+        assert frac == 0.0, (name, frac, worst)
+
+
+@pytest.mark.parametrize("causal", [True])
+def test_flash_attention_seq_2048(causal):
+    """Forward and backward at the benchmark's sequence length (16 key blocks per query block, causal skipping)."""
+    from oslo_b200.ops.attention import attention, attention_reference
+
+    torch.manual_seed(43)
+    b, s, nh, hd = 1, 2048, 2, 128
+    qkv = (torch.randn(b, s, nh, 3, hd, device=DEV) * 0.6).to(torch.bfloat16).requires_grad_()
+    out = attention(qkv[..., 0, :], qkv[..., 1, :], qkv[..., 2, :], causal=causal)
+    g = torch.randn_like(out)
+    out.backward(g)
+    ref_in = qkv.detach().float().requires_grad_()
+    ref = attention_reference(ref_in[..., 0, :], ref_in[..., 1, :], ref_in[..., 2, :], causal=causal)
+    ref.backward(g.float())
+    frac, worst = _close(out, ref, rtol=2e-2, atol=0.02)
+    assert frac == 0.0, ("out", frac, worst)
+    frac, worst = _close(qkv.grad, ref_in.grad, rtol=3e-2, atol=0.03 * ref_in.grad.abs().max().item())
+    assert frac < 1e-4, ("dqkv", frac, worst)

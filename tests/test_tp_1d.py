@@ -16,7 +16,13 @@ def _neox(seed=0):
     torch.manual_seed(seed)
     cfg = GPTNeoXConfig(vocab_size=509, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
                         intermediate_size=128, max_position_embeddings=32)
-    return GPTNeoXForCausalLM(cfg)
+    model = GPTNeoXForCausalLM(cfg)
+    # non-trivial LayerNorm parameters and biases, so that folding them into the next weights is really exercised
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if "layernorm" in n or "layer_norm" in n or n.endswith(".bias"):
+                p.add_(torch.randn_like(p) * 0.3)
+    return model
 
 
 def _worker(rank, world, sp, tmp):

@@ -55,7 +55,13 @@ def test_noalloc_colsum_matches_ordinary_entry_point_twice():
     lib = _lib()
     torch.manual_seed(0)
     # two calls in a row with different shapes and dtypes: the second reuses (and must overwrite) the built-in array
-    for rows, h, dtype in [(5000, 2048, torch.bfloat16), (777, 4096, torch.float32)]:
+    # the third case is wide enough that (row partitions x columns) exceeds the built-in array, so the entry point has to
+    # fall back to fewer partitions than the ordinary one uses
+    limit = lib.oslo_colsum_noalloc_max_scratch_floats()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    wide = (20000, 65536, torch.bfloat16)
+    assert lib.oslo_colsum_parts(ctypes.c_longlong(wide[0]), ctypes.c_int(sms)) * wide[1] > limit
+    for rows, h, dtype in [(5000, 2048, torch.bfloat16), (777, 4096, torch.float32), wide]:
         x = torch.randn(rows, h, device="cuda", dtype=dtype)
         got = _noalloc(lib, x)
         want = _ordinary(lib, x)
@@ -65,6 +71,19 @@ def test_noalloc_colsum_matches_ordinary_entry_point_twice():
         tol = 1e-5 if dtype == torch.float32 else 2e-2
         assert (got.float() - want.float()).abs().max().item() / scale < tol
         assert (got.float() - ref).abs().max().item() / scale < tol
+
+
+def test_noalloc_colsum_refuses_misaligned_pointers_before_launching():
+    lib = _lib()
+    buf = torch.zeros(64 * 1024 + 64, device="cuda", dtype=torch.bfloat16)
+    out = torch.zeros(1024 + 64, device="cuda", dtype=torch.bfloat16)
+    stream = torch.cuda.current_stream().cuda_stream
+    # an input that starts 2 bytes into an aligned buffer, then an output that does: both are refused with the argument code
+    assert lib.oslo_colsum_noalloc(buf.data_ptr() + 2, out.data_ptr(), 64, 1024, 2, stream) == -1
+    assert lib.oslo_colsum_noalloc(buf.data_ptr(), out.data_ptr() + 2, 64, 1024, 2, stream) == -1
+    assert lib.oslo_colsum_noalloc(buf.data_ptr(), out.data_ptr(), 64, 1024, 2, stream) == 0
+    torch.cuda.synchronize()
+    assert float(out[:1024].float().abs().max()) == 0.0
 
 
 def test_noalloc_colsum_rejects_inputs_beyond_the_builtin_scratch():
