@@ -88,12 +88,33 @@ def build(args, world):
         if pc.pipeline_parallel_size > 1:
             wrapped = PipelineParallel(model, pc, num_micro_batches=micro)
     oslo_b200.ready(wrapped, pc)
+    fused = []
+    if not args.no_fused:
+        from oslo_b200.distributed import symm
+
+        M = ParallelMode
+        tokens = batch * seq // max(micro, 1)
+        widest = max(getattr(cfg, "intermediate_size", 0) * 2, getattr(cfg, "n_inner", 0) or 0, 3 * getattr(cfg, "hidden_size", getattr(cfg, "n_embd", 0)))
+        if name == "llama-2d-pp2" and pc.tensor_parallel_size > 1:
+            rows = tokens // pc.summa_dim  # every rank keeps its share of the micro-batch
+            fused += [M.TENSOR_2D_ROW] if symm.enable(pc, M.TENSOR_2D_ROW, rows, widest) else []
+        elif name == "gpt-2p5d":
+            rows = tokens // (pc.summa_dim * (pc.tensor_parallel_depth or 1))
+            fused += [M.TENSOR_2P5D_ROW] if symm.enable(pc, M.TENSOR_2P5D_ROW, rows, widest) else []
+        elif name == "gpt-3d":
+            rows = tokens // pc.cubic_dim  # rows of the product after the INPUT gather
+            for mode in (M.TENSOR_3D_INPUT, M.TENSOR_3D_OUTPUT):
+                fused += [mode] if symm.enable(pc, mode, rows, widest // pc.cubic_dim if mode == M.TENSOR_3D_OUTPUT else widest) else []
+        elif name == "moe-ep-zero2":
+            symm._fused_small_ops = True  # expert dispatch / combine through peer memory, fused ZeRO step
+            fused += ["moe-peer-dispatch", "zero-step"]
+    args.fused_paths = [str(f) for f in fused]
     params = [p for p in model.parameters() if p.requires_grad and p.numel() > 0]
     if name == "moe-ep-zero2":
         dense = [p for p in params if not getattr(p, "oslo_expert_param", False)]
         experts = [p for p in params if getattr(p, "oslo_expert_param", False)]
         zero = ZeroRedundancyOptimizer(torch.optim.AdamW(dense, lr=1e-4, weight_decay=0.01), parallel_context=pc,
-                                       partition_grad=True, fused=args.fused_zero)
+                                       partition_grad=True, fused=not args.no_fused, overlap_communication=not args.no_fused)
         expert_opt = FusedAdam(experts, lr=1e-4, weight_decay=0.01, master_weights=True)
         opts = (zero, expert_opt)
     else:
@@ -101,14 +122,31 @@ def build(args, world):
     return pc, model, wrapped, opts, cfg, batch, seq
 
 
+def flops_per_token(name, cfg, seq) -> float:
+    """Training FLOPs per token: 6 x (matrix parameters a token passes through) + causal attention."""
+    h = getattr(cfg, "hidden_size", None) or cfg.n_embd
+    L = getattr(cfg, "num_hidden_layers", None) or cfg.n_layer
+    v = cfg.vocab_size
+    if name == "llama-2d-pp2":
+        per_layer = [4 * h * h + 3 * h * cfg.intermediate_size] * L
+    elif name == "moe-ep-zero2":
+        f = cfg.n_inner
+        moe = set(range(L)[1::2]) if cfg.moe_every == 2 else set()
+        per_layer = [4 * h * h + (cfg.top_k * 2 * h * f if i in moe else 2 * h * f) for i in range(L)]
+    else:
+        per_layer = [4 * h * h + 2 * h * cfg.n_inner] * L
+    return 6.0 * (sum(per_layer) + h * v) + L * 6.0 * seq * h
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", required=True, choices=["llama-2d-pp2", "gpt-3d", "gpt-2p5d", "moe-ep-zero2"])
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--scale-down", action="store_true")
-    ap.add_argument("--fused-zero", action="store_true")
+    ap.add_argument("--no-fused", action="store_true",
+                    help="run the NCCL collective + GEMM compositions instead of the fused peer-memory kernels")
     ap.add_argument("--tp", type=int, default=0, help="override the tensor-parallel size of llama-2d-pp2 (smoke runs)")
     args = ap.parse_args()
     world = int(os.environ["WORLD_SIZE"])
@@ -152,6 +190,10 @@ def main():
     torch.cuda.synchronize()
     _lib.check_status()
     dist.barrier()
+    from bench import ClockSampler  # NVML reader of the flagship benchmark (read-only)
+
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     last = None
@@ -163,6 +205,7 @@ def main():
     t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     _lib.check_status()
+    clocks = sampler.stop()
     ms = t.item() / args.steps
     lossv = torch.tensor([float(last) if last is not None else 0.0], device=dev)
     dist.all_reduce(lossv, op=dist.ReduceOp.MAX)
@@ -172,7 +215,8 @@ def main():
             "metric": "train tokens/sec (device-timed, max over ranks)", "config": args.config, "value": batch * seq / (ms / 1e3),
             "unit": "tokens/s", "n_gpus": world, "ms_per_step": ms, "steps": args.steps, "global_batch": batch, "seq_len": seq,
             "dtype": "bf16", "data": "synthetic", "rank_local_params": nparams, "loss": lossv.item(),
-            "shrunk": bool(args.layers or args.scale_down),
+            "shrunk": bool(args.layers or args.scale_down), "fused_paths": args.fused_paths, "clocks": clocks,
+            "per_gpu_model_tflops": batch * seq / (ms / 1e3) * flops_per_token(args.config, cfg, seq) / 1e12 / world,
             "parallelism": dict(tp=pc.tensor_parallel_size, pp=pc.pipeline_parallel_size, dp=pc.data_parallel_size,
                                 ep=pc.expert_parallel_size if isinstance(pc.expert_parallel_size, int) else 0,
                                 mode=str(pc.tensor_parallel_mode)),

@@ -61,6 +61,8 @@ extern "C" int oslo_ag_gemm(void* const* peer_in, void* x_full, const void* B, v
     if (Tl % cand == 0 && (Tl / cand) * tp <= 64) { chunk_rows = cand; break; }
   }
   fp.chunk_rows = chunk_rows;
+  fp.ag_tp = tp; fp.ag_rank = rank; fp.ag_shard_rows = Tl; fp.ag_chunk_rows = chunk_rows; fp.ag_epoch = epoch;
+  fp.ag_epoch_ptr = epoch_ptr; fp.copy_first = (rank + 1) % tp;  // the next rank's shard first, the own one last
   for (int i = 0; i < tp; ++i) {
     fp.peer_in[i] = peer_in[i];
     fp.peer_ag_ready[i] = static_cast<int*>(peer_ag_ready[i]);
@@ -95,15 +97,26 @@ extern "C" int oslo_ag_gemm(void* const* peer_in, void* x_full, const void* B, v
 extern "C" int oslo_gemm_rs(const void* A, long long lda, const void* B, long long ldb, int b_mn, void* out, const void* bias,
                             int T, int N, int K, int is_bf16, int tp, int rank, int epoch, void* const* peer_partial,
                             void* const* peer_rs_flag, int* tile_done, int reduce_ctas, int num_sms, int* status,
-                            void* stream_ptr, unsigned long long* debug_times, const int* epoch_ptr, const void* addend) {
-  if (tp > kMaxRanks || tp < 1 || T % tp) return -1;
-  const int Tl = T / tp;
-  if (Tl % kBlockM || N % 8 || K % 8 || lda % 8 || ldb % 8) return -5;
+                            void* stream_ptr, unsigned long long* debug_times, const int* epoch_ptr, const void* addend,
+                            int along_n) {
+  // along_n = 0: out[T/tp, N], the ROWS of the product are scattered (1-D sequence parallelism, 3-D);
+  // along_n = 1: out[T, N/tp], the COLUMNS are scattered (2-D / 2.5-D SUMMA: every rank keeps its tokens).
+  if (tp > kMaxRanks || tp < 1) return -1;
+  if (along_n ? (N % tp != 0) : (T % tp != 0)) return -1;
+  const int Tl = along_n ? T : T / tp;       // rows of one rank's output
+  const int Nl = along_n ? N / tp : N;       // columns of one rank's output
+  if (T % kBlockM || Tl % kBlockM || N % 8 || Nl % 8 || K % 8 || lda % 8 || ldb % 8) return -5;
   if (addend && (reinterpret_cast<uintptr_t>(addend) & 15)) return -5;
+  if (along_n && bias) return -5;  // the owner-side bias is indexed by global column: add it outside in this layout
   bind_context_to_thread();
-  reduce_ctas = 0;  // the reduction is folded into the epilogue of the tiles of our own rows
+  reduce_ctas = 0;  // the reduction is folded into the epilogue of the tiles of our own block
   const int gemm_ctas_max = num_sms;
-  const int block_n = pick_block_n(T, N, gemm_ctas_max, 256);
+  int block_n = pick_block_n(T, N, gemm_ctas_max, 256);
+  if (along_n) {
+    // a tile must not straddle two owners
+    while (block_n > 64 && Nl % block_n) block_n /= 2;
+    if (Nl % block_n) return -5;
+  }
   GemmParams p{};
   p.M = T; p.N = N; p.K = K; p.batch = 1; p.batch_inner = 1; p.causal = 0;
   p.m_blocks = T / kBlockM;
@@ -117,13 +130,17 @@ extern "C" int oslo_gemm_rs(const void* A, long long lda, const void* B, long lo
   p.status = status;
   FusedParams fp;
   fp.tp = tp; fp.rank = rank; fp.shard_rows = Tl; fp.epoch = epoch; fp.copy_ctas = reduce_ctas;
-  fp.tiles_per_shard = (Tl / kBlockM) * p.n_blocks;
+  fp.rs_along_n = along_n; fp.shard_cols = Nl; fp.n_blocks_per_shard = along_n ? Nl / block_n : p.n_blocks;
+  fp.tiles_per_shard = (Tl / kBlockM) * fp.n_blocks_per_shard;
   int chunk_rows = Tl;  // hand-off granularity: about 512 rows, at most 64 flags in total
   for (int cand = 512; cand >= kBlockM; cand -= kBlockM) {
     if (Tl % cand == 0 && (Tl / cand) * tp <= 64) { chunk_rows = cand; break; }
   }
+  if ((Tl / chunk_rows) * tp > 64) return -5;
   fp.chunk_rows = chunk_rows;
-  fp.tiles_per_chunk = (chunk_rows / kBlockM) * p.n_blocks;
+  fp.cps = Tl / chunk_rows;
+  fp.slot_rows = Tl; fp.slot_ld = Nl;
+  fp.tiles_per_chunk = (chunk_rows / kBlockM) * fp.n_blocks_per_shard;
   for (int i = 0; i < tp; ++i) {
     fp.peer_slots[i] = peer_partial[i];
     fp.peer_rs_flag[i] = static_cast<int*>(peer_rs_flag[i]);
@@ -136,14 +153,14 @@ extern "C" int oslo_gemm_rs(const void* A, long long lda, const void* B, long lo
   if (b_mn) rc = make_map(&tb, B, is_bf16, N, K, 1, 1, ldb, 0, 0, 64, kBlockK);
   else      rc = make_map(&tb, B, is_bf16, K, N, 1, 1, ldb, 0, 0, kBlockK, block_n);
   if (rc) return rc;
-  // one store map per destination: rank d's slot buffer viewed [tp * Tl, N]; our rows go to slot [rank]
+  // one store map per destination: rank d's slot buffer viewed [tp * Tl, Nl]; our block goes to slot [rank]
   PeerMaps maps;
   for (int d = 0; d < kMaxRanks; ++d) {
-    rc = make_map(&maps.m[d], peer_partial[d < tp ? d : rank], is_bf16, N, T, 1, 1, N, 0, 0, 64, 32);
+    rc = make_map(&maps.m[d], peer_partial[d < tp ? d : rank], is_bf16, Nl, (long long)tp * Tl, 1, 1, Nl, 0, 0, 64, 32);
     if (rc) return rc;
   }
   const PeerMaps* peer_maps_ptr = &maps;
-  rc = make_map(&tc, out, is_bf16, N, Tl, 1, 1, N, 0, 0, 64, 32);  // final rows of this rank
+  rc = make_map(&tc, out, is_bf16, Nl, Tl, 1, 1, Nl, 0, 0, 64, 32);  // final block of this rank
   if (rc) return rc;
   taux = tc;
   const long long total = (long long)p.m_blocks * p.n_blocks;
@@ -154,5 +171,89 @@ extern "C" int oslo_gemm_rs(const void* A, long long lda, const void* B, long lo
     case 256: return OSLO_FUSED_LAUNCH(256, kModeReduceScatter);
     case 128: return OSLO_FUSED_LAUNCH(128, kModeReduceScatter);
     default: return OSLO_FUSED_LAUNCH(64, kModeReduceScatter);
+  }
+}
+
+
+// All-gather of the A rows over one group, GEMM, reduce-scatter of the product's rows over ANOTHER group, in one launch:
+//
+//     out[T/rs_tp, N] = reduce_scatter_rows_over_RS( all_gather_rows_over_AG(x_shard)[T, K] x B[N, K]^T )
+//
+// (the 3-D tensor-parallel linear: activations gathered over the INPUT group, partial products reduced over the OUTPUT
+// group; both groups cut the token dimension into the same blocks).  The two sides keep separate flags and epochs, one
+// symmetric workspace per group.  x_full receives the gathered activations for the backward pass.
+extern "C" int oslo_ag_gemm_rs(void* const* peer_in, void* x_full, const void* B, long long ldb, int b_mn, void* out, int T, int N,
+                               int K, int is_bf16, int ag_tp, int ag_rank, int ag_epoch, void* const* peer_ag_ready,
+                               int* chunk_flag, int* chunk_arrive, const int* ag_epoch_ptr, int rs_tp, int rs_rank, int rs_epoch,
+                               void* const* peer_partial, void* const* peer_rs_flag, int* tile_done, const int* rs_epoch_ptr,
+                               int copy_ctas, int num_sms, int* status, void* stream_ptr) {
+  if (ag_tp > kMaxRanks || rs_tp > kMaxRanks || ag_tp < 1 || rs_tp < 1 || T % ag_tp || T % rs_tp) return -1;
+  if (ag_tp != rs_tp) return -1;  // both groups cut the rows into the same blocks
+  const int Tl = T / rs_tp;
+  if (Tl % kBlockM || N % 8 || K % 8 || ldb % 8) return -5;
+  bind_context_to_thread();
+  if (copy_ctas < 1) copy_ctas = 1;
+  if (copy_ctas > num_sms / 2) copy_ctas = num_sms / 2;
+  const int gemm_ctas_max = num_sms - copy_ctas;
+  const int block_n = pick_block_n(T, N, gemm_ctas_max, 256);
+  GemmParams p{};
+  p.M = T; p.N = N; p.K = K; p.batch = 1; p.batch_inner = 1; p.causal = 0;
+  p.m_blocks = T / kBlockM;
+  p.n_blocks = (N + block_n - 1) / block_n;
+  p.epilogue = 0; p.accumulate = 0; p.is_bf16 = is_bf16;
+  p.bias = nullptr; p.c_ptr = out; p.ldc = N; p.stride_c = 0; p.stride_c_outer = 0; p.aux_ptr = nullptr; p.status = status;
+  FusedParams fp;
+  // reduce-scatter side (also the tile order: the next rank's rows first, our own last)
+  fp.tp = rs_tp; fp.rank = rs_rank; fp.shard_rows = Tl; fp.epoch = rs_epoch; fp.epoch_ptr = rs_epoch_ptr;
+  fp.copy_ctas = copy_ctas; fp.k_elems = K;
+  fp.n_blocks_per_shard = p.n_blocks;
+  fp.tiles_per_shard = (Tl / kBlockM) * p.n_blocks;
+  int chunk_rows = Tl;
+  for (int cand = 512; cand >= kBlockM; cand -= kBlockM) {
+    if (Tl % cand == 0 && (Tl / cand) * rs_tp <= 64) { chunk_rows = cand; break; }
+  }
+  if ((Tl / chunk_rows) * rs_tp > 64) return -5;
+  fp.chunk_rows = chunk_rows; fp.cps = Tl / chunk_rows; fp.slot_rows = Tl; fp.slot_ld = N;
+  fp.tiles_per_chunk = (chunk_rows / kBlockM) * p.n_blocks;
+  for (int i = 0; i < rs_tp; ++i) {
+    fp.peer_slots[i] = peer_partial[i];
+    fp.peer_rs_flag[i] = static_cast<int*>(peer_rs_flag[i]);
+  }
+  fp.rs_flag = static_cast<int*>(peer_rs_flag[rs_rank]);
+  fp.tile_done = tile_done; fp.rs_out = out; fp.status = status;
+  // all-gather side: same row blocks, fetched in the order the tiles will ask for them
+  fp.ag_tp = ag_tp; fp.ag_rank = ag_rank; fp.ag_shard_rows = Tl; fp.ag_chunk_rows = chunk_rows; fp.ag_epoch = ag_epoch;
+  fp.ag_epoch_ptr = ag_epoch_ptr; fp.copy_first = (rs_rank + 1) % rs_tp;
+  for (int i = 0; i < ag_tp; ++i) {
+    fp.peer_in[i] = peer_in[i];
+    fp.peer_ag_ready[i] = static_cast<int*>(peer_ag_ready[i]);
+  }
+  fp.x_full = x_full;
+  fp.ag_ready = static_cast<int*>(peer_ag_ready[ag_rank]);
+  fp.chunk_flag = chunk_flag; fp.chunk_arrive = chunk_arrive;
+  CUtensorMap ta, tb, tc, taux;
+  int rc = make_map(&ta, x_full, is_bf16, K, T, 1, 1, K, 0, 0, kBlockK, kBlockM);
+  if (rc) return rc;
+  rc = make_map(&taux, peer_in[ag_rank], is_bf16, K, Tl, 1, 1, K, 0, 0, kBlockK, kBlockM);  // own shard, read in place
+  if (rc) return rc;
+  if (b_mn) rc = make_map(&tb, B, is_bf16, N, K, 1, 1, ldb, 0, 0, 64, kBlockK);
+  else      rc = make_map(&tb, B, is_bf16, K, N, 1, 1, ldb, 0, 0, kBlockK, block_n);
+  if (rc) return rc;
+  PeerMaps maps;
+  for (int d = 0; d < kMaxRanks; ++d) {
+    rc = make_map(&maps.m[d], peer_partial[d < rs_tp ? d : rs_rank], is_bf16, N, T, 1, 1, N, 0, 0, 64, 32);
+    if (rc) return rc;
+  }
+  const PeerMaps* peer_maps_ptr = &maps;
+  rc = make_map(&tc, out, is_bf16, N, Tl, 1, 1, N, 0, 0, 64, 32);
+  if (rc) return rc;
+  const long long total = (long long)p.m_blocks * p.n_blocks;
+  const int gemm_ctas = (int)(total < gemm_ctas_max ? total : gemm_ctas_max);
+  const int grid = copy_ctas + gemm_ctas;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  switch (block_n) {
+    case 256: return OSLO_FUSED_LAUNCH(256, kModeGatherScatter);
+    case 128: return OSLO_FUSED_LAUNCH(128, kModeGatherScatter);
+    default: return OSLO_FUSED_LAUNCH(64, kModeGatherScatter);
   }
 }

@@ -82,14 +82,18 @@ OSLO_DEVINL void tile_coords(int tile, const GemmParams& p, int& b, int& mb, int
 // ------------------------------------------------------------------------------------------------
 // Fused collective modes.  Ranks exchange data through peer-mapped ("symmetric") buffers; flags hold
 // the epoch (a per-group call counter) of the last completed hand-off, so they never need clearing.
+// MODE is a bit mask: both collectives may run in one launch (all-gather of the A rows over one group, reduce-scatter
+// of the result over another one: the 3-D tensor-parallel linear).
 constexpr int kModePlain = 0;
 constexpr int kModeAllGather = 1;      // A rows are gathered from all ranks while the GEMM runs
-constexpr int kModeReduceScatter = 2;  // partial row blocks are TMA-stored to their owner; the owner's own tiles add them in
+constexpr int kModeReduceScatter = 2;  // partial blocks are TMA-stored to their owner; the owner's own tiles add them in
+constexpr int kModeGatherScatter = 3;  // both
 constexpr int kMaxRanks = 8;
 
 struct FusedParams {
+  // Tile order and reduce-scatter side.  In all-gather-only launches these describe the gather group.
   int tp = 1, rank = 0;
-  int shard_rows = 0;       // rows of A (AG) / of C (RS) owned by one rank; a multiple of 128
+  int shard_rows = 0;       // rows of A (AG) / of C (RS along rows) owned by one rank; a multiple of 128
   int tiles_per_shard = 0;  // output tiles per shard
   int tiles_per_chunk = 0;  // RS: output tiles per row chunk
   int epoch = 0;
@@ -97,6 +101,19 @@ struct FusedParams {
   int copy_ctas = 0;        // AG: CTAs [0, copy_ctas) copy, the others multiply
   int k_elems = 0;          // AG: row length of A in elements
   int chunk_rows = 0;       // rows per hand-off chunk (a multiple of 128 dividing shard_rows); one flag per chunk
+  // Reduce-scatter along the COLUMNS of C (2-D / 2.5-D linears: every rank keeps all rows and one block of features).
+  int rs_along_n = 0;
+  int shard_cols = 0;       // columns of C owned by one rank (a multiple of the tile width)
+  int n_blocks_per_shard = 0;
+  int cps = 0;              // RS: row chunks per destination block
+  int slot_rows = 0;        // RS: rows of one source's slot in the owner's slot buffer
+  int slot_ld = 0;          // RS: row pitch of the slot buffer in elements
+  // All-gather side (its own group: in a gather + scatter launch the two groups differ).
+  int ag_tp = 1, ag_rank = 0;
+  int ag_shard_rows = 0, ag_chunk_rows = 0;
+  int ag_epoch = 0;
+  const int* ag_epoch_ptr = nullptr;
+  int copy_first = 0;       // first shard the copy CTAs fetch (the order the GEMM tiles will ask for them)
   // all-gather
   const void* peer_in[kMaxRanks] = {};  // every rank's symmetric input shard [shard_rows, K]
   void* x_full = nullptr;               // local [tp * shard_rows, K]
@@ -157,16 +174,36 @@ OSLO_DEVINL void fused_tile_coords(int tile, const GemmParams& p, const FusedPar
   b = 0;
   const int i = tile / fp.tiles_per_shard;
   const int t = tile - i * fp.tiles_per_shard;
-  const int shard = (fp.rank + i + (MODE == kModeReduceScatter ? 1 : 0)) % fp.tp;
+  const int shard = (fp.rank + i + ((MODE & kModeReduceScatter) ? 1 : 0)) % fp.tp;
+  const int blocks_per_chunk = fp.chunk_rows / kBlockM;
+  if ((MODE & kModeReduceScatter) && fp.rs_along_n) {
+    // the shard is a block of COLUMNS; walk it row chunk by row chunk, all its n-blocks before the next chunk
+    const int per_chunk = blocks_per_chunk * fp.n_blocks_per_shard;
+    const int c = t / per_chunk, r = t - c * per_chunk;
+    mb = c * blocks_per_chunk + r % blocks_per_chunk;
+    nb = shard * fp.n_blocks_per_shard + r / blocks_per_chunk;
+    return;
+  }
   const int blocks_per_shard = fp.shard_rows / kBlockM;
   // walk the shard chunk by chunk (the hand-off granularity of both modes): all n-blocks of a chunk before the next
   // chunk, so chunks are consumed (all-gather) or completed (reduce-scatter) in order
-  const int blocks_per_chunk = fp.chunk_rows / kBlockM;
   const int n_blocks = fp.tiles_per_shard / blocks_per_shard;
   const int per_chunk = blocks_per_chunk * n_blocks;
   const int c = t / per_chunk, r = t - c * per_chunk;
   mb = shard * blocks_per_shard + c * blocks_per_chunk + r % blocks_per_chunk;
   nb = r / blocks_per_chunk;
+}
+
+// Reduce-scatter bookkeeping of an output tile: the rank that owns it, the row chunk inside the owner's block, and the
+// index of that (owner, chunk) pair in the counter / flag arrays.
+OSLO_DEVINL void rs_tile_owner(const FusedParams& fp, int m0, int n0, int& dest, int& c_in_dest) {
+  if (fp.rs_along_n) {
+    dest = n0 / fp.shard_cols;
+    c_in_dest = m0 / fp.chunk_rows;
+  } else {
+    dest = m0 / fp.shard_rows;
+    c_in_dest = (m0 - dest * fp.shard_rows) / fp.chunk_rows;
+  }
 }
 
 // Untiled bulk copies (TMA engine, no multicast): global -> shared with mbarrier completion, shared -> global in a
@@ -195,22 +232,22 @@ static __device__ __noinline__ void ag_copy_role(const GemmParams& p, const Fuse
   fence_barrier_init();
   if (blockIdx.x == 0) {
     __threadfence_system();
-    for (int t = 0; t < fp.tp; ++t) st_release_sys(fp.peer_ag_ready[t] + fp.rank, fp.epoch);
+    for (int t = 0; t < fp.ag_tp; ++t) st_release_sys(fp.peer_ag_ready[t] + fp.ag_rank, fp.ag_epoch);
   }
-  const int cps = fp.shard_rows / fp.chunk_rows;  // chunks per shard
-  const long long chunk_bytes = static_cast<long long>(fp.chunk_rows) * fp.k_elems * 2;
+  const int cps = fp.ag_shard_rows / fp.ag_chunk_rows;  // chunks per shard
+  const long long chunk_bytes = static_cast<long long>(fp.ag_chunk_rows) * fp.k_elems * 2;
   const int ppc = static_cast<int>((chunk_bytes + kCopyPiece - 1) / kCopyPiece);  // pieces per chunk
-  const long long total = static_cast<long long>(fp.tp) * cps * ppc;
+  const long long total = static_cast<long long>(fp.ag_tp) * cps * ppc;
   const int owners = fp.copy_ctas < ppc ? fp.copy_ctas : ppc;
   const long long my_count = (total - blockIdx.x + fp.copy_ctas - 1) / fp.copy_ctas;  // pieces g = b + j * copy_ctas
-  int ready_shard = fp.rank;
+  int ready_shard = fp.ag_rank;
   bool ok = true;
   auto locate = [&](long long j, const uint8_t*& src, uint8_t*& dst, uint32_t& bytes, int& chunk, bool& last_of_chunk, int& shard) {
     const long long g = blockIdx.x + j * fp.copy_ctas;
     const long long o = g / ppc;                      // position of the chunk in copy order
     const int piece = static_cast<int>(g - o * ppc);
-    const int i = static_cast<int>(o / cps) + 1, c = static_cast<int>(o % cps);
-    shard = (fp.rank + i) % fp.tp;
+    const int i = static_cast<int>(o / cps), c = static_cast<int>(o % cps);
+    shard = (fp.copy_first + i) % fp.ag_tp;
     chunk = shard * cps + c;
     const long long off = static_cast<long long>(piece) * kCopyPiece;
     bytes = static_cast<uint32_t>(chunk_bytes - off < kCopyPiece ? chunk_bytes - off : kCopyPiece);
@@ -223,7 +260,7 @@ static __device__ __noinline__ void ag_copy_role(const GemmParams& p, const Fuse
       const uint8_t* src; uint8_t* dst; uint32_t bytes; int chunk, shard; bool last;
       locate(n, src, dst, bytes, chunk, last, shard);
       if (shard != ready_shard) {
-        if (!flag_wait_bounded(fp.ag_ready + shard, fp.epoch, nullptr, true)) {
+        if (!flag_wait_bounded(fp.ag_ready + shard, fp.ag_epoch, nullptr, true)) {
           if (fp.status) atomicCAS(fp.status, kStatusOk, kStatusPeerFlagTimeout);
           ok = false;
           break;
@@ -254,7 +291,7 @@ static __device__ __noinline__ void ag_copy_role(const GemmParams& p, const Fuse
         if (old == owners - 1) {
           fp.chunk_arrive[chunk] = 0;
           __threadfence();
-          st_release_gpu(fp.chunk_flag + chunk, fp.epoch);
+          st_release_gpu(fp.chunk_flag + chunk, fp.ag_epoch);
         }
       }
     }
@@ -279,7 +316,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     const GemmParams p, const FusedParams fp_in, const __grid_constant__ PeerMaps peer_maps) {
   FusedParams fp = fp_in;
   if (MODE != kModePlain && fp.epoch_ptr) fp.epoch = *fp.epoch_ptr;
-  if constexpr (MODE == kModeAllGather) {
+  if ((MODE & kModeAllGather) && fp.ag_epoch_ptr) fp.ag_epoch = *fp.ag_epoch_ptr;
+  if constexpr ((MODE & kModeAllGather) != 0) {
     // the first fp.copy_ctas CTAs stream the peers' shards into local memory; the rest run the GEMM
     if (static_cast<int>(blockIdx.x) < fp.copy_ctas) {
       extern __shared__ uint8_t copy_smem_raw[];
@@ -353,14 +391,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tile_k_range(p, m0, n0, num_kb, kb0, kb1, skip);
         if (skip) continue;
         bool a_local = false;
-        if constexpr (MODE == kModeAllGather) {
+        if constexpr ((MODE & kModeAllGather) != 0) {
           // rows of shard s become loadable once the copy CTAs have flagged the chunk; the own shard is read
           // straight from the symmetric input buffer through its own tensor map
-          const int shard = m0 / fp.shard_rows;
-          const int chunk = m0 / fp.chunk_rows;
-          a_local = shard == fp.rank;
+          const int shard = m0 / fp.ag_shard_rows;
+          const int chunk = m0 / fp.ag_chunk_rows;
+          a_local = shard == fp.ag_rank;
           if (!a_local && chunk != ready_shard) {
-            if (!flag_wait_bounded(fp.chunk_flag + chunk, fp.epoch, abort_flag, false)) {
+            if (!flag_wait_bounded(fp.chunk_flag + chunk, fp.ag_epoch, abort_flag, false)) {
               ok = false;
               if (p.status) atomicCAS(p.status, kStatusOk, kStatusPeerFlagTimeout);
               break;
@@ -383,7 +421,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
             for (int c = 0; c < kBlockM / 64; ++c) tma_load_4d(sa + c * 8192, &tmA, &full_bar[stage], m0 + c * 64, k0, bi, bo);
           } else {
-            if (MODE == kModeAllGather && a_local) tma_load_4d(sa, &tmAux, &full_bar[stage], k0, m0 - fp.rank * fp.shard_rows, bi, bo);
+            if ((MODE & kModeAllGather) && a_local) tma_load_4d(sa, &tmAux, &full_bar[stage], k0, m0 - fp.ag_rank * fp.ag_shard_rows, bi, bo);
             else tma_load_4d(sa, &tmA, &full_bar[stage], k0, m0, bi, bo);
           }
           if (B_MN) {
@@ -481,13 +519,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int row = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BLOCK_N;
       bool rs_own = false;
-      if constexpr (MODE == kModeReduceScatter) {
-        // tiles of OUR rows finish the reduction themselves: the other ranks' partial rows must have landed in our
-        // slot buffer (they compute our rows first, so this normally does not wait)
-        rs_own = (m0 / fp.shard_rows) == fp.rank;
+      int rs_dest = 0, rs_c = 0;  // owner of this tile and row chunk inside the owner's block
+      (void)rs_dest; (void)rs_c;
+      if constexpr ((MODE & kModeReduceScatter) != 0) {
+        // tiles of OUR block finish the reduction themselves: the other ranks' partials must have landed in our
+        // slot buffer (they compute our block first, so this normally does not wait)
+        rs_tile_owner(fp, m0, n0, rs_dest, rs_c);
+        rs_own = rs_dest == fp.rank;
         if (rs_own) {
-          const int cps = fp.shard_rows / fp.chunk_rows;
-          const int c = (m0 - fp.rank * fp.shard_rows) / fp.chunk_rows;
+          const int cps = fp.cps;
+          const int c = rs_c;
           bool got = true;
           if (lane < fp.tp && lane != fp.rank) got = flag_wait_bounded(fp.rs_flag + lane * cps + c, fp.epoch, abort_flag, true);
           got = __all_sync(0xffffffffu, got);
@@ -518,7 +559,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           v[i] = __uint_as_float(r0[i]);
           v[32 + i] = __uint_as_float(r1[i]);
         }
-        if (p.bias != nullptr && (MODE != kModeReduceScatter || rs_own)) {  // RS: the bias is added once, by the owner
+        if (p.bias != nullptr && (!(MODE & kModeReduceScatter) || rs_own)) {  // RS: the bias is added once, by the owner
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             if (col0 + g * 8 < p.N) {
@@ -566,13 +607,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
           }
         }
-        if constexpr (MODE == kModeReduceScatter) {
+        if constexpr ((MODE & kModeReduceScatter) != 0) {
           if (rs_own && ok) {
-            const long long r_local = static_cast<long long>(m0 - fp.rank * fp.shard_rows + q * 32 + lane);
+            const long long r_local = static_cast<long long>((fp.rs_along_n ? m0 : m0 - fp.rank * fp.shard_rows) + q * 32 + lane);
+            const int c_local = fp.rs_along_n ? col0 - fp.rank * fp.shard_cols : col0;
             for (int src = 0; src < fp.tp; ++src) {
               if (src == fp.rank) continue;
               const uint16_t* sp = static_cast<const uint16_t*>(fp.peer_slots[fp.rank]) +
-                                   (static_cast<long long>(src) * fp.shard_rows + r_local) * p.N + col0;
+                                   (static_cast<long long>(src) * fp.slot_rows + r_local) * fp.slot_ld + c_local;
 #pragma unroll
               for (int g = 0; g < 8; ++g) {
                 if (col0 + g * 8 < p.N) {
@@ -628,11 +670,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            if constexpr (MODE == kModeReduceScatter) {
-              // slot [this rank] of the rank that owns these rows (a peer-mapped buffer; plain bulk store, no multicast)
-              const int dest = m0 / fp.shard_rows;
-              if (rs_own) tma_store_4d(&tmC, sbuf_ptr, col0, m0 - fp.rank * fp.shard_rows + q * 32, 0, 0);  // final rows
-              else tma_store_4d(&peer_maps.m[dest], sbuf_ptr, col0, fp.rank * fp.shard_rows + (m0 - dest * fp.shard_rows) + q * 32, 0, 0);
+            if constexpr ((MODE & kModeReduceScatter) != 0) {
+              // slot [this rank] of the rank that owns this block (a peer-mapped buffer; plain bulk store, no multicast)
+              const int dest = rs_dest;
+              const int r_in = fp.rs_along_n ? m0 : m0 - dest * fp.shard_rows;
+              const int c_in = fp.rs_along_n ? col0 - dest * fp.shard_cols : col0;
+              if (rs_own) tma_store_4d(&tmC, sbuf_ptr, c_in, r_in + q * 32, 0, 0);  // final values
+              else tma_store_4d(&peer_maps.m[dest], sbuf_ptr, c_in, fp.rank * fp.slot_rows + r_in + q * 32, 0, 0);
             } else {
               tma_store_4d(pass == 0 ? &tmAux : &tmC, sbuf_ptr, col0, m0 + q * 32, bi, bo);
             }
@@ -641,18 +685,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           sbuf ^= 1;
         }
       }
-      if constexpr (MODE == kModeReduceScatter) {
+      if constexpr ((MODE & kModeReduceScatter) != 0) {
         // The partial tile went into the owner's slot buffer.  Count this warp's finished quarter-tiles per row chunk
         // and publish the count when the warp moves on to another chunk (or runs out of tiles): wait for its TMA
         // stores to be complete, then one atomic; the warp that completes a chunk raises the flag on the owner,
         // whose reducer CTAs then sum the tp slots of that chunk out of their local memory.
-        const int chunk = m0 / fp.chunk_rows;
+        const int chunk = rs_dest * fp.cps + rs_c;
         const int next_tile = tile + num_ctas;
         int next_chunk = -1;
         if (next_tile < num_tiles) {
-          int nb2, mb2, b2;
+          int nb2, mb2, b2, d2, c2;
           fused_tile_coords<MODE>(next_tile, p, fp, b2, mb2, nb2);
-          next_chunk = mb2 * kBlockM / fp.chunk_rows;
+          rs_tile_owner(fp, mb2 * kBlockM, nb2 * BLOCK_N, d2, c2);
+          next_chunk = d2 * fp.cps + c2;
         }
         if (!rs_own) ++rs_pending;
         if (next_chunk != chunk && rs_pending > 0) {
@@ -665,9 +710,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if (old + rs_pending == need) {
               fp.tile_done[chunk] = 0;
               __threadfence_system();
-              const int dest = m0 / fp.shard_rows;
-              const int cps = fp.shard_rows / fp.chunk_rows;
-              st_release_sys(fp.peer_rs_flag[dest] + fp.rank * cps + (chunk - dest * cps), fp.epoch);
+              st_release_sys(fp.peer_rs_flag[rs_dest] + fp.rank * fp.cps + rs_c, fp.epoch);
             }
           }
           rs_pending = 0;

@@ -266,9 +266,12 @@ class SymmetricWorkspace:
         return (self.supports(x_shard, w) and tl % 128 == 0 and tl * self.tp <= self.max_tokens
                 and k <= self.max_features and tl * k * x_shard.element_size() <= self.in_bytes)
 
-    def rs_ok(self, x, w) -> bool:
+    def rs_ok(self, x, w, along_n: bool = False) -> bool:
         t, _ = x.shape
         n = w.shape[0]
+        if along_n:  # every rank keeps its rows, the columns are scattered
+            return (self.supports(x, w) and t % 128 == 0 and n % self.tp == 0 and (n // self.tp) % 64 == 0
+                    and t * n * x.element_size() <= self.slot_bytes)
         return (self.supports(x, w) and t % self.tp == 0 and (t // self.tp) % 128 == 0 and t <= self.max_tokens
                 and n <= self.max_features and t * n * x.element_size() <= self.slot_bytes)
 
@@ -298,17 +301,18 @@ class SymmetricWorkspace:
         return out, x_full
 
     def gemm_rs(self, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                addend: Optional[torch.Tensor] = None):
-        """Returns this rank's rows of ``reduce_scatter(x @ weight^T + addend)``; ``addend`` is an optional local
-        ``[T, N]`` partial product that rides along in the same reduce-scatter."""
+                addend: Optional[torch.Tensor] = None, along_n: bool = False):
+        """Returns this rank's block of ``reduce_scatter(x @ weight^T + addend)``: its rows (``[T/tp, N]``), or with
+        ``along_n`` its columns (``[T, N/tp]``, the 2-D / 2.5-D layouts).  ``addend`` is an optional local ``[T, N]``
+        partial product that rides along in the same reduce-scatter."""
         t, k = x.shape
         n = weight.shape[0]
-        tl = t // self.tp
+        tl = t if along_n else t // self.tp
         if not x.is_contiguous():
             x = x.contiguous()
         self._next_epoch()
         parity = self.epoch & 1
-        out = torch.empty(tl, n, dtype=x.dtype, device=x.device)
+        out = torch.empty(tl, n // self.tp if along_n else n, dtype=x.dtype, device=x.device)
         w, b_mn, ldb = self._weight_operand(weight)
         if addend is not None:
             if addend.shape != (t, n) or addend.dtype != x.dtype:
@@ -320,10 +324,46 @@ class SymmetricWorkspace:
             ctypes.c_int(1 if self.dtype == torch.bfloat16 else 0), ctypes.c_int(self.tp), ctypes.c_int(self.rank),
             ctypes.c_int(self.epoch), self._slot_ptrs(parity), self._flag_ptrs(1), self._local_ptr(2),
             ctypes.c_int(self.copy_ctas), ctypes.c_int(_lib.num_sms()), _lib.ptr(_lib.status_word(self.device)),
-            _lib.stream_ptr(), _lib.ptr(self.debug_times), _lib.ptr(self.epoch_dev), _lib.ptr(addend))
+            _lib.stream_ptr(), _lib.ptr(self.debug_times), _lib.ptr(self.epoch_dev), _lib.ptr(addend),
+            ctypes.c_int(1 if along_n else 0))
         if rc:
             raise RuntimeError(f"oslo_gemm_rs failed ({rc})")
         return out
+
+    def ag_gemm_rs(self, rs_ws: "SymmetricWorkspace", x_shard: torch.Tensor, weight: torch.Tensor):
+        """``reduce_scatter_rows over rs_ws's group ( all_gather_rows over this group (x_shard) @ weight^T )`` in one
+        launch; returns ``(out [T / tp, N], gathered x [T, K])``.  Both groups must have the same size (they cut the
+        rows into the same blocks), e.g. the INPUT and OUTPUT groups of 3-D tensor parallelism."""
+        tl, k = x_shard.shape
+        t = tl * self.tp
+        n = weight.shape[0]
+        if rs_ws.tp != self.tp:
+            raise ValueError("ag_gemm_rs: the gather and scatter groups must have the same size")
+        self._next_epoch()
+        rs_ws._next_epoch()
+        ag_par, rs_par = self.epoch & 1, rs_ws.epoch & 1
+        self._local_in(ag_par, tl, k).copy_(x_shard)
+        x_full = torch.empty(t, k, dtype=x_shard.dtype, device=x_shard.device)
+        out = torch.empty(tl, n, dtype=x_shard.dtype, device=x_shard.device)
+        w, b_mn, ldb = self._weight_operand(weight)
+        rc = _lib.cuda_lib().oslo_ag_gemm_rs(
+            self._in_ptrs(ag_par), _lib.ptr(x_full), _lib.ptr(w), ctypes.c_longlong(ldb), ctypes.c_int(b_mn), _lib.ptr(out),
+            ctypes.c_int(t), ctypes.c_int(n), ctypes.c_int(k), ctypes.c_int(1 if self.dtype == torch.bfloat16 else 0),
+            ctypes.c_int(self.tp), ctypes.c_int(self.rank), ctypes.c_int(self.epoch), self._flag_ptrs(0),
+            self._local_ptr(0), self._local_ptr(1), _lib.ptr(self.epoch_dev),
+            ctypes.c_int(rs_ws.tp), ctypes.c_int(rs_ws.rank), ctypes.c_int(rs_ws.epoch), rs_ws._slot_ptrs(rs_par),
+            rs_ws._flag_ptrs(1), rs_ws._local_ptr(2), _lib.ptr(rs_ws.epoch_dev),
+            ctypes.c_int(self.copy_ctas), ctypes.c_int(_lib.num_sms()), _lib.ptr(_lib.status_word(self.device)),
+            _lib.stream_ptr())
+        if rc:
+            raise RuntimeError(f"oslo_ag_gemm_rs failed ({rc})")
+        return out, x_full
+
+    def ag_rs_ok(self, rs_ws, x_shard, w) -> bool:
+        tl, k = x_shard.shape
+        t, n = tl * self.tp, w.shape[0]
+        return (self.ag_ok(x_shard, w) and rs_ws is not None and rs_ws.tp == self.tp
+                and t * n * x_shard.element_size() <= rs_ws.slot_bytes)
 
 
 class _Runtime:
@@ -343,27 +383,30 @@ class _Runtime:
             raise RuntimeError("ag_gemm: operands not supported by the fused kernel")
         return self.ws.ag_gemm(x_shard, weight, bias)
 
-    def gemm_rs(self, x, weight, addend=None):
-        if not self.ws.rs_ok(x, weight):
+    def gemm_rs(self, x, weight, addend=None, along_n=False):
+        if not self.ws.rs_ok(x, weight, along_n):
             raise RuntimeError("gemm_rs: operands not supported by the fused kernel")
-        return self.ws.gemm_rs(x, weight, addend=addend)
+        return self.ws.gemm_rs(x, weight, addend=addend, along_n=along_n)
 
 
 def enable(pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 24, model=None) -> bool:
-    """Create the group's symmetric workspace and switch the sequence-parallel linears to the fused kernels.
-    With ``model`` given, its vocab-parallel embedding tables are moved to symmetric memory as well."""
+    """Create the group's symmetric workspace and switch the linears that communicate over ``mode`` to the fused kernels:
+    ``TENSOR_1D`` for the sequence-parallel 1-D linears, ``TENSOR_2D_ROW`` / ``TENSOR_2P5D_ROW`` for the feature
+    reduce-scatter of the SUMMA linears, ``TENSOR_3D_INPUT`` + ``TENSOR_3D_OUTPUT`` (call twice) for the 3-D linear.
+    ``max_tokens x max_features`` bounds the product that one call may exchange.  With ``model`` given, its
+    vocab-parallel embedding tables are moved to symmetric memory as well."""
     if not (torch.cuda.is_available() and pc.use_cuda) or pc.get_world_size(mode) == 1:
         return False
     if model is not None:
         rehome_vocab_embeddings(model, pc, mode)
     global _fused_small_ops
     ws = SymmetricWorkspace(pc, mode, max_tokens, max_features, dtype, copy_ctas)
-    fused_collectives.set_runtime(_Runtime(ws))
+    fused_collectives.set_runtime(_Runtime(ws), mode)
     _fused_small_ops = True
     return True
 
 
 def disable():
     global _fused_small_ops
-    fused_collectives.set_runtime(None)
+    fused_collectives.clear_runtimes()
     _fused_small_ops = False

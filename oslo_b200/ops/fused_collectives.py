@@ -9,16 +9,33 @@ from __future__ import annotations
 
 import torch
 
-_runtime = None  # set by oslo_b200.distributed.symm.enable(...)
+_runtime = None  # the 1-D group's runtime, set by oslo_b200.distributed.symm.enable(...)
+_runtimes = {}   # ParallelMode -> runtime, for the groups of the 2-D / 2.5-D / 3-D layouts
 
 
-def set_runtime(rt):
+def set_runtime(rt, mode=None):
+    """Register (or with ``rt=None`` drop) the runtime of one group.  ``mode=None`` or the 1-D tensor mode is the
+    runtime that the sequence-parallel linears use."""
     global _runtime
-    _runtime = rt
+    from oslo_b200.distributed import ParallelMode
+
+    if mode is None or mode == ParallelMode.TENSOR_1D:
+        _runtime = rt
+    if mode is not None:
+        if rt is None:
+            _runtimes.pop(mode, None)
+        else:
+            _runtimes[mode] = rt
 
 
-def runtime():
-    return _runtime
+def clear_runtimes():
+    global _runtime
+    _runtime = None
+    _runtimes.clear()
+
+
+def runtime(mode=None):
+    return _runtime if mode is None else _runtimes.get(mode)
 
 
 def available(x: torch.Tensor, w: torch.Tensor, kind: str = "any") -> bool:
@@ -41,3 +58,26 @@ def ag_gemm(x_shard, weight, pc, bias=None):
 def gemm_rs(x, weight, pc, addend=None):
     """``reduce_scatter(x @ weight^T + addend)`` over the token dim in one kernel (``addend``: optional local [T, N])."""
     return _runtime.gemm_rs(x, weight, addend=addend)
+
+
+def feature_rs_available(x: torch.Tensor, w: torch.Tensor, mode) -> bool:
+    """Can ``gemm_rs_features`` run for these operands over the group of ``mode``?"""
+    rt = _runtimes.get(mode)
+    return rt is not None and x.is_cuda and x.dim() == 2 and rt.ws.rs_ok(x, w, along_n=True)
+
+
+def gemm_rs_features(x, weight, mode):
+    """``reduce_scatter(x @ weight^T)`` over the FEATURE dim within the group of ``mode`` (2-D / 2.5-D linears):
+    ``[T, K] x [N, K]^T -> [T, N / q]`` in one kernel."""
+    return _runtimes[mode].gemm_rs(x, weight, along_n=True)
+
+
+def gather_scatter_available(x_shard: torch.Tensor, w: torch.Tensor, ag_mode, rs_mode) -> bool:
+    a, r = _runtimes.get(ag_mode), _runtimes.get(rs_mode)
+    return a is not None and r is not None and x_shard.is_cuda and x_shard.dim() == 2 and a.ws.ag_rs_ok(r.ws, x_shard, w)
+
+
+def ag_gemm_rs(x_shard, weight, ag_mode, rs_mode):
+    """``(reduce_scatter_rows over rs_mode (all_gather_rows over ag_mode (x_shard) @ weight^T), gathered x)`` in one
+    kernel (the 3-D linear: INPUT gather, OUTPUT scatter)."""
+    return _runtimes[ag_mode].ws.ag_gemm_rs(_runtimes[rs_mode].ws, x_shard, weight)

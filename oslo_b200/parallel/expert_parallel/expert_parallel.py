@@ -16,6 +16,7 @@ Parity: oslo/torch/nn/parallel/expert_parallel/expert_parallel.py:30-598.
 """
 from __future__ import annotations
 
+import copy
 import os
 from typing import Dict, Optional, Union
 
@@ -123,9 +124,11 @@ class ExpertParallel(ParallelWrapper):
                 gate.wg.weight.data.copy_(torch.randn(gate.wg.weight.shape, generator=ggen).mul_(std))
                 gate.wg.to(w.device)
                 gate.parallel_context = pc
-                new = ExpertParallelFrontBlock(gate, experts, link, pc, self.ep_size, e_local, skip_bias_add=skip)
+                new = ExpertParallelFrontBlock(gate, experts, link, pc, self.ep_size, e_local, skip_bias_add=skip,
+                                               residual=copy.deepcopy(child) if self.use_residual else None)
             else:
-                new = ExpertParallelBehindBlock(experts, link, pc, self.ep_size, e_local, skip_bias_add=skip)
+                new = ExpertParallelBehindBlock(experts, link, pc, self.ep_size, e_local, skip_bias_add=skip,
+                                                residual=copy.deepcopy(child) if self.use_residual else None)
             parent = module
             parts = name.split(".")
             for p in parts[:-1]:

@@ -189,7 +189,13 @@ class ExpertParallelFrontBlock(nn.Module):
         self.link, self.parallel_context = link, parallel_context
         self.ep_size, self.num_local_experts = ep_size, num_local_experts
         self.skip_bias_add = skip_bias_add
+        # Residual-MoE (reference layers.py:402-461): a dense copy of the replaced linear runs beside the experts and a
+        # learned 2-way softmax mixes the two results per token
         self.residual = residual
+        self.residual_mix = None
+        if residual is not None:
+            w = next(residual.parameters())
+            self.residual_mix = nn.Linear(gate.wg.weight.shape[1], 2, dtype=w.dtype, device=w.device)
 
     def forward(self, x):
         link = self.link
@@ -208,30 +214,52 @@ class ExpertParallelFrontBlock(nn.Module):
             buf = moe_ops.dispatch(tokens, slot, E * C)
             buf = _all_to_all_experts(buf, self.ep_size, self.num_local_experts, C, self.parallel_context)
         out = self.experts(buf)
+        link.residual_rows = 0
         if self.residual is not None:
-            link.residual_in = tokens
+            # the dense intermediate rides behind the expert rows, so whatever the model applies between the two
+            # linears of its MLP (activation, dropout) covers both; the behind block splits them again
+            inter = self.residual(tokens)
+            if isinstance(inter, tuple):  # a skip_bias_add linear hands its bias back: the experts have none to add it to
+                inter = inter[0] if inter[1] is None else inter[0] + inter[1]
+            link.residual_weight = torch.softmax(self.residual_mix(tokens).float(), dim=-1)
+            link.expert_shape = out.shape
+            link.residual_rows = inter.shape[0]
+            out = torch.cat([out.reshape(-1, out.shape[-1]), inter.to(out.dtype)], dim=0)
         return (out, None) if self.skip_bias_add else out
 
 
 class ExpertParallelBehindBlock(nn.Module):
-    def __init__(self, experts: Experts, link: MoELink, parallel_context, ep_size, num_local_experts, skip_bias_add=False):
+    def __init__(self, experts: Experts, link: MoELink, parallel_context, ep_size, num_local_experts, skip_bias_add=False,
+                 residual: Optional[nn.Module] = None):
         super().__init__()
         self.experts = experts
         self.link, self.parallel_context = link, parallel_context
         self.ep_size, self.num_local_experts = ep_size, num_local_experts
         self.skip_bias_add = skip_bias_add
+        self.residual = residual  # dense copy of the replaced linear (Residual-MoE)
 
-    def forward(self, x):  # x: [E_local, ep * C, ffn]
+    def forward(self, x):  # x: [E_local, ep * C, ffn]  (+ the dense rows behind it under Residual-MoE)
         link = self.link
+        dense = None
+        rows = getattr(link, "residual_rows", 0)
+        if rows:
+            dense = x[x.shape[0] - rows :]
+            x = x[: x.shape[0] - rows].view(link.expert_shape)
         out = self.experts(x)
         if getattr(link, "fused", False):
             from . import fused
 
             y = fused.PeerCombine.apply(out, link.weight, link.slot, self.parallel_context, self.ep_size, self.num_local_experts,
                                         link.capacity)
-            y = y.view(*link.in_shape[:-1], y.shape[-1])
-            return (y, None) if self.skip_bias_add else y
-        out = _all_to_all_experts(out, self.ep_size, self.num_local_experts, link.capacity, self.parallel_context, inverse=True)
-        y = moe_ops.combine(out.reshape(-1, out.shape[-1]), link.weight.to(out.dtype), link.slot)
+        else:
+            out = _all_to_all_experts(out, self.ep_size, self.num_local_experts, link.capacity, self.parallel_context, inverse=True)
+            y = moe_ops.combine(out.reshape(-1, out.shape[-1]), link.weight.to(out.dtype), link.slot)
+        if dense is not None:
+            if self.residual is None:
+                raise RuntimeError("the front block produced a dense residual but this block has no residual module")
+            r = self.residual(dense)
+            r = r[0] + r[1] if isinstance(r, tuple) and r[1] is not None else (r[0] if isinstance(r, tuple) else r)
+            w = link.residual_weight
+            y = (y.float() * w[:, 0:1] + r.float() * w[:, 1:2]).to(y.dtype)
         y = y.view(*link.in_shape[:-1], y.shape[-1])
         return (y, None) if self.skip_bias_add else y

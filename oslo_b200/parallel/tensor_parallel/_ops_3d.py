@@ -70,11 +70,54 @@ def transpose_3d(t, pc):
     return _Swap3D.apply(t, pc)
 
 
+class _GatherLinearScatter3D(torch.autograd.Function):
+    """``reduce_scatter_OUTPUT(all_gather_INPUT(x) W^T)`` as ONE kernel (``oslo_ag_gemm_rs``): copy CTAs pull the other
+    INPUT ranks' token blocks while the GEMM CTAs multiply, and each finished tile is TMA-stored straight into the OUTPUT
+    rank that owns its rows.  Backward: all-gather(dY over OUTPUT), two GEMMs, reduce-scatter(dX over INPUT)."""
+
+    @staticmethod
+    def forward(ctx, x, wg, pc):
+        from oslo_b200.ops import fused_collectives as fc
+
+        ctx.pc, ctx.shape = pc, x.shape
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        y, x_full = fc.ag_gemm_rs(x2, wg, INPUT, OUTPUT)
+        ctx.save_for_backward(x_full, wg)
+        return y.view(*x.shape[:-1], y.shape[-1])
+
+    @staticmethod
+    def backward(ctx, g):
+        from oslo_b200.distributed import comm
+        from oslo_b200.ops.gemm import matmul_nt
+
+        x_full, wg = ctx.saved_tensors
+        pc = ctx.pc
+        g2 = g.reshape(-1, g.shape[-1]).contiguous()
+        g_full = comm.all_gather(g2, dim=0, parallel_context=pc, parallel_mode=OUTPUT)
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            gx_full = matmul_nt(g_full, wg.t())
+            gx = comm.reduce_scatter(gx_full, dim=0, parallel_context=pc, parallel_mode=INPUT).view(ctx.shape)
+        if ctx.needs_input_grad[1]:
+            gw = matmul_nt(g_full.t(), x_full.t())
+        return gx, gw, None
+
+
 def linear_3d(x, weight, bias, pc):
-    xg = nd.all_gather(x, 0, INPUT, pc)
     wg = nd.all_gather(weight, 0, WEIGHT, pc)
-    partial = linear(xg, wg)
-    y = nd.reduce_scatter(partial, 0, OUTPUT, pc)
+    fused = False
+    if x.is_cuda and pc.cubic_dim > 1:
+        from oslo_b200.ops import fused_collectives as fc
+
+        fused = fc.gather_scatter_available(x.reshape(-1, x.shape[-1]), wg, INPUT, OUTPUT)
+    if fused:
+        y = _GatherLinearScatter3D.apply(x, wg, pc)
+    else:
+        xg = nd.all_gather(x, 0, INPUT, pc)
+        partial = linear(xg, wg)
+        y = nd.reduce_scatter(partial, 0, OUTPUT, pc)
     if bias is not None:
         y = y + bias
     return transpose_3d(y, pc)

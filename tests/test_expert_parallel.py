@@ -55,7 +55,7 @@ def _moe_model(seed=0):
     return MoEGPTLMHeadModel(cfg)
 
 
-def _worker(rank, world):
+def _worker(rank, world, use_residual=False):
     import oslo_b200
     from oslo_b200 import ParallelContext
     from oslo_b200.parallel import ExpertParallel
@@ -67,8 +67,12 @@ def _worker(rank, world):
     model = _moe_model()
     # large capacity: nothing is dropped, so routing is the same per token however the batch is split
     wrapped = ExpertParallel(model, pc, num_dec_experts={1: 4}, top_k=2, capacity_factor_train=8.0, use_rts=False,
-                             aux_loss_coef=0.0)
+                             aux_loss_coef=0.0, use_residual=use_residual)
     oslo_b200.ready(wrapped, pc)
+    if use_residual:
+        mixes = [n for n, _ in model.named_parameters() if "residual_mix" in n]
+        dense = [n for n, _ in model.named_parameters() if ".residual." in n]
+        assert len(mixes) == 2 and len(dense) >= 2, (mixes, dense)  # a 2-way mixer and dense copies of both linears
     wrapped.eval()  # no routing noise
     out = wrapped(input_ids=ids, labels=ids)
     out.loss.backward()
@@ -80,7 +84,7 @@ def _worker(rank, world):
 
     ref = _moe_model()
     ref_wrapped = ExpertParallel(ref, pc, num_dec_experts={1: 4}, top_k=2, capacity_factor_train=8.0, use_rts=False,
-                                 aux_loss_coef=0.0)
+                                 aux_loss_coef=0.0, use_residual=use_residual)
     ref_wrapped.ep_size, ref_wrapped.ep_rank, ref_wrapped.sync_dense_grads = 1, 0, False
     ref_wrapped.parallelize()
     ref_wrapped.eval()
@@ -106,6 +110,11 @@ def _worker(rank, world):
 
 def test_expert_parallel_matches_single_group():
     run_dist(_worker, 2)
+
+
+def test_residual_moe_matches_single_group():
+    """``use_residual=True``: a dense copy of the FFN runs beside the experts and a learned softmax mixes them."""
+    run_dist(_worker, 2, True)
 
 
 def test_gate_capacity_and_aux_loss():

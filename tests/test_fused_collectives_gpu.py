@@ -25,6 +25,9 @@ def _worker(rank, world):
                                     backend="nccl", seed=0)
     dev = pc.device
     assert symm.enable(pc, ParallelMode.TENSOR_1D, max_tokens=4096, max_features=1024)
+    # a second workspace over the same ranks stands for the second group of the 3-D linear (gather and scatter groups
+    # differ there; the kernel only sees two sets of peer pointers, flags and epochs)
+    ws2 = symm.SymmetricWorkspace(pc, ParallelMode.TENSOR_1D, 4096, 1024)
     M1 = ParallelMode.TENSOR_1D
     torch.manual_seed(100 + rank)
 
@@ -64,6 +67,22 @@ def _worker(rank, world):
         torch.cuda.synchronize()
         _lib.check_status()
         assert rel(out2, ref2) < 2e-2, (it, rel(out2, ref2))
+        # ---- reduce-scatter along the FEATURE dim (2-D / 2.5-D layouts): every rank keeps its rows
+        ws = fc.runtime().ws
+        if ws.rs_ok(xa, WN, along_n=True):
+            out3 = ws.gemm_rs(xa, WN, along_n=True)
+            ref3 = comm.reduce_scatter(part, dim=-1, parallel_context=pc, parallel_mode=M1)
+            torch.cuda.synchronize()
+            _lib.check_status()
+            assert out3.shape == ref3.shape, (out3.shape, ref3.shape)
+            assert rel(out3, ref3) < 2e-2, (it, rel(out3, ref3))
+        # ---- all-gather (one workspace) -> GEMM -> reduce-scatter of the rows (a second workspace) in one launch
+        out4, xf4 = ws.ag_gemm_rs(ws2, x, W)
+        ref4 = comm.reduce_scatter(y_ref, dim=0, parallel_context=pc, parallel_mode=M1)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        assert torch.equal(xf4, x_ref), f"gathered activations differ in the gather+scatter launch (case {it})"
+        assert rel(out4, ref4) < 2e-2, (it, rel(out4, ref4))
     dist.barrier()
     pc.destroy()
 
