@@ -1,5 +1,6 @@
 """Text generation for the in-tree causal language models: greedy, top-k / top-p sampling and beam search, with
-n-gram blocking on the fused kernel.
+n-gram blocking on the fused kernel and a key / value cache: the prompt is run once, after which every step feeds only
+the newest token and attends over the cached keys and values (``oslo_b200.ops.attention.DecodeCache``).
 
 A compact counterpart of LightSeq's inference engine entry points (oslo/lightseq2/inference/pywrapper/*, sampling and
 beam-search kernels in inference/kernels/transformerKernels.cc.cu): the model forward runs on this repository's
@@ -13,10 +14,19 @@ import torch
 import torch.nn.functional as F
 
 from oslo_b200.nn.ngram_repeat_block import NGramRepeatBlock
+from oslo_b200.ops.attention import DecodeCache, decode_cache
 
 
-def _logits(model, ids):
-    out = model(input_ids=ids)
+def _logits(model, ids, cache: Optional[DecodeCache] = None):
+    """Next-token logits.  With a cache only the tokens it has not seen yet are run through the model."""
+    if cache is None:
+        out = model(input_ids=ids)
+    else:
+        new = ids[:, cache.offset :]
+        cache.begin_forward()
+        with decode_cache(cache):
+            out = model(input_ids=new)
+        cache.advance(new.shape[1])
     logits = out.logits if hasattr(out, "logits") else out[0]
     return logits[:, -1, :].float()
 
@@ -37,16 +47,20 @@ def _filter(logits, top_k: int, top_p: float):
 @torch.no_grad()
 def generate(model, input_ids: torch.Tensor, max_new_tokens: int = 32, do_sample: bool = False, top_k: int = 0,
              top_p: float = 1.0, temperature: float = 1.0, num_beams: int = 1, no_repeat_ngram_size: int = 0,
-             eos_token_id: Optional[int] = None, length_penalty: float = 1.0, pad_multiple: int = 1):
-    """Returns ``[batch, prompt + new]`` token ids (best beam when ``num_beams > 1``)."""
+             eos_token_id: Optional[int] = None, length_penalty: float = 1.0, pad_multiple: int = 1,
+             use_cache: bool = True):
+    """Returns ``[batch, prompt + new]`` token ids (best beam when ``num_beams > 1``).  ``use_cache=False`` re-runs the
+    whole prefix every step (the reference behaviour for models whose attention does not go through ``oslo_b200.ops``)."""
     model.eval()
     if num_beams > 1:
-        return _beam_search(model, input_ids, max_new_tokens, num_beams, no_repeat_ngram_size, eos_token_id, length_penalty)
+        return _beam_search(model, input_ids, max_new_tokens, num_beams, no_repeat_ngram_size, eos_token_id, length_penalty,
+                            use_cache)
     ids = input_ids
     blocker = NGramRepeatBlock()
     done = torch.zeros(ids.shape[0], dtype=torch.bool, device=ids.device)
+    cache = DecodeCache() if use_cache else None
     for _ in range(max_new_tokens):
-        logits = _logits(model, ids) / max(temperature, 1e-6)
+        logits = _logits(model, ids, cache) / max(temperature, 1e-6)
         if no_repeat_ngram_size > 0:
             logits = blocker(ids, logits.contiguous(), ids.shape[0], ids.shape[1] - 1, 1, no_repeat_ngram_size)
         if do_sample:
@@ -62,7 +76,7 @@ def generate(model, input_ids: torch.Tensor, max_new_tokens: int = 32, do_sample
     return ids
 
 
-def _beam_search(model, input_ids, max_new_tokens, beams, ngram, eos, length_penalty):
+def _beam_search(model, input_ids, max_new_tokens, beams, ngram, eos, length_penalty, use_cache=True):
     b, prompt = input_ids.shape
     dev = input_ids.device
     ids = input_ids.repeat_interleave(beams, dim=0)  # [b * beams, t]
@@ -70,8 +84,9 @@ def _beam_search(model, input_ids, max_new_tokens, beams, ngram, eos, length_pen
     scores[:, 1:] = float("-inf")  # all beams start identical: keep one alive
     finished = torch.zeros(b * beams, dtype=torch.bool, device=dev)
     blocker = NGramRepeatBlock()
+    cache = DecodeCache() if use_cache else None
     for _ in range(max_new_tokens):
-        lp = F.log_softmax(_logits(model, ids), dim=-1)
+        lp = F.log_softmax(_logits(model, ids, cache), dim=-1)
         if ngram > 0:
             lp = blocker(ids, lp.contiguous(), b, ids.shape[1] - 1, beams, ngram)
         vocab = lp.shape[-1]
@@ -85,6 +100,8 @@ def _beam_search(model, input_ids, max_new_tokens, beams, ngram, eos, length_pen
         src = idx // vocab + (torch.arange(b, device=dev) * beams).unsqueeze(1)
         tok = idx % vocab
         ids = torch.cat([ids[src.view(-1)], tok.view(-1, 1)], dim=1)
+        if cache is not None:
+            cache.reorder(src.view(-1))  # the surviving hypotheses keep the keys / values of the beams they extend
         scores = top
         if eos is not None:
             finished = finished[src.view(-1)] | (tok.view(-1) == eos)

@@ -79,7 +79,9 @@ class GPT2Model(PreTrainedModel):
     def forward(self, input_ids, attention_mask=None, position_ids=None):
         s = input_ids.shape[-1]
         if position_ids is None:
-            position_ids = torch.arange(s, device=input_ids.device).unsqueeze(0)
+            from oslo_b200.ops.attention import decode_offset
+
+            position_ids = (torch.arange(s, device=input_ids.device) + decode_offset()).unsqueeze(0)
         x = self.wte(input_ids)
         pos = self.wpe(position_ids)
         if pos.shape[:-1] != x.shape[:-1] and pos.shape[0] != 1:

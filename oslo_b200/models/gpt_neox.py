@@ -42,7 +42,8 @@ class GPTNeoXAttention(nn.Module):
         if self._rope is None or self._rope[0].shape[0] < seq or self._rope[0].device != device:
             n = max(seq, self.max_positions)
             self._rope = OF.rope_tables(n, self.rotary_ndims, self.rotary_base, device)
-        return self._rope
+        # rows [0, seq): the kernels take a token's position as (flattened token index) mod (table rows)
+        return self._rope[0][:seq], self._rope[1][:seq]
 
     def forward(self, hidden_states, attention_mask=None):
         qkv = self.query_key_value(hidden_states)  # [b, s, heads_local * 3 * hd]
@@ -54,7 +55,9 @@ class GPTNeoXAttention(nn.Module):
         heads = qkv.shape[-1] // (3 * self.head_size)
         rope = None
         if self.rotary_ndims > 0:
-            cos, sin = self._tables(s, qkv.device)
+            from oslo_b200.ops.attention import decode_offset
+
+            cos, sin = self._tables(s + decode_offset(), qkv.device)  # incremental decoding rotates at offset positions
             rope = (cos, sin, self.rotary_ndims, True)
         return OF.qkv_attention(qkv, heads, self.head_size, layout="h3d", causal=True, rope=rope, mask=attention_mask)
 

@@ -35,7 +35,8 @@ class LlamaAttention(nn.Module):
     def _tables(self, seq, device):
         if self._rope is None or self._rope[0].shape[0] < seq or self._rope[0].device != device:
             self._rope = OF.rope_tables(max(seq, self.max_positions), self.head_dim, self.rope_theta, device)
-        return self._rope
+        # rows [0, seq): the kernels take a token's position as (flattened token index) mod (table rows)
+        return self._rope[0][:seq], self._rope[1][:seq]
 
     def forward(self, x, attention_mask=None):
         b, s = x.shape[0], x.shape[1]
@@ -44,9 +45,13 @@ class LlamaAttention(nn.Module):
         v = self.v_proj(x)
         hq, hkv = q.shape[-1] // self.head_dim, k.shape[-1] // self.head_dim
         q, k, v = q.view(b, s, hq, self.head_dim), k.view(b, s, hkv, self.head_dim), v.view(b, s, hkv, self.head_dim)
-        cos, sin = self._tables(s, x.device)
-        q = OF.apply_rope(q, cos, sin, self.head_dim, neox=True)
-        k = OF.apply_rope(k, cos, sin, self.head_dim, neox=True)
+        from oslo_b200.ops.attention import decode_offset
+
+        off = decode_offset()
+        cos, sin = self._tables(s + off, x.device)
+        pos = (torch.arange(s, device=x.device) + off).repeat(b) if off else None  # incremental decoding
+        q = OF.apply_rope(q, cos, sin, self.head_dim, neox=True, positions=pos)
+        k = OF.apply_rope(k, cos, sin, self.head_dim, neox=True, positions=pos)
         if hkv != hq:
             rep = hq // hkv
             k = k.repeat_interleave(rep, dim=2)

@@ -84,10 +84,89 @@ def _softmax_bwd_causal(dp, p, scale):
     return dp
 
 
+class DecodeCache:
+    """Keys and values of the tokens a model has already seen, for incremental decoding.
+
+    While a cache is active (``with decode_cache(cache):``) every attention call of a forward pass appends the keys and
+    values of the tokens it was given to its own slot (slots are taken in call order, one per attention layer) and
+    attends over everything stored so far; ``offset`` is the number of tokens stored before the current forward, which
+    the models add to their position ids / rotary positions.  ``advance(n)`` is called after each forward.
+    Replaces the per-step re-run of the whole prefix; LightSeq keeps the same state in its decoder's cache buffers
+    (oslo/lightseq2/inference/model/decoder.cc.cu, gpt_encoder.cc.cu)."""
+
+    def __init__(self):
+        self.k, self.v = [], []
+        self.offset = 0
+        self._layer = 0
+
+    def begin_forward(self):
+        self._layer = 0
+
+    def advance(self, n: int):
+        self.offset += n
+
+    def reorder(self, index: torch.Tensor):
+        """Beam search: hypothesis ``i`` continues hypothesis ``index[i]``."""
+        self.k = [t.index_select(0, index) for t in self.k]
+        self.v = [t.index_select(0, index) for t in self.v]
+
+    def append(self, k, v):
+        i = self._layer
+        self._layer += 1
+        if i == len(self.k):
+            self.k.append(k)
+            self.v.append(v)
+        else:
+            self.k[i] = torch.cat([self.k[i], k], dim=1)
+            self.v[i] = torch.cat([self.v[i], v], dim=1)
+        return self.k[i], self.v[i]
+
+
+_CACHE: Optional[DecodeCache] = None
+
+
+class decode_cache:
+    """Context manager that makes ``cache`` the active :class:`DecodeCache` (inference only)."""
+
+    def __init__(self, cache: DecodeCache):
+        self.cache = cache
+
+    def __enter__(self):
+        global _CACHE
+        self.prev, _CACHE = _CACHE, self.cache
+        return self.cache
+
+    def __exit__(self, *exc):
+        global _CACHE
+        _CACHE = self.prev
+
+
+def decode_offset() -> int:
+    """Tokens already held by the active decode cache (0 without one): the position of the first new token."""
+    return _CACHE.offset if _CACHE is not None else 0
+
+
+def _cached_attention(q, k, v, scale, mask=None):
+    """New queries ``[b, s, h, d]`` against all stored keys; query ``i`` sees keys up to its own position."""
+    K, V = _CACHE.append(k, v)
+    b, s, nh, hd = q.shape
+    S = K.shape[1]
+    scores = torch.einsum("bqhd,bkhd->bhqk", q.float(), K.float()) * scale
+    if s > 1:
+        qpos = torch.arange(S - s, S, device=q.device).unsqueeze(1)
+        scores = scores.masked_fill(torch.arange(S, device=q.device).unsqueeze(0) > qpos, float("-inf"))
+    if mask is not None:
+        scores = scores + mask[..., -s:, :S].float()
+    p = torch.softmax(scores, dim=-1)
+    return torch.einsum("bhqk,bkhd->bqhd", p, V.float()).to(q.dtype).reshape(b, s, nh * hd)
+
+
 def attention(q, k, v, causal: bool = True, scale: Optional[float] = None, mask=None):
     """Multi-head attention.  q, k, v: ``[b, s, heads, head_dim]``; returns ``[b, s, heads*head_dim]``."""
     b, s, nh, hd = q.shape
     scale = scale if scale is not None else 1.0 / math.sqrt(hd)
+    if _CACHE is not None and causal and not torch.is_grad_enabled():
+        return _cached_attention(q, k, v, scale, mask)
     if mask is None and flash_supported(q, k, v):
         return _FlashAttentionFn.apply(q, k, v, causal, float(scale))
     if mask is None and supported(q, k) and s % 8 == 0 and hd % 8 == 0 and k.shape[1] == s:
@@ -269,6 +348,15 @@ def qkv_attention(qkv, heads: int, head_dim: int, layout: str = "h3d", causal: b
 
     b, s = qkv.shape[0], qkv.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+    if _CACHE is not None and causal and not torch.is_grad_enabled():
+        shape5 = (b, s, heads, 3, head_dim) if layout == "h3d" else (b, s, 3, heads, head_dim)
+        q, k, v = _split_qkv(qkv.view(shape5), layout)
+        if rope is not None:
+            cos, sin, rot, neox = rope
+            pos = (torch.arange(s, device=qkv.device) + _CACHE.offset).repeat(b)
+            q = apply_rope(q.contiguous(), cos, sin, rot, neox, positions=pos)
+            k = apply_rope(k.contiguous(), cos, sin, rot, neox, positions=pos)
+        return _cached_attention(q, k, v, scale, mask)
     if mask is None and qkv.is_cuda and _lib.has_cuda_kernels() and qkv.dtype in (torch.bfloat16, torch.float16) \
             and s % 8 == 0 and head_dim % 8 == 0 and qkv.is_contiguous():
         if rope is not None and qkv.is_leaf:

@@ -85,3 +85,44 @@ def test_fake_quant_straight_through():
     y.sum().backward()
     ref = torch.nn.functional.linear(x, q.weight, q.bias)
     assert (y - ref).abs().max() < 0.2 and x.grad is not None and q.weight.grad is not None
+
+
+def test_kv_cache_generation_equals_full_prefix_generation():
+    """Greedy and beam decoding with the key / value cache give the same tokens as re-running the whole prefix,
+    for every in-tree causal model (learned positions, partial rotary, full rotary), and the cache grows by one
+    position per step instead of being rebuilt."""
+    from oslo_b200 import models
+    from oslo_b200.lightseq import generate
+    from oslo_b200.models.config import GPTNeoXConfig
+    from oslo_b200.models.gpt_neox import GPTNeoXForCausalLM
+    from oslo_b200.ops.attention import DecodeCache, decode_cache
+
+    torch.manual_seed(0)
+    built = [
+        models.GPT2LMHeadModel(models.GPT2Config(vocab_size=64, n_positions=48, n_embd=32, n_layer=2, n_head=4, resid_pdrop=0.0,
+                                                 embd_pdrop=0.0, attn_pdrop=0.0)),
+        GPTNeoXForCausalLM(GPTNeoXConfig(vocab_size=64, hidden_size=32, num_hidden_layers=2, num_attention_heads=4,
+                                         intermediate_size=64, rotary_pct=0.5, max_position_embeddings=48)),
+        models.LlamaForCausalLM(models.LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                                                   num_attention_heads=4, max_position_embeddings=48)),
+    ]
+    prompt = torch.randint(0, 64, (3, 5))
+    for m in built:
+        m.eval()
+        for kw in (dict(), dict(num_beams=3), dict(no_repeat_ngram_size=2)):
+            a = generate(m, prompt, max_new_tokens=10, use_cache=True, **kw)
+            b = generate(m, prompt, max_new_tokens=10, use_cache=False, **kw)
+            assert torch.equal(a, b), (type(m).__name__, kw)
+        # incremental logits equal full-prefix logits, and the cache holds one entry per layer of prompt + steps length
+        cache = DecodeCache()
+        ids = prompt
+        with torch.no_grad():
+            for step in range(3):
+                cache.begin_forward()
+                with decode_cache(cache):
+                    inc = m(input_ids=ids[:, cache.offset:]).logits[:, -1]
+                cache.advance(ids.shape[1] - cache.offset)
+                full = m(input_ids=ids).logits[:, -1]
+                assert torch.allclose(inc, full, atol=1e-5), (type(m).__name__, step, (inc - full).abs().max().item())
+                ids = torch.cat([ids, full.argmax(-1, keepdim=True)], dim=1)
+        assert len(cache.k) == 2 and cache.k[0].shape[1] == prompt.shape[1] + 2
