@@ -79,8 +79,12 @@ def bench_gemm(a):
     out = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
     A = x.t().contiguous().t() if a.a_mn else x
     B = w.t().contiguous().t() if a.b_mn else w
-    ms = time_op(lambda: gemm(A, B, out=out, block_n=a.block_n), a.iters)
+    ms = time_op(lambda: gemm(A, B, out=out, block_n=a.block_n, two_cta=False), a.iters)
     extra = ""
+    if a.m >= 256 and a.n >= 256 and not a.block_n:
+        ms_pair = time_op(lambda: gemm(A, B, out=out, two_cta=True), a.iters)
+        report(f"gemm_tcgen05_2cta M{a.m} N{a.n} K{a.k} a_mn{int(a.a_mn)} b_mn{int(a.b_mn)}", ms_pair,
+               flops=2.0 * a.m * a.n * a.k, extra=f"one-CTA kernel {ms * 1e3:.1f} us")
     if a.compare:
         ms2 = time_op(lambda: torch.matmul(x, w.t(), out=out), a.iters)
         extra = f"cuBLAS {ms2 * 1e3:.1f} us ({ms2 / ms:.2f}x of ours)"

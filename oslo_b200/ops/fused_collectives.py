@@ -9,6 +9,8 @@ from __future__ import annotations
 
 import torch
 
+from oslo_b200.utils.nvtx import annotate
+
 _runtime = None  # the 1-D group's runtime, set by oslo_b200.distributed.symm.enable(...)
 _runtimes = {}   # ParallelMode -> runtime, for the groups of the 2-D / 2.5-D / 3-D layouts
 
@@ -52,12 +54,14 @@ def available(x: torch.Tensor, w: torch.Tensor, kind: str = "any") -> bool:
 
 def ag_gemm(x_shard, weight, pc, bias=None):
     """``(all_gather(x_shard) @ weight^T (+ bias), all_gather(x_shard))`` in one kernel."""
-    return _runtime.ag_gemm(x_shard, weight, bias)
+    with annotate("oslo.ag_gemm"):
+        return _runtime.ag_gemm(x_shard, weight, bias)
 
 
 def gemm_rs(x, weight, pc, addend=None):
     """``reduce_scatter(x @ weight^T + addend)`` over the token dim in one kernel (``addend``: optional local [T, N])."""
-    return _runtime.gemm_rs(x, weight, addend=addend)
+    with annotate("oslo.gemm_rs"):
+        return _runtime.gemm_rs(x, weight, addend=addend)
 
 
 def feature_rs_available(x: torch.Tensor, w: torch.Tensor, mode) -> bool:
@@ -69,7 +73,8 @@ def feature_rs_available(x: torch.Tensor, w: torch.Tensor, mode) -> bool:
 def gemm_rs_features(x, weight, mode):
     """``reduce_scatter(x @ weight^T)`` over the FEATURE dim within the group of ``mode`` (2-D / 2.5-D linears):
     ``[T, K] x [N, K]^T -> [T, N / q]`` in one kernel."""
-    return _runtimes[mode].gemm_rs(x, weight, along_n=True)
+    with annotate("oslo.gemm_rs_features"):
+        return _runtimes[mode].gemm_rs(x, weight, along_n=True)
 
 
 def gather_scatter_available(x_shard: torch.Tensor, w: torch.Tensor, ag_mode, rs_mode) -> bool:
@@ -80,4 +85,5 @@ def gather_scatter_available(x_shard: torch.Tensor, w: torch.Tensor, ag_mode, rs
 def ag_gemm_rs(x_shard, weight, ag_mode, rs_mode):
     """``(reduce_scatter_rows over rs_mode (all_gather_rows over ag_mode (x_shard) @ weight^T), gathered x)`` in one
     kernel (the 3-D linear: INPUT gather, OUTPUT scatter)."""
-    return _runtimes[ag_mode].ws.ag_gemm_rs(_runtimes[rs_mode].ws, x_shard, weight)
+    with annotate("oslo.ag_gemm_rs"):
+        return _runtimes[ag_mode].ws.ag_gemm_rs(_runtimes[rs_mode].ws, x_shard, weight)

@@ -21,6 +21,9 @@ from . import _lib
 
 _EPI = {None: 0, "none": 0, "bias": 1, "gelu": 2}
 
+#: use the two-CTA kernel automatically for large products (set from the environment: OSLO_B200_GEMM_2CTA=0 / 1)
+AUTO_TWO_CTA = __import__("os").environ.get("OSLO_B200_GEMM_2CTA", "0") == "1"
+
 
 def _operand(t: torch.Tensor):
     """Classify an operand ``[.., rows, K]``: returns (tensor, mn_major, ld, inner_stride, outer_stride)."""
@@ -59,6 +62,7 @@ def gemm(
     aux: Optional[torch.Tensor] = None,
     block_n: int = 0,
     causal: int = 0,
+    two_cta: Optional[bool] = None,
 ) -> torch.Tensor:
     """``out[.., M, N] = epilogue(a[.., M, K] @ b[.., N, K]^T (+ bias))`` on tcgen05.
 
@@ -66,7 +70,9 @@ def gemm(
     ``a`` / ``b`` may be transposed views (MN-major) — nothing is copied.  ``aux``
     (optional, same layout as ``out``) receives the pre-activation ``acc + bias``
     when ``epilogue="gelu"``.  ``causal`` selects triangular work skipping for
-    attention products (see ``csrc/gemm_sm100a.cu``).
+    attention products (see ``csrc/gemm_sm100a.cu``).  ``two_cta`` picks the kernel in which an SM pair shares one
+    256 x 256 tile (``csrc/gemm2cta_sm100a.cu``); ``None`` = automatically for products with at least one such tile
+    per SM pair.
     """
     assert a.dim() == b.dim() and a.dim() in (2, 3, 4), "gemm takes 2-D or batched 3-D / 4-D operands"
     M, K = a.shape[-2], a.shape[-1]
@@ -93,6 +99,23 @@ def gemm(
     lib = _lib.cuda_lib()
     status = _lib.status_word(a.device)
     use_epi = _EPI[epilogue] if (bias is not None or epilogue == "gelu") else 0
+    if two_cta is None:
+        pairs = _lib.num_sms() // 2
+        tiles = b_in * b_out * ((M + 255) // 256) * ((N + 255) // 256)
+        two_cta = AUTO_TWO_CTA and causal == 0 and block_n == 0 and M >= 256 and N >= 256 and tiles >= pairs
+    if two_cta:
+        rc = lib.oslo_gemm_tcgen05_2cta(
+            _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(aux),
+            ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(b_in),
+            ctypes.c_longlong(lda), ctypes.c_longlong(ldb), ctypes.c_longlong(ldc),
+            ctypes.c_longlong(sa), ctypes.c_longlong(sb), ctypes.c_longlong(sc),
+            ctypes.c_int(a_mn), ctypes.c_int(b_mn), ctypes.c_int(1 if a.dtype == torch.bfloat16 else 0),
+            ctypes.c_int(use_epi), ctypes.c_int(1 if accumulate else 0), ctypes.c_int(_lib.num_sms()), _lib.ptr(status),
+            _lib.stream_ptr(), ctypes.c_int(b_out), ctypes.c_longlong(osa), ctypes.c_longlong(osb), ctypes.c_longlong(osc))
+        if rc == 0:
+            return out
+        if rc != -8:  # -8: shape too small for a 256-wide tile, use the one-CTA kernel below
+            raise RuntimeError(f"oslo_gemm_tcgen05_2cta failed with code {rc} for {tuple(a.shape)} x {tuple(b.shape)}")
     rc = lib.oslo_gemm_tcgen05(
         _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(aux),
         ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(b_in),

@@ -364,7 +364,9 @@ class ZeroRedundancyOptimizer:
         stream = self._comm_stream if overlapped else torch.cuda.current_stream()
         if overlapped:
             stream.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(stream):
+        from oslo_b200.utils.nvtx import annotate
+
+        with torch.cuda.stream(stream), annotate("oslo.zero_bucket"):
             sbuf.barrier()
             rc = lib.oslo_zero_step(
                 grads, params, _lib.ptr(g.master.data[moff:]), _lib.ptr(st["m"][moff:]), _lib.ptr(st["v"][moff:]),

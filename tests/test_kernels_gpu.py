@@ -505,3 +505,47 @@ def test_flash_attention_seq_2048(causal):
     assert frac == 0.0, ("out", frac, worst)
     frac, worst = _close(qkv.grad, ref_in.grad, rtol=3e-2, atol=0.03 * ref_in.grad.abs().max().item())
     assert frac < 1e-4, ("dqkv", frac, worst)
+
+
+@pytest.mark.parametrize("a_t,b_t", [(False, False), (False, True), (True, False), (True, True)])
+def test_gemm_two_cta(a_t, b_t):
+    """The SM-pair kernel (tcgen05.mma.cta_group::2, 256 x 256 tiles) against fp32: all four operand layouts, a K that
+    wraps the 6-stage ring several times, more tiles than SM pairs (both accumulator buffers reused), ragged M and N."""
+    from oslo_b200.ops.gemm import gemm
+
+    torch.manual_seed(44)
+    M, N, K = 4096 + 128, 3072 + 64, 2048
+    a = (torch.randn((K, M) if a_t else (M, K), device=DEV) * 0.5).to(torch.bfloat16)
+    b = (torch.randn((K, N) if b_t else (N, K), device=DEV) * 0.5).to(torch.bfloat16)
+    A, B = (a.t() if a_t else a), (b.t() if b_t else b)
+    ref = A.float() @ B.float().t()
+    y = gemm(A, B, two_cta=True)
+    frac, worst = _close(y, ref, rtol=1e-2, atol=0.05)
+    assert frac == 0.0, (frac, worst)
+
+
+def test_gemm_two_cta_epilogues():
+    from oslo_b200.ops.gemm import gemm
+
+    torch.manual_seed(45)
+    a = (torch.randn(1024, 512, device=DEV) * 0.5).to(torch.bfloat16)
+    b = (torch.randn(768, 512, device=DEV) * 0.1).to(torch.bfloat16)
+    bias = torch.randn(768, device=DEV, dtype=torch.bfloat16)
+    ref = a.float() @ b.float().t() + bias.float()
+    frac, worst = _close(gemm(a, b, bias=bias, epilogue="bias", two_cta=True), ref, rtol=1e-2, atol=0.05)
+    assert frac == 0.0, ("bias", frac, worst)
+    aux = torch.empty(1024, 768, device=DEV, dtype=torch.bfloat16)
+    y = gemm(a, b, bias=bias, epilogue="gelu", aux=aux, two_cta=True)
+    frac, worst = _close(y, F.gelu(ref, approximate="tanh"), rtol=1e-2, atol=0.05)
+    assert frac == 0.0, ("gelu", frac, worst)
+    frac, worst = _close(aux, ref, rtol=1e-2, atol=0.05)
+    assert frac == 0.0, ("aux", frac, worst)
+    c = torch.randn(1024, 768, device=DEV, dtype=torch.bfloat16)
+    c0 = c.float().clone()
+    gemm(a, b, out=c, accumulate=True, two_cta=True)
+    frac, worst = _close(c, c0 + a.float() @ b.float().t(), rtol=1e-2, atol=0.06)
+    assert frac == 0.0, ("accumulate", frac, worst)
+    a3 = (torch.randn(3, 512, 256, device=DEV) * 0.5).to(torch.float16)
+    b3 = (torch.randn(3, 512, 256, device=DEV) * 0.5).to(torch.float16)
+    frac, worst = _close(gemm(a3, b3, two_cta=True), a3.float() @ b3.float().transpose(-1, -2), rtol=1e-2, atol=0.05)
+    assert frac == 0.0, ("batched fp16", frac, worst)
