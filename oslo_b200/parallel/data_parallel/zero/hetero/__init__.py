@@ -22,6 +22,7 @@ from oslo_b200.distributed import ParallelMode
 from oslo_b200.parallel.utils import ParallelWrapper, add_wrapper, get_parallel_context
 
 from .chunk import Chunk, ChunkManager, search_chunk_size
+from .memory_manager import MemoryManager, MemTracer
 
 
 class MemStats:
@@ -54,7 +55,8 @@ class HeteroDataParallel(ParallelWrapper):
     parallelism_priority = 99
 
     def __init__(self, module: nn.Module, parallel_context=None, placement_policy: str = "cuda", chunk_size_mb: Optional[float] = None,
-                 pin_memory: bool = True, min_free_fraction: float = 0.2):
+                 pin_memory: bool = True, min_free_fraction: float = 0.2, device_budget_bytes: Optional[int] = None,
+                 memory_probe=None, warmup_steps: int = 1):
         super().__init__()
         self.module = module
         self.parallel_context = pc = get_parallel_context(module, parallel_context)
@@ -63,6 +65,9 @@ class HeteroDataParallel(ParallelWrapper):
         self.policy_name, self.chunk_size_mb, self.min_free_fraction = placement_policy, chunk_size_mb, min_free_fraction
         self.manager: Optional[ChunkManager] = None
         self.mem_stats = MemStats()
+        # run-time placement ("auto"): budget of device bytes, probe of the device memory in use, traced warm-up steps
+        self.device_budget_bytes, self.memory_probe, self.warmup_steps = device_budget_bytes, memory_probe, warmup_steps
+        self.memory_manager: Optional[MemoryManager] = None
         self._hooks = []
         add_wrapper(module, ParallelMode.DATA, self)
 
@@ -87,6 +92,12 @@ class HeteroDataParallel(ParallelWrapper):
             size = search_chunk_size([p.numel() for p in params], self.world, elem_bytes=esz)
         self.manager = ChunkManager(self.world, self.rank, pc.get_group(ParallelMode.DATA), dev, policy.shard_device(), size)
         self.manager.register(params)
+        if self.policy_name == "auto":
+            for c in self.manager.chunks:  # under "auto" shards start on the device (logically, on a CPU-only run)
+                c.on_device = True
+            self.memory_manager = MemoryManager(self.manager.chunks, dev, self.device_budget_bytes, self.memory_probe,
+                                                self.mem_stats, self.warmup_steps)
+            self.manager.before_access = self.memory_manager.adjust_layout
         for m in self.module.modules():
             own = [p for p in m.parameters(recurse=False) if id(p) in self.manager.param_to_chunk]
             if not own:
@@ -127,6 +138,12 @@ class HeteroDataParallel(ParallelWrapper):
                 c.reduce_grads()
                 c.release()
                 c.pending_grads = len(c.params)
+
+    def end_step(self):
+        """Called by the optimizer after its update: lets the memory manager close the step (freeze the traced
+        schedule after the warm-up, bring shards back to the device where they fit)."""
+        if self.memory_manager is not None:
+            self.memory_manager.end_step()
 
     def zero_grad(self, set_to_none=True):
         for c in self.manager.chunks:
@@ -215,6 +232,7 @@ class HeteroOptimizer:
             c.shard.copy_(m.data.to(c.shard.dtype))
             c.write_back()
             c.grad_shard = None
+        self.model.end_step()
 
     def state_dict(self):
         return self.optim.state_dict()
@@ -225,4 +243,5 @@ class HeteroOptimizer:
         self.optim.load_state_dict(sd)
 
 
-__all__ = ["HeteroDataParallel", "HeteroOptimizer", "ChunkManager", "Chunk", "PlacementPolicy", "MemStats", "search_chunk_size"]
+__all__ = ["HeteroDataParallel", "HeteroOptimizer", "ChunkManager", "Chunk", "PlacementPolicy", "MemStats", "MemoryManager",
+           "MemTracer", "search_chunk_size"]

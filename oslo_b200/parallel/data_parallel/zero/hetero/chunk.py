@@ -147,6 +147,7 @@ class ChunkManager:
         self.chunks: List[Chunk] = []
         self.param_to_chunk: Dict[int, Chunk] = {}
         self.gather_calls = 0
+        self.before_access = None  # optional hook(chunk): the memory manager adjusts the layout before a gather
 
     def register(self, params: Sequence[torch.nn.Parameter], keep_gathered_small: bool = False):
         cur: Optional[Chunk] = None
@@ -174,6 +175,8 @@ class ChunkManager:
     def access(self, chunks):
         for c in chunks:
             if not c.is_gathered:
+                if self.before_access is not None:
+                    self.before_access(c)
                 self.gather_calls += 1
                 c.access()
 

@@ -122,6 +122,70 @@ def test_hetero_zero3_matches_single_process(policy):
     run_dist(_hetero_worker, 2, policy)
 
 
+def _hetero_auto_worker(rank, world):
+    """``auto`` placement with a device budget too small for every shard: shards are evicted at run time (furthest next
+    use first), the budget holds at every access, and training is unchanged."""
+    import oslo_b200
+    from oslo_b200 import ParallelContext
+    from oslo_b200.parallel import DistributedDataParallel, ShardingStrategy
+
+    pc = ParallelContext.from_torch(data_parallel_size=world, backend="gloo", seed=0)
+    model = _mlp()
+    inner = torch.optim.AdamW(model.parameters(), lr=1e-2)
+    activations = {"bytes": 4096}
+    holder = {}
+
+    def probe():  # what torch.cuda.memory_allocated() would say: everything in use, chunk memory included
+        return activations["bytes"] + (holder["mm"].model_bytes_on_device() if "mm" in holder else 0)
+
+    wrapped, opt = DistributedDataParallel(
+        model, pc, sharding_strategy=ShardingStrategy.HETERO_SHARD, optimizer=inner,
+        model_wrapper_config=dict(placement_policy="auto", chunk_size_mb=0.004, memory_probe=probe))
+    oslo_b200.ready(wrapped, pc)
+    mm = holder["mm"] = wrapped.memory_manager
+    chunks = wrapped.manager.chunks
+    assert mm is not None and len(chunks) >= 3
+    full = max(mm._full_bytes(c) for c in chunks)
+    shard = max(mm._shard_bytes(c) for c in chunks)
+    # room for the activations, one gathered buffer and about half of the shards
+    mm.budget = activations["bytes"] + full + shard * (len(chunks) // 2) + shard // 2
+    assert sum(mm._shard_bytes(c) for c in chunks) + full + activations["bytes"] > mm.budget
+    # the invariant of adjust_layout, checked at every access: afterwards the access fits the budget, or there is nothing
+    # left that could have been evicted (only the chunk itself and gathered chunks still hold device memory)
+    inner_adjust = mm.adjust_layout
+    checked = {"n": 0}
+
+    def checked_adjust(chunk):
+        need = 0 if chunk.full is not None else mm._full_bytes(chunk)
+        inner_adjust(chunk)
+        used = activations["bytes"] + mm.model_bytes_on_device() + need
+        evictable = [c for c in chunks if c.on_device and c is not chunk and c.full is None]
+        assert used <= mm.budget or not evictable, (used, mm.budget, len(evictable))
+        checked["n"] += 1
+
+    wrapped.manager.before_access = checked_adjust
+    for s in range(4):
+        x, y = _data(s)
+        xs, ys = x.chunk(world)[rank], y.chunk(world)[rank]
+        opt.zero_grad()
+        loss = ((wrapped(xs) - ys) ** 2).mean()
+        opt.backward(loss)
+        opt.step()
+    assert checked["n"] > 8
+    assert mm.evictions > 0 and wrapped.mem_stats.d2h_bytes > 0
+    assert not mm.tracer.recording and len(mm.tracer.schedule) >= 2 * len(chunks)  # forward and backward accesses traced
+    assert any(not c.on_device for c in chunks)  # the budget cannot hold every shard
+    ref = _reference(4)
+    sd = wrapped.state_dict()
+    for (n, r) in ref.named_parameters():
+        assert torch.allclose(sd[n], r, rtol=1e-5, atol=1e-6), (n, (sd[n] - r).abs().max())
+    pc.destroy()
+
+
+def test_hetero_zero3_auto_placement_evicts_at_run_time():
+    run_dist(_hetero_auto_worker, 2)
+
+
 def test_chunk_size_search_reduces_waste():
     from oslo_b200.parallel.data_parallel.zero.hetero import search_chunk_size
 
