@@ -152,11 +152,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       int st = 0;
       uint32_t ph = 0, sph = 0, dsph = 0;
       const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sDO), ds_addr = smem_u32(sDS);
-      for (int j = 0; j < nkv && ok; ++j) {
-        if (!mbar_wait_bounded(&k_full[st], ph, abort_flag) || !mbar_wait_bounded(&v_full[st], ph, abort_flag) ||
-            !mbar_wait_bounded(s_empty, sph ^ 1, abort_flag)) { ok = false; break; }
+      int st_s = 0;          // stage of the next S / dP product (runs one key block ahead of the dQ product)
+      uint32_t ph_s = 0;
+      auto issue_s = [&]() -> bool {
+        if (!mbar_wait_bounded(&k_full[st_s], ph_s, abort_flag) || !mbar_wait_bounded(&v_full[st_s], ph_s, abort_flag) ||
+            !mbar_wait_bounded(s_empty, sph ^ 1, abort_flag))
+          return false;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(sK + st * Cfg::kTile), v_addr = smem_u32(sV + st * Cfg::kTile);
+        const uint32_t k_addr = smem_u32(sK + st_s * Cfg::kTile), v_addr = smem_u32(sV + st_s * Cfg::kTile);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const int half = kk / 4, k = kk % 4;
@@ -169,12 +172,22 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           umma_f16(tm_dp, make_smem_desc_sw128(do_addr + half * 16384 + k * 32, 16, 1024),
                    make_smem_desc_sw128(v_addr + half * 16384 + k * 32, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
         }
-        umma_commit(&v_empty[st]);
+        umma_commit(&v_empty[st_s]);
         umma_commit(s_full);
         sph ^= 1;
+        if (++st_s == 2) { st_s = 0; ph_s ^= 1; }
+        return true;
+      };
+      if (ok) ok = issue_s();
+      for (int j = 0; j < nkv && ok; ++j) {
+        // the next block's S and dP are issued as soon as the element-wise warps have taken this block's out of tensor
+        // memory, so they are computed while dS of this block is still being formed
+        if (j + 1 < nkv) ok = issue_s();
+        if (!ok) break;
         // dQ += dS K_j once the element-wise warps have written dS
         if (!mbar_wait_bounded(ds_full, dsph, abort_flag)) { ok = false; break; }
         tc_fence_after();
+        const uint32_t k_addr = smem_u32(sK + st * Cfg::kTile);
 #pragma unroll
         for (int kk = 0; kk < 128 / 16; ++kk) {
           const int half = kk / 4, k = kk % 4;
@@ -200,41 +213,57 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     uint32_t sph = 0, deph = 0;
     bool ok = true;
     for (int j = 0; j < nkv && ok; ++j) {
-      if (!mbar_wait_bounded(s_full, sph, abort_flag) || !mbar_wait_bounded(ds_empty, deph ^ 1, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_bounded(s_full, sph, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const bool diag = p.causal && j == qb;
+      // two round trips to tensor memory per tile (64 columns of S and of dP each) instead of four; the accumulators go
+      // back to the MMA warp as soon as the second half is in registers, before the exponentials of that half run
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rs[32], rp[32];
+      for (int hc = 0; hc < 2; ++hc) {
+        uint32_t rs[2][32], rp[2][32];
         __syncwarp();
-        tmem_ld_32x32(tm_s + lane_base + c * 32, rs);
-        tmem_ld_32x32(tm_dp + lane_base + c * 32, rp);
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          tmem_ld_32x32(tm_s + lane_base + (hc * 2 + u) * 32, rs[u]);
+          tmem_ld_32x32(tm_dp + lane_base + (hc * 2 + u) * 32, rp[u]);
+        }
         tmem_ld_wait();
+        if (hc == 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(s_empty);
+        } else if (!mbar_wait_bounded(ds_empty, deph ^ 1, abort_flag)) {  // dS of the previous tile has been consumed
+          ok = false;
+        }
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint32_t packed[4];
+        for (int u2 = 0; u2 < 2; ++u2) {
+          const int c = hc * 2 + u2;
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float d[2];
+          for (int g = 0; g < 4; ++g) {
+            uint32_t packed[4];
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int i = g * 8 + 2 * e + u;
-              float pr = exp2f(__uint_as_float(rs[i]) * p.scale_log2 - lse2);
-              if (diag && c * 32 + i > row) pr = 0.f;
-              d[u] = pr * (__uint_as_float(rp[i]) - dl) * p.scale;
+            for (int e = 0; e < 4; ++e) {
+              float d[2];
+#pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                const int i = g * 8 + 2 * e + u;
+                float pr = exp2f(__uint_as_float(rs[u2][i]) * p.scale_log2 - lse2);
+                if (diag && c * 32 + i > row) pr = 0.f;
+                d[u] = pr * (__uint_as_float(rp[u2][i]) - dl) * p.scale;
+              }
+              packed[e] = pack2(d[0], d[1], bf);
             }
-            packed[e] = pack2(d[0], d[1], bf);
+            const int col = c * 32 + g * 8;
+            const int half = col / 64, chunk = (col % 64) / 8;
+            *reinterpret_cast<uint4*>(sDS + half * 16384 + row * 128 + ((chunk ^ (row & 7)) << 4)) =
+                make_uint4(packed[0], packed[1], packed[2], packed[3]);
           }
-          const int col = c * 32 + g * 8;
-          const int half = col / 64, chunk = (col % 64) / 8;
-          *reinterpret_cast<uint4*>(sDS + half * 16384 + row * 128 + ((chunk ^ (row & 7)) << 4)) =
-              make_uint4(packed[0], packed[1], packed[2], packed[3]);
         }
       }
-      tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) { mbar_arrive(s_empty); mbar_arrive(ds_full); }
+      if (lane == 0) mbar_arrive(ds_full);
+      if (!ok) break;
       sph ^= 1;
       deph ^= 1;
     }

@@ -194,44 +194,52 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tc_fence_after();
       const bool diag = p.causal && j == qb;
       float bm = -INFINITY;
+      // the whole 128-column row in one round trip to tensor memory, then the buffer goes straight back to the MMA warp
+      uint32_t r[4][32];
+      __syncwarp();
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld_32x32(tmem_base + lane_base + sb * 128 + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float t = __uint_as_float(r[i]);
-          if (!(diag && c * 32 + i > row)) bm = fmaxf(bm, t);
-        }
-      }
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_base + lane_base + sb * 128 + c * 32, r[c]);
+      tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[sb]);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float t = __uint_as_float(r[c][i]);
+          if (!(diag && c * 32 + i > row)) bm = fmaxf(bm, t);
+        }
+      }
       m = fmaxf(m, bm * p.scale_log2);
       if (++sb == 2) { sb = 0; sph ^= 1; }
     }
     // pass 2: P tiles
     for (int j = 0; j < nkv && ok; ++j) {
       if (!mbar_wait_bounded(&s_full[sb], sph, abort_flag)) { ok = false; break; }
-      if (!mbar_wait_bounded(p_empty, peph ^ 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const bool diag = p.causal && j == qb;
+      uint32_t r[4][32];
+      __syncwarp();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_base + lane_base + sb * 128 + c * 32, r[c]);
+      tmem_ld_wait();
+      // the scores are in registers: the S buffer can take the next product while the exponentials run
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[sb]);
+      // P is rewritten only once the previous P V product has finished reading it (the loads above ran meanwhile)
+      if (!mbar_wait_bounded(p_empty, peph ^ 1, abort_flag)) { ok = false; break; }
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld_32x32(tmem_base + lane_base + sb * 128 + c * 32, r);
-        tmem_ld_wait();
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           uint32_t packed[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int i0 = g * 8 + 2 * e;
-            float a0 = exp2f(__uint_as_float(r[i0]) * p.scale_log2 - m);
-            float a1 = exp2f(__uint_as_float(r[i0 + 1]) * p.scale_log2 - m);
+            float a0 = exp2f(__uint_as_float(r[c][i0]) * p.scale_log2 - m);
+            float a1 = exp2f(__uint_as_float(r[c][i0 + 1]) * p.scale_log2 - m);
             if (diag && c * 32 + i0 > row) a0 = 0.f;
             if (diag && c * 32 + i0 + 1 > row) a1 = 0.f;
             l += a0 + a1;
@@ -244,10 +252,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
               make_uint4(packed[0], packed[1], packed[2], packed[3]);
         }
       }
-      tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) { mbar_arrive(&s_empty[sb]); mbar_arrive(p_full); }
+      if (lane == 0) mbar_arrive(p_full);
       peph ^= 1;
       if (++sb == 2) { sb = 0; sph ^= 1; }
     }

@@ -223,7 +223,7 @@ extern "C" int oslo_ag_gemm_rs(void* const* peer_in, void* x_full, const void* B
   fp.tile_done = tile_done; fp.rs_out = out; fp.status = status;
   // all-gather side: same row blocks, fetched in the order the tiles will ask for them
   fp.ag_tp = ag_tp; fp.ag_rank = ag_rank; fp.ag_shard_rows = Tl; fp.ag_chunk_rows = chunk_rows; fp.ag_epoch = ag_epoch;
-  fp.ag_epoch_ptr = ag_epoch_ptr; fp.copy_first = (rs_rank + 1) % rs_tp;
+  fp.ag_epoch_ptr = ag_epoch_ptr; fp.copy_first = (rs_rank + 1) % rs_tp; fp.copy_chunk_major = 1;
   for (int i = 0; i < ag_tp; ++i) {
     fp.peer_in[i] = peer_in[i];
     fp.peer_ag_ready[i] = static_cast<int*>(peer_ag_ready[i]);

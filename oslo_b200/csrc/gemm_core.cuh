@@ -114,6 +114,7 @@ struct FusedParams {
   int ag_epoch = 0;
   const int* ag_epoch_ptr = nullptr;
   int copy_first = 0;       // first shard the copy CTAs fetch (the order the GEMM tiles will ask for them)
+  int copy_chunk_major = 0; // fetch chunk c of every shard before chunk c + 1 of any (gather + scatter launches)
   // all-gather
   const void* peer_in[kMaxRanks] = {};  // every rank's symmetric input shard [shard_rows, K]
   void* x_full = nullptr;               // local [tp * shard_rows, K]
@@ -172,21 +173,33 @@ OSLO_DEVINL bool flag_wait_bounded(const int* flag, int target, volatile int* ab
 template <int MODE>
 OSLO_DEVINL void fused_tile_coords(int tile, const GemmParams& p, const FusedParams& fp, int& b, int& mb, int& nb) {
   b = 0;
-  const int i = tile / fp.tiles_per_shard;
-  const int t = tile - i * fp.tiles_per_shard;
-  const int shard = (fp.rank + i + ((MODE & kModeReduceScatter) ? 1 : 0)) % fp.tp;
   const int blocks_per_chunk = fp.chunk_rows / kBlockM;
-  if ((MODE & kModeReduceScatter) && fp.rs_along_n) {
-    // the shard is a block of COLUMNS; walk it row chunk by row chunk, all its n-blocks before the next chunk
-    const int per_chunk = blocks_per_chunk * fp.n_blocks_per_shard;
-    const int c = t / per_chunk, r = t - c * per_chunk;
-    mb = c * blocks_per_chunk + r % blocks_per_chunk;
-    nb = shard * fp.n_blocks_per_shard + r / blocks_per_chunk;
+  if constexpr ((MODE & kModeReduceScatter) != 0) {
+    // Row chunk by row chunk; inside a chunk the other ranks' blocks first (next rank first), our own block last.
+    // A rank's own chunk c needs the peers' partials of chunk c, which every peer computes earlier in this same order,
+    // so the dependencies only point backwards; and the tiles that leave over NVLink are spread over the whole launch
+    // instead of being bunched in its first (tp - 1) / tp.
+    const int per_shard = fp.tiles_per_chunk;            // tiles of one (owner, row chunk)
+    const int per_chunk = per_shard * fp.tp;
+    const int c = tile / per_chunk;
+    const int t = tile - c * per_chunk;
+    const int i = t / per_shard, r = t - i * per_shard;
+    const int shard = (fp.rank + i + 1) % fp.tp;
+    if (fp.rs_along_n) {
+      mb = c * blocks_per_chunk + r % blocks_per_chunk;
+      nb = shard * fp.n_blocks_per_shard + r / blocks_per_chunk;
+    } else {
+      mb = shard * (fp.shard_rows / kBlockM) + c * blocks_per_chunk + r % blocks_per_chunk;
+      nb = r / blocks_per_chunk;
+    }
     return;
   }
+  // all-gather only: shard by shard, starting with the local one; inside a shard chunk by chunk (the hand-off
+  // granularity), all n-blocks of a chunk before the next chunk, so chunks are consumed in the order they are copied
+  const int i = tile / fp.tiles_per_shard;
+  const int t = tile - i * fp.tiles_per_shard;
+  const int shard = (fp.rank + i) % fp.tp;
   const int blocks_per_shard = fp.shard_rows / kBlockM;
-  // walk the shard chunk by chunk (the hand-off granularity of both modes): all n-blocks of a chunk before the next
-  // chunk, so chunks are consumed (all-gather) or completed (reduce-scatter) in order
   const int n_blocks = fp.tiles_per_shard / blocks_per_shard;
   const int per_chunk = blocks_per_chunk * n_blocks;
   const int c = t / per_chunk, r = t - c * per_chunk;
@@ -246,7 +259,10 @@ static __device__ __noinline__ void ag_copy_role(const GemmParams& p, const Fuse
     const long long g = blockIdx.x + j * fp.copy_ctas;
     const long long o = g / ppc;                      // position of the chunk in copy order
     const int piece = static_cast<int>(g - o * ppc);
-    const int i = static_cast<int>(o / cps), c = static_cast<int>(o % cps);
+    // shard-major (all chunks of the next rank, then the one after ...) for a plain all-gather; chunk-major when a
+    // reduce-scatter sets the tile order (chunk 0 of every shard, then chunk 1 ...)
+    const int i = static_cast<int>(fp.copy_chunk_major ? o % fp.ag_tp : o / cps);
+    const int c = static_cast<int>(fp.copy_chunk_major ? o / fp.ag_tp : o % cps);
     shard = (fp.copy_first + i) % fp.ag_tp;
     chunk = shard * cps + c;
     const long long off = static_cast<long long>(piece) * kCopyPiece;

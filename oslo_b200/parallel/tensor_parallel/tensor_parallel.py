@@ -86,11 +86,16 @@ class TensorParallel(ParallelWrapper):
     parallelism_priority = 0
 
     def __init__(self, module: nn.Module, parallel_context=None, mapping: Optional[dict] = None,
-                 module_args: Optional[dict] = None, sequence_parallel: bool = False):
+                 module_args: Optional[dict] = None, sequence_parallel: bool = False, vocab_parallel_loss: bool = False):
         super().__init__()
         self.module = module
         self.parallel_context = get_parallel_context(module, parallel_context)
         self.sequence_parallel = sequence_parallel
+        #: stock Hugging Face language models (1-D mode): keep the head's logits sharded over the vocabulary and compute
+        #: the loss with the vocab-parallel cross-entropy instead of gathering [tokens, vocab] logits on every rank (what
+        #: the reference's model forks do, oslo/transformers/models/gpt2/modeling_gpt2.py:845-875).  ``output.logits``
+        #: then holds this rank's vocabulary slice.
+        self.vocab_parallel_loss = vocab_parallel_loss
         self._mapping_arg = mapping
         self.module_args = module_args
         mode = self.parallel_context.tensor_parallel_mode
@@ -114,7 +119,35 @@ class TensorParallel(ParallelWrapper):
             from ._wrapper_nd import scatter_batch_inputs
 
             args, kwargs = scatter_batch_inputs(self.module, args, kwargs, pc)
+        if self._vp_loss_active and kwargs.get("labels") is not None:
+            return self._forward_vocab_parallel_loss(args, kwargs)
         return self.module(*args, **kwargs)
+
+    @property
+    def _vp_loss_active(self) -> bool:
+        pc = self.parallel_context
+        return (self.vocab_parallel_loss and getattr(self, "_parallelized", False) and pc.tensor_parallel_size > 1
+                and pc.tensor_parallel_mode == ParallelMode.TENSOR_1D and not isinstance(self.module, onn_marker()))
+
+    def _forward_vocab_parallel_loss(self, args, kwargs):
+        """Run the model without labels (its head leaves the logits sharded), then the vocab-parallel cross-entropy:
+        next-token targets for causal language models, the labels as they are for masked ones."""
+        from oslo_b200.models.losses import shift_labels
+
+        kwargs = dict(kwargs)
+        labels = kwargs.pop("labels")
+        out = self.module(*args, **kwargs)
+        logits = out.logits if hasattr(out, "logits") else out[0]
+        name = type(self.module).__name__
+        causal = name.endswith(("ForCausalLM", "LMHeadModel")) or "CausalLM" in name
+        targets = shift_labels(labels) if causal else labels
+        fn = onn.VocabParallelCrossEntropyLoss1D(parallel_context=self.parallel_context, ignore_index=-100)
+        fn.orig_vocab_size = getattr(self.module, "orig_vocab_size", self.module.config.vocab_size)
+        loss = fn(logits, targets.to(logits.device))
+        if hasattr(out, "loss"):
+            out.loss = loss
+            return out
+        return (loss,) + tuple(out)
 
     # ------------------------------------------------------------ parallelize
     def _mapping(self):
@@ -280,6 +313,8 @@ class TensorParallel(ParallelWrapper):
             if has_bias:
                 b = self._shard_param(head.bias, ShardSpec([Split(M1, 0)]), (head.orig_num_classes,))
             gather = mapping.is_gather_output(module, name) and not is_oslo_model
+            if self.vocab_parallel_loss and head is getattr(module, "get_output_embeddings", lambda: None)():
+                gather = False  # the loss consumes the vocabulary shards directly
             new = _bare(onn.ColLinear1D, in_features=w.shape[in_dim], out_features=w.shape[out_dim],
                         skip_bias_add=False, gather_output=gather, parallel_context=pc, sequence_parallel=sp,
                         world_size=tp, reversed=conv, sequence_parallel_state=self.sp_state)

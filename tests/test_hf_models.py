@@ -139,3 +139,40 @@ def _pp_worker(rank, world, kind):
 @pytest.mark.parametrize("kind", ["gpt2", "gpt_neox"])
 def test_hf_model_pipeline_parallel_from_module_tree(kind):
     run_dist(_pp_worker, 2, kind, timeout=600)
+
+
+def _vp_loss_worker(rank, world, kind):
+    """Stock Hugging Face causal LM under 1-D TensorParallel with the vocab-parallel loss: the head's logits stay
+    sharded over the vocabulary, loss and gradients equal the unsharded model's."""
+    import oslo_b200
+    from oslo_b200 import ParallelContext
+    from oslo_b200.parallel import TensorParallel
+    from oslo_b200.parallel.tensor_parallel._sharding import merge
+
+    pc = ParallelContext.from_torch(tensor_parallel_size=world, backend="gloo", seed=0)
+    ref = _build(kind).train()
+    model = _build(kind).train()
+    wrapped = TensorParallel(model, pc, vocab_parallel_loss=True)
+    oslo_b200.ready(wrapped, pc)
+    ids = torch.randint(0, 100, (2, 12), generator=torch.Generator().manual_seed(1))
+    want = ref(input_ids=ids, labels=ids)
+    want.loss.backward()
+    got = wrapped(input_ids=ids, labels=ids)
+    got.loss.backward()
+    assert got.logits.shape[-1] == want.logits.shape[-1] // world  # a vocabulary slice, never the gathered logits
+    assert torch.allclose(got.loss, want.loss, rtol=1e-5, atol=1e-6), (got.loss.item(), want.loss.item())
+    ref_grads = {k: p.grad for k, p in ref.named_parameters()}
+    checked = 0
+    for k, p in model.named_parameters():
+        g = merge(p.grad, p.oslo_shard, pc) if hasattr(p, "oslo_shard") else p.grad
+        full = ref_grads[k]
+        g = g[: full.shape[0]] if g.shape != full.shape else g
+        assert torch.allclose(g, full, rtol=1e-3, atol=1e-5), (k, (g - full).abs().max().item())
+        checked += 1
+    assert checked > 8
+    pc.destroy()
+
+
+@pytest.mark.parametrize("kind", ["gpt2", "gpt_neox", "llama"])
+def test_hf_causal_lm_with_vocab_parallel_loss(kind):
+    run_dist(_vp_loss_worker, 2, kind, timeout=600)
