@@ -26,6 +26,8 @@ import oslo_b200
 from oslo_b200.distributed import ParallelMode
 from oslo_b200.utils.logging import get_dist_logger
 
+from .trainer_callback import (CallbackHandler, PredictionOutput, TrainerCallback, TrainerControl,  # noqa: F401
+                               TrainerMemoryTracker)
 from .training_args import TrainingArguments
 
 
@@ -66,6 +68,10 @@ class Trainer:
         self.data_collator = data_collator
         self.compute_metrics = compute_metrics
         self.callbacks = callbacks or []
+        self.callback_handler = CallbackHandler(self.callbacks, model=model)
+        self.control = TrainerControl()
+        self._memory_tracker = TrainerMemoryTracker(getattr(args, "skip_memory_metrics", True))
+        self._memory_tracker.start("init")
         self.state = TrainerState()
         self.base_model = model
         if args.dtype != torch.float32:
@@ -95,6 +101,18 @@ class Trainer:
         self.optimizer, self.lr_scheduler = optimizers
         self.is_pipeline = self.pc is not None and self.pc.pipeline_parallel_size > 1
         self.profiler = None
+        self._memory_tracker.stop_and_update_metrics("init")
+        self.control = self.callback_handler.call_event("on_init_end", self.args, self.state, self.control)
+
+    def add_callback(self, callback):
+        self.callback_handler.add_callback(callback)
+
+    def remove_callback(self, callback):
+        self.callback_handler.remove_callback(callback)
+
+    def _event(self, name: str, **kwargs):
+        self.callback_handler.optimizer, self.callback_handler.lr_scheduler = self.optimizer, self.lr_scheduler
+        self.control = self.callback_handler.call_event(name, self.args, self.state, self.control, **kwargs)
 
     def _ddp_over(self, wrapped):
         from oslo_b200.parallel.data_parallel import _DistributedDataParallel
@@ -203,6 +221,8 @@ class Trainer:
         if resume:
             skip_batches = self._load_checkpoint(resume) * a.gradient_accumulation_steps
         self.base_model.train()
+        self._memory_tracker.start("train")
+        self._event("on_train_begin")
         t0 = time.time()
         tokens = 0
         running, epoch = 0.0, int(self.state.epoch)
@@ -210,11 +230,15 @@ class Trainer:
         while not done:
             if hasattr(loader.sampler, "set_epoch"):
                 loader.sampler.set_epoch(epoch)
+            self._event("on_epoch_begin")
             for i, batch in enumerate(loader):
                 if skip_batches > 0:
                     skip_batches -= 1
                     continue
                 sync_now = (i + 1) % a.gradient_accumulation_steps == 0
+                if i % a.gradient_accumulation_steps == 0:
+                    self.control._new_step()
+                    self._event("on_step_begin")
                 profile = a.flops_profiler and self.state.global_step == a.flops_profiler_step and self._rank() == 0
                 if profile:
                     from .profiler import FlopsProfiler
@@ -243,24 +267,31 @@ class Trainer:
                     opt.zero_grad()
                 self.state.global_step += 1
                 self.state.epoch = epoch + (i + 1) / len(loader)
-                if a.logging_steps and self.state.global_step % a.logging_steps == 0:
+                self._event("on_step_end")
+                if (a.logging_steps and self.state.global_step % a.logging_steps == 0) or self.control.should_log:
                     n = a.logging_steps * a.gradient_accumulation_steps
                     self.log({"loss": self._mean_over_dp(running / n), "learning_rate": self.lr_scheduler.get_last_lr()[0],
                               "epoch": round(self.state.epoch, 3), "step": self.state.global_step})
                     running = 0.0
-                if a.eval_steps and self.eval_dataset is not None and self.state.global_step % a.eval_steps == 0:
+                if self.eval_dataset is not None and ((a.eval_steps and self.state.global_step % a.eval_steps == 0)
+                                                      or self.control.should_evaluate):
                     self._track_best(self.evaluate())
                     self.base_model.train()
-                if a.save_steps and self.state.global_step % a.save_steps == 0:
+                if (a.save_steps and self.state.global_step % a.save_steps == 0) or self.control.should_save:
                     self.save_checkpoint()
-                if self.state.global_step >= max_steps:
+                if self.state.global_step >= max_steps or self.control.should_training_stop:
                     done = True
                     break
+            self._event("on_epoch_end")
+            if self.control.should_training_stop:
+                done = True
             epoch += 1
         elapsed = time.time() - t0
         dp_world, _ = self._dp()
         metrics = {"train_runtime": elapsed, "train_steps_per_second": self.state.global_step / max(elapsed, 1e-9),
                    "train_tokens_per_second": tokens * dp_world / max(elapsed, 1e-9)}
+        self._memory_tracker.stop_and_update_metrics("train", metrics)
+        self._event("on_train_end")
         self.log(metrics)
         return metrics
 
@@ -277,14 +308,13 @@ class Trainer:
     def log(self, logs: dict):
         self.state.log_history.append(dict(logs))
         self.logger.info(json.dumps(logs), ranks=[0])
-        for cb in self.callbacks:
-            if hasattr(cb, "on_log"):
-                cb.on_log(self.args, self.state, logs)
+        self._event("on_log", logs=logs)
 
     # ------------------------------------------------------------- evaluation
     @torch.no_grad()
-    def evaluate(self, eval_dataset=None) -> Dict[str, float]:
+    def evaluate(self, eval_dataset=None, metric_key_prefix: str = "eval") -> Dict[str, float]:
         self.base_model.eval()
+        self._memory_tracker.start(metric_key_prefix)
         losses = []
         for batch in self.get_eval_dataloader(eval_dataset):
             batch = self._move(batch)
@@ -298,13 +328,58 @@ class Trainer:
             else:
                 losses.append(float(self.model(**batch).loss))
         loss = self._mean_over_dp(sum(losses) / max(1, len(losses)))
-        metrics = {"eval_loss": loss, "eval_ppl": math.exp(min(loss, 50.0))}
+        metrics = {f"{metric_key_prefix}_loss": loss, f"{metric_key_prefix}_ppl": math.exp(min(loss, 50.0))}
         if self.compute_metrics:
             metrics.update(self.compute_metrics(metrics))
+        self._memory_tracker.stop_and_update_metrics(metric_key_prefix, metrics)
         self.log(metrics)
+        self._event("on_evaluate", metrics=metrics)
         return metrics
 
-    predict = evaluate
+    @torch.no_grad()
+    def predict(self, test_dataset, metric_key_prefix: str = "test") -> PredictionOutput:
+        """Run the model over ``test_dataset`` and return the gathered predictions (``argmax`` of the logits), the labels
+        when the dataset has them, and metrics (loss over the batches that carry labels, ``compute_metrics`` on
+        ``(predictions, label_ids)`` when given).  Under pipeline parallelism only the loss is available."""
+        self.base_model.eval()
+        self._memory_tracker.start(metric_key_prefix)
+        preds, labels, losses = [], [], []
+        for batch in self.get_eval_dataloader(test_dataset):
+            batch = self._move(batch)
+            if self.is_pipeline:
+                total = None
+                for _, out in self.model(**batch):
+                    if torch.is_tensor(out.loss):
+                        total = out.loss if total is None else total + out.loss
+                if total is not None:
+                    losses.append(float(total))
+                continue
+            out = self.model(**batch)
+            if getattr(out, "loss", None) is not None:
+                losses.append(float(out.loss))
+            logits = getattr(out, "logits", None)
+            if logits is None and "labels" in batch:  # the fused loss consumed the logits: run once more without labels
+                logits = self.model(**{k: v for k, v in batch.items() if k != "labels"}).logits
+            if logits is not None:
+                preds.append(logits.argmax(-1).cpu())
+            if "labels" in batch:
+                labels.append(batch["labels"].cpu())
+        metrics: Dict[str, float] = {}
+        if losses:
+            loss = self._mean_over_dp(sum(losses) / len(losses))
+            metrics[f"{metric_key_prefix}_loss"] = loss
+        predictions = torch.cat(preds) if preds else None
+        label_ids = torch.cat(labels) if labels else None
+        if self.compute_metrics is not None and predictions is not None:
+            try:
+                extra = self.compute_metrics((predictions, label_ids))
+            except Exception:
+                extra = self.compute_metrics(metrics)
+            metrics.update({k if k.startswith(metric_key_prefix) else f"{metric_key_prefix}_{k}": v for k, v in (extra or {}).items()})
+        self._memory_tracker.stop_and_update_metrics(metric_key_prefix, metrics)
+        self.log(metrics)
+        self._event("on_predict", metrics=metrics)
+        return PredictionOutput(predictions, label_ids, metrics)
 
     def _track_best(self, metrics):
         key = self.args.metric_for_best_model or "eval_loss"
@@ -340,6 +415,7 @@ class Trainer:
             self._rotate()
         if dist.is_initialized():
             dist.barrier()
+        self._event("on_save")
         return out
 
     def _rotate(self):

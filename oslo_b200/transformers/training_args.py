@@ -43,6 +43,7 @@ class TrainingArguments:
     resume_from_checkpoint: Optional[str] = None
     metric_for_best_model: Optional[str] = None
     greater_is_better: bool = False
+    skip_memory_metrics: bool = True  # False: per-stage host / device memory deltas are added to the metrics
     flops_profiler: bool = False
     flops_profiler_step: int = 1
     flops_profiler_output_path: Optional[str] = None
