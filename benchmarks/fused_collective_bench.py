@@ -99,7 +99,7 @@ def main():
         if kind == "ag":
             x, w = rnd(tl, K), rnd(N, K)
             x_full = torch.empty(T, K, dtype=torch.bfloat16, device=dev)
-            fused = timed(lambda: fc.ag_gemm(x, w, pc))
+            fused = timed(lambda: fc.ag_gemm(x, w, pc, keep=False))
 
             def comp():
                 dist.all_gather_into_tensor(x_full, x, group=group)
@@ -113,7 +113,7 @@ def main():
             x_full = torch.empty(T, K, dtype=torch.bfloat16, device=dev)
 
             def fused_fn():
-                y1, xf = fc.ag_gemm(x, w1, pc)
+                y1, xf = fc.ag_gemm(x, w1, pc, keep=False)
                 return y1, matmul_nt(xf, w2)
 
             def comp():

@@ -4,9 +4,10 @@
 //   oslo_gemm_rs   out[T/tp, N] = reduce_scatter_rows( A[T, K] x B[N, K]^T )
 //
 // Both are ONE launch of the tcgen05 GEMM kernel in a fused mode (gemm_core.cuh):
-//   * all-gather: a few CTAs stream the peers' shards over NVLink into local memory with plain 16-byte loads
-//     while the remaining CTAs multiply, starting with the local shard and taking each remote shard as soon
-//     as its "copied" flag is up; TMA only ever reads local memory.
+//   * all-gather: a few CTAs PUSH this rank's shard into the gathered buffer of every rank (bulk stores to peer memory;
+//     posted writes are not bound by the NVLink round trip the way remote reads are) while the remaining CTAs multiply,
+//     starting with the local shard and taking each remote row chunk as soon as its source has flagged it; TMA loads
+//     only ever read local memory.
 //   * reduce-scatter: tiles are computed in destination order (next rank first, own rows last).  The epilogue of a
 //     tile of another rank's rows TMA-stores the partial tile straight into slot [this rank] of the OWNER's slot
 //     buffer (a plain bulk tensor store to peer memory) and flags each finished chunk of rows there; the epilogue of
@@ -33,14 +34,15 @@ static int pick_block_n(int M, int N, int ctas, int max_bn) {
   (b_mn ? launch<BN, false, true, MODE>(ta, tb, tc, taux, p, grid, stream, fp, peer_maps_ptr)             \
         : launch<BN, false, false, MODE>(ta, tb, tc, taux, p, grid, stream, fp, peer_maps_ptr))
 
-// peer_in / peer_ag_ready: host arrays of `tp` device pointers (entry [rank] is the local buffer).
-extern "C" int oslo_ag_gemm(void* const* peer_in, void* x_full, const void* B, void* C, const void* bias, int T, int N, int K,
-                            long long ldb, int b_mn, int is_bf16, int tp, int rank, int epoch, void* const* peer_ag_ready,
-                            int* chunk_flag, int* chunk_arrive, int copy_ctas, int num_sms, int* status, void* stream_ptr,
-                            const int* epoch_ptr) {
+// x_shard: this rank's [T/tp, K] rows (any 16-byte aligned local memory).  peer_xfull / peer_chunk_flag: host arrays of
+// `tp` device pointers to every rank's gathered buffer [T, K] and chunk-flag array (entry [rank] is the local one).
+extern "C" int oslo_ag_gemm(const void* x_shard, void* const* peer_xfull, const void* B, void* C, const void* bias, int T, int N,
+                            int K, long long ldb, int b_mn, int is_bf16, int tp, int rank, int epoch,
+                            void* const* peer_chunk_flag, int* chunk_arrive, int copy_ctas, int num_sms, int* status,
+                            void* stream_ptr, const int* epoch_ptr) {
   if (tp > kMaxRanks || tp < 1 || T % tp) return -1;
   const int Tl = T / tp;
-  if (Tl % kBlockM || N % 8 || K % 8 || ldb % 8) return -5;
+  if (Tl % kBlockM || N % 8 || K % 8 || ldb % 8 || (reinterpret_cast<uintptr_t>(x_shard) & 15)) return -5;
   bind_context_to_thread();
   if (copy_ctas < 1) copy_ctas = 1;
   if (copy_ctas > num_sms / 2) copy_ctas = num_sms / 2;
@@ -55,25 +57,26 @@ extern "C" int oslo_ag_gemm(void* const* peer_in, void* x_full, const void* B, v
   FusedParams fp;
   fp.tp = tp; fp.rank = rank; fp.shard_rows = Tl; fp.epoch = epoch; fp.copy_ctas = copy_ctas; fp.k_elems = K;
   fp.tiles_per_shard = (Tl / kBlockM) * p.n_blocks;
-  // copy granularity: about 1024 rows, at most 16 chunks per shard, always a multiple of 128 dividing Tl
+  // hand-off granularity: about 1024 rows, at most 64 chunks over all shards, always a multiple of 128 dividing Tl
   int chunk_rows = Tl;
   for (int cand = 1024; cand >= kBlockM; cand -= kBlockM) {
     if (Tl % cand == 0 && (Tl / cand) * tp <= 64) { chunk_rows = cand; break; }
   }
   fp.chunk_rows = chunk_rows;
   fp.ag_tp = tp; fp.ag_rank = rank; fp.ag_shard_rows = Tl; fp.ag_chunk_rows = chunk_rows; fp.ag_epoch = epoch;
-  fp.ag_epoch_ptr = epoch_ptr; fp.copy_first = (rank + 1) % tp;  // the next rank's shard first, the own one last
+  fp.ag_epoch_ptr = epoch_ptr;
   for (int i = 0; i < tp; ++i) {
-    fp.peer_in[i] = peer_in[i];
-    fp.peer_ag_ready[i] = static_cast<int*>(peer_ag_ready[i]);
+    fp.peer_xfull[i] = peer_xfull[i];
+    fp.peer_chunk_flag[i] = static_cast<int*>(peer_chunk_flag[i]);
   }
+  fp.peer_in[rank] = x_shard;
+  void* x_full = peer_xfull[rank];
   fp.x_full = x_full;
-  fp.ag_ready = static_cast<int*>(peer_ag_ready[rank]);
-  fp.chunk_flag = chunk_flag; fp.chunk_arrive = chunk_arrive; fp.status = status; fp.epoch_ptr = epoch_ptr;
+  fp.chunk_flag = static_cast<int*>(peer_chunk_flag[rank]); fp.chunk_arrive = chunk_arrive; fp.status = status; fp.epoch_ptr = epoch_ptr;
   CUtensorMap ta, tb, tc, taux;
   int rc = make_map(&ta, x_full, is_bf16, K, T, 1, 1, K, 0, 0, kBlockK, kBlockM);
   if (rc) return rc;
-  rc = make_map(&taux, peer_in[rank], is_bf16, K, Tl, 1, 1, K, 0, 0, kBlockK, kBlockM);  // local shard, read in place
+  rc = make_map(&taux, x_shard, is_bf16, K, Tl, 1, 1, K, 0, 0, kBlockK, kBlockM);  // local shard, read in place
   if (rc) return rc;
   if (b_mn) rc = make_map(&tb, B, is_bf16, N, K, 1, 1, ldb, 0, 0, 64, kBlockK);
   else      rc = make_map(&tb, B, is_bf16, K, N, 1, 1, ldb, 0, 0, kBlockK, block_n);
@@ -182,15 +185,15 @@ extern "C" int oslo_gemm_rs(const void* A, long long lda, const void* B, long lo
 // (the 3-D tensor-parallel linear: activations gathered over the INPUT group, partial products reduced over the OUTPUT
 // group; both groups cut the token dimension into the same blocks).  The two sides keep separate flags and epochs, one
 // symmetric workspace per group.  x_full receives the gathered activations for the backward pass.
-extern "C" int oslo_ag_gemm_rs(void* const* peer_in, void* x_full, const void* B, long long ldb, int b_mn, void* out, int T, int N,
-                               int K, int is_bf16, int ag_tp, int ag_rank, int ag_epoch, void* const* peer_ag_ready,
-                               int* chunk_flag, int* chunk_arrive, const int* ag_epoch_ptr, int rs_tp, int rs_rank, int rs_epoch,
+extern "C" int oslo_ag_gemm_rs(const void* x_shard, void* const* peer_xfull, const void* B, long long ldb, int b_mn, void* out, int T,
+                               int N, int K, int is_bf16, int ag_tp, int ag_rank, int ag_epoch, void* const* peer_chunk_flag,
+                               int* chunk_arrive, const int* ag_epoch_ptr, int rs_tp, int rs_rank, int rs_epoch,
                                void* const* peer_partial, void* const* peer_rs_flag, int* tile_done, const int* rs_epoch_ptr,
                                int copy_ctas, int num_sms, int* status, void* stream_ptr) {
   if (ag_tp > kMaxRanks || rs_tp > kMaxRanks || ag_tp < 1 || rs_tp < 1 || T % ag_tp || T % rs_tp) return -1;
   if (ag_tp != rs_tp) return -1;  // both groups cut the rows into the same blocks
   const int Tl = T / rs_tp;
-  if (Tl % kBlockM || N % 8 || K % 8 || ldb % 8) return -5;
+  if (Tl % kBlockM || N % 8 || K % 8 || ldb % 8 || (reinterpret_cast<uintptr_t>(x_shard) & 15)) return -5;
   bind_context_to_thread();
   if (copy_ctas < 1) copy_ctas = 1;
   if (copy_ctas > num_sms / 2) copy_ctas = num_sms / 2;
@@ -221,20 +224,21 @@ extern "C" int oslo_ag_gemm_rs(void* const* peer_in, void* x_full, const void* B
   }
   fp.rs_flag = static_cast<int*>(peer_rs_flag[rs_rank]);
   fp.tile_done = tile_done; fp.rs_out = out; fp.status = status;
-  // all-gather side: same row blocks, fetched in the order the tiles will ask for them
+  // all-gather side: the same row blocks; every rank pushes its block to all the others, chunk by chunk
   fp.ag_tp = ag_tp; fp.ag_rank = ag_rank; fp.ag_shard_rows = Tl; fp.ag_chunk_rows = chunk_rows; fp.ag_epoch = ag_epoch;
-  fp.ag_epoch_ptr = ag_epoch_ptr; fp.copy_first = (rs_rank + 1) % rs_tp; fp.copy_chunk_major = 1;
+  fp.ag_epoch_ptr = ag_epoch_ptr;
   for (int i = 0; i < ag_tp; ++i) {
-    fp.peer_in[i] = peer_in[i];
-    fp.peer_ag_ready[i] = static_cast<int*>(peer_ag_ready[i]);
+    fp.peer_xfull[i] = peer_xfull[i];
+    fp.peer_chunk_flag[i] = static_cast<int*>(peer_chunk_flag[i]);
   }
+  fp.peer_in[ag_rank] = x_shard;
+  void* x_full = peer_xfull[ag_rank];
   fp.x_full = x_full;
-  fp.ag_ready = static_cast<int*>(peer_ag_ready[ag_rank]);
-  fp.chunk_flag = chunk_flag; fp.chunk_arrive = chunk_arrive;
+  fp.chunk_flag = static_cast<int*>(peer_chunk_flag[ag_rank]); fp.chunk_arrive = chunk_arrive;
   CUtensorMap ta, tb, tc, taux;
   int rc = make_map(&ta, x_full, is_bf16, K, T, 1, 1, K, 0, 0, kBlockK, kBlockM);
   if (rc) return rc;
-  rc = make_map(&taux, peer_in[ag_rank], is_bf16, K, Tl, 1, 1, K, 0, 0, kBlockK, kBlockM);  // own shard, read in place
+  rc = make_map(&taux, x_shard, is_bf16, K, Tl, 1, 1, K, 0, 0, kBlockK, kBlockM);  // own shard, read in place
   if (rc) return rc;
   if (b_mn) rc = make_map(&tb, B, is_bf16, N, K, 1, 1, ldb, 0, 0, 64, kBlockK);
   else      rc = make_map(&tb, B, is_bf16, K, N, 1, 1, ldb, 0, 0, kBlockK, block_n);

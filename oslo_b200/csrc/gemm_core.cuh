@@ -113,15 +113,13 @@ struct FusedParams {
   int ag_shard_rows = 0, ag_chunk_rows = 0;
   int ag_epoch = 0;
   const int* ag_epoch_ptr = nullptr;
-  int copy_first = 0;       // first shard the copy CTAs fetch (the order the GEMM tiles will ask for them)
-  int copy_chunk_major = 0; // fetch chunk c of every shard before chunk c + 1 of any (gather + scatter launches)
   // all-gather
-  const void* peer_in[kMaxRanks] = {};  // every rank's symmetric input shard [shard_rows, K]
-  void* x_full = nullptr;               // local [tp * shard_rows, K]
-  int* ag_ready = nullptr;              // local [tp]: peer p's shard for `epoch` is in its buffer
-  int* peer_ag_ready[kMaxRanks] = {};   // the same array on every rank (to announce our shard)
-  int* chunk_flag = nullptr;            // local [tp * chunks_per_shard]: that chunk of x_full is complete
-  int* chunk_arrive = nullptr;          // local, same size: copy-CTA arrival counters
+  const void* peer_in[kMaxRanks] = {};  // entry [ag_rank]: this rank's shard [shard_rows, K], read in place (any local memory)
+  void* x_full = nullptr;               // local gathered buffer [tp * shard_rows, K] (= peer_xfull[ag_rank])
+  void* peer_xfull[kMaxRanks] = {};     // every rank's gathered buffer: our shard is pushed into slot [ag_rank] of each
+  int* chunk_flag = nullptr;            // local [tp * chunks_per_shard], written by the SOURCE rank: that chunk has landed
+  int* peer_chunk_flag[kMaxRanks] = {}; // the same array on every rank
+  int* chunk_arrive = nullptr;          // local [chunks_per_shard]: copy-CTA arrival counters for our own shard's chunks
   // reduce-scatter
   void* peer_slots[kMaxRanks] = {};     // every rank's slot buffer [tp, shard_rows, N] (slot s = rows from rank s)
   int* rs_flag = nullptr;               // local [tp * chunks_per_shard]: source p finished that chunk of our rows
@@ -175,16 +173,15 @@ OSLO_DEVINL void fused_tile_coords(int tile, const GemmParams& p, const FusedPar
   b = 0;
   const int blocks_per_chunk = fp.chunk_rows / kBlockM;
   if constexpr ((MODE & kModeReduceScatter) != 0) {
-    // Row chunk by row chunk; inside a chunk the other ranks' blocks first (next rank first), our own block last.
-    // A rank's own chunk c needs the peers' partials of chunk c, which every peer computes earlier in this same order,
-    // so the dependencies only point backwards; and the tiles that leave over NVLink are spread over the whole launch
-    // instead of being bunched in its first (tp - 1) / tp.
-    const int per_shard = fp.tiles_per_chunk;            // tiles of one (owner, row chunk)
-    const int per_chunk = per_shard * fp.tp;
-    const int c = tile / per_chunk;
-    const int t = tile - c * per_chunk;
-    const int i = t / per_shard, r = t - i * per_shard;
+    // Block by block in destination order: the next rank's block first, our own block LAST (by then the other ranks'
+    // partials of it have long arrived, so the tiles that finish the reduction do not wait; an order that interleaved
+    // own and foreign row chunks measured slower: every skew between ranks stalled a persistent CTA).  Inside a block,
+    // row chunk by row chunk, so chunks are completed, and flagged, in order.
+    const int i = tile / fp.tiles_per_shard;
+    const int t = tile - i * fp.tiles_per_shard;
     const int shard = (fp.rank + i + 1) % fp.tp;
+    const int per_chunk = fp.tiles_per_chunk;
+    const int c = t / per_chunk, r = t - c * per_chunk;
     if (fp.rs_along_n) {
       mb = c * blocks_per_chunk + r % blocks_per_chunk;
       nb = shard * fp.n_blocks_per_shard + r / blocks_per_chunk;
@@ -194,15 +191,24 @@ OSLO_DEVINL void fused_tile_coords(int tile, const GemmParams& p, const FusedPar
     }
     return;
   }
-  // all-gather only: shard by shard, starting with the local one; inside a shard chunk by chunk (the hand-off
-  // granularity), all n-blocks of a chunk before the next chunk, so chunks are consumed in the order they are copied
-  const int i = tile / fp.tiles_per_shard;
-  const int t = tile - i * fp.tiles_per_shard;
-  const int shard = (fp.rank + i) % fp.tp;
+  // all-gather only: the local shard first (no waiting), then row chunk by row chunk over the other ranks' shards, which
+  // is the order in which every rank pushes its shard out (chunk 0 to everybody, then chunk 1 ...)
   const int blocks_per_shard = fp.shard_rows / kBlockM;
   const int n_blocks = fp.tiles_per_shard / blocks_per_shard;
   const int per_chunk = blocks_per_chunk * n_blocks;
-  const int c = t / per_chunk, r = t - c * per_chunk;
+  int shard, c, r;
+  if (tile < fp.tiles_per_shard) {
+    shard = fp.rank;
+    c = tile / per_chunk;
+    r = tile - c * per_chunk;
+  } else {
+    const int t = tile - fp.tiles_per_shard;
+    const int per_round = per_chunk * (fp.tp - 1);  // chunk c of every other shard
+    c = t / per_round;
+    const int u = t - c * per_round;
+    shard = (fp.rank + 1 + u / per_chunk) % fp.tp;
+    r = u % per_chunk;
+  }
   mb = shard * blocks_per_shard + c * blocks_per_chunk + r % blocks_per_chunk;
   nb = r / blocks_per_chunk;
 }
@@ -233,81 +239,68 @@ OSLO_DEVINL void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
 constexpr int kCopyPiece = 32768;  // bytes per bulk copy
 constexpr int kCopyDepth = 6;      // pieces in flight per copy CTA (6 x 32 KiB of shared memory)
 
-// AG copy role.  ONE thread per copy CTA drives the TMA engine: it announces our shard, then streams the other
-// ranks' shards (next rank first, the own shard last) through a shared-memory ring into x_full, keeping
-// kCopyDepth - 1 peer loads in flight to cover the NVLink round trip, and raises a flag per chunk of rows once all
-// copy CTAs have stored their pieces of it.  The GEMM CTAs take a chunk as soon as its flag is up.
+// AG copy role: PUSH.  Reading a peer's memory is bound by the NVLink round trip (a few KB in flight per SM: measured
+// ~6 GB/s per copy CTA), writing to it is not: writes are posted.  So every rank pushes ITS OWN shard into the gathered
+// buffer of every rank.  One thread per copy CTA drives the TMA engine: 32 KiB pieces of the local shard go through a
+// shared-memory ring (bulk load, local memory) and out again as one bulk store per destination (peers and ourselves).
+// When all copy CTAs have finished the stores of a row chunk, the last one raises that chunk's flag ON EVERY
+// DESTINATION; a GEMM CTA there takes the chunk as soon as the flag holds this call's epoch.
 static __device__ __noinline__ void ag_copy_role(const GemmParams& p, const FusedParams& fp, uint8_t* ring, uint64_t* bars) {
   if (threadIdx.x != 0) return;
   __shared__ int s_abort;
   s_abort = 0;
   for (int i = 0; i < kCopyDepth; ++i) mbar_init(&bars[i], 1);
   fence_barrier_init();
-  if (blockIdx.x == 0) {
-    __threadfence_system();
-    for (int t = 0; t < fp.ag_tp; ++t) st_release_sys(fp.peer_ag_ready[t] + fp.ag_rank, fp.ag_epoch);
-  }
   const int cps = fp.ag_shard_rows / fp.ag_chunk_rows;  // chunks per shard
   const long long chunk_bytes = static_cast<long long>(fp.ag_chunk_rows) * fp.k_elems * 2;
+  const long long shard_bytes = chunk_bytes * cps;
   const int ppc = static_cast<int>((chunk_bytes + kCopyPiece - 1) / kCopyPiece);  // pieces per chunk
-  const long long total = static_cast<long long>(fp.ag_tp) * cps * ppc;
-  const int owners = fp.copy_ctas < ppc ? fp.copy_ctas : ppc;
-  const long long my_count = (total - blockIdx.x + fp.copy_ctas - 1) / fp.copy_ctas;  // pieces g = b + j * copy_ctas
-  int ready_shard = fp.ag_rank;
+  const long long total = static_cast<long long>(cps) * ppc;                      // pieces of OUR shard
+  const int owners = fp.copy_ctas < ppc ? fp.copy_ctas : ppc;                     // copy CTAs with pieces in a chunk
+  const long long my_count = total > blockIdx.x ? (total - blockIdx.x + fp.copy_ctas - 1) / fp.copy_ctas : 0;
+  const uint8_t* my_shard = static_cast<const uint8_t*>(fp.peer_in[fp.ag_rank]);
   bool ok = true;
-  auto locate = [&](long long j, const uint8_t*& src, uint8_t*& dst, uint32_t& bytes, int& chunk, bool& last_of_chunk, int& shard) {
+  auto locate = [&](long long j, long long& off, uint32_t& bytes, int& c, bool& last_of_chunk) {
     const long long g = blockIdx.x + j * fp.copy_ctas;
-    const long long o = g / ppc;                      // position of the chunk in copy order
-    const int piece = static_cast<int>(g - o * ppc);
-    // shard-major (all chunks of the next rank, then the one after ...) for a plain all-gather; chunk-major when a
-    // reduce-scatter sets the tile order (chunk 0 of every shard, then chunk 1 ...)
-    const int i = static_cast<int>(fp.copy_chunk_major ? o % fp.ag_tp : o / cps);
-    const int c = static_cast<int>(fp.copy_chunk_major ? o / fp.ag_tp : o % cps);
-    shard = (fp.copy_first + i) % fp.ag_tp;
-    chunk = shard * cps + c;
-    const long long off = static_cast<long long>(piece) * kCopyPiece;
-    bytes = static_cast<uint32_t>(chunk_bytes - off < kCopyPiece ? chunk_bytes - off : kCopyPiece);
-    src = static_cast<const uint8_t*>(fp.peer_in[shard]) + static_cast<long long>(c) * chunk_bytes + off;
-    dst = static_cast<uint8_t*>(fp.x_full) + static_cast<long long>(chunk) * chunk_bytes + off;
-    last_of_chunk = (g + fp.copy_ctas) / ppc != o;    // our next piece (if any) belongs to a later chunk
+    c = static_cast<int>(g / ppc);
+    const long long in_chunk = (g - static_cast<long long>(c) * ppc) * kCopyPiece;
+    bytes = static_cast<uint32_t>(chunk_bytes - in_chunk < kCopyPiece ? chunk_bytes - in_chunk : kCopyPiece);
+    off = static_cast<long long>(c) * chunk_bytes + in_chunk;
+    last_of_chunk = (g + fp.copy_ctas) / ppc != c;  // our next piece (if any) belongs to a later chunk
   };
   for (long long n = 0; n < my_count + kCopyDepth - 1 && ok; ++n) {
     if (n < my_count) {
-      const uint8_t* src; uint8_t* dst; uint32_t bytes; int chunk, shard; bool last;
-      locate(n, src, dst, bytes, chunk, last, shard);
-      if (shard != ready_shard) {
-        if (!flag_wait_bounded(fp.ag_ready + shard, fp.ag_epoch, nullptr, true)) {
-          if (fp.status) atomicCAS(fp.status, kStatusOk, kStatusPeerFlagTimeout);
-          ok = false;
-          break;
-        }
-        ready_shard = shard;
-      }
-      if (n >= kCopyDepth) tma_store_wait_read<0>();  // the store that last used this ring slot has drained it
+      long long off; uint32_t bytes; int c; bool last;
+      locate(n, off, bytes, c, last);
+      if (n >= kCopyDepth) tma_store_wait_read<0>();  // the stores that last used this ring slot have drained it
       uint64_t* bar = &bars[n % kCopyDepth];
       mbar_arrive_expect_tx(bar, bytes);
-      bulk_load(ring + (n % kCopyDepth) * kCopyPiece, src, bytes, bar);
+      bulk_load(ring + (n % kCopyDepth) * kCopyPiece, my_shard + off, bytes, bar);
     }
     const long long m = n - (kCopyDepth - 1);
     if (m >= 0 && m < my_count) {
-      const uint8_t* src; uint8_t* dst; uint32_t bytes; int chunk, shard; bool last;
-      locate(m, src, dst, bytes, chunk, last, shard);
+      long long off; uint32_t bytes; int c; bool last;
+      locate(m, off, bytes, c, last);
       if (!mbar_wait_bounded(&bars[m % kCopyDepth], static_cast<uint32_t>((m / kCopyDepth) & 1), &s_abort)) {
         if (fp.status) atomicCAS(fp.status, kStatusOk, kStatusPeerFlagTimeout);
         ok = false;
         break;
       }
-      bulk_store(dst, ring + (m % kCopyDepth) * kCopyPiece, bytes);
+      // farthest destination first is as good as any: all links are symmetric through the switch
+      for (int i = 1; i <= fp.ag_tp; ++i) {
+        const int d = (fp.ag_rank + i) % fp.ag_tp;
+        bulk_store(static_cast<uint8_t*>(fp.peer_xfull[d]) + fp.ag_rank * shard_bytes + off, ring + (m % kCopyDepth) * kCopyPiece, bytes);
+      }
       tma_store_commit();
       if (last) {
-        tma_store_wait_all();  // our pieces of this chunk are in memory
+        tma_store_wait_all();  // our pieces of this chunk have been written everywhere
         fence_proxy_async_global();
-        __threadfence();
-        const int old = atomicAdd(fp.chunk_arrive + chunk, 1);
+        __threadfence_system();
+        const int old = atomicAdd(fp.chunk_arrive + c, 1);
         if (old == owners - 1) {
-          fp.chunk_arrive[chunk] = 0;
-          __threadfence();
-          st_release_gpu(fp.chunk_flag + chunk, fp.ag_epoch);
+          fp.chunk_arrive[c] = 0;
+          __threadfence_system();
+          for (int d = 0; d < fp.ag_tp; ++d) st_release_sys(fp.peer_chunk_flag[d] + fp.ag_rank * cps + c, fp.ag_epoch);
         }
       }
     }
@@ -414,7 +407,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const int chunk = m0 / fp.ag_chunk_rows;
           a_local = shard == fp.ag_rank;
           if (!a_local && chunk != ready_shard) {
-            if (!flag_wait_bounded(fp.chunk_flag + chunk, fp.ag_epoch, abort_flag, false)) {
+            if (!flag_wait_bounded(fp.chunk_flag + chunk, fp.ag_epoch, abort_flag, true)) {
               ok = false;
               if (p.status) atomicCAS(p.status, kStatusOk, kStatusPeerFlagTimeout);
               break;

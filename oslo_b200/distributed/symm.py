@@ -6,11 +6,13 @@ run as single fused kernels (``csrc/fused_collectives_sm100a.cu``).
 
 Workspace layout per rank (all offsets identical on every rank)::
 
-    [ flags 4 KiB | in[0] | in[1] | slots[0] | slots[1] ]
+    [ flags 4 KiB | gathered[0] | gathered[1] | slots[0] | slots[1] ]
 
-* ``in[p]``     this rank's shard of the all-gather input for calls with parity ``p`` (``Tl x F`` elements);
-* ``slots[p]``  ``tp`` blocks of ``Tl x F``: block ``s`` receives rank ``s``'s partial rows of a reduce-scatter;
-* flags        ``ag_ready[tp]``, ``rs_flag[tp]``, ``barrier[tp]`` written by peers, holding call epochs.
+* ``gathered[p]``  the all-gather result of calls with parity ``p`` (``T x F`` elements): rank ``s`` PUSHES its shard into
+                   block ``s`` of this buffer on every rank (remote writes are posted, remote reads are latency-bound);
+* ``slots[p]``     ``tp`` blocks of ``Tl x F``: block ``s`` receives rank ``s``'s partial rows of a reduce-scatter;
+* flags           ``chunk_flag[tp * chunks]`` (a source has delivered that row chunk), ``rs_flag[..]``, ``barrier[tp]``,
+                   all written by peers and holding call epochs.
 
 Double buffering by call parity is what makes the scheme free of write-after-read races without a trailing
 barrier: a rank can only be one call ahead of any peer, because each call needs data from every peer.
@@ -149,7 +151,7 @@ def small_ops_enabled() -> bool:
 
 
 class SymmetricWorkspace:
-    def __init__(self, pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 24):
+    def __init__(self, pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 16):
         self.pc, self.mode = pc, mode
         self.tp = pc.get_world_size(mode)
         self.rank = pc.get_local_rank(mode)
@@ -160,8 +162,7 @@ class SymmetricWorkspace:
         self.copy_ctas = copy_ctas
         self.max_tokens, self.max_features = max_tokens, max_features
         esz = torch.empty((), dtype=dtype).element_size()
-        shard_elems = (max_tokens // self.tp) * max_features
-        self.in_bytes = (shard_elems * esz + 1023) // 1024 * 1024
+        self.in_bytes = (max_tokens * max_features * esz + 1023) // 1024 * 1024  # one gathered buffer
         self.slot_bytes = (max_tokens * max_features * esz + 1023) // 1024 * 1024
         self.total = _FLAG_BYTES + 2 * self.in_bytes + 2 * self.slot_bytes
         lib = _lib.cuda_lib()
@@ -199,10 +200,10 @@ class SymmetricWorkspace:
 
     # ------------------------------------------------------------ addressing
     def _flag_ptrs(self, which: int):
-        # which: 0 ag_ready, 1 rs_flag, 2 barrier ; each 64 ints apart
+        # which: 0 chunk_flag (all-gather), 1 rs_flag, 2 barrier ; each 64 ints apart
         return (ctypes.c_void_p * self.tp)(*[b + which * 256 for b in self.peer_base])
 
-    def _in_ptrs(self, parity: int):
+    def _gathered_ptrs(self, parity: int):
         off = _FLAG_BYTES + parity * self.in_bytes
         return (ctypes.c_void_p * self.tp)(*[b + off for b in self.peer_base])
 
@@ -210,13 +211,13 @@ class SymmetricWorkspace:
         off = _FLAG_BYTES + 2 * self.in_bytes + parity * self.slot_bytes
         return (ctypes.c_void_p * self.tp)(*[b + off for b in self.peer_base])
 
-    def _local_in(self, parity: int, rows: int, cols: int):
+    def _local_gathered(self, parity: int, rows: int, cols: int):
         off = _FLAG_BYTES + parity * self.in_bytes
         n = rows * cols * self._local_bytes.new_empty((), dtype=self.dtype).element_size()
         return self._local_bytes[off : off + n].view(self.dtype).view(rows, cols)
 
     def _local_ptr(self, idx: int) -> ctypes.c_void_p:
-        # three local int arrays of 64 entries: chunk flags, chunk arrival counters, per-destination tile counters
+        # local int arrays of 64 entries: [1] chunk arrival counters of the push role, [2] per-destination tile counters
         return ctypes.c_void_p(self.local.data_ptr() + idx * 4 * 64)
 
     # ------------------------------------------------------------------ ops
@@ -264,7 +265,7 @@ class SymmetricWorkspace:
     def ag_ok(self, x_shard, w) -> bool:
         tl, k = x_shard.shape
         return (self.supports(x_shard, w) and tl % 128 == 0 and tl * self.tp <= self.max_tokens
-                and k <= self.max_features and tl * k * x_shard.element_size() <= self.in_bytes)
+                and k <= self.max_features and tl * self.tp * k * x_shard.element_size() <= self.in_bytes)
 
     def rs_ok(self, x, w, along_n: bool = False) -> bool:
         t, _ = x.shape
@@ -275,15 +276,19 @@ class SymmetricWorkspace:
         return (self.supports(x, w) and t % self.tp == 0 and (t // self.tp) % 128 == 0 and t <= self.max_tokens
                 and n <= self.max_features and t * n * x.element_size() <= self.slot_bytes)
 
-    def ag_gemm(self, x_shard: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None):
-        """Returns ``(all_gather(x_shard) @ weight^T (+ bias, added in the epilogue), all_gather(x_shard))``."""
+    def ag_gemm(self, x_shard: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, keep: bool = True):
+        """Returns ``(all_gather(x_shard) @ weight^T (+ bias, added in the epilogue), all_gather(x_shard))``.
+
+        The gathered activations live in the workspace's symmetric buffer of this call's parity, which the peers
+        overwrite two fused calls later.  ``keep=True`` (default) returns a private copy, e.g. to save for a backward
+        pass; ``keep=False`` returns the view for consumers that are enqueued right away."""
         tl, k = x_shard.shape
         t = tl * self.tp
         n = weight.shape[0]
         self._next_epoch()
         parity = self.epoch & 1
-        self._local_in(parity, tl, k).copy_(x_shard)
-        x_full = torch.empty(t, k, dtype=x_shard.dtype, device=x_shard.device)
+        if not x_shard.is_contiguous() or x_shard.data_ptr() % 16:
+            x_shard = x_shard.contiguous()
         out = torch.empty(t, n, dtype=x_shard.dtype, device=x_shard.device)
         w, b_mn, ldb = self._weight_operand(weight)
         if bias is not None:
@@ -291,14 +296,15 @@ class SymmetricWorkspace:
                 raise ValueError("ag_gemm: bias must be [N]")
             bias = bias.to(x_shard.dtype).contiguous()
         rc = _lib.cuda_lib().oslo_ag_gemm(
-            self._in_ptrs(parity), _lib.ptr(x_full), _lib.ptr(w), _lib.ptr(out), _lib.ptr(bias), ctypes.c_int(t), ctypes.c_int(n),
-            ctypes.c_int(k), ctypes.c_longlong(ldb), ctypes.c_int(b_mn), ctypes.c_int(1 if self.dtype == torch.bfloat16 else 0),
-            ctypes.c_int(self.tp), ctypes.c_int(self.rank), ctypes.c_int(self.epoch), self._flag_ptrs(0),
-            self._local_ptr(0), self._local_ptr(1), ctypes.c_int(self.copy_ctas), ctypes.c_int(_lib.num_sms()),
-            _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr(), _lib.ptr(self.epoch_dev))
+            _lib.ptr(x_shard), self._gathered_ptrs(parity), _lib.ptr(w), _lib.ptr(out), _lib.ptr(bias), ctypes.c_int(t),
+            ctypes.c_int(n), ctypes.c_int(k), ctypes.c_longlong(ldb), ctypes.c_int(b_mn),
+            ctypes.c_int(1 if self.dtype == torch.bfloat16 else 0), ctypes.c_int(self.tp), ctypes.c_int(self.rank),
+            ctypes.c_int(self.epoch), self._flag_ptrs(0), self._local_ptr(1), ctypes.c_int(self.copy_ctas),
+            ctypes.c_int(_lib.num_sms()), _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr(), _lib.ptr(self.epoch_dev))
         if rc:
             raise RuntimeError(f"oslo_ag_gemm failed ({rc})")
-        return out, x_full
+        x_full = self._local_gathered(parity, t, k)
+        return out, (x_full.clone() if keep else x_full)
 
     def gemm_rs(self, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
                 addend: Optional[torch.Tensor] = None, along_n: bool = False):
@@ -342,22 +348,22 @@ class SymmetricWorkspace:
         self._next_epoch()
         rs_ws._next_epoch()
         ag_par, rs_par = self.epoch & 1, rs_ws.epoch & 1
-        self._local_in(ag_par, tl, k).copy_(x_shard)
-        x_full = torch.empty(t, k, dtype=x_shard.dtype, device=x_shard.device)
+        if not x_shard.is_contiguous() or x_shard.data_ptr() % 16:
+            x_shard = x_shard.contiguous()
         out = torch.empty(tl, n, dtype=x_shard.dtype, device=x_shard.device)
         w, b_mn, ldb = self._weight_operand(weight)
         rc = _lib.cuda_lib().oslo_ag_gemm_rs(
-            self._in_ptrs(ag_par), _lib.ptr(x_full), _lib.ptr(w), ctypes.c_longlong(ldb), ctypes.c_int(b_mn), _lib.ptr(out),
+            _lib.ptr(x_shard), self._gathered_ptrs(ag_par), _lib.ptr(w), ctypes.c_longlong(ldb), ctypes.c_int(b_mn), _lib.ptr(out),
             ctypes.c_int(t), ctypes.c_int(n), ctypes.c_int(k), ctypes.c_int(1 if self.dtype == torch.bfloat16 else 0),
             ctypes.c_int(self.tp), ctypes.c_int(self.rank), ctypes.c_int(self.epoch), self._flag_ptrs(0),
-            self._local_ptr(0), self._local_ptr(1), _lib.ptr(self.epoch_dev),
+            self._local_ptr(1), _lib.ptr(self.epoch_dev),
             ctypes.c_int(rs_ws.tp), ctypes.c_int(rs_ws.rank), ctypes.c_int(rs_ws.epoch), rs_ws._slot_ptrs(rs_par),
             rs_ws._flag_ptrs(1), rs_ws._local_ptr(2), _lib.ptr(rs_ws.epoch_dev),
             ctypes.c_int(self.copy_ctas), ctypes.c_int(_lib.num_sms()), _lib.ptr(_lib.status_word(self.device)),
             _lib.stream_ptr())
         if rc:
             raise RuntimeError(f"oslo_ag_gemm_rs failed ({rc})")
-        return out, x_full
+        return out, self._local_gathered(ag_par, t, k).clone()
 
     def ag_rs_ok(self, rs_ws, x_shard, w) -> bool:
         tl, k = x_shard.shape
@@ -378,10 +384,10 @@ class _Runtime:
         # called with either a token shard (all-gather side) or full tokens (reduce-scatter side)
         return self.ws.ag_ok(x, w) or self.ws.rs_ok(x, w)
 
-    def ag_gemm(self, x_shard, weight, bias=None):
+    def ag_gemm(self, x_shard, weight, bias=None, keep=True):
         if not self.ws.ag_ok(x_shard, weight):
             raise RuntimeError("ag_gemm: operands not supported by the fused kernel")
-        return self.ws.ag_gemm(x_shard, weight, bias)
+        return self.ws.ag_gemm(x_shard, weight, bias, keep)
 
     def gemm_rs(self, x, weight, addend=None, along_n=False):
         if not self.ws.rs_ok(x, weight, along_n):
@@ -389,7 +395,7 @@ class _Runtime:
         return self.ws.gemm_rs(x, weight, addend=addend, along_n=along_n)
 
 
-def enable(pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 24, model=None) -> bool:
+def enable(pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 16, model=None) -> bool:
     """Create the group's symmetric workspace and switch the linears that communicate over ``mode`` to the fused kernels:
     ``TENSOR_1D`` for the sequence-parallel 1-D linears, ``TENSOR_2D_ROW`` / ``TENSOR_2P5D_ROW`` for the feature
     reduce-scatter of the SUMMA linears, ``TENSOR_3D_INPUT`` + ``TENSOR_3D_OUTPUT`` (call twice) for the 3-D linear.

@@ -52,10 +52,11 @@ def available(x: torch.Tensor, w: torch.Tensor, kind: str = "any") -> bool:
     return rt.supports(x, w)
 
 
-def ag_gemm(x_shard, weight, pc, bias=None):
-    """``(all_gather(x_shard) @ weight^T (+ bias), all_gather(x_shard))`` in one kernel."""
+def ag_gemm(x_shard, weight, pc, bias=None, keep=True):
+    """``(all_gather(x_shard) @ weight^T (+ bias), all_gather(x_shard))`` in one kernel.  ``keep=False`` returns the gathered
+    activations as a view of the workspace, valid until two more fused calls have been issued."""
     with annotate("oslo.ag_gemm"):
-        return _runtime.ag_gemm(x_shard, weight, bias)
+        return _runtime.ag_gemm(x_shard, weight, bias, keep)
 
 
 def gemm_rs(x, weight, pc, addend=None):

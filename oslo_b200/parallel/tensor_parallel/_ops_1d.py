@@ -200,8 +200,8 @@ class _LinearRS(torch.autograd.Function):
         if _use_fused(gy, weight.t(), "ag"):
             from oslo_b200.ops import fused_collectives as fc
 
-            # dX = all_gather(dY) @ W ; the gathered dY is reused for dW
-            gx, gy_full = fc.ag_gemm(gy, weight.t(), pc)
+            # dX = all_gather(dY) @ W ; the gathered dY is reused for dW right away, so the workspace view is enough
+            gx, gy_full = fc.ag_gemm(gy, weight.t(), pc, keep=False)
         else:
             gy_full = comm.all_gather(gy, dim=0, parallel_context=pc, parallel_mode=_MODE)
             gx = matmul_nt(gy_full, weight.t()) if ctx.needs_input_grad[0] else None
@@ -309,7 +309,7 @@ class _LinearPairRS(torch.autograd.Function):
         if _use_fused(gy, w2.t(), "ag"):
             from oslo_b200.ops import fused_collectives as fc
 
-            gx2, gy_full = fc.ag_gemm(gy, w2.t(), pc)
+            gx2, gy_full = fc.ag_gemm(gy, w2.t(), pc, keep=False)  # consumed by the GEMMs below before two more fused calls
         else:
             gy_full = comm.all_gather(gy, dim=0, parallel_context=pc, parallel_mode=_MODE)
             gx2 = matmul_nt(gy_full, w2.t())
