@@ -1,6 +1,7 @@
 """Counterparts of the vendored LightSeq subset of the reference (``oslo/lightseq2``), on this repository's kernels."""
 from .gcq import GCQState, gcq_hook, quantized_all_reduce
 from .inference import generate
+from .kernels import filter_logits, ls_dequantize_int8, ls_embedding, ls_quantize_int8, sample_tokens
 from .layers import (
     LSAdam,
     LSCrossEntropyLayer,

@@ -64,7 +64,9 @@ def generate(model, input_ids: torch.Tensor, max_new_tokens: int = 32, do_sample
         if no_repeat_ngram_size > 0:
             logits = blocker(ids, logits.contiguous(), ids.shape[0], ids.shape[1] - 1, 1, no_repeat_ngram_size)
         if do_sample:
-            nxt = torch.multinomial(_filter(logits, top_k, top_p).softmax(-1), 1)
+            from .kernels import sample_tokens
+
+            nxt = sample_tokens(logits, top_k, top_p)  # the device kernel on CUDA (no vocabulary sort)
         else:
             nxt = logits.argmax(-1, keepdim=True)
         if eos_token_id is not None:

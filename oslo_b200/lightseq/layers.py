@@ -175,11 +175,15 @@ class LSTransformerEmbeddingLayer(nn.Module):
         self.register_buffer("pos_embeddings", table, persistent=False)
 
     def forward(self, input_ids, step: int = 0):
-        s = input_ids.shape[1]
-        x = self.embeddings(input_ids) * math.sqrt(self.config.hidden_size)
-        x = x + self.pos_embeddings[step : step + s].to(x.dtype)
-        x = x.masked_fill((input_ids == self.config.padding_idx).unsqueeze(-1), 0)
-        return F.dropout(x, self.config.hidden_dropout_ratio, self.training)
+        from .kernels import ls_embedding
+
+        w = self.embeddings.weight
+        pos = self.pos_embeddings
+        if pos.dtype != w.dtype or pos.device != w.device:
+            pos = self.pos_embeddings = pos.to(device=w.device, dtype=w.dtype)
+        # lookup x sqrt(d) + positions + dropout with padding rows zeroed: one kernel on CUDA
+        return ls_embedding(input_ids, w, pos, step, self.config.padding_idx, math.sqrt(self.config.hidden_size),
+                            self.config.hidden_dropout_ratio, self.training)
 
 
 class LSCrossEntropyLayer(nn.Module):

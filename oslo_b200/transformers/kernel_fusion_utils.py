@@ -45,3 +45,66 @@ def fused_layer_norm(model: nn.Module) -> nn.Module:
 
     _swap(model, lambda m: type(m) is nn.LayerNorm, make)
     return model
+
+
+def fused_linear(model: nn.Module) -> nn.Module:
+    """Every plain ``nn.Linear`` computes through the tcgen05 GEMM (forward, dX and dW) instead of cuBLAS."""
+    import torch
+
+    def make(old):
+        new = onn.Linear.__new__(onn.Linear)
+        nn.Module.__init__(new)
+        new.in_features, new.out_features, new.skip_bias_add = old.in_features, old.out_features, False
+        new.weight, new.bias = old.weight, old.bias
+        return new
+
+    _swap(model, lambda m: type(m) is torch.nn.Linear, make)
+    return model
+
+
+_ATTENTION_NAME = "oslo_b200"
+
+
+def _oslo_attention_forward(module, query, key, value, attention_mask, dropout: float = 0.0, scaling=None, is_causal=None,
+                            **kwargs):
+    """Hugging Face attention-interface function backed by the fused tcgen05 attention kernels.
+
+    ``query / key / value`` arrive as ``[batch, heads, seq, head_dim]``; the result is ``[batch, seq, heads, head_dim]`` as
+    the interface expects.  Calls the kernels cannot take (an explicit mask, attention dropout in training, a key length
+    different from the query length) go to the stock scaled-dot-product implementation."""
+    from transformers.integrations.sdpa_attention import sdpa_attention_forward
+
+    from oslo_b200.ops.attention import attention
+
+    b, h, s, d = query.shape
+    if attention_mask is not None or (dropout and module.training) or key.shape[2] != s:
+        return sdpa_attention_forward(module, query, key, value, attention_mask, dropout=dropout, scaling=scaling,
+                                      is_causal=is_causal, **kwargs)
+    if key.shape[1] != h:  # grouped-query attention: repeat the key / value heads
+        rep = h // key.shape[1]
+        key, value = key.repeat_interleave(rep, dim=1), value.repeat_interleave(rep, dim=1)
+    causal = is_causal if is_causal is not None else (s > 1 and getattr(module, "is_causal", True))
+    out = attention(query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2), causal=bool(causal), scale=scaling)
+    return out.view(b, s, h, d), None
+
+
+def fused_attention(model: nn.Module) -> nn.Module:
+    """Route the attention of a Hugging Face model through the fused attention kernels: registers the
+    ``"oslo_b200"`` implementation with the transformers attention interface and selects it in the model's config (the
+    reference's forks hard-wire their fused softmax / LightSeq attention per model family,
+    oslo/transformers/models/bert/modeling_bert.py:349-401)."""
+    from transformers import AttentionInterface
+
+    AttentionInterface.register(_ATTENTION_NAME, _oslo_attention_forward)
+    cfg = getattr(model, "config", None)
+    if cfg is not None:
+        cfg._attn_implementation = _ATTENTION_NAME
+        for sub in model.modules():
+            if getattr(sub, "config", None) is not None and sub.config is not cfg and hasattr(sub.config, "_attn_implementation"):
+                sub.config._attn_implementation = _ATTENTION_NAME
+    return model
+
+
+def fuse_all(model: nn.Module) -> nn.Module:
+    """LayerNorm / RMSNorm, linears and attention of a stock Hugging Face model on this library's kernels."""
+    return fused_attention(fused_linear(fused_layer_norm(fused_rms_norm(model))))

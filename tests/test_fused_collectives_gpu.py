@@ -241,3 +241,61 @@ def _moe_worker(rank, world):
 @pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
 def test_moe_peer_dispatch_combine_matches_all_to_all():
     run_dist(_moe_worker, 2, timeout=600)
+
+
+def _nd_worker(rank, world, mode_name):
+    """2-D / 2.5-D / 3-D tensor parallel model step: fused kernels (feature reduce-scatter, gather + GEMM + scatter)
+    against the NCCL collective + GEMM compositions of the same layers."""
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import oslo_b200
+    from oslo_b200 import ParallelContext, ParallelMode
+    from oslo_b200 import models
+    from oslo_b200.distributed import symm
+    from oslo_b200.ops import _lib
+    from oslo_b200.parallel import TensorParallel
+
+    M = ParallelMode
+    mode = getattr(M, mode_name)
+    depth = 2 if (mode == M.TENSOR_2P5D and world == 8) else (1 if mode == M.TENSOR_2P5D else None)
+    pc = ParallelContext.from_torch(tensor_parallel_size=world, tensor_parallel_mode=mode, tensor_parallel_depth=depth,
+                                    backend="nccl", seed=0)
+    dev = pc.device
+    cfg = models.GPT2Config(vocab_size=2048, n_positions=256, n_embd=512, n_layer=2, n_head=8, n_inner=2048, resid_pdrop=0.0,
+                            embd_pdrop=0.0, attn_pdrop=0.0)
+    res = {}
+    for fused in (False, True):
+        torch.manual_seed(3)
+        model = models.GPT2LMHeadModel(cfg).to(dev, torch.bfloat16)
+        wrapped = TensorParallel(model, pc)
+        oslo_b200.ready(wrapped, pc)
+        symm.disable()
+        if fused:
+            rows, widest = 8 * 256, 3 * 512
+            if mode == M.TENSOR_3D:
+                assert symm.enable(pc, M.TENSOR_3D_INPUT, rows, widest) and symm.enable(pc, M.TENSOR_3D_OUTPUT, rows, widest)
+            else:
+                assert symm.enable(pc, M.TENSOR_2D_ROW if mode == M.TENSOR_2D else M.TENSOR_2P5D_ROW, rows, widest)
+        torch.manual_seed(4)
+        ids = torch.randint(0, 2048, (8, 256), device=dev)
+        loss = wrapped(input_ids=ids, labels=ids).loss
+        loss.backward()
+        torch.cuda.synchronize()
+        _lib.check_status()
+        res[fused] = (loss.item(), {k: p.grad.float().clone() for k, p in model.named_parameters() if p.grad is not None})
+    symm.disable()
+    assert abs(res[True][0] - res[False][0]) < 2e-2, (res[True][0], res[False][0])
+    for k, g in res[False][1].items():
+        a = res[True][1][k]
+        assert (a - g).abs().max().item() <= 5e-2 * (g.abs().max().item() + 1e-3), k
+    pc.destroy()
+
+
+@pytest.mark.skipif(_n_gpus() < 4, reason="needs at least 4 GPUs")
+@pytest.mark.parametrize("mode", ["TENSOR_2D", "TENSOR_2P5D"])
+def test_fused_2d_model_step_matches_composition(mode):
+    run_dist(_nd_worker, 4, mode, timeout=600)
+
+
+@pytest.mark.skipif(_n_gpus() < 8, reason="needs 8 GPUs")
+def test_fused_3d_model_step_matches_composition():
+    run_dist(_nd_worker, 8, "TENSOR_3D", timeout=600)

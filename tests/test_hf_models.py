@@ -176,3 +176,23 @@ def _vp_loss_worker(rank, world, kind):
 @pytest.mark.parametrize("kind", ["gpt2", "gpt_neox", "llama"])
 def test_hf_causal_lm_with_vocab_parallel_loss(kind):
     run_dist(_vp_loss_worker, 2, kind, timeout=600)
+
+
+@pytest.mark.parametrize("kind", ["gpt_neox", "llama", "bert"])
+def test_kernel_fusion_surgery_keeps_hf_outputs(kind):
+    """``fuse_all``: norms, linears and attention of a stock Hugging Face model go through this library's ops
+    (their torch paths on CPU) without changing the outputs."""
+    from oslo_b200.transformers.kernel_fusion_utils import fuse_all
+
+    import oslo_b200.nn as onn
+
+    ref = _build(kind)
+    model = fuse_all(_build(kind))
+    assert model.config._attn_implementation == "oslo_b200"
+    assert any(isinstance(m, onn.Linear) for m in model.modules())
+    assert not any(type(m) is torch.nn.LayerNorm for m in model.modules())
+    ids = torch.randint(0, 100, (2, 12), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = ref(input_ids=ids).logits
+        got = model(input_ids=ids).logits
+    assert torch.allclose(got, want, rtol=1e-4, atol=1e-5), (got - want).abs().max()

@@ -549,3 +549,51 @@ def test_gemm_two_cta_epilogues():
     b3 = (torch.randn(3, 512, 256, device=DEV) * 0.5).to(torch.float16)
     frac, worst = _close(gemm(a3, b3, two_cta=True), a3.float() @ b3.float().transpose(-1, -2), rtol=1e-2, atol=0.05)
     assert frac == 0.0, ("batched fp16", frac, worst)
+
+
+def test_lightseq_kernels_match_torch_paths():
+    """Embedding (forward + backward, with and without dropout), int8 quantise / dequantise and the device-side top-k /
+    top-p sampler against their plain-torch statements."""
+    from oslo_b200.lightseq.kernels import filter_logits, ls_dequantize_int8, ls_embedding, ls_quantize_int8, sample_tokens
+
+    torch.manual_seed(50)
+    vocab, hid, seq = 500, 256, 48
+    emb = (torch.randn(vocab, hid, device=DEV) * 0.5).to(torch.bfloat16).requires_grad_()
+    pos = torch.randn(64, hid, device=DEV).to(torch.bfloat16)
+    ids = torch.randint(1, vocab, (4, seq), device=DEV)
+    ids[:, -5:] = 0  # padding
+    out = ls_embedding(ids, emb, pos, step=3, padding_idx=0, scale=16.0, p=0.0)
+    ref = torch.nn.functional.embedding(ids, emb.detach().float()) * 16.0 + pos[3 : 3 + seq].float()
+    ref = ref.masked_fill((ids == 0).unsqueeze(-1), 0)
+    assert _rel(out, ref) < 1e-2
+    g = torch.randn_like(out)
+    out.backward(g)
+    want = torch.zeros(vocab, hid, device=DEV)
+    want.index_add_(0, ids.view(-1), (g.float() * 16.0).view(-1, hid) * (ids.view(-1, 1) != 0))
+    assert _rel(emb.grad, want) < 2e-2
+    # dropout: the kept pattern of the forward output is the mask that backward must recompute
+    emb.grad = None
+    out = ls_embedding(ids, emb, pos, step=0, padding_idx=0, scale=1.0, p=0.3, training=True, seed=7)
+    kept = out.detach() != 0
+    frac = kept[ids != 0].float().mean().item()
+    assert 0.6 < frac < 0.8, frac
+    out.backward(torch.ones_like(out))
+    want = torch.zeros(vocab, hid, device=DEV)
+    want.index_add_(0, ids.view(-1), kept.view(-1, hid).float() / 0.7)
+    assert _rel(emb.grad, want) < 2e-2
+    # int8
+    x = (torch.randn(4096, 129, device=DEV) * 2).to(torch.bfloat16)
+    q, mask = ls_quantize_int8(x, 3.0, return_mask=True)
+    qr = torch.round(x.float().clamp(-3, 3) * (127 / 3.0)).to(torch.int8)
+    assert (q.int() - qr.int()).abs().max().item() <= 1 and torch.equal(mask, x.float().abs() > 3.0)
+    assert _rel(ls_dequantize_int8(q, 3.0, torch.bfloat16), q.float() * (3.0 / 127)) < 1e-2
+    # sampling: every draw lies in the filtered set, and the empirical distribution follows the renormalised probabilities
+    logits = torch.randn(1, 2000, device=DEV) * 2
+    for top_k, top_p in ((0, 1.0), (50, 1.0), (0, 0.8), (100, 0.5)):
+        allowed = torch.isfinite(filter_logits(logits.float(), top_k, top_p))[0]
+        draws = sample_tokens(logits.repeat(4096, 1), top_k, top_p).view(-1)
+        assert bool(allowed[draws].all()), (top_k, top_p, int((~allowed[draws]).sum()))
+        probs = filter_logits(logits.float(), top_k, top_p).softmax(-1)[0]
+        top = probs.argmax()
+        emp = (draws == top).float().mean().item()
+        assert abs(emp - probs[top].item()) < 0.05, (top_k, top_p, emp, probs[top].item())

@@ -126,3 +126,29 @@ def test_kv_cache_generation_equals_full_prefix_generation():
                 assert torch.allclose(inc, full, atol=1e-5), (type(m).__name__, step, (inc - full).abs().max().item())
                 ids = torch.cat([ids, full.argmax(-1, keepdim=True)], dim=1)
         assert len(cache.k) == 2 and cache.k[0].shape[1] == prompt.shape[1] + 2
+
+
+def test_sampling_filter_and_embedding_reference_paths():
+    """CPU statements of the LightSeq kernels: nucleus / top-k filtering keeps the right set, sampled tokens come from it,
+    the embedding op zeroes padding rows and int8 quantisation round-trips within one step."""
+    from oslo_b200.lightseq import filter_logits, ls_dequantize_int8, ls_embedding, ls_quantize_int8, sample_tokens
+
+    torch.manual_seed(0)
+    logits = torch.tensor([[4.0, 3.0, 2.0, 1.0, 0.0, -1.0]])
+    kept = torch.isfinite(filter_logits(logits, top_k=3, top_p=1.0))[0].tolist()
+    assert kept == [True, True, True, False, False, False]
+    probs = logits.softmax(-1)[0]
+    kept_p = torch.isfinite(filter_logits(logits, top_k=0, top_p=float(probs[0] + probs[1] / 2)))[0].tolist()
+    assert kept_p == [True, True, False, False, False, False]  # the smallest prefix whose mass reaches top_p
+    draws = torch.cat([sample_tokens(logits.repeat(64, 1), top_k=2) for _ in range(4)])
+    assert set(draws.view(-1).tolist()) <= {0, 1} and len(set(draws.view(-1).tolist())) == 2
+    emb = torch.randn(10, 16)
+    pos = torch.randn(8, 16)
+    ids = torch.tensor([[1, 2, 0, 3]])
+    out = ls_embedding(ids, emb, pos, step=2, padding_idx=0, scale=4.0)
+    assert torch.allclose(out[0, 0], emb[1] * 4.0 + pos[2]) and float(out[0, 2].abs().sum()) == 0.0
+    x = torch.randn(1000) * 2
+    q, mask = ls_quantize_int8(x, 3.0, return_mask=True)
+    back = ls_dequantize_int8(q, 3.0)
+    assert q.dtype == torch.int8 and (back - x.clamp(-3, 3)).abs().max() <= 3.0 / 127 / 2 + 1e-6
+    assert torch.equal(mask, x.abs() > 3.0)
