@@ -10,7 +10,7 @@
 //
 // Roles per CTA (192 threads, persistent, one cluster per SM pair):
 //   warp 0      TMA producer for this CTA's halves (cp.async.bulk.tensor with .cta_group::2: the bytes are counted on
-//               the LEADER's "full" barrier; no multicast qualifier anywhere);
+//               the LEADER's "full" barrier, which only the leader arms; no multicast qualifier anywhere);
 //   warp 1      leader CTA only: one elected thread issues the MMAs for the pair and commits them to the "stage empty"
 //               and "accumulator full" barriers of BOTH CTAs (tcgen05.commit ... multicast::cluster);
 //               in both CTAs this warp allocates / frees tensor memory (cta_group::2 needs the same warp of both);
@@ -51,10 +51,6 @@ OSLO_DEVINL uint32_t mapa_u32(const void* p, uint32_t rank) {
 }
 OSLO_DEVINL void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-OSLO_DEVINL void mbar_arrive_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr), "r"(bytes)
-               : "memory");
 }
 // Tiled load into THIS CTA's shared memory whose bytes are counted on a barrier that may live in the partner CTA.
 OSLO_DEVINL void tma_load_4d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y, int z, int w) {
@@ -129,7 +125,7 @@ gemm2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < k2Stages; ++s) {
-      mbar_init(&full_bar[s], 2);   // one arrive.expect_tx per CTA
+      mbar_init(&full_bar[s], 1);   // the leader arms it with the bytes of BOTH CTAs
       mbar_init(&empty_bar[s], 1);  // one commit arrival per use
     }
     for (int i = 0; i < 2; ++i) {
@@ -172,8 +168,12 @@ gemm2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
           uint8_t* sa = stage_base + stage * k2StageBytes;
           uint8_t* sb = sa + k2StageA;
-          const uint32_t bar = mapa_u32(&full_bar[stage], 0);  // the leader's barrier counts the pair's bytes
-          mbar_arrive_expect_tx_cluster(bar, k2StageBytes);
+          // The leader's barrier counts the pair's bytes: the leader arms it (a local arrive, no fence), the partner only
+          // issues loads that signal it.  The partner cannot be a phase ahead: it refills a stage only after the leader's
+          // MMAs have consumed it, i.e. after this barrier's previous phase completed.  (A remote arrive with release
+          // semantics here cost a cluster-scope memory barrier per k-block and halved the throughput.)
+          const uint32_t bar = mapa_u32(&full_bar[stage], 0);
+          if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * k2StageBytes);
           const int k0 = kb * kBlockK;
           if (A_MN) {
 #pragma unroll

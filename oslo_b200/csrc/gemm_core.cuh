@@ -237,7 +237,9 @@ OSLO_DEVINL void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
 }
 
 constexpr int kCopyPiece = 32768;  // bytes per bulk copy
-constexpr int kCopyDepth = 6;      // pieces in flight per copy CTA (6 x 32 KiB of shared memory)
+constexpr int kCopyDepth = 6;      // ring slots per copy CTA (6 x 32 KiB of shared memory)
+constexpr int kCopyAhead = 2;      // local loads run this many pieces ahead of the stores; the other ring slots hold
+                                   // pieces whose stores are still draining (several store groups in flight)
 
 // AG copy role: PUSH.  Reading a peer's memory is bound by the NVLink round trip (a few KB in flight per SM: measured
 // ~6 GB/s per copy CTA), writing to it is not: writes are posted.  So every rank pushes ITS OWN shard into the gathered
@@ -268,16 +270,18 @@ static __device__ __noinline__ void ag_copy_role(const GemmParams& p, const Fuse
     off = static_cast<long long>(c) * chunk_bytes + in_chunk;
     last_of_chunk = (g + fp.copy_ctas) / ppc != c;  // our next piece (if any) belongs to a later chunk
   };
-  for (long long n = 0; n < my_count + kCopyDepth - 1 && ok; ++n) {
+  for (long long n = 0; n < my_count + kCopyAhead && ok; ++n) {
     if (n < my_count) {
       long long off; uint32_t bytes; int c; bool last;
       locate(n, off, bytes, c, last);
-      if (n >= kCopyDepth) tma_store_wait_read<0>();  // the stores that last used this ring slot have drained it
+      // slot n % depth last held piece n - depth; the store groups committed since then are pieces n - depth + 1 ..
+      // n - 1 - ahead, so that many may still be pending when its own stores have finished reading the slot
+      if (n >= kCopyDepth) tma_store_wait_read<kCopyDepth - 1 - kCopyAhead>();
       uint64_t* bar = &bars[n % kCopyDepth];
       mbar_arrive_expect_tx(bar, bytes);
       bulk_load(ring + (n % kCopyDepth) * kCopyPiece, my_shard + off, bytes, bar);
     }
-    const long long m = n - (kCopyDepth - 1);
+    const long long m = n - kCopyAhead;
     if (m >= 0 && m < my_count) {
       long long off; uint32_t bytes; int c; bool last;
       locate(m, off, bytes, c, last);
