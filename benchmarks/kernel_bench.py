@@ -151,6 +151,17 @@ def bench_attention(a):
     fl = 4.0 * a.batch * a.heads * a.seq * a.seq * a.head_dim / 2  # causal
     ms = time_op(lambda: qkv_attention(qkv.detach(), a.heads, a.head_dim, "h3d", True), a.iters)
     report(f"attention_fwd B{a.batch} S{a.seq} H{a.heads}x{a.head_dim}", ms, flops=fl)
+    if a.seq % 256 == 0:
+        import math
+
+        from oslo_b200.ops.attention import flash_attention_forward
+
+        q5 = qkv.detach().view(a.batch, a.seq, a.heads, 3, a.head_dim)
+        q, k, v = q5[..., 0, :], q5[..., 1, :], q5[..., 2, :]
+        for pp in (False, True):
+            ms = time_op(lambda: flash_attention_forward(q, k, v, True, 1.0 / math.sqrt(a.head_dim), pingpong=pp), a.iters)
+            report(f"attention_fwd kernel only ({'one-pass ping-pong' if pp else 'two-pass'}) B{a.batch} S{a.seq} "
+                   f"H{a.heads}x{a.head_dim}", ms, flops=fl)
     out = qkv_attention(qkv, a.heads, a.head_dim, "h3d", True)
     g = torch.randn_like(out)
     ms = time_op(lambda: torch.autograd.grad(out, qkv, g, retain_graph=True), a.iters)

@@ -42,9 +42,22 @@ OSLO_DEVINL float gelu_tanh_grad(float x) {
   return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
 }
 
-// y = gelu(x + bias); bias broadcast over rows (may be null). n = rows * H, H % pack == 0.
+// activation selected at run time (uniform over the launch): 0 tanh-form GELU, 1 erf-form GELU, 2 ReLU
+OSLO_DEVINL float act_apply(float v, int act) {
+  if (act == 0) return gelu_tanh(v);
+  if (act == 1) return 0.5f * v * (1.0f + erff(v * 0.7071067811865476f));
+  return fmaxf(v, 0.f);
+}
+OSLO_DEVINL float act_grad(float v, int act) {
+  if (act == 0) return gelu_tanh_grad(v);
+  if (act == 1) return 0.5f * (1.0f + erff(v * 0.7071067811865476f)) + v * 0.3989422804014327f * __expf(-0.5f * v * v);
+  return v > 0.f ? 1.f : 0.f;
+}
+
+// y = act(x + bias); bias broadcast over rows (may be null). n = rows * H, H % pack == 0.
 template <typename T>
-__global__ void bias_gelu_fwd_kernel(const T* __restrict__ x, const T* __restrict__ bias, T* __restrict__ y, size_t n, int H) {
+__global__ void bias_gelu_fwd_kernel(const T* __restrict__ x, const T* __restrict__ bias, T* __restrict__ y, size_t n, int H,
+                                     int act) {
   constexpr int P = Pack<T>::N;
   const size_t nv = n / P;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nv; i += (size_t)gridDim.x * blockDim.x) {
@@ -54,16 +67,16 @@ __global__ void bias_gelu_fwd_kernel(const T* __restrict__ x, const T* __restric
 #pragma unroll
     for (int j = 0; j < P; ++j) {
       float v = to_f(a.v[j]) + (bias ? to_f(b.v[j]) : 0.f);
-      o.v[j] = from_f<T>(gelu_tanh(v));
+      o.v[j] = from_f<T>(act_apply(v, act));
     }
     st_pack(y + i * P, o);
   }
 }
 
-// dx = dy * gelu'(x + bias)
+// dx = dy * act'(x + bias)
 template <typename T>
 __global__ void bias_gelu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ bias,
-                                     T* __restrict__ dx, size_t n, int H) {
+                                     T* __restrict__ dx, size_t n, int H, int act) {
   constexpr int P = Pack<T>::N;
   const size_t nv = n / P;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nv; i += (size_t)gridDim.x * blockDim.x) {
@@ -73,7 +86,7 @@ __global__ void bias_gelu_bwd_kernel(const T* __restrict__ dy, const T* __restri
 #pragma unroll
     for (int j = 0; j < P; ++j) {
       float v = to_f(a.v[j]) + (bias ? to_f(b.v[j]) : 0.f);
-      o.v[j] = from_f<T>(to_f(g.v[j]) * gelu_tanh_grad(v));
+      o.v[j] = from_f<T>(to_f(g.v[j]) * act_grad(v, act));
     }
     st_pack(dx + i * P, o);
   }
@@ -343,32 +356,44 @@ static inline int grid_for(size_t work_items, int threads, int num_sms) {
 
 using namespace oslo;
 
-extern "C" int oslo_bias_gelu_forward(const void* x, const void* bias, void* y, long long n, int H, int dtype, int num_sms,
-                                      void* stream) {
+extern "C" int oslo_bias_act_forward(const void* x, const void* bias, void* y, long long n, int H, int dtype, int act,
+                                     int num_sms, void* stream) {
   if (n <= 0) return 0;
+  if (act < 0 || act > 2) return -3;
   cudaStream_t st = (cudaStream_t)stream;
   const int P = dtype == 0 ? 4 : 8;
   if (H % P || n % P) return -1;
   const int g = grid_for(n / P, 256, num_sms);
-  OSLO_BY_DTYPE((bias_gelu_fwd_kernel<float><<<g, 256, 0, st>>>((const float*)x, (const float*)bias, (float*)y, n, H)),
-                (bias_gelu_fwd_kernel<__half><<<g, 256, 0, st>>>((const __half*)x, (const __half*)bias, (__half*)y, n, H)),
+  OSLO_BY_DTYPE((bias_gelu_fwd_kernel<float><<<g, 256, 0, st>>>((const float*)x, (const float*)bias, (float*)y, n, H, act)),
+                (bias_gelu_fwd_kernel<__half><<<g, 256, 0, st>>>((const __half*)x, (const __half*)bias, (__half*)y, n, H, act)),
                 (bias_gelu_fwd_kernel<__nv_bfloat16><<<g, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)bias,
-                                                                        (__nv_bfloat16*)y, n, H)));
+                                                                        (__nv_bfloat16*)y, n, H, act)));
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int oslo_bias_act_backward(const void* dy, const void* x, const void* bias, void* dx, long long n, int H, int dtype,
+                                      int act, int num_sms, void* stream) {
+  if (n <= 0) return 0;
+  if (act < 0 || act > 2) return -3;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int P = dtype == 0 ? 4 : 8;
+  if (H % P || n % P) return -1;
+  const int g = grid_for(n / P, 256, num_sms);
+  OSLO_BY_DTYPE((bias_gelu_bwd_kernel<float><<<g, 256, 0, st>>>((const float*)dy, (const float*)x, (const float*)bias, (float*)dx, n, H, act)),
+                (bias_gelu_bwd_kernel<__half><<<g, 256, 0, st>>>((const __half*)dy, (const __half*)x, (const __half*)bias, (__half*)dx, n, H, act)),
+                (bias_gelu_bwd_kernel<__nv_bfloat16><<<g, 256, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                                                        (const __nv_bfloat16*)bias, (__nv_bfloat16*)dx, n, H, act)));
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int oslo_bias_gelu_forward(const void* x, const void* bias, void* y, long long n, int H, int dtype, int num_sms,
+                                      void* stream) {
+  return oslo_bias_act_forward(x, bias, y, n, H, dtype, 0, num_sms, stream);
 }
 
 extern "C" int oslo_bias_gelu_backward(const void* dy, const void* x, const void* bias, void* dx, long long n, int H, int dtype,
                                        int num_sms, void* stream) {
-  if (n <= 0) return 0;
-  cudaStream_t st = (cudaStream_t)stream;
-  const int P = dtype == 0 ? 4 : 8;
-  if (H % P || n % P) return -1;
-  const int g = grid_for(n / P, 256, num_sms);
-  OSLO_BY_DTYPE((bias_gelu_bwd_kernel<float><<<g, 256, 0, st>>>((const float*)dy, (const float*)x, (const float*)bias, (float*)dx, n, H)),
-                (bias_gelu_bwd_kernel<__half><<<g, 256, 0, st>>>((const __half*)dy, (const __half*)x, (const __half*)bias, (__half*)dx, n, H)),
-                (bias_gelu_bwd_kernel<__nv_bfloat16><<<g, 256, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
-                                                                        (const __nv_bfloat16*)bias, (__nv_bfloat16*)dx, n, H)));
-  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  return oslo_bias_act_backward(dy, x, bias, dx, n, H, dtype, 0, num_sms, stream);
 }
 
 extern "C" int oslo_swiglu_forward(const void* gate, const void* up, void* y, long long rows, int F, long long ld_in, int dtype,

@@ -119,3 +119,127 @@ class MoEGPTConfig(GPT2Config):
         self.num_experts, self.moe_every, self.top_k = num_experts, moe_every, top_k
         self.capacity_factor, self.aux_loss_coef = capacity_factor, aux_loss_coef
         super().__init__(**kwargs)
+
+
+def _defaults(self, given: Dict[str, Any], **defaults):
+    """Set every default as an attribute, overridden by what the caller gave; the rest of ``given`` is returned."""
+    for k, v in defaults.items():
+        setattr(self, k, given.pop(k, v))
+    return given
+
+
+class BertConfig(PretrainedConfig):
+    model_type = "bert"
+
+    def __init__(self, **kwargs):
+        kwargs = _defaults(self, kwargs, vocab_size=30522, hidden_size=768, num_hidden_layers=12, num_attention_heads=12,
+                           intermediate_size=3072, hidden_act="gelu", hidden_dropout_prob=0.1,
+                           attention_probs_dropout_prob=0.1, max_position_embeddings=512, type_vocab_size=2,
+                           initializer_range=0.02, layer_norm_eps=1e-12, pad_token_id=0, num_labels=2,
+                           classifier_dropout=None)
+        super().__init__(**kwargs)
+
+
+class RobertaConfig(BertConfig):
+    model_type = "roberta"
+
+    def __init__(self, **kwargs):
+        kwargs.setdefault("vocab_size", 50265)
+        kwargs.setdefault("max_position_embeddings", 514)
+        kwargs.setdefault("type_vocab_size", 1)
+        kwargs.setdefault("pad_token_id", 1)
+        super().__init__(**kwargs)
+
+
+class ElectraConfig(BertConfig):
+    model_type = "electra"
+
+    def __init__(self, **kwargs):
+        kwargs = _defaults(self, kwargs, embedding_size=128)
+        kwargs.setdefault("hidden_size", 256)
+        kwargs.setdefault("num_attention_heads", 4)
+        kwargs.setdefault("intermediate_size", 1024)
+        super().__init__(**kwargs)
+
+
+class AlbertConfig(PretrainedConfig):
+    model_type = "albert"
+
+    def __init__(self, **kwargs):
+        kwargs = _defaults(self, kwargs, vocab_size=30000, embedding_size=128, hidden_size=4096, num_hidden_layers=12,
+                           num_hidden_groups=1, num_attention_heads=64, intermediate_size=16384, inner_group_num=1,
+                           hidden_act="gelu_new", hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0,
+                           max_position_embeddings=512, type_vocab_size=2, initializer_range=0.02, layer_norm_eps=1e-12,
+                           classifier_dropout_prob=0.1, pad_token_id=0, num_labels=2)
+        super().__init__(**kwargs)
+
+
+class DistilBertConfig(PretrainedConfig):
+    model_type = "distilbert"
+
+    def __init__(self, **kwargs):
+        kwargs = _defaults(self, kwargs, vocab_size=30522, max_position_embeddings=512, n_layers=6, n_heads=12, dim=768,
+                           hidden_dim=3072, dropout=0.1, attention_dropout=0.1, activation="gelu", initializer_range=0.02,
+                           qa_dropout=0.1, seq_classif_dropout=0.2, pad_token_id=0, num_labels=2)
+        super().__init__(**kwargs)
+
+    hidden_size = property(lambda self: self.dim)
+    num_hidden_layers = property(lambda self: self.n_layers)
+    num_attention_heads = property(lambda self: self.n_heads)
+
+
+class BartConfig(PretrainedConfig):
+    model_type = "bart"
+
+    def __init__(self, **kwargs):
+        kwargs = _defaults(self, kwargs, vocab_size=50265, max_position_embeddings=1024, encoder_layers=12,
+                           encoder_ffn_dim=4096, encoder_attention_heads=16, decoder_layers=12, decoder_ffn_dim=4096,
+                           decoder_attention_heads=16, activation_function="gelu", d_model=1024, dropout=0.1,
+                           attention_dropout=0.0, activation_dropout=0.0, init_std=0.02, classifier_dropout=0.0,
+                           scale_embedding=False, pad_token_id=1, bos_token_id=0, eos_token_id=2,
+                           decoder_start_token_id=2, num_labels=3)
+        super().__init__(**kwargs)
+        self.initializer_range = self.init_std
+
+    hidden_size = property(lambda self: self.d_model)
+    num_hidden_layers = property(lambda self: self.encoder_layers)
+    num_attention_heads = property(lambda self: self.encoder_attention_heads)
+
+
+class MBartConfig(BartConfig):
+    model_type = "mbart"
+
+    def __init__(self, **kwargs):
+        kwargs.setdefault("vocab_size", 50265)
+        super().__init__(**kwargs)
+
+
+class T5Config(PretrainedConfig):
+    model_type = "t5"
+
+    def __init__(self, **kwargs):
+        kwargs = _defaults(self, kwargs, vocab_size=32128, d_model=512, d_kv=64, d_ff=2048, num_layers=6,
+                           num_decoder_layers=None, num_heads=8, relative_attention_num_buckets=32,
+                           relative_attention_max_distance=128, dropout_rate=0.1, layer_norm_epsilon=1e-6,
+                           initializer_factor=1.0, feed_forward_proj="relu", pad_token_id=0, eos_token_id=1,
+                           decoder_start_token_id=0)
+        if self.num_decoder_layers is None:
+            self.num_decoder_layers = self.num_layers
+        super().__init__(**kwargs)
+
+    hidden_size = property(lambda self: self.d_model)
+    num_hidden_layers = property(lambda self: self.num_layers)
+    num_attention_heads = property(lambda self: self.num_heads)
+    is_gated_act = property(lambda self: self.feed_forward_proj.startswith("gated-"))
+    # "gated-gelu" means the tanh form of GELU (as in the released mT5 / T5 v1.1 checkpoints)
+    dense_act_fn = property(lambda self: "gelu_new" if self.feed_forward_proj == "gated-gelu" else self.feed_forward_proj.split("-")[-1])
+
+
+class MT5Config(T5Config):
+    model_type = "mt5"
+
+    def __init__(self, **kwargs):
+        kwargs.setdefault("vocab_size", 250112)
+        kwargs.setdefault("feed_forward_proj", "gated-gelu")
+        kwargs.setdefault("tie_word_embeddings", False)
+        super().__init__(**kwargs)

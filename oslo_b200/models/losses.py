@@ -29,8 +29,13 @@ def shift_labels(labels: torch.Tensor, ignore_index: int = -100) -> torch.Tensor
 
 
 def causal_lm_loss(model, logits, labels, ignore_index: int = -100) -> LossResult:
+    return token_lm_loss(model, logits, shift_labels(labels, ignore_index), ignore_index)
+
+
+def token_lm_loss(model, logits, targets, ignore_index: int = -100) -> LossResult:
+    """Cross-entropy of ``logits[..., t, :]`` against ``targets[..., t]`` (masked-LM and sequence-to-sequence heads use it
+    directly; the causal heads shift the labels first)."""
     pc = getattr(model, "parallel_context", None)
-    targets = shift_labels(labels, ignore_index)
     sharded_vocab = logits.shape[-1] != getattr(model, "padded_vocab_size", model.config.vocab_size) \
         and logits.shape[-1] != model.config.vocab_size
     mode = pc.tensor_parallel_mode if pc is not None else None

@@ -25,6 +25,40 @@ class CausalLMOutput:
         return tuple(v for v in (self.loss, self.logits) if v is not None)[k]
 
 
+class ModelOutput(dict):
+    """Named outputs with attribute, key and index access (index skips entries that are ``None``)."""
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+
+    def __getattr__(self, k):
+        try:
+            return self[k]
+        except KeyError:
+            raise AttributeError(k)
+
+    def __setattr__(self, k, v):
+        self[k] = v
+
+    def __getitem__(self, k):
+        if isinstance(k, str):
+            return dict.__getitem__(self, k)
+        return tuple(v for v in self.values() if v is not None)[k]
+
+    def to_tuple(self):
+        return tuple(v for v in self.values() if v is not None)
+
+
+def additive_mask(attention_mask, dtype=torch.float32, tgt_len=None):
+    """``[b, s]`` mask of ones (keep) and zeros (padding) -> additive ``[b, 1, tgt or 1, s]`` mask; ``None`` stays."""
+    if attention_mask is None:
+        return None
+    if attention_mask.dim() == 4:
+        return attention_mask
+    m = (1.0 - attention_mask[:, None, None, :].to(dtype)) * torch.finfo(dtype).min
+    return m if tgt_len is None else m.expand(-1, 1, tgt_len, -1)
+
+
 class PreTrainedModel(nn.Module, OsloModel):
     config_class = None
     base_model_prefix = ""

@@ -37,10 +37,14 @@ def _masked_lookup(ids, weight, start, end, padding_idx=None):
 
 
 class Embedding1D(nn.Embedding):
-    """Hidden dim split over TP; output gathered on the last dim."""
+    """Hidden dim split over TP; output gathered on the last dim unless ``gather_output`` is off (a per-head table such as
+    T5's relative attention bias, whose consumer works on the local heads)."""
 
-    def __init__(self, num_embeddings, embedding_dim, dtype=None, parallel_context=None, device=None, **kw):
+    gather_output = True
+
+    def __init__(self, num_embeddings, embedding_dim, dtype=None, parallel_context=None, device=None, gather_output=True, **kw):
         self.parallel_context = parallel_context
+        self.gather_output = gather_output
         self.world_size = parallel_context.get_world_size(ParallelMode.TENSOR_1D)
         assert embedding_dim % self.world_size == 0
         super().__init__(num_embeddings, embedding_dim // self.world_size, dtype=dtype, device=device, **kw)
@@ -49,7 +53,7 @@ class Embedding1D(nn.Embedding):
         from oslo_b200.parallel.tensor_parallel import _ops_1d as ops
 
         out = F.embedding(input, self.weight, self.padding_idx)
-        return ops.gather_tensor_1d(out, -1, self.parallel_context)
+        return ops.gather_tensor_1d(out, -1, self.parallel_context) if self.gather_output else out
 
 
 class VocabParallelEmbedding1D(nn.Embedding):

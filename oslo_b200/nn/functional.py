@@ -3,6 +3,7 @@
 Parity: oslo/torch/nn/modules/functional.py:23-298.
 """
 from oslo_b200.ops.activation import (  # noqa: F401
+    bias_act,
     bias_dropout_add,
     bias_gelu,
     fused_bias_dropout,

@@ -97,13 +97,15 @@ class ColLinear1D(Linear):
                 out = _linear(x, self._w, self.bias)
             else:
                 out = _linear(x, self._w)
-        if self.bias is not None and self.skip_bias_add:
-            return out, self.bias
         if self.gather_output:
             out = ops.gather_tensor_1d(out, -1, self.parallel_context)
             if hasattr(self, "orig_num_classes"):
                 out = out[..., : self.orig_num_classes]
             out = out.contiguous()
+        if self.bias is not None and self.skip_bias_add:
+            # the caller adds the bias to what it got: the full width when the output was gathered
+            bias = ops.gather_tensor_1d(self.bias, -1, self.parallel_context) if self.gather_output else self.bias
+            return out, bias
         return out
 
 

@@ -47,18 +47,29 @@ def colsum(x2: torch.Tensor) -> torch.Tensor:
     return out
 
 
-class _BiasGeluFn(torch.autograd.Function):
+_ACTS = {"gelu_new": 0, "gelu_tanh": 0, "gelu_pytorch_tanh": 0, "gelu_fast": 0, "gelu": 1, "gelu_erf": 1, "relu": 2}
+
+
+def act_reference(x, act: str):
+    code = _ACTS[act]
+    if code == 0:
+        return gelu_tanh_reference(x)
+    return F.gelu(x) if code == 1 else F.relu(x)
+
+
+class _BiasActFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, bias):
+    def forward(ctx, x, bias, act):
         xc = x.contiguous()
         y = torch.empty_like(xc)
         h = xc.shape[-1]
-        rc = _lib.cuda_lib().oslo_bias_gelu_forward(
+        rc = _lib.cuda_lib().oslo_bias_act_forward(
             _lib.ptr(xc), _lib.ptr(bias), _lib.ptr(y), ctypes.c_longlong(xc.numel()), ctypes.c_int(h),
-            ctypes.c_int(_DT[xc.dtype]), ctypes.c_int(_lib.num_sms()), _lib.stream_ptr())
+            ctypes.c_int(_DT[xc.dtype]), ctypes.c_int(act), ctypes.c_int(_lib.num_sms()), _lib.stream_ptr())
         if rc:
-            raise RuntimeError(f"oslo_bias_gelu_forward failed ({rc})")
+            raise RuntimeError(f"oslo_bias_act_forward failed ({rc})")
         ctx.save_for_backward(xc, bias)
+        ctx.act = act
         return y
 
     @staticmethod
@@ -67,22 +78,29 @@ class _BiasGeluFn(torch.autograd.Function):
         gy = gy.contiguous()
         dx = torch.empty_like(xc)
         h = xc.shape[-1]
-        rc = _lib.cuda_lib().oslo_bias_gelu_backward(
+        rc = _lib.cuda_lib().oslo_bias_act_backward(
             _lib.ptr(gy), _lib.ptr(xc), _lib.ptr(bias), _lib.ptr(dx), ctypes.c_longlong(xc.numel()), ctypes.c_int(h),
-            ctypes.c_int(_DT[xc.dtype]), ctypes.c_int(_lib.num_sms()), _lib.stream_ptr())
+            ctypes.c_int(_DT[xc.dtype]), ctypes.c_int(ctx.act), ctypes.c_int(_lib.num_sms()), _lib.stream_ptr())
         if rc:
-            raise RuntimeError(f"oslo_bias_gelu_backward failed ({rc})")
+            raise RuntimeError(f"oslo_bias_act_backward failed ({rc})")
         db = None
         if bias is not None and ctx.needs_input_grad[1]:
             db = colsum(dx.view(-1, h))
-        return dx, db
+        return dx, db, None
+
+
+def bias_act(x, bias=None, act: str = "gelu_new"):
+    """``act(x + bias)`` in one pass; ``act`` is ``gelu_new`` (tanh form), ``gelu`` (erf form) or ``relu``."""
+    if act not in _ACTS:
+        raise ValueError(f"unsupported activation {act!r}; one of {sorted(_ACTS)}")
+    if _cuda_ok(x) and (bias is None or bias.dtype == x.dtype):
+        return _BiasActFn.apply(x, bias, _ACTS[act])
+    return act_reference(x if bias is None else x + bias, act)
 
 
 def bias_gelu(x, bias=None):
     """``gelu_tanh(x + bias)``."""
-    if _cuda_ok(x) and (bias is None or bias.dtype == x.dtype):
-        return _BiasGeluFn.apply(x, bias)
-    return gelu_tanh_reference(x if bias is None else x + bias)
+    return bias_act(x, bias, "gelu_new")
 
 
 fused_bias_gelu = lambda bias, y: bias_gelu(y, bias)  # argument order of the reference's fused_bias_gelu(bias, y)

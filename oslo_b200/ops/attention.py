@@ -181,15 +181,33 @@ def flash_supported(q, k, v) -> bool:
             and q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1)
 
 
-def flash_attention_forward(q, k, v, causal: bool, scale: float):
-    """Fused attention forward (``csrc/attention_sm100a.cu``): returns ``(out [b, s, heads*hd], lse [b, heads, s])``.
-    q, k, v are ``[b, s, heads, hd]`` views (any token / head / batch strides, unit stride on ``hd``)."""
+#: one-pass forward with two query tiles per CTA taking turns on the tensor cores (``csrc/attention_pingpong_sm100a.cu``)
+#: for sequence lengths that are multiples of 256; OSLO_B200_ATTN_PINGPONG=0 keeps the two-pass kernel everywhere
+PINGPONG = __import__("os").environ.get("OSLO_B200_ATTN_PINGPONG", "0") == "1"
+
+
+def flash_attention_forward(q, k, v, causal: bool, scale: float, pingpong=None):
+    """Fused attention forward: returns ``(out [b, s, heads*hd], lse [b, heads, s])``.
+    q, k, v are ``[b, s, heads, hd]`` views (any token / head / batch strides, unit stride on ``hd``).  ``pingpong`` picks the
+    one-pass kernel (``csrc/attention_pingpong_sm100a.cu``, needs ``s % 256 == 0``) over the two-pass kernel
+    (``csrc/attention_sm100a.cu``); ``None`` follows :data:`PINGPONG`."""
     import ctypes
 
     b, s, nh, hd = q.shape
     out = torch.empty(b, s, nh, hd, dtype=q.dtype, device=q.device)
     lse = torch.empty(b, nh, s, dtype=torch.float32, device=q.device)
     st = lambda t: (ctypes.c_longlong(t.stride(1)), ctypes.c_longlong(t.stride(2)), ctypes.c_longlong(t.stride(0)))
+    if pingpong is None:
+        pingpong = PINGPONG
+    if pingpong and s % 256 == 0:
+        rc = _lib.cuda_lib().oslo_attention_forward_pingpong(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse), ctypes.c_int(b), ctypes.c_int(s),
+            ctypes.c_int(nh), ctypes.c_int(hd), *st(q), *st(k), *st(v), *st(out), ctypes.c_float(scale),
+            ctypes.c_int(1 if causal else 0), ctypes.c_int(1 if q.dtype == torch.bfloat16 else 0),
+            _lib.ptr(_lib.status_word(q.device)), _lib.stream_ptr())
+        if rc:
+            raise RuntimeError(f"oslo_attention_forward_pingpong failed ({rc})")
+        return out.view(b, s, nh * hd), lse
     rc = _lib.cuda_lib().oslo_attention_forward(
         _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse), ctypes.c_int(b), ctypes.c_int(s), ctypes.c_int(nh),
         ctypes.c_int(hd), *st(q), *st(k), *st(v), *st(out), ctypes.c_float(scale), ctypes.c_int(1 if causal else 0),

@@ -21,8 +21,9 @@ from . import _lib
 
 _EPI = {None: 0, "none": 0, "bias": 1, "gelu": 2}
 
-#: use the two-CTA kernel automatically for large products (set from the environment: OSLO_B200_GEMM_2CTA=0 / 1)
-AUTO_TWO_CTA = __import__("os").environ.get("OSLO_B200_GEMM_2CTA", "0") == "1"
+#: use the two-CTA kernel (256 x 256 tile on a CTA pair) automatically for large products; OSLO_B200_GEMM_2CTA=0 turns it
+#: off.  Measured against the one-CTA kernel it is 7 - 12 % faster from K = 2048 up and slower at K = 256.
+AUTO_TWO_CTA = __import__("os").environ.get("OSLO_B200_GEMM_2CTA", "1") == "1"
 
 
 def _operand(t: torch.Tensor):
@@ -102,7 +103,7 @@ def gemm(
     if two_cta is None:
         pairs = _lib.num_sms() // 2
         tiles = b_in * b_out * ((M + 255) // 256) * ((N + 255) // 256)
-        two_cta = AUTO_TWO_CTA and causal == 0 and block_n == 0 and M >= 256 and N >= 256 and tiles >= pairs
+        two_cta = AUTO_TWO_CTA and causal == 0 and block_n == 0 and M >= 256 and N >= 256 and K >= 1024 and tiles >= pairs
     if two_cta:
         rc = lib.oslo_gemm_tcgen05_2cta(
             _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(aux),

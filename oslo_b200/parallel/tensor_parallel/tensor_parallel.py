@@ -267,7 +267,16 @@ class TensorParallel(ParallelWrapper):
             if head is not None and child is head:
                 continue  # after the loop (needs the tied weight)
             if not _is_linear_like(child):
-                if isinstance(child, nn.Embedding) and mapping.is_other(module, name) and sp:
+                if isinstance(child, nn.Embedding) and mapping.is_other(module, name) and tp > 1 \
+                        and not mapping.is_gather_output(module, name) and child.embedding_dim % tp == 0:
+                    # a table with one column per head (T5's relative attention bias): every rank keeps its heads' columns
+                    w = self._shard_param(child.weight, ShardSpec([Split(M1, 1)]))
+                    new = _bare(onn.Embedding1D, num_embeddings=w.shape[0], embedding_dim=w.shape[1], padding_idx=None,
+                                max_norm=None, norm_type=2.0, scale_grad_by_freq=False, sparse=False, parallel_context=pc,
+                                world_size=tp, gather_output=False)
+                    new.weight = w
+                    _set_child(module, name, new)
+                elif isinstance(child, nn.Embedding) and mapping.is_other(module, name) and sp:
                     self._mark_sp(child)
                 elif child.__class__.__name__ in _NORM_NAMES + _RMS_NAMES:
                     if sp:
@@ -282,7 +291,7 @@ class TensorParallel(ParallelWrapper):
                 w = self._shard_param(child.weight, ShardSpec([Split(M1, out_dim, parts)]))
                 b = self._shard_param(child.bias, ShardSpec([Split(M1, 0, parts)])) if has_bias else None
                 new = _bare(onn.ColLinear1D, in_features=w.shape[in_dim], out_features=w.shape[out_dim],
-                            skip_bias_add=skip, gather_output=mapping.is_gather_output(module, name) and not is_oslo_model,
+                            skip_bias_add=skip, gather_output=mapping.is_gather_output(module, name),
                             parallel_context=pc, sequence_parallel=sp, world_size=tp, reversed=conv,
                             sequence_parallel_state=self.sp_state)
                 new.weight, new.bias = w, b

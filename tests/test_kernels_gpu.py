@@ -412,6 +412,37 @@ def test_flash_attention_forward(causal, hd):
     assert _rel(lse, torch.logsumexp(scores, dim=-1)) < 1e-3
 
 
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("hd,dtype", [(128, torch.bfloat16), (64, torch.bfloat16), (128, torch.float16)])
+def test_flash_attention_forward_pingpong(causal, hd, dtype):
+    """The one-pass forward (two query tiles per CTA, probabilities through tensor memory, lazy rescale of the output)
+    against fp32: output and log-sum-exp, at a length with several key tiles per query block and scores large enough
+    that the running maximum grows by more than the rescale threshold after the first tile."""
+    from oslo_b200.ops.attention import attention_reference, flash_attention_forward
+
+    torch.manual_seed(61)
+    b, s, nh = 2, 1024, 3
+    qkv = (torch.randn(b, s, nh, 3, hd, device=DEV) * 1.5).to(dtype)
+    q, k, v = qkv[..., 0, :], qkv[..., 1, :], qkv[..., 2, :]
+    scale = 1.0 / math.sqrt(hd)
+    out, lse = flash_attention_forward(q, k, v, causal, scale, pingpong=True)
+    torch.cuda.synchronize()
+    from oslo_b200.ops import _lib
+
+    _lib.check_status()
+    ref = attention_reference(q.float(), k.float(), v.float(), causal=causal, scale=scale)
+    frac, worst = _close(out, ref, rtol=2e-2, atol=0.02)
+    assert frac == 0.0, ("out", frac, worst)
+    scores = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) * scale
+    if causal:
+        scores = scores.masked_fill(~torch.ones(s, s, dtype=torch.bool, device=DEV).tril(), float("-inf"))
+    assert (lse - torch.logsumexp(scores, dim=-1)).abs().max().item() < 2e-2
+    # the two kernels agree with each other as well
+    out2, lse2 = flash_attention_forward(q, k, v, causal, scale, pingpong=False)
+    frac, worst = _close(out, out2, rtol=2e-2, atol=0.02)
+    assert frac == 0.0, ("vs two-pass", frac, worst)
+
+
 def _close(a, b, rtol, atol):
     """Per-element check ``|a - b| <= atol + rtol * |b|`` (a single large element cannot hide errors elsewhere);
     returns the fraction of elements outside the bound and the worst excess, for the assertion message."""
@@ -571,9 +602,10 @@ def test_lightseq_kernels_match_torch_paths():
     want = torch.zeros(vocab, hid, device=DEV)
     want.index_add_(0, ids.view(-1), (g.float() * 16.0).view(-1, hid) * (ids.view(-1, 1) != 0))
     assert _rel(emb.grad, want) < 2e-2
-    # dropout: the kept pattern of the forward output is the mask that backward must recompute
+    # dropout: the kept pattern of the forward output is the mask that backward must recompute (zero positional table, so
+    # that an output is zero only where it was dropped and never because a word and a position value cancel exactly)
     emb.grad = None
-    out = ls_embedding(ids, emb, pos, step=0, padding_idx=0, scale=1.0, p=0.3, training=True, seed=7)
+    out = ls_embedding(ids, emb, torch.zeros_like(pos), step=0, padding_idx=0, scale=1.0, p=0.3, training=True, seed=7)
     kept = out.detach() != 0
     frac = kept[ids != 0].float().mean().item()
     assert 0.6 < frac < 0.8, frac
