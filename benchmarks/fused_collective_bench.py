@@ -45,6 +45,7 @@ def main():
     ap.add_argument("--ffn", type=int, default=8192)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--copy-ctas", type=int, default=None)
+    ap.add_argument("--no-multimem", action="store_true", help="plain peer stores even where NVSwitch multicast is available")
     args = ap.parse_args()
 
     from oslo_b200 import ParallelContext, ParallelMode
@@ -59,6 +60,7 @@ def main():
     group = pc.get_group(ParallelMode.TENSOR_1D)
     T, H, F = args.tokens, args.hidden, args.ffn
     kw = {} if args.copy_ctas is None else {"copy_ctas": args.copy_ctas}
+    kw["multimem"] = not args.no_multimem
     assert symm.enable(pc, ParallelMode.TENSOR_1D, max_tokens=T, max_features=max(H, F // world, 3 * H // world), **kw)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
     tl = T // world
@@ -147,6 +149,10 @@ def main():
         _lib.check_status()
         rows.append((name, K, N, fused, nccl, alone, roof_ms, roof_ms / fused))
     if rank == 0:
+        ws = fc.runtime().ws
+        print(f"transport: {'NVSwitch multicast (multimem.st / multimem.ld_reduce)' if ws.mc_base else 'peer stores'}"
+              + ("" if ws.mc_base or args.no_multimem else f" (multicast not available: {symm._multicast_alloc.last_error})")
+              + f", {ws.copy_ctas} copy / reduce CTAs")
         print(f"tp = {world}, tokens = {T}, hidden = {H}, ffn = {F}; bf16; roofline = max(FLOPs / {peak:.0f} TFLOP/s ({src}), "
               f"NVLink bytes / {LINK_GBS:.0f} GB/s)")
         print("| op | K | N | fused ms | NCCL + GEMM ms | GEMM alone ms | roofline ms | fused / roofline |")

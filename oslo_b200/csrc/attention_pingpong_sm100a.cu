@@ -55,7 +55,7 @@ struct AttnPPCfg {
 };
 
 template <int HD>
-__global__ void __maxnreg__(200)
+__global__ void __maxnreg__(192)
 attention_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
                               const AttnPPParams p) {

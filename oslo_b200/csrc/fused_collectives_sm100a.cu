@@ -39,7 +39,9 @@ static int pick_block_n(int M, int N, int ctas, int max_bn) {
 extern "C" int oslo_ag_gemm(const void* x_shard, void* const* peer_xfull, const void* B, void* C, const void* bias, int T, int N,
                             int K, long long ldb, int b_mn, int is_bf16, int tp, int rank, int epoch,
                             void* const* peer_chunk_flag, int* chunk_arrive, int copy_ctas, int num_sms, int* status,
-                            void* stream_ptr, const int* epoch_ptr) {
+                            void* stream_ptr, const int* epoch_ptr, void* mc_xfull) {
+  // mc_xfull: the same gathered buffer through an NVSwitch multicast mapping over the group (or null): the copy CTAs then
+  // store each piece of the shard once, to that address, instead of once per peer.
   if (tp > kMaxRanks || tp < 1 || T % tp) return -1;
   const int Tl = T / tp;
   if (Tl % kBlockM || N % 8 || K % 8 || ldb % 8 || (reinterpret_cast<uintptr_t>(x_shard) & 15)) return -5;
@@ -72,6 +74,7 @@ extern "C" int oslo_ag_gemm(const void* x_shard, void* const* peer_xfull, const 
   fp.peer_in[rank] = x_shard;
   void* x_full = peer_xfull[rank];
   fp.x_full = x_full;
+  fp.mc_xfull = mc_xfull;
   fp.chunk_flag = static_cast<int*>(peer_chunk_flag[rank]); fp.chunk_arrive = chunk_arrive; fp.status = status; fp.epoch_ptr = epoch_ptr;
   CUtensorMap ta, tb, tc, taux;
   int rc = make_map(&ta, x_full, is_bf16, K, T, 1, 1, K, 0, 0, kBlockK, kBlockM);
@@ -101,7 +104,10 @@ extern "C" int oslo_gemm_rs(const void* A, long long lda, const void* B, long lo
                             int T, int N, int K, int is_bf16, int tp, int rank, int epoch, void* const* peer_partial,
                             void* const* peer_rs_flag, int* tile_done, int reduce_ctas, int num_sms, int* status,
                             void* stream_ptr, unsigned long long* debug_times, const int* epoch_ptr, const void* addend,
-                            int along_n) {
+                            int along_n, const void* mc_partial) {
+  // mc_partial: this call's partial buffer through an NVSwitch multicast mapping over the group (or null).  With it (row
+  // scatter only) every rank stores its partial tiles into its OWN buffer and `reduce_ctas` CTAs of the owner read the
+  // sums with multimem.ld_reduce; without it partial tiles are stored into the owner's slots and its own tiles fold them.
   // along_n = 0: out[T/tp, N], the ROWS of the product are scattered (1-D sequence parallelism, 3-D);
   // along_n = 1: out[T, N/tp], the COLUMNS are scattered (2-D / 2.5-D SUMMA: every rank keeps its tokens).
   if (tp > kMaxRanks || tp < 1) return -1;
@@ -112,8 +118,14 @@ extern "C" int oslo_gemm_rs(const void* A, long long lda, const void* B, long lo
   if (addend && (reinterpret_cast<uintptr_t>(addend) & 15)) return -5;
   if (along_n && bias) return -5;  // the owner-side bias is indexed by global column: add it outside in this layout
   bind_context_to_thread();
-  reduce_ctas = 0;  // the reduction is folded into the epilogue of the tiles of our own block
-  const int gemm_ctas_max = num_sms;
+  if (along_n) mc_partial = nullptr;
+  if (mc_partial) {
+    if (reduce_ctas < 1) reduce_ctas = 1;
+    if (reduce_ctas > num_sms / 2) reduce_ctas = num_sms / 2;
+  } else {
+    reduce_ctas = 0;  // the reduction is folded into the epilogue of the tiles of our own block
+  }
+  const int gemm_ctas_max = num_sms - reduce_ctas;
   int block_n = pick_block_n(T, N, gemm_ctas_max, 256);
   if (along_n) {
     // a tile must not straddle two owners
@@ -150,6 +162,7 @@ extern "C" int oslo_gemm_rs(const void* A, long long lda, const void* B, long lo
   }
   fp.rs_flag = static_cast<int*>(peer_rs_flag[rank]);
   fp.tile_done = tile_done; fp.rs_out = out; fp.rs_bias = bias; fp.status = status; fp.debug_times = debug_times; fp.epoch_ptr = epoch_ptr;
+  fp.mc_slots = mc_partial;
   CUtensorMap ta, tb, tc, taux;
   int rc = make_map(&ta, A, is_bf16, K, T, 1, 1, lda, 0, 0, kBlockK, kBlockM);
   if (rc) return rc;

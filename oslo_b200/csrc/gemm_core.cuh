@@ -129,6 +129,12 @@ struct FusedParams {
   const void* rs_bias = nullptr;        // optional [N]
   int* status = nullptr;
   unsigned long long* debug_times = nullptr;  // optional [8]: globaltimer stamps for tuning (null in normal use)
+  // NVSwitch multicast (both null without it).  mc_xfull: the gathered buffer of this call mapped on a multicast object
+  // over the group: one multimem.st delivers a piece of our shard to every rank.  mc_slots: the partial-product buffer
+  // [T, N] mapped the same way: every rank stores its partial tiles LOCALLY and the owner of a row block reads the sum
+  // over all ranks with multimem.ld_reduce (the switch adds in fp32).
+  void* mc_xfull = nullptr;
+  const void* mc_slots = nullptr;
 };
 
 // Tensor maps over every rank's slot buffer (reduce-scatter mode: the epilogue TMA-stores straight into the owner).
@@ -172,6 +178,19 @@ template <int MODE>
 OSLO_DEVINL void fused_tile_coords(int tile, const GemmParams& p, const FusedParams& fp, int& b, int& mb, int& nb) {
   b = 0;
   const int blocks_per_chunk = fp.chunk_rows / kBlockM;
+  if constexpr (MODE == kModeReduceScatter) {
+    if (fp.mc_slots != nullptr) {
+      // Multicast reduce-scatter: every rank walks the SAME order, row chunk by row chunk and inside a chunk owner by
+      // owner, so chunk c of an owner's block is complete on all ranks at about the same time and the owners' reducer
+      // CTAs pull a steady stream while the products of later chunks are still running.
+      const int round = fp.tiles_per_chunk * fp.tp;
+      const int c = tile / round, u = tile - c * round;
+      const int shard = u / fp.tiles_per_chunk, r = u - shard * fp.tiles_per_chunk;
+      mb = shard * (fp.shard_rows / kBlockM) + c * blocks_per_chunk + r % blocks_per_chunk;
+      nb = r / blocks_per_chunk;
+      return;
+    }
+  }
   if constexpr ((MODE & kModeReduceScatter) != 0) {
     // Block by block in destination order: the next rank's block first, our own block LAST (by then the other ranks'
     // partials of it have long arrived, so the tiles that finish the reduction do not wait; an order that interleaved
@@ -312,6 +331,112 @@ static __device__ __noinline__ void ag_copy_role(const GemmParams& p, const Fuse
   tma_store_wait_all();
 }
 
+OSLO_DEVINL void multimem_st_v4(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+OSLO_DEVINL uint4 multimem_ld_reduce_v4(const void* mc, bool bf16) {
+  uint4 v;
+  if (bf16) asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  else asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                    : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+
+// AG copy role over NVSwitch multicast: all threads of the copy CTAs read our shard (local memory, 16 bytes per thread and
+// step) and store each vector ONCE to the multicast address of the gathered buffer; the switch delivers it to every rank
+// (ourselves included), so our links carry the shard once instead of once per peer.  Chunk flags as in the unicast role.
+static __device__ __noinline__ void ag_mc_copy_role(const GemmParams& p, const FusedParams& fp) {
+  constexpr int kUnroll = 8;
+  const int cps = fp.ag_shard_rows / fp.ag_chunk_rows;
+  const long long chunk_vecs = static_cast<long long>(fp.ag_chunk_rows) * fp.k_elems * 2 / 16;
+  const uint4* src = static_cast<const uint4*>(fp.peer_in[fp.ag_rank]);
+  uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(fp.mc_xfull)) + static_cast<long long>(fp.ag_rank) * cps * chunk_vecs;
+  const long long stride = static_cast<long long>(fp.copy_ctas) * blockDim.x;
+  for (int c = 0; c < cps; ++c) {
+    const uint4* s = src + c * chunk_vecs;
+    uint4* d = dst + c * chunk_vecs;
+    long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (; i + (kUnroll - 1) * stride < chunk_vecs; i += kUnroll * stride) {
+      uint4 v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) v[u] = __ldg(s + i + u * stride);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) multimem_st_v4(d + i + u * stride, v[u]);
+    }
+    for (; i < chunk_vecs; i += stride) multimem_st_v4(d + i, __ldg(s + i));
+    __threadfence_system();  // this thread's multicast stores are performed everywhere before the arrival below
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int old = atomicAdd(fp.chunk_arrive + c, 1);
+      if (old == fp.copy_ctas - 1) {
+        fp.chunk_arrive[c] = 0;
+        __threadfence_system();
+        for (int r = 0; r < fp.ag_tp; ++r) st_release_sys(fp.peer_chunk_flag[r] + fp.ag_rank * cps + c, fp.ag_epoch);
+      }
+    }
+  }
+}
+
+// RS reduce role over NVSwitch multicast: the reducer CTAs of the rank that owns a row block wait until every rank has
+// flagged row chunk c of that block (all partial tiles of the chunk are in the ranks' local partial buffers), then read
+// the chunk through the multicast address with multimem.ld_reduce (one load returns the sum over all ranks, accumulated in
+// fp32 inside the switch), add the bias and write the final rows.  Many independent loads per thread: the reduction is a
+// round trip through the switch and only bytes in flight hide it.
+static __device__ __noinline__ void rs_mc_reduce_role(const GemmParams& p, const FusedParams& fp) {
+  constexpr int kUnroll = 8;
+  __shared__ int s_ok;
+  const int vec_per_row = p.N / 8;
+  const long long chunk_vecs = static_cast<long long>(fp.chunk_rows) * vec_per_row;
+  const long long stride = static_cast<long long>(fp.copy_ctas) * blockDim.x;
+  const bool bf16 = p.is_bf16 != 0;
+  for (int c = 0; c < fp.cps; ++c) {
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (static_cast<int>(threadIdx.x) < fp.tp &&
+        !flag_wait_bounded(fp.rs_flag + threadIdx.x * fp.cps + c, fp.epoch, nullptr, true)) s_ok = 0;
+    __syncthreads();
+    if (!s_ok) {
+      if (threadIdx.x == 0 && fp.status) atomicCAS(fp.status, kStatusOk, kStatusPeerFlagTimeout);
+      return;
+    }
+    const long long row0 = static_cast<long long>(fp.rank) * fp.shard_rows + static_cast<long long>(c) * fp.chunk_rows;
+    const uint4* src = static_cast<const uint4*>(fp.mc_slots) + row0 * vec_per_row;       // partial buffer [T, N]
+    uint4* dst = static_cast<uint4*>(fp.rs_out) + static_cast<long long>(c) * chunk_vecs;  // out [T / tp, N]
+    auto finish = [&](long long i, uint4 v) {
+      if (fp.rs_bias != nullptr) {
+        const int col = static_cast<int>(i % vec_per_row) * 8;
+        const uint4 braw = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(fp.rs_bias) + col));
+        uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+        const uint32_t* bw = reinterpret_cast<const uint32_t*>(&braw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (bf16) {
+            const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&w[j]), b = *reinterpret_cast<const __nv_bfloat162*>(&bw[j]);
+            const __nv_bfloat162 r = __floats2bfloat162_rn(__low2float(a) + __low2float(b), __high2float(a) + __high2float(b));
+            w[j] = *reinterpret_cast<const uint32_t*>(&r);
+          } else {
+            const __half2 a = *reinterpret_cast<const __half2*>(&w[j]), b = *reinterpret_cast<const __half2*>(&bw[j]);
+            const __half2 r = __floats2half2_rn(__low2float(a) + __low2float(b), __high2float(a) + __high2float(b));
+            w[j] = *reinterpret_cast<const uint32_t*>(&r);
+          }
+        }
+      }
+      dst[i] = v;
+    };
+    long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (; i + (kUnroll - 1) * stride < chunk_vecs; i += kUnroll * stride) {
+      uint4 v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) v[u] = multimem_ld_reduce_v4(src + i + u * stride, bf16);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) finish(i + u * stride, v[u]);
+    }
+    for (; i < chunk_vecs; i += stride) finish(i, multimem_ld_reduce_v4(src + i, bf16));
+  }
+}
+
 // k-block range [kb0, kb1) a tile has to reduce over, or skip = true when it has no work.
 OSLO_DEVINL void tile_k_range(const GemmParams& p, int m0, int n0, int num_kb, int& kb0, int& kb1, bool& skip) {
   kb0 = 0;
@@ -333,9 +458,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if constexpr ((MODE & kModeAllGather) != 0) {
     // the first fp.copy_ctas CTAs stream the peers' shards into local memory; the rest run the GEMM
     if (static_cast<int>(blockIdx.x) < fp.copy_ctas) {
+      if (fp.mc_xfull != nullptr) {
+        ag_mc_copy_role(p, fp);
+        return;
+      }
       extern __shared__ uint8_t copy_smem_raw[];
       uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(copy_smem_raw) + 1023) & ~uintptr_t(1023));
       ag_copy_role(p, fp, ring, reinterpret_cast<uint64_t*>(ring + kCopyDepth * kCopyPiece));
+      return;
+    }
+  }
+  if constexpr (MODE == kModeReduceScatter) {
+    // multicast reduce-scatter: the first fp.copy_ctas CTAs pull the reduced rows of our block; the rest run the GEMM
+    if (fp.mc_slots != nullptr && static_cast<int>(blockIdx.x) < fp.copy_ctas) {
+      rs_mc_reduce_role(p, fp);
       return;
     }
   }
@@ -538,7 +674,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         // tiles of OUR block finish the reduction themselves: the other ranks' partials must have landed in our
         // slot buffer (they compute our block first, so this normally does not wait)
         rs_tile_owner(fp, m0, n0, rs_dest, rs_c);
-        rs_own = rs_dest == fp.rank;
+        // with a multicast partial buffer no tile is finished here: all go to local memory and the reducer CTAs pull sums
+        rs_own = fp.mc_slots == nullptr && rs_dest == fp.rank;
         if (rs_own) {
           const int cps = fp.cps;
           const int c = rs_c;
@@ -689,6 +826,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               const int r_in = fp.rs_along_n ? m0 : m0 - dest * fp.shard_rows;
               const int c_in = fp.rs_along_n ? col0 - dest * fp.shard_cols : col0;
               if (rs_own) tma_store_4d(&tmC, sbuf_ptr, c_in, r_in + q * 32, 0, 0);  // final values
+              else if (fp.mc_slots != nullptr) tma_store_4d(&peer_maps.m[fp.rank], sbuf_ptr, col0, m0 + q * 32, 0, 0);  // local partial [T, N]
               else tma_store_4d(&peer_maps.m[dest], sbuf_ptr, c_in, fp.rank * fp.slot_rows + r_in + q * 32, 0, 0);
             } else {
               tma_store_4d(pass == 0 ? &tmAux : &tmC, sbuf_ptr, col0, m0 + q * 32, bi, bo);

@@ -29,6 +29,42 @@ from oslo_b200.ops import _lib, fused_collectives
 
 _FLAG_BYTES = 4096
 
+#: use NVSwitch multicast (``multimem`` stores and in-switch reductions) in the fused kernels when the group's workspace can
+#: be bound to a multicast object; OSLO_B200_MULTIMEM=0 keeps plain peer loads / stores (required for any test in which a
+#: rank may leave while others still run: a rank that dies while bound to a multicast object faults its peers' links).
+USE_MULTIMEM = __import__("os").environ.get("OSLO_B200_MULTIMEM", "1") == "1"
+
+
+def _multicast_alloc(pc, mode, nbytes: int):
+    """Allocate ``nbytes`` per rank through ``torch.distributed._symmetric_memory`` and rendezvous over the group.
+
+    Returns ``(tensor, peer_pointers, multicast_pointer)`` or ``None`` when the allocation, the exchange of handles or the
+    multicast binding is not available (the caller then uses its CUDA-IPC allocation).  Collective over the group: every
+    rank must take the same branch, so the outcome is agreed on with an all-reduce."""
+    ok, out = 1, None
+    try:
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = pc.get_group(mode)
+        t = symm_mem.empty(nbytes, dtype=torch.uint8, device=pc.device)
+        hdl = symm_mem.rendezvous(t, group)
+        mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
+        ptrs = [int(x) for x in hdl.buffer_ptrs]
+        if mc == 0 or len(ptrs) != pc.get_world_size(mode):
+            ok = 0
+        else:
+            out = (t, hdl, ptrs, mc)
+    except Exception as e:  # noqa: BLE001 - any failure means "not available here"
+        ok = 0
+        out = None
+        _multicast_alloc.last_error = repr(e)
+    flag = torch.tensor([ok], dtype=torch.int32)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=pc.get_cpu_group(mode))
+    return out if int(flag.item()) == 1 else None
+
+
+_multicast_alloc.last_error = None
+
 
 class _RawCudaBuffer:
     """Exposes a raw device pointer to torch through ``__cuda_array_interface__`` (zero copy)."""
@@ -151,7 +187,8 @@ def small_ops_enabled() -> bool:
 
 
 class SymmetricWorkspace:
-    def __init__(self, pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 16):
+    def __init__(self, pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 16,
+                 multimem: bool = True):
         self.pc, self.mode = pc, mode
         self.tp = pc.get_world_size(mode)
         self.rank = pc.get_local_rank(mode)
@@ -166,35 +203,51 @@ class SymmetricWorkspace:
         self.slot_bytes = (max_tokens * max_features * esz + 1023) // 1024 * 1024
         self.total = _FLAG_BYTES + 2 * self.in_bytes + 2 * self.slot_bytes
         lib = _lib.cuda_lib()
-        base = ctypes.c_void_p()
-        rc = lib.oslo_symm_alloc(ctypes.c_ulonglong(self.total), ctypes.byref(base))
-        if rc:
-            raise RuntimeError(f"symmetric allocation of {self.total} bytes failed (cuda error {-rc})")
-        self.base = base.value
-        hbytes = lib.oslo_ipc_handle_bytes()
-        handle = (ctypes.c_ubyte * hbytes)()
-        rc = lib.oslo_ipc_get_handle(ctypes.c_void_p(self.base), handle)
-        if rc:
-            raise RuntimeError(f"cudaIpcGetMemHandle failed (cuda error {-rc})")
-        gathered: List[Optional[bytes]] = [None] * self.tp
-        dist.all_gather_object(gathered, bytes(handle), group=pc.get_cpu_group(mode))
-        self.peer_base: List[int] = []
-        for r, h in enumerate(gathered):
-            if r == self.rank:
-                self.peer_base.append(self.base)
-                continue
-            buf = (ctypes.c_ubyte * hbytes).from_buffer_copy(h)
-            out = ctypes.c_void_p()
-            rc = lib.oslo_ipc_open_handle(buf, ctypes.byref(out))
+        #: address of the whole workspace through the group's NVSwitch multicast object (0: not bound)
+        self.mc_base = 0
+        self._symm_keep = None
+        mc = _multicast_alloc(pc, mode, self.total) if (USE_MULTIMEM and multimem) else None
+        if mc is not None:
+            tensor, hdl, ptrs, mc_ptr = mc
+            tensor.zero_()
+            torch.cuda.synchronize(self.device)
+            self._symm_keep = (tensor, hdl)
+            self.base = tensor.data_ptr()
+            self.peer_base: List[int] = ptrs
+            self.mc_base = mc_ptr
+        else:
+            base = ctypes.c_void_p()
+            rc = lib.oslo_symm_alloc(ctypes.c_ulonglong(self.total), ctypes.byref(base))
             if rc:
-                raise RuntimeError(f"cudaIpcOpenMemHandle for peer {r} failed (cuda error {-rc})")
-            self.peer_base.append(out.value)
+                raise RuntimeError(f"symmetric allocation of {self.total} bytes failed (cuda error {-rc})")
+            self.base = base.value
+            hbytes = lib.oslo_ipc_handle_bytes()
+            handle = (ctypes.c_ubyte * hbytes)()
+            rc = lib.oslo_ipc_get_handle(ctypes.c_void_p(self.base), handle)
+            if rc:
+                raise RuntimeError(f"cudaIpcGetMemHandle failed (cuda error {-rc})")
+            gathered: List[Optional[bytes]] = [None] * self.tp
+            dist.all_gather_object(gathered, bytes(handle), group=pc.get_cpu_group(mode))
+            self.peer_base = []
+            for r, h in enumerate(gathered):
+                if r == self.rank:
+                    self.peer_base.append(self.base)
+                    continue
+                buf = (ctypes.c_ubyte * hbytes).from_buffer_copy(h)
+                out = ctypes.c_void_p()
+                rc = lib.oslo_ipc_open_handle(buf, ctypes.byref(out))
+                if rc:
+                    raise RuntimeError(f"cudaIpcOpenMemHandle for peer {r} failed (cuda error {-rc})")
+                self.peer_base.append(out.value)
         # local scratch counters (not shared): chunk_flag[64], chunk_arrive[64], tile_done[64]
         self.local = torch.zeros(256, dtype=torch.int32, device=self.device)
         self.epoch = 0
         self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=self.device)  # what the kernels actually read
         self.debug_times = None  # set to a uint64[8] device tensor to collect in-kernel time stamps
-        self._local_bytes = torch.as_tensor(_RawCudaBuffer(self.base, self.total), device=self.device)
+        if self._symm_keep is not None:
+            self._local_bytes = self._symm_keep[0]
+        else:
+            self._local_bytes = torch.as_tensor(_RawCudaBuffer(self.base, self.total), device=self.device)
         dist.barrier(group=pc.get_cpu_group(mode))
         self.barrier()
 
@@ -210,6 +263,14 @@ class SymmetricWorkspace:
     def _slot_ptrs(self, parity: int):
         off = _FLAG_BYTES + 2 * self.in_bytes + parity * self.slot_bytes
         return (ctypes.c_void_p * self.tp)(*[b + off for b in self.peer_base])
+
+    def _mc_gathered(self, parity: int):
+        return ctypes.c_void_p(self.mc_base + _FLAG_BYTES + parity * self.in_bytes) if self.mc_base else ctypes.c_void_p(0)
+
+    def _mc_slots(self, parity: int):
+        if not self.mc_base:
+            return ctypes.c_void_p(0)
+        return ctypes.c_void_p(self.mc_base + _FLAG_BYTES + 2 * self.in_bytes + parity * self.slot_bytes)
 
     def _local_gathered(self, parity: int, rows: int, cols: int):
         off = _FLAG_BYTES + parity * self.in_bytes
@@ -300,7 +361,8 @@ class SymmetricWorkspace:
             ctypes.c_int(n), ctypes.c_int(k), ctypes.c_longlong(ldb), ctypes.c_int(b_mn),
             ctypes.c_int(1 if self.dtype == torch.bfloat16 else 0), ctypes.c_int(self.tp), ctypes.c_int(self.rank),
             ctypes.c_int(self.epoch), self._flag_ptrs(0), self._local_ptr(1), ctypes.c_int(self.copy_ctas),
-            ctypes.c_int(_lib.num_sms()), _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr(), _lib.ptr(self.epoch_dev))
+            ctypes.c_int(_lib.num_sms()), _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr(), _lib.ptr(self.epoch_dev),
+            self._mc_gathered(parity))
         if rc:
             raise RuntimeError(f"oslo_ag_gemm failed ({rc})")
         x_full = self._local_gathered(parity, t, k)
@@ -331,7 +393,7 @@ class SymmetricWorkspace:
             ctypes.c_int(self.epoch), self._slot_ptrs(parity), self._flag_ptrs(1), self._local_ptr(2),
             ctypes.c_int(self.copy_ctas), ctypes.c_int(_lib.num_sms()), _lib.ptr(_lib.status_word(self.device)),
             _lib.stream_ptr(), _lib.ptr(self.debug_times), _lib.ptr(self.epoch_dev), _lib.ptr(addend),
-            ctypes.c_int(1 if along_n else 0))
+            ctypes.c_int(1 if along_n else 0), self._mc_slots(parity))
         if rc:
             raise RuntimeError(f"oslo_gemm_rs failed ({rc})")
         return out
@@ -395,7 +457,8 @@ class _Runtime:
         return self.ws.gemm_rs(x, weight, addend=addend, along_n=along_n)
 
 
-def enable(pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 16, model=None) -> bool:
+def enable(pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 16, model=None,
+           multimem: bool = True) -> bool:
     """Create the group's symmetric workspace and switch the linears that communicate over ``mode`` to the fused kernels:
     ``TENSOR_1D`` for the sequence-parallel 1-D linears, ``TENSOR_2D_ROW`` / ``TENSOR_2P5D_ROW`` for the feature
     reduce-scatter of the SUMMA linears, ``TENSOR_3D_INPUT`` + ``TENSOR_3D_OUTPUT`` (call twice) for the 3-D linear.
@@ -406,7 +469,7 @@ def enable(pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, c
     if model is not None:
         rehome_vocab_embeddings(model, pc, mode)
     global _fused_small_ops
-    ws = SymmetricWorkspace(pc, mode, max_tokens, max_features, dtype, copy_ctas)
+    ws = SymmetricWorkspace(pc, mode, max_tokens, max_features, dtype, copy_ctas, multimem=multimem)
     fused_collectives.set_runtime(_Runtime(ws), mode)
     _fused_small_ops = True
     return True

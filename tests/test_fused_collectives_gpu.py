@@ -13,7 +13,7 @@ def _n_gpus():
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
 
-def _worker(rank, world):
+def _worker(rank, world, multimem=False):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     import torch.distributed as dist
 
@@ -24,7 +24,12 @@ def _worker(rank, world):
     pc = ParallelContext.from_torch(tensor_parallel_size=world, tensor_parallel_mode=ParallelMode.TENSOR_1D,
                                     backend="nccl", seed=0)
     dev = pc.device
-    assert symm.enable(pc, ParallelMode.TENSOR_1D, max_tokens=4096, max_features=1024)
+    # multimem: the workspace is bound to an NVSwitch multicast object when the box allows it (the all-gather then uses
+    # multimem.st, the row reduce-scatter multimem.ld_reduce); otherwise, and with multimem off, plain peer stores
+    assert symm.enable(pc, ParallelMode.TENSOR_1D, max_tokens=4096, max_features=1024, multimem=multimem)
+    if multimem and rank == 0:
+        print(f"multicast workspace: {'bound' if fc.runtime().ws.mc_base else 'not available (' + str(symm._multicast_alloc.last_error) + ')'}",
+              flush=True)
     # a second workspace over the same ranks stands for the second group of the 3-D linear (gather and scatter groups
     # differ there; the kernel only sees two sets of peer pointers, flags and epochs)
     ws2 = symm.SymmetricWorkspace(pc, ParallelMode.TENSOR_1D, 4096, 1024)
@@ -93,9 +98,10 @@ def _world_sizes():
 
 
 @pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+@pytest.mark.parametrize("multimem", [False, True], ids=["peer", "multicast"])
 @pytest.mark.parametrize("world", _world_sizes())
-def test_fused_collectives_match_nccl(world):
-    run_dist(_worker, world, timeout=600)
+def test_fused_collectives_match_nccl(world, multimem):
+    run_dist(_worker, world, multimem, timeout=600)
 
 
 def _model_worker(rank, world):
