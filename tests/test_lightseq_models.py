@@ -1,0 +1,181 @@
+"""LightSeq-interface models, CRF layer, weight export and the batching server (CPU)."""
+import asyncio
+import itertools
+import os
+
+import pytest
+import torch
+
+
+def test_transformer_trains_and_translates():
+    from oslo_b200.lightseq import LSTransformer, get_config
+
+    torch.manual_seed(0)
+    cfg = get_config(model="transformer-base", vocab_size=40, padding_idx=0, max_seq_len=32, hidden_size=32,
+                     intermediate_size=64, nhead=4, num_encoder_layer=2, num_decoder_layer=2, bos_id=1, eos_id=2)
+    model = LSTransformer(cfg)
+    opt = torch.optim.Adam(model.parameters(), lr=3e-3)
+    # copy task: the target is the source
+    src = torch.randint(3, 40, (16, 6))
+    trg_in = torch.cat([torch.full((16, 1), 1), src], dim=1)
+    labels = torch.cat([src, torch.full((16, 1), 2)], dim=1)
+    first = None
+    for _ in range(150):
+        loss, logits = model(src, trg_in, labels)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        first = first if first is not None else loss.item()
+    assert loss.item() < 0.3 * first, (first, loss.item())
+    assert logits.shape == (16, 7, 40)
+    model.eval()
+    greedy = model.infer(src[:4], max_new_tokens=8)
+    beam = model.infer(src[:4], max_new_tokens=8, beam_size=3)
+    assert greedy.shape[0] == 4 and bool((greedy[:, 0] == 1).all())
+    # a trained copy model reproduces most of the source with either search
+    for out in (greedy, beam):
+        n = min(out.shape[1] - 1, 6)
+        assert (out[:, 1 : 1 + n] == src[:4, :n]).float().mean().item() > 0.7
+    with pytest.raises(ValueError):
+        get_config(model="transformer-huge")
+
+
+def test_gpt_and_bert_models():
+    from oslo_b200.lightseq import LSBert, LSGpt, get_config
+
+    torch.manual_seed(1)
+    cfg = get_config(vocab_size=50, padding_idx=0, max_seq_len=32, hidden_size=32, intermediate_size=64, nhead=4,
+                     num_decoder_layer=2, num_encoder_layer=2, num_labels=3)
+    gpt = LSGpt(cfg)
+    ids = torch.randint(1, 50, (2, 10))
+    out = gpt(ids, labels=ids)
+    out.loss.backward()
+    assert out.logits.shape == (2, 10, 50) and torch.isfinite(out.loss)
+    gpt.eval()
+    cached = gpt.infer(ids, max_new_tokens=4)
+    full = gpt.infer(ids, max_new_tokens=4, use_cache=False)
+    assert torch.equal(cached, full)  # the key / value cache (and the position offset of the embedding) change nothing
+    bert = LSBert(cfg)
+    loss, logits = bert(ids, labels=torch.tensor([0, 2]))
+    loss.backward()
+    assert logits.shape == (2, 3)
+
+
+def _crf_brute_force(crf, e, mask):
+    """All tag sequences of one example: log partition function and best path."""
+    n = int(mask.sum())
+    tags = crf.num_tags
+    scores = {}
+    for seq in itertools.product(range(tags), repeat=n):
+        s = crf.start_transitions[seq[0]] + e[0, seq[0]]
+        for t in range(1, n):
+            s = s + crf.transitions[seq[t - 1], seq[t]] + e[t, seq[t]]
+        scores[seq] = (s + crf.end_transitions[seq[-1]]).item()
+    logz = torch.logsumexp(torch.tensor(list(scores.values())), 0).item()
+    return scores, logz, max(scores, key=scores.get)
+
+
+def test_crf_matches_brute_force():
+    from oslo_b200.lightseq import LSCRFLayer
+
+    torch.manual_seed(2)
+    crf = LSCRFLayer(3)
+    e = torch.randn(2, 5, 3)
+    mask = torch.tensor([[1, 1, 1, 1, 1], [1, 1, 1, 0, 0]], dtype=torch.bool)
+    tags = torch.tensor([[0, 1, 2, 1, 0], [2, 2, 1, 0, 0]])
+    nll = crf(e, tags, mask, reduction="none")
+    paths = crf.decode(e, mask)
+    for i in range(2):
+        scores, logz, best = _crf_brute_force(crf, e[i], mask[i])
+        n = int(mask[i].sum())
+        assert abs(nll[i].item() - (logz - scores[tuple(tags[i, :n].tolist())])) < 1e-4
+        assert tuple(paths[i]) == best
+    crf(e, tags, mask).backward()
+    assert crf.transitions.grad is not None and torch.isfinite(crf.transitions.grad).all()
+
+
+def test_export_roundtrip_plain_and_int8(tmp_path):
+    from oslo_b200.lightseq import LSGpt, export_model, get_config, import_into, load_exported
+    from oslo_b200.lightseq.export import read_header
+
+    torch.manual_seed(3)
+    cfg = get_config(vocab_size=64, padding_idx=0, max_seq_len=16, hidden_size=32, intermediate_size=64, nhead=4, num_decoder_layer=2)
+    model = LSGpt(cfg).to(torch.bfloat16)
+    path = os.path.join(tmp_path, "gpt.lsw")
+    header = export_model(model, path, metadata={"note": "unit test"})
+    assert header["config"]["hidden_size"] == 32 and read_header(path)[0]["metadata"]["note"] == "unit test"
+    # the tied output projection is stored once
+    assert "alias" in header["tensors"]["lm_head.weight"] or "alias" in header["tensors"]["embed_tokens.embeddings.weight"]
+    state, _ = load_exported(path)
+    for k, v in model.state_dict().items():
+        assert torch.equal(state[k], v.cpu()), k
+    fresh = LSGpt(cfg).to(torch.bfloat16)
+    import_into(fresh, path)
+    ids = torch.randint(1, 64, (2, 8))
+    assert torch.equal(fresh(ids).logits, model(ids).logits)
+    # int8: matrices within half a quantisation step, vectors exact, file a good deal smaller
+    qpath = os.path.join(tmp_path, "gpt_int8.lsw")
+    export_model(model.float(), qpath, quantize=True)
+    qstate, qh = load_exported(qpath)
+    assert qh["quantized"]
+    for k, v in model.state_dict().items():
+        e = qh["tensors"][k]
+        if "alias" in e:
+            continue
+        if "clip" in e:
+            assert (qstate[k] - v).abs().max().item() <= e["clip"] / 127 * 0.5 + 1e-6, k
+        else:
+            assert torch.equal(qstate[k], v), k
+    raw, _ = load_exported(qpath, dequantize=False)
+    assert raw["layers.0.attn.qkv.weight"].dtype == torch.int8
+    export_model(model, os.path.join(tmp_path, "f32.lsw"))
+    assert os.path.getsize(qpath) < 0.5 * os.path.getsize(os.path.join(tmp_path, "f32.lsw"))
+    with open(os.path.join(tmp_path, "bad"), "wb") as f:
+        f.write(b"not a weight file")
+    with pytest.raises(ValueError):
+        read_header(os.path.join(tmp_path, "bad"))
+
+
+def test_dynamic_batcher_groups_requests():
+    from oslo_b200.lightseq.serving import DynamicBatcher
+
+    calls = []
+
+    def fake_generate(ids, max_new_tokens=1):
+        calls.append(tuple(ids.shape))
+        return torch.cat([ids, ids[:, -1:].repeat(1, max_new_tokens) + 1], dim=1)
+
+    async def main():
+        b = DynamicBatcher(fake_generate, max_batch=4, max_wait_ms=50)
+        res = await asyncio.gather(b.submit([1, 2, 3], max_new_tokens=2), b.submit([4, 5, 6], max_new_tokens=2),
+                                   b.submit([7, 8], max_new_tokens=2), b.submit([9, 9, 9], max_new_tokens=1))
+        await b.stop()
+        return b, res
+
+    b, res = asyncio.run(main())
+    assert res[0][0] == [1, 2, 3, 4, 4] and res[1][0] == [4, 5, 6, 7, 7] and res[2][0] == [7, 8, 9, 9] and res[3][0] == [9, 9, 9, 10]
+    assert res[0][1] == 2 and res[1][1] == 2  # the two same-length, same-settings prompts shared a batch
+    assert sorted(calls) == [(1, 2), (1, 3), (2, 3)]
+    assert b.requests == 4 and b.batches == 3
+
+
+def test_http_server_generates():
+    pytest.importorskip("fastapi")
+    pytest.importorskip("httpx")
+    from fastapi.testclient import TestClient
+
+    from oslo_b200.lightseq import LSGpt, get_config
+    from oslo_b200.lightseq.inference import generate
+    from oslo_b200.lightseq.serving import create_app
+
+    torch.manual_seed(4)
+    cfg = get_config(vocab_size=50, padding_idx=0, max_seq_len=32, hidden_size=32, intermediate_size=64, nhead=4, num_decoder_layer=2)
+    model = LSGpt(cfg).eval()
+    with TestClient(create_app(model, max_batch=4, max_wait_ms=1)) as client:
+        assert client.get("/health").json()["status"] == "ok"
+        r = client.post("/generate", json={"input_ids": [[5, 6, 7], [8, 9, 10]], "max_new_tokens": 3})
+        assert r.status_code == 200, r.text
+        want = generate(model, torch.tensor([[5, 6, 7], [8, 9, 10]]), max_new_tokens=3).tolist()
+        assert r.json()["output_ids"] == want
+        assert client.post("/generate", json={"max_new_tokens": 3}).status_code == 422
+        assert "oslo_requests_total 2" in client.get("/metrics").text
