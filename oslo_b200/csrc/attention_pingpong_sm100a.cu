@@ -332,7 +332,8 @@ static int launch_attention_pingpong(const CUtensorMap& tq, const CUtensorMap& t
   }
   const int grid = p.batch * p.heads * (p.seq / (2 * kPPRows));
   kern<<<grid, kPPThreads, Cfg::kSmem, stream>>>(tq, tk, tv, to, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  const cudaError_t err = cudaGetLastError();
+  return err == cudaSuccess ? 0 : -(1000 + static_cast<int>(err));  // the CUDA error code of a refused launch
 }
 
 }  // namespace oslo

@@ -310,7 +310,16 @@ __global__ void colsum_kernel(const T* __restrict__ x, float* __restrict__ parti
 #pragma unroll
   for (int j = 0; j < P; ++j) acc[j] = 0.f;
   if (col < H) {
-    for (size_t r = blockIdx.y * (size_t)blockDim.y + threadIdx.y; r < rows; r += (size_t)gridDim.y * blockDim.y) {
+    // four independent 16-byte loads in flight per thread
+    const size_t stride = (size_t)gridDim.y * blockDim.y;
+    size_t r = blockIdx.y * (size_t)blockDim.y + threadIdx.y;
+    for (; r + 3 * stride < rows; r += 4 * stride) {
+      Pack<T> a0 = ld_pack(x + r * H + col), a1 = ld_pack(x + (r + stride) * H + col);
+      Pack<T> a2 = ld_pack(x + (r + 2 * stride) * H + col), a3 = ld_pack(x + (r + 3 * stride) * H + col);
+#pragma unroll
+      for (int j = 0; j < P; ++j) acc[j] += (to_f(a0.v[j]) + to_f(a1.v[j])) + (to_f(a2.v[j]) + to_f(a3.v[j]));
+    }
+    for (; r < rows; r += stride) {
       Pack<T> a = ld_pack(x + r * H + col);
 #pragma unroll
       for (int j = 0; j < P; ++j) acc[j] += to_f(a.v[j]);
@@ -330,13 +339,22 @@ __global__ void colsum_kernel(const T* __restrict__ x, float* __restrict__ parti
     }
   }
 }
+// Sum of the partial rows: block (32 columns x 8 row groups), every thread adds parts / 8 values, shared-memory fold.
 template <typename T>
 __global__ void colsum_finish_kernel(const float* __restrict__ partial, T* __restrict__ out, int parts, int H) {
-  const int col = blockIdx.x * blockDim.x + threadIdx.x;
-  if (col >= H) return;
+  const int col = blockIdx.x * 32 + threadIdx.x;
   float s = 0.f;
-  for (int r = 0; r < parts; ++r) s += partial[(size_t)r * H + col];
-  out[col] = from_f<T>(s);
+  if (col < H)
+    for (int r = threadIdx.y; r < parts; r += 8) s += partial[(size_t)r * H + col];
+  __shared__ float sm[8][33];
+  sm[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && col < H) {
+    float t = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) t += sm[r][threadIdx.x];
+    out[col] = from_f<T>(t);
+  }
 }
 
 static inline int grid_for(size_t work_items, int threads, int num_sms) {
@@ -496,7 +514,7 @@ extern "C" int oslo_softmax_backward_causal(const void* dy, const void* y, void*
 // Number of partial rows used by oslo_colsum (scratch = parts * H floats).
 extern "C" int oslo_colsum_parts(long long rows, int num_sms) {
   long long p = (rows + 63) / 64;
-  long long cap = num_sms * 2;
+  long long cap = num_sms / 2 > 0 ? num_sms / 2 : 1;  // enough blocks to fill the GPU, few enough rows for the second pass
   return (int)(p < cap ? (p ? p : 1) : cap);
 }
 
@@ -510,10 +528,11 @@ extern "C" int oslo_colsum(const void* x, void* out, float* partial, long long r
   OSLO_BY_DTYPE((colsum_kernel<float><<<grid, block, 0, st>>>((const float*)x, partial, rows, H)),
                 (colsum_kernel<__half><<<grid, block, 0, st>>>((const __half*)x, partial, rows, H)),
                 (colsum_kernel<__nv_bfloat16><<<grid, block, 0, st>>>((const __nv_bfloat16*)x, partial, rows, H)));
-  const int fb = (H + 255) / 256;
-  OSLO_BY_DTYPE((colsum_finish_kernel<float><<<fb, 256, 0, st>>>(partial, (float*)out, parts, H)),
-                (colsum_finish_kernel<__half><<<fb, 256, 0, st>>>(partial, (__half*)out, parts, H)),
-                (colsum_finish_kernel<__nv_bfloat16><<<fb, 256, 0, st>>>(partial, (__nv_bfloat16*)out, parts, H)));
+  const int fb = (H + 31) / 32;
+  const dim3 fblock(32, 8);
+  OSLO_BY_DTYPE((colsum_finish_kernel<float><<<fb, fblock, 0, st>>>(partial, (float*)out, parts, H)),
+                (colsum_finish_kernel<__half><<<fb, fblock, 0, st>>>(partial, (__half*)out, parts, H)),
+                (colsum_finish_kernel<__nv_bfloat16><<<fb, fblock, 0, st>>>(partial, (__nv_bfloat16*)out, parts, H)));
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -602,9 +621,10 @@ extern "C" int oslo_colsum_noalloc(const void* x, void* out, long long rows, int
   OSLO_BY_DTYPE((colsum_kernel<float><<<grid, block, 0, s>>>((const float*)x, partial, rows, H)),
                 (colsum_kernel<__half><<<grid, block, 0, s>>>((const __half*)x, partial, rows, H)),
                 (colsum_kernel<__nv_bfloat16><<<grid, block, 0, s>>>((const __nv_bfloat16*)x, partial, rows, H)));
-  const int fb = (H + 255) / 256;
-  OSLO_BY_DTYPE((colsum_finish_kernel<float><<<fb, 256, 0, s>>>(partial, (float*)out, (int)parts, H)),
-                (colsum_finish_kernel<__half><<<fb, 256, 0, s>>>(partial, (__half*)out, (int)parts, H)),
-                (colsum_finish_kernel<__nv_bfloat16><<<fb, 256, 0, s>>>(partial, (__nv_bfloat16*)out, (int)parts, H)));
+  const int fb = (H + 31) / 32;
+  const dim3 fblock(32, 8);  // the second pass folds 8 row groups per column in shared memory
+  OSLO_BY_DTYPE((colsum_finish_kernel<float><<<fb, fblock, 0, s>>>(partial, (float*)out, (int)parts, H)),
+                (colsum_finish_kernel<__half><<<fb, fblock, 0, s>>>(partial, (__half*)out, (int)parts, H)),
+                (colsum_finish_kernel<__nv_bfloat16><<<fb, fblock, 0, s>>>(partial, (__nv_bfloat16*)out, (int)parts, H)));
   return cudaGetLastError() == cudaSuccess ? 0 : OSLO_NOALLOC_ERR_LAUNCH;
 }

@@ -348,7 +348,7 @@ OSLO_DEVINL uint4 multimem_ld_reduce_v4(const void* mc, bool bf16) {
 // step) and store each vector ONCE to the multicast address of the gathered buffer; the switch delivers it to every rank
 // (ourselves included), so our links carry the shard once instead of once per peer.  Chunk flags as in the unicast role.
 static __device__ __noinline__ void ag_mc_copy_role(const GemmParams& p, const FusedParams& fp) {
-  constexpr int kUnroll = 8;
+  constexpr int kUnroll = 16;
   const int cps = fp.ag_shard_rows / fp.ag_chunk_rows;
   const long long chunk_vecs = static_cast<long long>(fp.ag_chunk_rows) * fp.k_elems * 2 / 16;
   const uint4* src = static_cast<const uint4*>(fp.peer_in[fp.ag_rank]);
@@ -385,7 +385,7 @@ static __device__ __noinline__ void ag_mc_copy_role(const GemmParams& p, const F
 // fp32 inside the switch), add the bias and write the final rows.  Many independent loads per thread: the reduction is a
 // round trip through the switch and only bytes in flight hide it.
 static __device__ __noinline__ void rs_mc_reduce_role(const GemmParams& p, const FusedParams& fp) {
-  constexpr int kUnroll = 8;
+  constexpr int kUnroll = 16;
   __shared__ int s_ok;
   const int vec_per_row = p.N / 8;
   const long long chunk_vecs = static_cast<long long>(fp.chunk_rows) * vec_per_row;

@@ -206,7 +206,10 @@ class SymmetricWorkspace:
         #: address of the whole workspace through the group's NVSwitch multicast object (0: not bound)
         self.mc_base = 0
         self._symm_keep = None
-        mc = _multicast_alloc(pc, mode, self.total) if (USE_MULTIMEM and multimem) else None
+        # multicast pays once a shard would otherwise cross the links several times: at two ranks the peer-store kernels
+        # measured faster (one copy either way), so the default starts at four ranks; OSLO_B200_MULTIMEM_MIN_RANKS moves it
+        min_ranks = int(__import__("os").environ.get("OSLO_B200_MULTIMEM_MIN_RANKS", "4"))
+        mc = _multicast_alloc(pc, mode, self.total) if (USE_MULTIMEM and multimem and self.tp >= min_ranks) else None
         if mc is not None:
             tensor, hdl, ptrs, mc_ptr = mc
             tensor.zero_()

@@ -15,6 +15,7 @@ def _n_gpus():
 
 def _worker(rank, world, multimem=False):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["OSLO_B200_MULTIMEM_MIN_RANKS"] = "2"  # exercise the multicast kernels on two ranks as well
     import torch.distributed as dist
 
     from oslo_b200 import ParallelContext, ParallelMode

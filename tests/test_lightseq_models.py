@@ -179,3 +179,31 @@ def test_http_server_generates():
         assert r.json()["output_ids"] == want
         assert client.post("/generate", json={"max_new_tokens": 3}).status_code == 422
         assert "oslo_requests_total 2" in client.get("/metrics").text
+
+
+def test_cpu_gemms_match_torch():
+    from oslo_b200.lightseq.cpu_gemm import gemm_u8s8s32, quantized_linear, sgemm
+
+    torch.manual_seed(5)
+    for ta, tb in itertools.product((False, True), repeat=2):
+        a = torch.randn((37, 50) if ta else (50, 37))
+        b = torch.randn((29, 37) if tb else (37, 29))
+        want = (a.t() if ta else a) @ (b.t() if tb else b)
+        got = sgemm(a, b, ta, tb)
+        assert torch.allclose(got, want, rtol=1e-4, atol=1e-4), (ta, tb, (got - want).abs().max())
+        c0 = torch.randn(50, 29)
+        got = sgemm(a, b, ta, tb, alpha=0.5, beta=2.0, out=c0.clone())
+        assert torch.allclose(got, 0.5 * want + 2.0 * c0, rtol=1e-4, atol=1e-4)
+        au = torch.randint(0, 256, (37, 50) if ta else (50, 37), dtype=torch.uint8)
+        bs = torch.randint(-128, 128, (29, 37) if tb else (37, 29), dtype=torch.int8)
+        comp = torch.randint(-1000, 1000, (29,), dtype=torch.int32)
+        want_i = (au.t() if ta else au).to(torch.int64) @ (bs.t() if tb else bs).to(torch.int64) + comp
+        got_i = gemm_u8s8s32(au, bs, ta, tb, compensation=comp)
+        assert torch.equal(got_i.to(torch.int64), want_i), (ta, tb)
+    # the quantised linear follows the fp32 one to quantisation accuracy
+    x, w = torch.randn(64, 96), torch.randn(48, 96) * 0.2
+    w_clip = float(w.abs().max())
+    w_q = torch.round(w * (127.0 / w_clip)).to(torch.int8)
+    y = quantized_linear(x, w_q, w_clip, x_clip=4.0, bias=torch.ones(48))
+    ref = x.clamp(-4, 4) @ w.t() + 1.0
+    assert (y - ref).abs().max().item() < 0.05 * ref.abs().max().item()
