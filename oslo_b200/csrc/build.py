@@ -53,10 +53,11 @@ def _stamp(src: Path, flags) -> str:
     return h.hexdigest()
 
 
-def _compile_one(src: Path, verbose: bool) -> Path:
-    obj = OBJ_DIR / (src.stem + ".o")
-    stamp_file = OBJ_DIR / (src.stem + ".stamp")
-    flags = list(NVCC_FLAGS)
+def _compile_one(src: Path, verbose: bool, debug_bounds: bool = False) -> Path:
+    obj_dir = OBJ_DIR.with_name("obj_debug") if debug_bounds else OBJ_DIR
+    obj = obj_dir / (src.stem + ".o")
+    stamp_file = obj_dir / (src.stem + ".stamp")
+    flags = list(NVCC_FLAGS) + (["-DOSLO_DEBUG_BOUNDS"] if debug_bounds else [])
     if verbose:
         flags += ["-Xptxas", "-v"]
     stamp = _stamp(src, flags)
@@ -72,12 +73,15 @@ def _compile_one(src: Path, verbose: bool) -> Path:
     return obj
 
 
-def build_cuda(verbose: bool = False) -> Path:
-    OBJ_DIR.mkdir(parents=True, exist_ok=True)
+def build_cuda(verbose: bool = False, debug_bounds: bool = False) -> Path:
+    """Compile every ``*.cu`` and link the CUDA library.  ``debug_bounds`` builds ``liboslo_b200_cuda_debug.so`` with
+    ``-DOSLO_DEBUG_BOUNDS``: index checks that record a status code and skip the access (never trap); it is loaded instead
+    of the normal library when ``OSLO_B200_DEBUG_BOUNDS=1``."""
+    (OBJ_DIR.with_name("obj_debug") if debug_bounds else OBJ_DIR).mkdir(parents=True, exist_ok=True)
     sources = sorted(CSRC.glob("*.cu"))
     with cf.ThreadPoolExecutor(max_workers=min(8, len(sources) or 1)) as pool:
-        objs = list(pool.map(lambda s: _compile_one(s, verbose), sources))
-    out = LIB_DIR / "liboslo_b200_cuda.so"
+        objs = list(pool.map(lambda s: _compile_one(s, verbose, debug_bounds), sources))
+    out = LIB_DIR / ("liboslo_b200_cuda_debug.so" if debug_bounds else "liboslo_b200_cuda.so")
     newest = max(o.stat().st_mtime for o in objs)
     if not out.exists() or out.stat().st_mtime < newest:
         cmd = [_nvcc(), "-shared", "-o", str(out), *map(str, objs), "-lcudart", "-Xcompiler", "-fPIC"]
@@ -108,4 +112,7 @@ def build_all(verbose: bool = False):
 
 
 if __name__ == "__main__":
-    print(*build_all(verbose="-v" in sys.argv), sep="\n")
+    if "--debug-bounds" in sys.argv:
+        print(build_cuda(verbose="-v" in sys.argv, debug_bounds=True))
+    else:
+        print(*build_all(verbose="-v" in sys.argv), sep="\n")

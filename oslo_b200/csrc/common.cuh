@@ -23,7 +23,22 @@ enum : int {
   kStatusWaitTimeoutEpilogue = 3,
   kStatusPeerFlagTimeout = 4,
   kStatusBadArgument = 5,
+  kStatusBoundsViolation = 6,  // debug builds (-DOSLO_DEBUG_BOUNDS): an index left its buffer; the access was skipped
 };
+
+// Debug bounds checks.  With -DOSLO_DEBUG_BOUNDS (python -m oslo_b200.csrc.build --debug-bounds; OSLO_B200_DEBUG_BOUNDS=1
+// loads that library) OSLO_IN_BOUNDS(cond, status) records kStatusBoundsViolation in the status word when `cond` is false
+// and evaluates to false, so the caller SKIPS the access: no trap, no assert, the context stays usable and the host reads
+// the status.  In normal builds it is the constant `true` and costs nothing.
+#ifdef OSLO_DEBUG_BOUNDS
+OSLO_DEVINL bool bounds_record(bool ok, int* status) {
+  if (!ok && status) atomicCAS(status, kStatusOk, kStatusBoundsViolation);
+  return ok;
+}
+#define OSLO_IN_BOUNDS(cond, status) (::oslo::bounds_record((cond), (status)))
+#else
+#define OSLO_IN_BOUNDS(cond, status) (true)
+#endif
 
 OSLO_DEVINL uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 

@@ -293,6 +293,7 @@ static __device__ __noinline__ void ag_copy_role(const GemmParams& p, const Fuse
     if (n < my_count) {
       long long off; uint32_t bytes; int c; bool last;
       locate(n, off, bytes, c, last);
+      if (!OSLO_IN_BOUNDS(off >= 0 && off + bytes <= shard_bytes && c < cps, fp.status)) { ok = false; break; }
       // slot n % depth last held piece n - depth; the store groups committed since then are pieces n - depth + 1 ..
       // n - 1 - ahead, so that many may still be pending when its own stores have finished reading the slot
       if (n >= kCopyDepth) tma_store_wait_read<kCopyDepth - 1 - kCopyAhead>();
@@ -357,6 +358,8 @@ static __device__ __noinline__ void ag_mc_copy_role(const GemmParams& p, const F
   for (int c = 0; c < cps; ++c) {
     const uint4* s = src + c * chunk_vecs;
     uint4* d = dst + c * chunk_vecs;
+    if (!OSLO_IN_BOUNDS(static_cast<long long>(c + 1) * chunk_vecs * 16 <= static_cast<long long>(fp.ag_shard_rows) * fp.k_elems * 2,
+                        fp.status)) return;
     long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     for (; i + (kUnroll - 1) * stride < chunk_vecs; i += kUnroll * stride) {
       uint4 v[kUnroll];
@@ -402,6 +405,7 @@ static __device__ __noinline__ void rs_mc_reduce_role(const GemmParams& p, const
       return;
     }
     const long long row0 = static_cast<long long>(fp.rank) * fp.shard_rows + static_cast<long long>(c) * fp.chunk_rows;
+    if (!OSLO_IN_BOUNDS(row0 + fp.chunk_rows <= p.M && (c + 1) * fp.chunk_rows <= fp.shard_rows, fp.status)) return;
     const uint4* src = static_cast<const uint4*>(fp.mc_slots) + row0 * vec_per_row;       // partial buffer [T, N]
     uint4* dst = static_cast<uint4*>(fp.rs_out) + static_cast<long long>(c) * chunk_vecs;  // out [T / tp, N]
     auto finish = [&](long long i, uint4 v) {
@@ -533,6 +537,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         int b, mb, nb;
         if constexpr (MODE == kModePlain) tile_coords(tile, p, b, mb, nb);
         else fused_tile_coords<MODE>(tile, p, fp, b, mb, nb);
+        if (!OSLO_IN_BOUNDS(mb >= 0 && mb < p.m_blocks && nb >= 0 && nb < p.n_blocks && b >= 0 && b < p.batch, p.status)) {
+          *abort_flag = 1;  // the other roles leave through their bounded waits
+          ok = false;
+          break;
+        }
         const int m0 = mb * kBlockM, n0 = nb * BLOCK_N;
         const int bi = b % p.batch_inner, bo = b / p.batch_inner;
         int kb0, kb1;
@@ -825,6 +834,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               const int dest = rs_dest;
               const int r_in = fp.rs_along_n ? m0 : m0 - dest * fp.shard_rows;
               const int c_in = fp.rs_along_n ? col0 - dest * fp.shard_cols : col0;
+              const int rows_in_slot = fp.rs_along_n ? p.M : fp.shard_rows;
+              if (!OSLO_IN_BOUNDS(dest >= 0 && dest < fp.tp && r_in >= 0 && r_in + q * 32 < rows_in_slot && c_in >= 0 &&
+                                  c_in < fp.slot_ld, fp.status)) {
+                // debug builds: a tile that would leave its slot is not stored
+              } else
               if (rs_own) tma_store_4d(&tmC, sbuf_ptr, c_in, r_in + q * 32, 0, 0);  // final values
               else if (fp.mc_slots != nullptr) tma_store_4d(&peer_maps.m[fp.rank], sbuf_ptr, col0, m0 + q * 32, 0, 0);  // local partial [T, N]
               else tma_store_4d(&peer_maps.m[dest], sbuf_ptr, c_in, fp.rank * fp.slot_rows + r_in + q * 32, 0, 0);

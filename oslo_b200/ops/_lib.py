@@ -55,12 +55,14 @@ def cuda_lib():
 
 @lru_cache(maxsize=None)
 def _load_cuda_lib() -> ctypes.CDLL:
-    path = _LIB_DIR / "liboslo_b200_cuda.so"
+    # OSLO_B200_DEBUG_BOUNDS=1: the library built with index checks that record a status code and skip the access
+    debug = os.environ.get("OSLO_B200_DEBUG_BOUNDS", "0") == "1"
+    path = _LIB_DIR / ("liboslo_b200_cuda_debug.so" if debug else "liboslo_b200_cuda.so")
     if not path.exists():
         if os.environ.get("OSLO_B200_AUTOBUILD", "1") == "1":
             from oslo_b200.csrc.build import build_cuda
 
-            build_cuda()
+            build_cuda(debug_bounds=debug)
         if not path.exists():
             raise NativeLibraryMissing(
                 f"{path} not found: run `python -m oslo_b200.csrc.build` (needs nvcc) before using the CUDA ops"
@@ -120,5 +122,6 @@ def check_status(device=None) -> None:
     code = int(status_word(device).item())
     if code != 0:
         status_word(device).zero_()
-        names = {1: "TMA producer wait", 2: "MMA wait", 3: "epilogue wait", 4: "peer flag wait", 5: "bad argument"}
+        names = {1: "TMA producer wait", 2: "MMA wait", 3: "epilogue wait", 4: "peer flag wait", 5: "bad argument",
+                 6: "index out of bounds (debug build; the access was skipped)"}
         raise RuntimeError(f"oslo_b200 kernel reported status {code} ({names.get(code, 'unknown')})")
