@@ -22,6 +22,8 @@
 //
 // Replaces the unfused QK^T -> mask -> softmax -> dropout -> PV chains of the reference
 // (oslo/transformers/models/gpt2/modeling_gpt2.py:113-165; lightseq2 csrc/layers_new/sdpa_layer.cpp:10-66).
+#include <cstdio>
+
 #include "gemm_core.cuh"
 
 namespace oslo {
@@ -333,7 +335,17 @@ static int launch_attention_pingpong(const CUtensorMap& tq, const CUtensorMap& t
   const int grid = p.batch * p.heads * (p.seq / (2 * kPPRows));
   kern<<<grid, kPPThreads, Cfg::kSmem, stream>>>(tq, tk, tv, to, p);
   const cudaError_t err = cudaGetLastError();
-  return err == cudaSuccess ? 0 : -(1000 + static_cast<int>(err));  // the CUDA error code of a refused launch
+  if (err != cudaSuccess) {
+    cudaFuncAttributes fa{};
+    cudaFuncGetAttributes(&fa, kern);
+    fprintf(stderr,
+            "attention_fwd_pingpong launch refused: %s (grid %d, %d threads, %d B dynamic smem; kernel: %d regs, max %d "
+            "threads / block, %zu B static smem, %d B max dynamic smem)\n",
+            cudaGetErrorString(err), grid, kPPThreads, Cfg::kSmem, fa.numRegs, fa.maxThreadsPerBlock, fa.sharedSizeBytes,
+            fa.maxDynamicSharedSizeBytes);
+    return -(1000 + static_cast<int>(err));
+  }
+  return 0;
 }
 
 }  // namespace oslo

@@ -207,3 +207,64 @@ def test_cpu_gemms_match_torch():
     y = quantized_linear(x, w_q, w_clip, x_clip=4.0, bias=torch.ones(48))
     ref = x.clamp(-4, 4) @ w.t() + 1.0
     assert (y - ref).abs().max().item() < 0.05 * ref.abs().max().item()
+
+
+def test_layer_id_interface_with_flat_buffers():
+    from oslo_b200.lightseq import registry as R
+    from oslo_b200.lightseq.layers import LSLayerConfig, LSTransformerEncoderLayer
+
+    torch.manual_seed(6)
+    R.clear()
+    assert R.create_transformer_encoder_layer(3, max_batch_tokens=64, max_seq_len=16, hidden_dim=32, num_heads=4,
+                                              intermediate_size=64, is_pre_ln=True, activation_fn="gelu") == 0
+    n = R.layer_param_numel("TransformerEncoderLayer", 3)
+    flat_w, flat_g = torch.zeros(n), torch.zeros(n)
+    before = [p.detach().clone() for p in R.get_layer("TransformerEncoderLayer", 3).parameters()]
+    R.assign_layer_weight_grad(flat_w, flat_g, "TransformerEncoderLayer", 3)
+    assert torch.equal(torch.cat([b.flatten() for b in before]), flat_w)  # the values moved into the flat buffer
+    x = torch.randn(2, 5, 32)
+    (y,) = R.transformer_encoder_layer_fw(3, x, torch.zeros(2, 5), True)
+    (gx,) = R.transformer_encoder_layer_bw(3, torch.ones_like(y))
+    # reference: the same module driven directly
+    ref = LSTransformerEncoderLayer(LSLayerConfig(max_batch_tokens=64, max_seq_len=16, hidden_size=32, nhead=4, intermediate_size=64))
+    ref.load_state_dict(R.get_layer("TransformerEncoderLayer", 3).state_dict())
+    xr = x.clone().requires_grad_()
+    yr = ref(xr)
+    yr.backward(torch.ones_like(yr))
+    assert torch.allclose(y, yr, atol=1e-6) and torch.allclose(gx, xr.grad, atol=1e-6)
+    assert torch.allclose(flat_g, torch.cat([p.grad.flatten() for p in ref.parameters()]), atol=1e-6)
+    # an update of the flat tensor is an update of the layer
+    flat_w.sub_(0.1 * flat_g)
+    (y2,) = R.transformer_encoder_layer_fw(3, x, None, False)
+    assert not torch.allclose(y2, y)
+    with pytest.raises(ValueError):
+        R.assign_layer_weight_grad(torch.zeros(3), torch.zeros(3), "TransformerEncoderLayer", 3)
+    R.clear()
+
+
+def test_cli_train_validate_generate_export(tmp_path, capsys):
+    from oslo_b200.lightseq import cli
+    from oslo_b200.lightseq.export import read_header
+
+    data = os.path.join(tmp_path, "pairs.tsv")
+    g = torch.Generator().manual_seed(7)
+    with open(data, "w") as f:
+        for _ in range(48):
+            s = torch.randint(3, 20, (5,), generator=g).tolist()
+            f.write(" ".join(map(str, s)) + "\t" + " ".join(map(str, s)) + "\n")
+    ckpt = os.path.join(tmp_path, "m.pt")
+    assert cli.main(["train", "--data", data, "--save", ckpt, "--epochs", "30", "--batch-size", "16", "--lr", "0.003", "--hidden", "32",
+                     "--heads", "4", "--layers", "1", "--max-len", "16", "--device", "cpu"]) == 0
+    losses = [float(l.split("loss")[1]) for l in capsys.readouterr().out.splitlines() if l.startswith("epoch")]
+    assert losses[-1] < 0.5 * losses[0]
+    assert cli.main(["validate", "--load", ckpt, "--data", data, "--device", "cpu"]) == 0
+    assert "perplexity" in capsys.readouterr().out
+    src = os.path.join(tmp_path, "src.txt")
+    with open(src, "w") as f:
+        f.write("4 5 6 7 8\n9 10 11 12 13\n")
+    assert cli.main(["generate", "--load", ckpt, "--input", src, "--beam", "2", "--max-new-tokens", "8", "--device", "cpu"]) == 0
+    lines = capsys.readouterr().out.strip().splitlines()
+    assert len(lines) == 2 and all(l.replace(" ", "").isdigit() for l in lines if l)
+    out = os.path.join(tmp_path, "m.lsw")
+    assert cli.main(["export", "--load", ckpt, "--out", out, "--int8"]) == 0
+    assert read_header(out)[0]["quantized"]
