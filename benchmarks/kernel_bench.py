@@ -164,8 +164,14 @@ def bench_attention(a):
                    f"H{a.heads}x{a.head_dim}", ms, flops=fl)
     out = qkv_attention(qkv, a.heads, a.head_dim, "h3d", True)
     g = torch.randn_like(out)
-    ms = time_op(lambda: torch.autograd.grad(out, qkv, g, retain_graph=True), a.iters)
-    report(f"attention_bwd B{a.batch} S{a.seq} H{a.heads}x{a.head_dim}", ms, flops=2.5 * fl)
+    from oslo_b200.ops.attention import set_backward_groups
+
+    for groups in (1, 2):
+        set_backward_groups(groups)
+        ms = time_op(lambda: torch.autograd.grad(out, qkv, g, retain_graph=True), a.iters)
+        report(f"attention_bwd ({groups} element-wise group{'s' if groups > 1 else ''} in dK/dV) B{a.batch} S{a.seq} "
+               f"H{a.heads}x{a.head_dim}", ms, flops=2.5 * fl)
+    set_backward_groups(1)
 
 
 KERNELS = {"gemm": bench_gemm, "layernorm": bench_layernorm, "softmax": bench_softmax, "bias_gelu": bench_bias_gelu,

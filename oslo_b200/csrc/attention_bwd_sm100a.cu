@@ -12,6 +12,8 @@
 // (rows = K), so every tile is loaded once and used in both roles (K_j for S and for dQ; Q_i / dO_i for S^T / dP^T and
 // for dK / dV).  Warp roles as in the forward kernel: warp 0 TMA, warp 1 MMA issue, warps 2-5 the element-wise math.
 // All waits are bounded.
+#include <cstdlib>
+
 #include "gemm_core.cuh"
 
 namespace oslo {
@@ -308,41 +310,45 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 namespace oslo {
 
 // ------------------------------------------------------------------------------------------------ dK, dV
-template <int HD>
+// NG = number of element-wise warp groups (4 warps each).  With two groups consecutive query tiles go to alternating
+// groups and P^T / dS^T are double-buffered in shared memory, so the exponentials of tile t + 1 run while the tensor cores
+// accumulate tile t (and compute the scores of tile t + 2).
+template <int HD, int NG>
 struct DkvCfg {
   static constexpr int kHalves = HD / 64;
+  static constexpr int kThreads = 64 + 128 * NG;
   static constexpr int kKv = 128 * HD * 2;      // K_j / V_j tile
   static constexpr int kQt = 64 * HD * 2;       // Q_i / dO_i tile of 64 query rows
   static constexpr int kPt = 128 * 64 * 2;      // P^T / dS^T tile [128 keys, 64 queries]
-  static constexpr int kSmem = 2 * kKv + 4 * kQt + 2 * kPt + 4096 /*lse, delta per warp*/ + 1024 + 256;
+  static constexpr int kSmem = 2 * kKv + 4 * kQt + 2 * NG * kPt + 4096 * NG /*lse, delta per warp*/ + 1024 + 256;
 };
 
-template <int HD>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+template <int HD, int NG>
+__global__ void __launch_bounds__(64 + 128 * NG, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                     const __grid_constant__ CUtensorMap tmDK, const __grid_constant__ CUtensorMap tmDV,
                     const AttnBwdParams p) {
-  using Cfg = DkvCfg<HD>;
+  using Cfg = DkvCfg<HD, NG>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
   uint8_t* sV = sK + Cfg::kKv;
   uint8_t* sQ = sV + Cfg::kKv;            // [2 stages]
   uint8_t* sDO = sQ + 2 * Cfg::kQt;       // [2 stages]
-  uint8_t* sP = sDO + 2 * Cfg::kQt;
-  uint8_t* sDS = sP + Cfg::kPt;
-  float* sStat = reinterpret_cast<float*>(sDS + Cfg::kPt);  // [4 warps][2 stages][lse 64 | delta 64]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sStat) + 4096);
+  uint8_t* sP = sDO + 2 * Cfg::kQt;       // [NG stages]
+  uint8_t* sDS = sP + NG * Cfg::kPt;      // [NG stages]
+  float* sStat = reinterpret_cast<float*>(sDS + NG * Cfg::kPt);  // [4 NG warps][2 stages][lse 64 | delta 64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sStat) + 4096 * NG);
   uint64_t* kv_full = bars;
   uint64_t* q_full = bars + 1;    // [2] Q_i and dO_i landed
   uint64_t* q_empty = bars + 3;   // [2]
   uint64_t* s_full = bars + 5;    // [2] S^T, dP^T computed
   uint64_t* s_empty = bars + 7;   // [2]
-  uint64_t* p_full = bars + 9;    // P^T, dS^T written (4 warps)
-  uint64_t* p_empty = bars + 10;  // dV, dK products done with them
-  uint64_t* out_full = bars + 11;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* p_full = bars + 9;    // [NG] P^T, dS^T written (4 warps)
+  uint64_t* p_empty = bars + 11;  // [NG] dV, dK products done with them
+  uint64_t* out_full = bars + 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -358,7 +364,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4); }
-    mbar_init(p_full, 4); mbar_init(p_empty, 1); mbar_init(out_full, 1);
+    for (int i = 0; i < NG; ++i) { mbar_init(&p_full[i], 4); mbar_init(&p_empty[i], 1); }
+    mbar_init(out_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -399,7 +406,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       bool ok = mbar_wait_bounded(kv_full, 0, abort_flag);
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), p_addr = smem_u32(sP), ds_addr = smem_u32(sDS);
       int st = 0, sb = 0;
-      uint32_t ph = 0, sph = 0, pph = 0;
+      uint32_t ph = 0, sph = 0;
       const int n_tiles = qt_end - qt_first;
       auto issue_scores = [&](int stage) -> bool {
         if (!mbar_wait_bounded(&q_full[stage], ph, abort_flag) || !mbar_wait_bounded(&s_empty[sb], sph ^ 1, abort_flag)) return false;
@@ -436,22 +443,22 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       for (int t = 0; t < n_tiles && ok; ++t) {
         if (t + 1 < n_tiles) ok = next_scores();
         if (!ok) break;
-        if (!mbar_wait_bounded(p_full, pph, abort_flag)) { ok = false; break; }
+        const int ps = t % NG;  // P^T / dS^T stage of this tile (the group that wrote it)
+        if (!mbar_wait_bounded(&p_full[ps], static_cast<uint32_t>((t / NG) & 1), abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t q_addr = smem_u32(sQ + st * Cfg::kQt), do_addr = smem_u32(sDO + st * Cfg::kQt);
 #pragma unroll
         for (int kk = 0; kk < 64 / 16; ++kk) {
-          umma_f16(tm_dv, make_smem_desc_sw128(p_addr + kk * 32, 16, 1024),
+          umma_f16(tm_dv, make_smem_desc_sw128(p_addr + ps * Cfg::kPt + kk * 32, 16, 1024),
                    make_smem_desc_sw128(do_addr + kk * 2048, 8192, 1024), idesc_acc, (t > 0 || kk > 0) ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < 64 / 16; ++kk) {
-          umma_f16(tm_dk, make_smem_desc_sw128(ds_addr + kk * 32, 16, 1024),
+          umma_f16(tm_dk, make_smem_desc_sw128(ds_addr + ps * Cfg::kPt + kk * 32, 16, 1024),
                    make_smem_desc_sw128(q_addr + kk * 2048, 8192, 1024), idesc_acc, (t > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&q_empty[st]);
-        umma_commit(p_empty);
-        pph ^= 1;
+        umma_commit(&p_empty[ps]);
         if (++st == 2) { st = 0; }
       }
       if (ok) umma_commit(out_full);
@@ -459,22 +466,28 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   } else {
     const int q = warp & 3;
+    const int grp = (warp - 2) >> 2;  // element-wise group: takes the tiles t with t % NG == grp
     const int row = q * 32 + lane;  // key row inside the block
     const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
     const bool bf = p.is_bf16 != 0;
-    int sb = 0;
-    uint32_t sph = 0, peph = 0;
     bool ok = true;
-    for (int i = qt_first; i < qt_end && ok; ++i) {
+    for (int t = grp; qt_first + t < qt_end && ok; t += NG) {
+      const int i = qt_first + t;
+      const int sb = t & 1;                                       // tensor-memory buffer of the scores of tile t
+      const uint32_t sph = static_cast<uint32_t>((t >> 1) & 1);  // its phase
+      const int ps = t % NG;                                      // shared-memory stage for P^T / dS^T
+      const uint32_t peph = static_cast<uint32_t>((t / NG) & 1);
+      uint8_t* const sPt = sP + ps * Cfg::kPt;
+      uint8_t* const sDSt = sDS + ps * Cfg::kPt;
       // row statistics of this query tile (the same for every key row): stage them through shared memory
-      float* stat = sStat + ((warp - 2) * 2 + sb) * 128;  // a private copy per warp: no barrier between warps needed
+      float* stat = sStat + ((warp - 2) * 2 + ((t / NG) & 1)) * 128;  // a private copy per warp: no barrier between warps needed
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         stat[lane + 32 * u] = p.lse[stat_base + i * 64 + lane + 32 * u] * 1.4426950408889634f;
         stat[64 + lane + 32 * u] = p.delta[stat_base + i * 64 + lane + 32 * u];
       }
       __syncwarp();
-      if (!mbar_wait_bounded(&s_full[sb], sph, abort_flag) || !mbar_wait_bounded(p_empty, peph ^ 1, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_bounded(&s_full[sb], sph, abort_flag) || !mbar_wait_bounded(&p_empty[ps], peph ^ 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const bool diag = p.causal && (i * 64 < k0 + 128);  // some (query, key) pairs of this tile are masked
 #pragma unroll
@@ -503,18 +516,18 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
           const int chunk = (c * 32 + g * 8) / 8;
           const int off = row * 128 + ((chunk ^ (row & 7)) << 4);
-          *reinterpret_cast<uint4*>(sP + off) = make_uint4(pk_p[0], pk_p[1], pk_p[2], pk_p[3]);
-          *reinterpret_cast<uint4*>(sDS + off) = make_uint4(pk_d[0], pk_d[1], pk_d[2], pk_d[3]);
+          *reinterpret_cast<uint4*>(sPt + off) = make_uint4(pk_p[0], pk_p[1], pk_p[2], pk_p[3]);
+          *reinterpret_cast<uint4*>(sDSt + off) = make_uint4(pk_d[0], pk_d[1], pk_d[2], pk_d[3]);
         }
       }
       tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) { mbar_arrive(&s_empty[sb]); mbar_arrive(p_full); }
-      peph ^= 1;
-      if (++sb == 2) { sb = 0; sph ^= 1; }
+      if (lane == 0) { mbar_arrive(&s_empty[sb]); mbar_arrive(&p_full[ps]); }
     }
-    if (ok && mbar_wait_bounded(out_full, 0, abort_flag)) {
+    if (grp != 0) {
+      // the first group alone writes dV and dK out (its four warps cover all 128 key rows)
+    } else if (ok && mbar_wait_bounded(out_full, 0, abort_flag)) {
       tc_fence_after();
       uint8_t* stage = sQ + q * (Cfg::kHalves * 4096);  // the query-tile ring is free now
 #pragma unroll 1
@@ -565,6 +578,18 @@ static int set_smem(K kern, int bytes) {
 
 // q, k, v, o, d_o, dq, dk, dv: [batch, seq, heads, head_dim] views given by element strides (token, head, batch).
 // lse: [batch, heads, seq] from the forward pass; delta: [batch, heads, seq] scratch written here.
+// Element-wise warp groups of the dK / dV kernel (1 or 2); OSLO_B200_ATTN_BWD_GROUPS sets the start value.
+static int g_dkv_groups = [] {
+  const char* e = getenv("OSLO_B200_ATTN_BWD_GROUPS");
+  return (e && e[0] == '2') ? 2 : 1;
+}();
+
+extern "C" int oslo_attention_backward_set_groups(int groups) {
+  if (groups != 1 && groups != 2) return -1;
+  g_dkv_groups = groups;
+  return 0;
+}
+
 extern "C" int oslo_attention_backward(const void* q, const void* k, const void* v, const void* o, const void* d_o, void* dq,
                                        void* dk, void* dv, const float* lse, float* delta, int batch, int seq, int heads,
                                        int head_dim, const long long* strides /* 8 x (tok, head, batch) */, float scale,
@@ -598,15 +623,19 @@ extern "C" int oslo_attention_backward(const void* q, const void* k, const void*
   static bool configured = false;
   if (!configured) {
     if (set_smem(attn_bwd_dq_kernel<128>, DqCfg<128>::kSmem) || set_smem(attn_bwd_dq_kernel<64>, DqCfg<64>::kSmem) ||
-        set_smem(attn_bwd_dkv_kernel<128>, DkvCfg<128>::kSmem) || set_smem(attn_bwd_dkv_kernel<64>, DkvCfg<64>::kSmem))
+        set_smem(attn_bwd_dkv_kernel<128, 1>, DkvCfg<128, 1>::kSmem) || set_smem(attn_bwd_dkv_kernel<64, 1>, DkvCfg<64, 1>::kSmem) ||
+        set_smem(attn_bwd_dkv_kernel<128, 2>, DkvCfg<128, 2>::kSmem) || set_smem(attn_bwd_dkv_kernel<64, 2>, DkvCfg<64, 2>::kSmem))
       return -3;
     configured = true;
   }
+  const int groups = g_dkv_groups;
   if (head_dim == 128) {
-    attn_bwd_dkv_kernel<128><<<grid, kBwdThreads, DkvCfg<128>::kSmem, st>>>(tq64, tk128, tv128, tdo64, tdk, tdv, p);
+    if (groups == 2) attn_bwd_dkv_kernel<128, 2><<<grid, DkvCfg<128, 2>::kThreads, DkvCfg<128, 2>::kSmem, st>>>(tq64, tk128, tv128, tdo64, tdk, tdv, p);
+    else attn_bwd_dkv_kernel<128, 1><<<grid, DkvCfg<128, 1>::kThreads, DkvCfg<128, 1>::kSmem, st>>>(tq64, tk128, tv128, tdo64, tdk, tdv, p);
     attn_bwd_dq_kernel<128><<<grid, kBwdThreads, DqCfg<128>::kSmem, st>>>(tq128, tk128, tv128, tdo128, tdq, p);
   } else {
-    attn_bwd_dkv_kernel<64><<<grid, kBwdThreads, DkvCfg<64>::kSmem, st>>>(tq64, tk128, tv128, tdo64, tdk, tdv, p);
+    if (groups == 2) attn_bwd_dkv_kernel<64, 2><<<grid, DkvCfg<64, 2>::kThreads, DkvCfg<64, 2>::kSmem, st>>>(tq64, tk128, tv128, tdo64, tdk, tdv, p);
+    else attn_bwd_dkv_kernel<64, 1><<<grid, DkvCfg<64, 1>::kThreads, DkvCfg<64, 1>::kSmem, st>>>(tq64, tk128, tv128, tdo64, tdk, tdv, p);
     attn_bwd_dq_kernel<64><<<grid, kBwdThreads, DqCfg<64>::kSmem, st>>>(tq128, tk128, tv128, tdo128, tdq, p);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;

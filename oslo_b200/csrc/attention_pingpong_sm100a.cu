@@ -57,7 +57,7 @@ struct AttnPPCfg {
 };
 
 template <int HD>
-__global__ void __maxnreg__(192)
+__global__ void __launch_bounds__(kPPThreads, 1)
 attention_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
                               const AttnPPParams p) {
@@ -252,22 +252,23 @@ attention_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQ, const __g
           tmem_st_wait();
         }
       }
-      // probabilities against the kept maximum, packed two per 32-bit column over the first 64 columns of S
+      // probabilities against the kept maximum, packed two per 32-bit column over the first 64 columns of S; 32 scores
+      // (16 packed columns) at a time so few registers are live next to the scores
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t pk[32];
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int col = c * 64 + 2 * i;
-          float a0 = ex2_fast(__uint_as_float(r[col >> 5][col & 31]) * p.scale_log2 - m);
-          float a1 = ex2_fast(__uint_as_float(r[(col + 1) >> 5][(col + 1) & 31]) * p.scale_log2 - m);
+        for (int i = 0; i < 16; ++i) {
+          const int col = c * 32 + 2 * i;
+          float a0 = ex2_fast(__uint_as_float(r[c][2 * i]) * p.scale_log2 - m);
+          float a1 = ex2_fast(__uint_as_float(r[c][2 * i + 1]) * p.scale_log2 - m);
           if (diag && col > row) a0 = 0.f;
           if (diag && col + 1 > row) a1 = 0.f;
           l += a0 + a1;
           if (p.is_bf16) { const __nv_bfloat162 hh = __floats2bfloat162_rn(a0, a1); pk[i] = *reinterpret_cast<const uint32_t*>(&hh); }
           else { const __half2 hh = __floats2half2_rn(a0, a1); pk[i] = *reinterpret_cast<const uint32_t*>(&hh); }
         }
-        tmem_st_32x32(tmem_s + c * 32, pk);
+        tmem_st_32x16(tmem_s + c * 16, pk);
       }
       tmem_st_wait();
       tc_fence_before();

@@ -217,6 +217,14 @@ def flash_attention_forward(q, k, v, causal: bool, scale: float, pingpong=None):
     return out.view(b, s, nh * hd), lse
 
 
+def set_backward_groups(groups: int) -> None:
+    """1 or 2 element-wise warp groups in the dK / dV kernel of the fused attention backward (2: consecutive query tiles
+    alternate between two groups of four warps and the probabilities are double-buffered)."""
+    rc = _lib.cuda_lib().oslo_attention_backward_set_groups(int(groups))
+    if rc:
+        raise ValueError("groups must be 1 or 2")
+
+
 def flash_attention_backward(q, k, v, out, d_out, lse, dq, dk, dv, causal: bool, scale: float):
     """Fused attention backward (``csrc/attention_bwd_sm100a.cu``).  All tensors ``[b, s, heads, hd]`` views; ``dq, dk, dv``
     are written (they may be slices of one fused buffer)."""

@@ -518,6 +518,39 @@ def test_linear_gelu_fused_epilogue():
         assert frac == 0.0, (name, frac, worst)
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("causal", [True, False])
+def test_flash_attention_backward_two_groups(causal, hd):
+    """The dK / dV kernel with two element-wise warp groups gives the gradients of the one-group kernel and of fp32."""
+    from oslo_b200.ops import _lib
+    from oslo_b200.ops.attention import attention, attention_reference, set_backward_groups
+
+    torch.manual_seed(71)
+    b, s, nh = 2, 768, 3  # 12 query tiles per key block: both groups and both buffer stages wrap several times
+    qkv0 = (torch.randn(b, s, nh, 3, hd, device=DEV) * 0.7).to(torch.bfloat16)
+    g = (torch.randn(b, s, nh * hd, device=DEV) * 0.5).to(torch.bfloat16)
+    grads = {}
+    try:
+        for groups in (1, 2):
+            set_backward_groups(groups)
+            qkv = qkv0.clone().requires_grad_()
+            out = attention(qkv[..., 0, :], qkv[..., 1, :], qkv[..., 2, :], causal=causal)
+            out.backward(g)
+            torch.cuda.synchronize()
+            _lib.check_status()
+            grads[groups] = qkv.grad.float()
+    finally:
+        set_backward_groups(1)
+    ref_in = qkv0.float().requires_grad_()
+    attention_reference(ref_in[..., 0, :], ref_in[..., 1, :], ref_in[..., 2, :], causal=causal).backward(g.float())
+    tol = 0.03 * ref_in.grad.abs().max().item()
+    for groups in (1, 2):
+        frac, worst = _close(grads[groups], ref_in.grad, rtol=3e-2, atol=tol)
+        assert frac < 1e-4, (groups, frac, worst)
+    frac, worst = _close(grads[2], grads[1], rtol=1e-2, atol=0.01 * ref_in.grad.abs().max().item())
+    assert frac < 1e-4, ("two groups vs one", frac, worst)
+
+
 @pytest.mark.parametrize("causal", [True])
 def test_flash_attention_seq_2048(causal):
     """Forward and backward at the benchmark's sequence length (16 key blocks per query block, causal skipping)."""
