@@ -171,7 +171,7 @@ def bench_attention(a):
         ms = time_op(lambda: torch.autograd.grad(out, qkv, g, retain_graph=True), a.iters)
         report(f"attention_bwd ({groups} element-wise group{'s' if groups > 1 else ''} in dK/dV) B{a.batch} S{a.seq} "
                f"H{a.heads}x{a.head_dim}", ms, flops=2.5 * fl)
-    set_backward_groups(1)
+    set_backward_groups(2)  # the default
 
 
 KERNELS = {"gemm": bench_gemm, "layernorm": bench_layernorm, "softmax": bench_softmax, "bias_gelu": bench_bias_gelu,

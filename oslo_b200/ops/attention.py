@@ -182,8 +182,9 @@ def flash_supported(q, k, v) -> bool:
 
 
 #: one-pass forward with two query tiles per CTA taking turns on the tensor cores (``csrc/attention_pingpong_sm100a.cu``)
-#: for sequence lengths that are multiples of 256; OSLO_B200_ATTN_PINGPONG=0 keeps the two-pass kernel everywhere
-PINGPONG = __import__("os").environ.get("OSLO_B200_ATTN_PINGPONG", "0") == "1"
+#: for sequence lengths that are multiples of 256 (measured 1.2 - 1.3x the two-pass kernel); OSLO_B200_ATTN_PINGPONG=0 keeps
+#: the two-pass kernel everywhere
+PINGPONG = __import__("os").environ.get("OSLO_B200_ATTN_PINGPONG", "1") == "1"
 
 
 def flash_attention_forward(q, k, v, causal: bool, scale: float, pingpong=None):

@@ -540,7 +540,7 @@ def test_flash_attention_backward_two_groups(causal, hd):
             _lib.check_status()
             grads[groups] = qkv.grad.float()
     finally:
-        set_backward_groups(1)
+        set_backward_groups(2)  # the default
     ref_in = qkv0.float().requires_grad_()
     attention_reference(ref_in[..., 0, :], ref_in[..., 1, :], ref_in[..., 2, :], causal=causal).backward(g.float())
     tol = 0.03 * ref_in.grad.abs().max().item()
