@@ -30,8 +30,18 @@ struct AttnBwdParams {
   int* status;
 };
 
+OSLO_DEVINL float ex2_approx(float x) {  // one special-function instruction; 2^-inf = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 OSLO_DEVINL uint32_t pack2(float a, float b, bool bf16) {
-  if (bf16) { const __nv_bfloat162 h = __floats2bfloat162_rn(a, b); return *reinterpret_cast<const uint32_t*>(&h); }
+  if (bf16) {
+    // bf16 pair by integer arithmetic (round half away from zero on the dropped 16 bits, then the two high halves): the
+    // float -> bf16 conversion instruction shares the special-function unit with the exponentials, integer adds do not
+    return __byte_perm(__float_as_uint(a) + 0x8000u, __float_as_uint(b) + 0x8000u, 0x7632);
+  }
   const __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<const uint32_t*>(&h);
 }
@@ -249,7 +259,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
               for (int u = 0; u < 2; ++u) {
                 const int i = g * 8 + 2 * e + u;
-                float pr = exp2f(__uint_as_float(rs[u2][i]) * p.scale_log2 - lse2);
+                float pr = ex2_approx(__uint_as_float(rs[u2][i]) * p.scale_log2 - lse2);
                 if (diag && c * 32 + i > row) pr = 0.f;
                 d[u] = pr * (__uint_as_float(rp[u2][i]) - dl) * p.scale;
               }
@@ -506,7 +516,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
               const int col = c * 32 + g * 8 + 2 * e + u;  // query inside the tile
-              float pr = exp2f(__uint_as_float(rs[g * 8 + 2 * e + u]) * p.scale_log2 - stat[col]);
+              float pr = ex2_approx(__uint_as_float(rs[g * 8 + 2 * e + u]) * p.scale_log2 - stat[col]);
               if (diag && k0 + row > i * 64 + col) pr = 0.f;
               pv[u] = pr;
               dv[u] = pr * (__uint_as_float(rp[g * 8 + 2 * e + u]) - stat[64 + col]) * p.scale;

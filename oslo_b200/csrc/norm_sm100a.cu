@@ -92,6 +92,29 @@ OSLO_DEVINL float block_sum(float v, float* scratch) {
   return total;
 }
 
+// Two sums with ONE barrier: the scratch is double-buffered by call parity, so the write of call n + 2 cannot overtake a
+// read of call n (every thread passes the barrier of call n + 1 in between, after its reads of call n).
+template <int THREADS>
+OSLO_DEVINL float2 block_sum2(float a, float b, float2* scratch /* [2][THREADS / 32] */, int parity) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    a += __shfl_xor_sync(0xffffffffu, a, o);
+    b += __shfl_xor_sync(0xffffffffu, b, o);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float2* buf = scratch + parity * (THREADS / 32);
+  if (lane == 0) buf[warp] = make_float2(a, b);
+  __syncthreads();
+  float2 total = make_float2(0.f, 0.f);
+#pragma unroll
+  for (int w = 0; w < THREADS / 32; ++w) {
+    const float2 v = buf[w];
+    total.x += v.x;
+    total.y += v.y;
+  }
+  return total;
+}
+
 // gamma / beta may be stored in T (same as x) or in fp32 ("mixed" variants of the reference).
 template <typename T, typename W, int THREADS, int ITERS, bool RMS>
 __global__ void __launch_bounds__(THREADS) norm_fwd_kernel(const T* __restrict__ x, const W* __restrict__ gamma,
@@ -170,7 +193,7 @@ __global__ void __launch_bounds__(THREADS) norm_bwd_kernel(const T* __restrict__
                                                            const float* __restrict__ rstd_in, const W* __restrict__ gamma,
                                                            T* __restrict__ dx, float* __restrict__ dgamma_part,
                                                            float* __restrict__ dbeta_part, int rows, int H) {
-  __shared__ float scratch[THREADS / 32];
+  __shared__ float2 scratch[2 * (THREADS / 32)];
   const int nvec = H >> 3;
   float acc_g[ITERS][8], acc_b[ITERS][8], g[ITERS][8];
 #pragma unroll
@@ -184,7 +207,22 @@ __global__ void __launch_bounds__(THREADS) norm_bwd_kernel(const T* __restrict__
       t.to_float(g[i]);
     }
   }
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+  // the next row's x and dy are requested before this row is reduced, so the loads overlap the barrier and the stores
+  Vec8<T> nx[ITERS], nd[ITERS];
+  auto fetch = [&](int row) {
+    const size_t off = static_cast<size_t>(row) * H;
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i) {
+      const int vi = threadIdx.x + i * THREADS;
+      if (vi < nvec) {
+        nx[i].load(x + off + vi * 8);
+        nd[i].load(dy + off + vi * 8);
+      }
+    }
+  };
+  if (static_cast<int>(blockIdx.x) < rows) fetch(blockIdx.x);
+  int parity = 0;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x, parity ^= 1) {
     const size_t off = static_cast<size_t>(row) * H;
     const float mean = RMS ? 0.f : mean_in[row];
     const float rstd = rstd_in[row];
@@ -194,12 +232,9 @@ __global__ void __launch_bounds__(THREADS) norm_bwd_kernel(const T* __restrict__
     for (int i = 0; i < ITERS; ++i) {
       const int vi = threadIdx.x + i * THREADS;
       if (vi < nvec) {
-        Vec8<T> t;
         float d[8];
-        t.load(x + off + vi * 8);
-        t.to_float(xh[i]);
-        t.load(dy + off + vi * 8);
-        t.to_float(d);
+        nx[i].to_float(xh[i]);
+        nd[i].to_float(d);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           xh[i][j] = (xh[i][j] - mean) * rstd;
@@ -211,8 +246,10 @@ __global__ void __launch_bounds__(THREADS) norm_bwd_kernel(const T* __restrict__
         }
       }
     }
-    const float m2 = block_sum<THREADS>(s2, scratch) / H;
-    const float m1 = RMS ? 0.f : block_sum<THREADS>(s1, scratch) / H;
+    if (row + static_cast<int>(gridDim.x) < rows) fetch(row + gridDim.x);
+    const float2 sums = block_sum2<THREADS>(s1, s2, scratch, parity);
+    const float m2 = sums.y / H;
+    const float m1 = RMS ? 0.f : sums.x / H;
 #pragma unroll
     for (int i = 0; i < ITERS; ++i) {
       const int vi = threadIdx.x + i * THREADS;

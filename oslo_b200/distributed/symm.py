@@ -206,9 +206,9 @@ class SymmetricWorkspace:
         #: address of the whole workspace through the group's NVSwitch multicast object (0: not bound)
         self.mc_base = 0
         self._symm_keep = None
-        # multicast pays once a shard would otherwise cross the links several times: at two ranks the peer-store kernels
-        # measured faster (one copy either way), so the default starts at four ranks; OSLO_B200_MULTIMEM_MIN_RANKS moves it
-        min_ranks = int(__import__("os").environ.get("OSLO_B200_MULTIMEM_MIN_RANKS", "4"))
+        # measured on the flagship step: multicast is ahead at eight ranks (47.5 vs 49.1 ms) and behind at four (63.8 vs 60.6)
+        # and two, where a shard crosses the links once or thrice either way; OSLO_B200_MULTIMEM_MIN_RANKS moves the threshold
+        min_ranks = int(__import__("os").environ.get("OSLO_B200_MULTIMEM_MIN_RANKS", "8"))
         mc = _multicast_alloc(pc, mode, self.total) if (USE_MULTIMEM and multimem and self.tp >= min_ranks) else None
         if mc is not None:
             tensor, hdl, ptrs, mc_ptr = mc
