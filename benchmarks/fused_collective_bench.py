@@ -11,8 +11,9 @@ For every linear of a GPT-NeoX-style block at the given tensor-parallel size (= 
 * the roofline: the slower of FLOPs / measured bf16 peak and bytes-that-must-cross-NVLink / 770 GB/s per direction,
   and ``fused`` as a fraction of it.
 
-Timing: CUDA events on the launching stream, 3 warm-up launches, a barrier before each timed launch, an L2 flush
-between launches, median of ``--iters``, MAX over ranks.  Rank 0 prints a markdown table.
+Timing: CUDA events on the launching stream, 3 warm-up launches, a barrier before each timed region, an L2 flush
+between regions, median of ``--iters``, MAX over ranks; ``--inner`` calls per region (1: an isolated call, including the
+skew between ranks after the barrier; more: the steady state inside a training step).  Rank 0 prints a markdown table.
 """
 from __future__ import annotations
 
@@ -45,6 +46,10 @@ def main():
     ap.add_argument("--ffn", type=int, default=8192)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--copy-ctas", type=int, default=None)
+    ap.add_argument("--inner", type=int, default=1,
+                    help="calls issued back to back per timed region (times are per call): 1 shows an isolated call including "
+                         "the skew between ranks after the barrier, larger values the steady state inside a step")
+    ap.add_argument("--ce", action="store_true", help="copy-engine transport (cudaMemcpyAsync on side streams, every SM multiplies)")
     ap.add_argument("--no-multimem", action="store_true", help="plain peer stores even where NVSwitch multicast is available")
     args = ap.parse_args()
 
@@ -60,7 +65,8 @@ def main():
     group = pc.get_group(ParallelMode.TENSOR_1D)
     T, H, F = args.tokens, args.hidden, args.ffn
     kw = {} if args.copy_ctas is None else {"copy_ctas": args.copy_ctas}
-    kw["multimem"] = not args.no_multimem
+    kw["multimem"] = not args.no_multimem and not args.ce
+    kw["ce_transport"] = args.ce
     assert symm.enable(pc, ParallelMode.TENSOR_1D, max_tokens=T, max_features=max(H, F // world, 3 * H // world), **kw)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
     tl = T // world
@@ -76,10 +82,11 @@ def main():
             dist.barrier(group=group)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            fn()
+            for _ in range(args.inner):
+                fn()
             e1.record()
             torch.cuda.synchronize()
-            ts.append(e0.elapsed_time(e1))
+            ts.append(e0.elapsed_time(e1) / args.inner)
         ts.sort()
         t = torch.tensor([ts[len(ts) // 2]], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
@@ -138,7 +145,7 @@ def main():
             k1 = H // world
             x1, w1, x2, w2 = rnd(T, k1), rnd(N, k1), rnd(T, K - k1), rnd(N, K - k1)
             out = torch.empty(tl, N, dtype=torch.bfloat16, device=dev)
-            fused = timed(lambda: fc.gemm_rs(x2, w2, pc, addend=matmul_nt(x1, w1)))
+            fused = timed(lambda: fc.gemm_rs(x2, w2, pc, pair=(x1, w1)))
 
             def comp():
                 dist.reduce_scatter_tensor(out, matmul_nt(x1, w1) + matmul_nt(x2, w2), group=group)
@@ -150,7 +157,7 @@ def main():
         rows.append((name, K, N, fused, nccl, alone, roof_ms, roof_ms / fused))
     if rank == 0:
         ws = fc.runtime().ws
-        print(f"transport: {'NVSwitch multicast (multimem.st / multimem.ld_reduce)' if ws.mc_base else 'peer stores'}"
+        print(f"transport: {'copy engine' if ws.ce_transport else 'NVSwitch multicast (multimem.st / multimem.ld_reduce)' if ws.mc_base else 'peer stores'}"
               + ("" if ws.mc_base or args.no_multimem else f" (multicast not available: {symm._multicast_alloc.last_error})")
               + f", {ws.copy_ctas} copy / reduce CTAs")
         print(f"tp = {world}, tokens = {T}, hidden = {H}, ffn = {F}; bf16; roofline = max(FLOPs / {peak:.0f} TFLOP/s ({src}), "

@@ -30,6 +30,17 @@ static int pick_block_n(int M, int N, int ctas, int max_bn) {
   return bn;
 }
 
+// Rows per hand-off chunk of the all-gather side: about 1024, at most 64 chunks over all shards, always a multiple of 128
+// dividing the shard.  Exported so that a host-driven transport flags the same chunks the kernel waits for.
+static int ag_chunk_rows(int Tl, int tp) {
+  int chunk_rows = Tl;
+  for (int cand = 1024; cand >= kBlockM; cand -= kBlockM) {
+    if (Tl % cand == 0 && (Tl / cand) * tp <= 64) { chunk_rows = cand; break; }
+  }
+  return chunk_rows;
+}
+extern "C" int oslo_ag_chunk_rows(int Tl, int tp) { return (Tl > 0 && tp > 0 && Tl % kBlockM == 0) ? ag_chunk_rows(Tl, tp) : -1; }
+
 #define OSLO_FUSED_LAUNCH(BN, MODE)                                                                       \
   (b_mn ? launch<BN, false, true, MODE>(ta, tb, tc, taux, p, grid, stream, fp, peer_maps_ptr)             \
         : launch<BN, false, false, MODE>(ta, tb, tc, taux, p, grid, stream, fp, peer_maps_ptr))
@@ -39,15 +50,22 @@ static int pick_block_n(int M, int N, int ctas, int max_bn) {
 extern "C" int oslo_ag_gemm(const void* x_shard, void* const* peer_xfull, const void* B, void* C, const void* bias, int T, int N,
                             int K, long long ldb, int b_mn, int is_bf16, int tp, int rank, int epoch,
                             void* const* peer_chunk_flag, int* chunk_arrive, int copy_ctas, int num_sms, int* status,
-                            void* stream_ptr, const int* epoch_ptr, void* mc_xfull) {
+                            void* stream_ptr, const int* epoch_ptr, void* mc_xfull, int external_push) {
+  // external_push: the shards are delivered (and the chunk flags raised) by somebody else, e.g. copy-engine transfers on
+  // other streams: no CTA copies, all of them multiply and take remote row chunks as their flags come up.
   // mc_xfull: the same gathered buffer through an NVSwitch multicast mapping over the group (or null): the copy CTAs then
   // store each piece of the shard once, to that address, instead of once per peer.
   if (tp > kMaxRanks || tp < 1 || T % tp) return -1;
   const int Tl = T / tp;
   if (Tl % kBlockM || N % 8 || K % 8 || ldb % 8 || (reinterpret_cast<uintptr_t>(x_shard) & 15)) return -5;
   bind_context_to_thread();
-  if (copy_ctas < 1) copy_ctas = 1;
-  if (copy_ctas > num_sms / 2) copy_ctas = num_sms / 2;
+  if (external_push) {
+    copy_ctas = 0;
+    mc_xfull = nullptr;
+  } else {
+    if (copy_ctas < 1) copy_ctas = 1;
+    if (copy_ctas > num_sms / 2) copy_ctas = num_sms / 2;
+  }
   const int gemm_ctas_max = num_sms - copy_ctas;
   const int block_n = pick_block_n(T, N, gemm_ctas_max, 256);
   GemmParams p{};
@@ -59,11 +77,7 @@ extern "C" int oslo_ag_gemm(const void* x_shard, void* const* peer_xfull, const 
   FusedParams fp;
   fp.tp = tp; fp.rank = rank; fp.shard_rows = Tl; fp.epoch = epoch; fp.copy_ctas = copy_ctas; fp.k_elems = K;
   fp.tiles_per_shard = (Tl / kBlockM) * p.n_blocks;
-  // hand-off granularity: about 1024 rows, at most 64 chunks over all shards, always a multiple of 128 dividing Tl
-  int chunk_rows = Tl;
-  for (int cand = 1024; cand >= kBlockM; cand -= kBlockM) {
-    if (Tl % cand == 0 && (Tl / cand) * tp <= 64) { chunk_rows = cand; break; }
-  }
+  const int chunk_rows = ag_chunk_rows(Tl, tp);
   fp.chunk_rows = chunk_rows;
   fp.ag_tp = tp; fp.ag_rank = rank; fp.ag_shard_rows = Tl; fp.ag_chunk_rows = chunk_rows; fp.ag_epoch = epoch;
   fp.ag_epoch_ptr = epoch_ptr;

@@ -144,3 +144,46 @@ extern "C" int oslo_ce_loss_grad(void* logits, const long long* target, const vo
 #undef OSLO_CE
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
+
+
+// x[r, :] *= g[r] in place, 16 bytes per thread and step (the cross-entropy backward: the gradient written into the logits
+// at forward time is scaled by the upstream per-token gradient).  V % 8 == 0, rows of x are `ld` elements apart.
+template <bool BF16>
+__global__ void row_scale_kernel(uint16_t* __restrict__ x, const float* __restrict__ g, long long rows, int V, long long ld) {
+  const int vec_per_row = V / 8;
+  const long long total = rows * vec_per_row;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vec_per_row;
+    const int c = static_cast<int>(i - r * vec_per_row) * 8;
+    const float s = g[r];
+    uint4* p = reinterpret_cast<uint4*>(x + r * ld + c);
+    uint4 v = *p;
+    uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (BF16) {
+        const float lo = __uint_as_float(w[j] << 16) * s, hi = __uint_as_float(w[j] & 0xffff0000u) * s;
+        const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+        w[j] = *reinterpret_cast<const uint32_t*>(&h);
+      } else {
+        const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+        const __half2 o = __floats2half2_rn(__low2float(h) * s, __high2float(h) * s);
+        w[j] = *reinterpret_cast<const uint32_t*>(&o);
+      }
+    }
+    *p = v;
+  }
+}
+
+extern "C" int oslo_row_scale(void* x, const float* g, long long rows, int V, long long ld, int is_bf16, int num_sms, void* stream) {
+  if (rows <= 0 || V <= 0) return 0;
+  if (V % 8 || ld % 8 || (reinterpret_cast<uintptr_t>(x) & 15)) return -1;
+  const long long total = rows * (V / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 16LL * num_sms) blocks = 16LL * num_sms;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (is_bf16) row_scale_kernel<true><<<static_cast<int>(blocks), 256, 0, st>>>(static_cast<uint16_t*>(x), g, rows, V, ld);
+  else row_scale_kernel<false><<<static_cast<int>(blocks), 256, 0, st>>>(static_cast<uint16_t*>(x), g, rows, V, ld);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

@@ -79,3 +79,82 @@ extern "C" int oslo_symm_barrier(void* const* peer_flags, int* local_flags, int 
   symm_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pf, local_flags, rank, tp, epoch, status, epoch_ptr);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
+
+
+// Final step of a reduce-scatter whose transport was the copy engine: every other rank's partial block already sits in
+// slot [source] of the local slot buffer (flag [source] holds the call epoch once that copy has landed).
+//     out[rows, N] = own[rows, N] + sum over sources s != rank of slots[s][rows, N]  (+ bias[N])
+// Blocks wait (bounded) for the flags of all sources, then stream 16-byte vectors; sums in fp32.
+__global__ void rs_fold_kernel(const uint16_t* __restrict__ own, const uint16_t* __restrict__ slots, const int* __restrict__ flags,
+                               int rank, int tp, long long rows, int N, uint16_t* __restrict__ out,
+                               const uint16_t* __restrict__ bias, int is_bf16, int epoch, const int* epoch_ptr, int* status) {
+  __shared__ int s_ok;
+  if (epoch_ptr) epoch = *epoch_ptr;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (static_cast<int>(threadIdx.x) < tp && static_cast<int>(threadIdx.x) != rank &&
+      !flag_wait_bounded(flags + threadIdx.x, epoch, nullptr, true)) s_ok = 0;
+  __syncthreads();
+  if (!s_ok) {
+    if (threadIdx.x == 0 && status) atomicCAS(status, kStatusOk, kStatusPeerFlagTimeout);
+    return;
+  }
+  const long long slot_elems = rows * N;
+  const long long nvec = slot_elems / 8;
+  const int vec_per_row = N / 8;
+  auto unpack = [&](const uint4& v, float* f) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (is_bf16) {
+        f[2 * j] = __uint_as_float(w[j] << 16);
+        f[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+      } else {
+        const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+        f[2 * j] = __low2float(h);
+        f[2 * j + 1] = __high2float(h);
+      }
+    }
+  };
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc[8], t[8];
+    unpack(*reinterpret_cast<const uint4*>(own + i * 8), acc);
+    for (int s = 0; s < tp; ++s) {
+      if (s == rank) continue;
+      unpack(*reinterpret_cast<const uint4*>(slots + s * slot_elems + i * 8), t);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += t[j];
+    }
+    if (bias) {
+      unpack(__ldg(reinterpret_cast<const uint4*>(bias + (i % vec_per_row) * 8)), t);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += t[j];
+    }
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (is_bf16) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        w[j] = *reinterpret_cast<const uint32_t*>(&h);
+      } else {
+        const __half2 h = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+        w[j] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+    }
+    *reinterpret_cast<uint4*>(out + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+// own, out: local [rows, N]; slots: the local slot buffer [tp, rows, N]; flags: local int[tp] written by the sources' copies.
+extern "C" int oslo_rs_fold(const void* own, const void* slots, const int* flags, int rank, int tp, long long rows, int N, void* out,
+                            const void* bias, int is_bf16, int epoch, const int* epoch_ptr, int* status, int num_sms, void* stream) {
+  if (tp > kMaxRanks || tp < 1 || rows <= 0 || N % 8) return -1;
+  const long long nvec = rows * N / 8;
+  long long blocks = (nvec + 255) / 256;
+  if (blocks > 4LL * num_sms) blocks = 4LL * num_sms;
+  rs_fold_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(own), static_cast<const uint16_t*>(slots), flags, rank, tp, rows, N, static_cast<uint16_t*>(out),
+      static_cast<const uint16_t*>(bias), is_bf16, epoch, epoch_ptr, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

@@ -35,6 +35,12 @@ _FLAG_BYTES = 4096
 USE_MULTIMEM = __import__("os").environ.get("OSLO_B200_MULTIMEM", "1") == "1"
 
 
+#: move the shards of the fused 1-D kernels with the copy engines (``cudaMemcpyAsync`` between peer mappings on side
+#: streams, flags written the same way) instead of with copy CTAs / epilogue stores: the links then run at copy-engine
+#: speed and every SM multiplies.  OSLO_B200_CE_TRANSPORT=0 keeps the in-kernel transports.
+USE_CE_TRANSPORT = __import__("os").environ.get("OSLO_B200_CE_TRANSPORT", "0") == "1"
+
+
 def _multicast_alloc(pc, mode, nbytes: int):
     """Allocate ``nbytes`` per rank through ``torch.distributed._symmetric_memory`` and rendezvous over the group.
 
@@ -188,7 +194,7 @@ def small_ops_enabled() -> bool:
 
 class SymmetricWorkspace:
     def __init__(self, pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 16,
-                 multimem: bool = True):
+                 multimem: bool = True, ce_transport: Optional[bool] = None):
         self.pc, self.mode = pc, mode
         self.tp = pc.get_world_size(mode)
         self.rank = pc.get_local_rank(mode)
@@ -199,6 +205,8 @@ class SymmetricWorkspace:
         self.copy_ctas = copy_ctas
         self.max_tokens, self.max_features = max_tokens, max_features
         esz = torch.empty((), dtype=dtype).element_size()
+        if ce_transport is None:
+            ce_transport = USE_CE_TRANSPORT
         self.in_bytes = (max_tokens * max_features * esz + 1023) // 1024 * 1024  # one gathered buffer
         self.slot_bytes = (max_tokens * max_features * esz + 1023) // 1024 * 1024
         self.total = _FLAG_BYTES + 2 * self.in_bytes + 2 * self.slot_bytes
@@ -251,6 +259,15 @@ class SymmetricWorkspace:
             self._local_bytes = self._symm_keep[0]
         else:
             self._local_bytes = torch.as_tensor(_RawCudaBuffer(self.base, self.total), device=self.device)
+        # Copy-engine transport (see ``_ag_gemm_ce`` / ``_gemm_rs_ce``): every rank's workspace as a tensor in this process,
+        # one stream per destination so the transfers to different peers run on different copy engines, two local staging
+        # buffers for partial blocks on their way out.
+        self.ce_transport = bool(ce_transport) and not self.mc_base
+        self._peer_bytes = [self._local_bytes if r == self.rank else torch.as_tensor(_RawCudaBuffer(b, self.total), device=self.device)
+                            for r, b in enumerate(self.peer_base)]
+        self._ce_streams = [torch.cuda.Stream(device=self.device) for _ in range(self.tp)] if self.ce_transport else []
+        self._stage = None
+        self._stage_free = [None, None]
         dist.barrier(group=pc.get_cpu_group(mode))
         self.barrier()
 
@@ -359,20 +376,133 @@ class SymmetricWorkspace:
             if bias.shape != (n,):
                 raise ValueError("ag_gemm: bias must be [N]")
             bias = bias.to(x_shard.dtype).contiguous()
+        external = 0
+        if self.ce_transport:
+            self._ce_push_shard(x_shard, parity, tl, k)
+            external = 1
         rc = _lib.cuda_lib().oslo_ag_gemm(
             _lib.ptr(x_shard), self._gathered_ptrs(parity), _lib.ptr(w), _lib.ptr(out), _lib.ptr(bias), ctypes.c_int(t),
             ctypes.c_int(n), ctypes.c_int(k), ctypes.c_longlong(ldb), ctypes.c_int(b_mn),
             ctypes.c_int(1 if self.dtype == torch.bfloat16 else 0), ctypes.c_int(self.tp), ctypes.c_int(self.rank),
             ctypes.c_int(self.epoch), self._flag_ptrs(0), self._local_ptr(1), ctypes.c_int(self.copy_ctas),
             ctypes.c_int(_lib.num_sms()), _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr(), _lib.ptr(self.epoch_dev),
-            self._mc_gathered(parity))
+            self._mc_gathered(parity), ctypes.c_int(external))
         if rc:
             raise RuntimeError(f"oslo_ag_gemm failed ({rc})")
+        if external:
+            self._ce_join()
         x_full = self._local_gathered(parity, t, k)
         return out, (x_full.clone() if keep else x_full)
 
+    # ------------------------------------------------------------ copy-engine transport
+    def _ce_fork(self):
+        """Side streams start after everything enqueued so far on the current stream (inputs ready, epoch advanced)."""
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream())
+        return ev
+
+    def _ce_join(self):
+        """The current stream continues only after our outgoing transfers: their sources may be reused afterwards."""
+        main = torch.cuda.current_stream()
+        for r, s in enumerate(self._ce_streams):
+            if r != self.rank:
+                main.wait_stream(s)
+
+    def _flag_view(self, r: int, which: int) -> torch.Tensor:
+        """int32 view of rank ``r``'s flag array ``which`` (0 chunk flags, 1 reduce-scatter flags), 64 entries."""
+        return self._peer_bytes[r][which * 256 : which * 256 + 256].view(torch.int32)
+
+    def _ce_push_shard(self, x_shard: torch.Tensor, parity: int, tl: int, k: int):
+        """All-gather transport by copy engine: our shard goes into block [rank] of every rank's gathered buffer, row chunk
+        by row chunk, each chunk followed by its flag (a 4-byte copy of the device-resident epoch), one stream per
+        destination.  The consuming kernel runs meanwhile on the current stream and takes chunks as flags come up."""
+        esz = x_shard.element_size()
+        chunk_rows = _lib.cuda_lib().oslo_ag_chunk_rows(ctypes.c_int(tl), ctypes.c_int(self.tp))
+        if chunk_rows <= 0:
+            raise RuntimeError("all-gather chunking failed")
+        cps = tl // chunk_rows
+        chunk_bytes = chunk_rows * k * esz
+        src = x_shard.view(torch.uint8).view(-1)
+        base = _FLAG_BYTES + parity * self.in_bytes + self.rank * tl * k * esz
+        ev = self._ce_fork()
+        for i in range(1, self.tp + 1):
+            d = (self.rank + i) % self.tp
+            dst = self._peer_bytes[d]
+            if d == self.rank:
+                # our own block of the gathered buffer (callers get the whole gathered tensor back): a local copy
+                dst[base : base + cps * chunk_bytes].copy_(src)
+                continue
+            stream = self._ce_streams[d]
+            stream.wait_event(ev)
+            flags = self._flag_view(d, 0)
+            with torch.cuda.stream(stream):
+                for c in range(cps):
+                    dst[base + c * chunk_bytes : base + (c + 1) * chunk_bytes].copy_(src[c * chunk_bytes : (c + 1) * chunk_bytes])
+                    flags[self.rank * cps + c : self.rank * cps + c + 1].copy_(self.epoch_dev)
+
+    def _gemm_rs_ce(self, x, weight, bias, addend, pair):
+        """Reduce-scatter transport by copy engine.  The product is computed block of rows by block of rows in destination
+        order (next rank first, our own block last); each finished block leaves for its owner's slot [rank] on that
+        destination's stream while the next block is multiplied, followed by its flag; our own block is summed with the
+        other ranks' blocks, which have arrived in our slot buffer meanwhile, by a small kernel that waits on the flags."""
+        from oslo_b200.ops.gemm import gemm
+
+        t, k = x.shape
+        n = weight.shape[0]
+        tl = t // self.tp
+        esz = x.element_size()
+        self._next_epoch()
+        parity = self.epoch & 1
+        blk_bytes = tl * n * esz
+        if self._stage is None or self._stage.numel() < 2 * blk_bytes:
+            self._stage = torch.empty(2 * blk_bytes, dtype=torch.uint8, device=self.device)
+            self._stage_free = [None, None]
+        main = torch.cuda.current_stream()
+        slot_base = _FLAG_BYTES + 2 * self.in_bytes + parity * self.slot_bytes
+        out = torch.empty(tl, n, dtype=x.dtype, device=x.device)
+        own = None
+        for i in range(1, self.tp + 1):
+            d = (self.rank + i) % self.tp
+            rows = slice(d * tl, (d + 1) * tl)
+            if d == self.rank:
+                own = torch.empty(tl, n, dtype=x.dtype, device=x.device)
+                part = own
+            else:
+                b = i & 1
+                if self._stage_free[b] is not None:
+                    main.wait_event(self._stage_free[b])  # the transfer that last read this staging buffer is done
+                part = self._stage[b * blk_bytes : (b + 1) * blk_bytes].view(x.dtype).view(tl, n)
+            if addend is not None:
+                part.copy_(addend[rows])
+                gemm(x[rows], weight, out=part, accumulate=True)
+            else:
+                gemm(x[rows], weight, out=part)
+            if pair is not None:
+                gemm(pair[0][rows], pair[1], out=part, accumulate=True)
+            if d == self.rank:
+                continue
+            ev = self._ce_fork()
+            stream = self._ce_streams[d]
+            stream.wait_event(ev)
+            with torch.cuda.stream(stream):
+                off = slot_base + self.rank * blk_bytes
+                self._peer_bytes[d][off : off + blk_bytes].copy_(part.view(torch.uint8).view(-1))
+                self._flag_view(d, 1)[self.rank : self.rank + 1].copy_(self.epoch_dev)
+                done = torch.cuda.Event()
+                done.record(stream)
+                self._stage_free[i & 1] = done
+        rc = _lib.cuda_lib().oslo_rs_fold(
+            _lib.ptr(own), ctypes.c_void_p(self.base + slot_base), ctypes.c_void_p(self.base + 256), ctypes.c_int(self.rank),
+            ctypes.c_int(self.tp), ctypes.c_longlong(tl), ctypes.c_int(n), _lib.ptr(out), _lib.ptr(bias),
+            ctypes.c_int(1 if self.dtype == torch.bfloat16 else 0), ctypes.c_int(self.epoch), _lib.ptr(self.epoch_dev),
+            _lib.ptr(_lib.status_word(self.device)), ctypes.c_int(_lib.num_sms()), _lib.stream_ptr())
+        if rc:
+            raise RuntimeError(f"oslo_rs_fold failed ({rc})")
+        self._ce_join()
+        return out
+
     def gemm_rs(self, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                addend: Optional[torch.Tensor] = None, along_n: bool = False):
+                addend: Optional[torch.Tensor] = None, along_n: bool = False, pair=None):
         """Returns this rank's block of ``reduce_scatter(x @ weight^T + addend)``: its rows (``[T/tp, N]``), or with
         ``along_n`` its columns (``[T, N/tp]``, the 2-D / 2.5-D layouts).  ``addend`` is an optional local ``[T, N]``
         partial product that rides along in the same reduce-scatter."""
@@ -381,6 +511,13 @@ class SymmetricWorkspace:
         tl = t if along_n else t // self.tp
         if not x.is_contiguous():
             x = x.contiguous()
+        if self.ce_transport and not along_n and tl * n * x.element_size() % 16 == 0:
+            return self._gemm_rs_ce(x, weight, bias, addend, pair)
+        if pair is not None:  # the in-kernel transports take the second product as a ready [T, N] addend
+            from oslo_b200.ops.gemm import matmul_nt
+
+            extra = matmul_nt(pair[0], pair[1])
+            addend = extra if addend is None else addend + extra
         self._next_epoch()
         parity = self.epoch & 1
         out = torch.empty(tl, n // self.tp if along_n else n, dtype=x.dtype, device=x.device)
@@ -454,14 +591,14 @@ class _Runtime:
             raise RuntimeError("ag_gemm: operands not supported by the fused kernel")
         return self.ws.ag_gemm(x_shard, weight, bias, keep)
 
-    def gemm_rs(self, x, weight, addend=None, along_n=False):
+    def gemm_rs(self, x, weight, addend=None, along_n=False, pair=None):
         if not self.ws.rs_ok(x, weight, along_n):
             raise RuntimeError("gemm_rs: operands not supported by the fused kernel")
-        return self.ws.gemm_rs(x, weight, addend=addend, along_n=along_n)
+        return self.ws.gemm_rs(x, weight, addend=addend, along_n=along_n, pair=pair)
 
 
 def enable(pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, copy_ctas: int = 16, model=None,
-           multimem: bool = True) -> bool:
+           multimem: bool = True, ce_transport: Optional[bool] = None) -> bool:
     """Create the group's symmetric workspace and switch the linears that communicate over ``mode`` to the fused kernels:
     ``TENSOR_1D`` for the sequence-parallel 1-D linears, ``TENSOR_2D_ROW`` / ``TENSOR_2P5D_ROW`` for the feature
     reduce-scatter of the SUMMA linears, ``TENSOR_3D_INPUT`` + ``TENSOR_3D_OUTPUT`` (call twice) for the 3-D linear.
@@ -472,7 +609,7 @@ def enable(pc, mode, max_tokens: int, max_features: int, dtype=torch.bfloat16, c
     if model is not None:
         rehome_vocab_embeddings(model, pc, mode)
     global _fused_small_ops
-    ws = SymmetricWorkspace(pc, mode, max_tokens, max_features, dtype, copy_ctas, multimem=multimem)
+    ws = SymmetricWorkspace(pc, mode, max_tokens, max_features, dtype, copy_ctas, multimem=multimem, ce_transport=ce_transport)
     fused_collectives.set_runtime(_Runtime(ws), mode)
     _fused_small_ops = True
     return True

@@ -59,10 +59,11 @@ def ag_gemm(x_shard, weight, pc, bias=None, keep=True):
         return _runtime.ag_gemm(x_shard, weight, bias, keep)
 
 
-def gemm_rs(x, weight, pc, addend=None):
-    """``reduce_scatter(x @ weight^T + addend)`` over the token dim in one kernel (``addend``: optional local [T, N])."""
+def gemm_rs(x, weight, pc, addend=None, pair=None):
+    """``reduce_scatter(x @ weight^T + addend + pair[0] @ pair[1]^T)`` over the token dim (``addend``: optional local
+    ``[T, N]``; ``pair``: an optional second ``(x', weight')`` product that leaves in the same reduce-scatter)."""
     with annotate("oslo.gemm_rs"):
-        return _runtime.gemm_rs(x, weight, addend=addend)
+        return _runtime.gemm_rs(x, weight, addend=addend, pair=pair)
 
 
 def feature_rs_available(x: torch.Tensor, w: torch.Tensor, mode) -> bool:

@@ -140,9 +140,21 @@ class _VPCECudaFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         (grad,) = ctx.saved_tensors
-        g2 = g.reshape(-1, 1).to(grad.dtype)
         v = grad.shape[-1]
-        out = grad.view(-1, v).mul_(g2).view(grad.shape)
+        g2d = grad.view(-1, v)
+        if grad.dtype in (torch.bfloat16, torch.float16) and v % 8 == 0 and g2d.stride(-1) == 1 and g2d.stride(0) % 8 == 0 \
+                and g2d.data_ptr() % 16 == 0:
+            # one vectorised in-place pass over the vocabulary-sized buffer (the broadcast multiply below runs at a third
+            # of the memory bandwidth)
+            gs = g.reshape(-1).float().contiguous()
+            rc = _lib.cuda_lib().oslo_row_scale(_lib.ptr(g2d), _lib.ptr(gs), ctypes.c_longlong(g2d.shape[0]), ctypes.c_int(v),
+                                                ctypes.c_longlong(g2d.stride(0)), ctypes.c_int(1 if grad.dtype == torch.bfloat16 else 0),
+                                                ctypes.c_int(_lib.num_sms()), _lib.stream_ptr())
+            if rc:
+                raise RuntimeError(f"oslo_row_scale failed ({rc})")
+            return grad, None, None, None, None, None
+        g2 = g.reshape(-1, 1).to(grad.dtype)
+        out = g2d.mul_(g2).view(grad.shape)
         return out, None, None, None, None, None
 
 

@@ -291,12 +291,13 @@ class _LinearPairRS(torch.autograd.Function):
 
         ctx.pc = pc
         ctx.save_for_backward(x1, w1, x2, w2)
-        part = matmul_nt(x1, w1)  # local [T, N]
         if _use_fused(x2, w2, "rs"):
             from oslo_b200.ops import fused_collectives as fc
 
-            return fc.gemm_rs(x2, w2, pc, addend=part)
-        part = part + matmul_nt(x2, w2)
+            # the second product rides along: as a ready [T, N] addend in the one-kernel transports, block by block
+            # (accumulated into the same staging block) with the copy-engine transport
+            return fc.gemm_rs(x2, w2, pc, pair=(x1, w1))
+        part = matmul_nt(x1, w1) + matmul_nt(x2, w2)
         return comm.reduce_scatter(part, dim=0, parallel_context=pc, parallel_mode=_MODE)
 
     @staticmethod

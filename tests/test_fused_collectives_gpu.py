@@ -13,7 +13,7 @@ def _n_gpus():
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
 
-def _worker(rank, world, multimem=False):
+def _worker(rank, world, multimem=False, ce=False):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     os.environ["OSLO_B200_MULTIMEM_MIN_RANKS"] = "2"  # exercise the multicast kernels on two ranks as well
     import torch.distributed as dist
@@ -27,7 +27,8 @@ def _worker(rank, world, multimem=False):
     dev = pc.device
     # multimem: the workspace is bound to an NVSwitch multicast object when the box allows it (the all-gather then uses
     # multimem.st, the row reduce-scatter multimem.ld_reduce); otherwise, and with multimem off, plain peer stores
-    assert symm.enable(pc, ParallelMode.TENSOR_1D, max_tokens=4096, max_features=1024, multimem=multimem)
+    assert symm.enable(pc, ParallelMode.TENSOR_1D, max_tokens=4096, max_features=1024, multimem=multimem, ce_transport=ce)
+    assert fc.runtime().ws.ce_transport == ce
     if multimem and rank == 0:
         print(f"multicast workspace: {'bound' if fc.runtime().ws.mc_base else 'not available (' + str(symm._multicast_alloc.last_error) + ')'}",
               flush=True)
@@ -73,6 +74,15 @@ def _worker(rank, world, multimem=False):
         torch.cuda.synchronize()
         _lib.check_status()
         assert rel(out2, ref2) < 2e-2, (it, rel(out2, ref2))
+        # ---- the same with the second product given as operands (x', w') instead of a ready addend
+        k2 = 256
+        xb = (torch.randn(T, k2, device=dev) * 0.5).to(torch.bfloat16)
+        wb = (torch.randn(N, k2, device=dev) * 0.1).to(torch.bfloat16)
+        out2b = fc.gemm_rs(xa, WN, pc, pair=(xb, wb))
+        ref2b = comm.reduce_scatter(part + xb.float() @ wb.float().t(), dim=0, parallel_context=pc, parallel_mode=M1)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        assert rel(out2b, ref2b) < 2e-2, (it, rel(out2b, ref2b))
         # ---- reduce-scatter along the FEATURE dim (2-D / 2.5-D layouts): every rank keeps its rows
         ws = fc.runtime().ws
         if ws.rs_ok(xa, WN, along_n=True):
@@ -99,10 +109,12 @@ def _world_sizes():
 
 
 @pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
-@pytest.mark.parametrize("multimem", [False, True], ids=["peer", "multicast"])
+@pytest.mark.parametrize("transport", ["peer", "multicast", "copy-engine"])
 @pytest.mark.parametrize("world", _world_sizes())
-def test_fused_collectives_match_nccl(world, multimem):
-    run_dist(_worker, world, multimem, timeout=600)
+def test_fused_collectives_match_nccl(world, transport):
+    """peer: copy CTAs / epilogue stores inside the kernel; multicast: multimem.st / multimem.ld_reduce; copy-engine: the
+    shards travel by cudaMemcpyAsync between peer mappings on side streams while every SM multiplies."""
+    run_dist(_worker, world, transport == "multicast", transport == "copy-engine", timeout=600)
 
 
 def _model_worker(rank, world):

@@ -233,10 +233,11 @@ def test_cross_entropy():
     lr_masked = lr.clone()
     lr_masked[..., 990:] = float("-inf")
     ref = F.cross_entropy(lr_masked.view(-1, v), tgt.view(-1), ignore_index=-100, reduction="none").view(5, 10)
-    ref.sum().backward()
+    wts = torch.rand(5, 10, device=DEV) + 0.25  # a different upstream gradient per token: the backward scales row by row
+    (ref * wts).sum().backward()
     x = logits.clone().requires_grad_()
     loss = vocab_parallel_cross_entropy(x * 1.0, tgt, None, valid_vocab=990)
-    loss.sum().backward()
+    (loss * wts).sum().backward()
     assert _rel(loss, ref) < 1e-3
     assert _rel(x.grad, lr.grad) < 2e-2
 
