@@ -232,4 +232,14 @@ OSLO_DEVINL float gelu_tanh(float x) {
   return 0.5f * x * (1.0f + t);
 }
 
+// derivative of gelu_tanh
+OSLO_DEVINL float gelu_tanh_grad(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const float u = k0 * x * (1.0f + k1 * x * x);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  const float du = k0 * (1.0f + 3.0f * k1 * x * x);
+  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
+}
+
 }  // namespace oslo

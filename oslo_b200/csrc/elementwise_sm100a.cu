@@ -34,14 +34,6 @@ template <typename T> OSLO_DEVINL void st_pack(T* p, const Pack<T>& r) {
   *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(r.v);
 }
 
-OSLO_DEVINL float gelu_tanh_grad(float x) {
-  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  const float u = k0 * x * (1.0f + k1 * x * x);
-  const float t = tanhf(u);
-  const float du = k0 * (1.0f + 3.0f * k1 * x * x);
-  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
-}
-
 // activation selected at run time (uniform over the launch): 0 tanh-form GELU, 1 erf-form GELU, 2 ReLU
 OSLO_DEVINL float act_apply(float v, int act) {
   if (act == 0) return gelu_tanh(v);

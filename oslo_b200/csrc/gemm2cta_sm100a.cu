@@ -320,7 +320,34 @@ gemm2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
           }
         }
-        const bool want_aux = (p.aux_ptr != nullptr);
+        if (p.epilogue == 3 && row < p.M) {
+          // multiply by gelu'(aux): aux holds a pre-activation laid out like C (the backward of a fused bias-GELU linear:
+          // dPre = (dY W) * gelu'(pre) without a separate element-wise pass)
+          const uint16_t* ain = static_cast<const uint16_t*>(p.aux_ptr) + static_cast<long long>(bi) * p.stride_c +
+                                static_cast<long long>(bo) * p.stride_c_outer + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            if (col0 + g * 8 < p.N) {
+              const uint4 raw = *reinterpret_cast<const uint4*>(ain + g * 8);
+              const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float lo, hi;
+                if (p.is_bf16) {
+                  lo = __uint_as_float(w[j] << 16);
+                  hi = __uint_as_float(w[j] & 0xffff0000u);
+                } else {
+                  const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+                  lo = __low2float(h);
+                  hi = __high2float(h);
+                }
+                v[g * 8 + 2 * j] *= gelu_tanh_grad(lo);
+                v[g * 8 + 2 * j + 1] *= gelu_tanh_grad(hi);
+              }
+            }
+          }
+        }
+        const bool want_aux = (p.aux_ptr != nullptr) && p.epilogue != 3;
         for (int pass = want_aux ? 0 : 1; pass < 2; ++pass) {
           uint8_t* sbuf_ptr = my_staging + sbuf * 4096;
           if (lane == 0) tma_store_wait_read<1>();

@@ -69,7 +69,12 @@ class GPTNeoXMLP(nn.Module):
         self.dense_4h_to_h = onn.Linear(config.intermediate_size, config.hidden_size, skip_bias_add=True)
 
     def forward(self, hidden_states):
-        up = self.dense_h_to_4h
+        up, down = self.dense_h_to_4h, self.dense_4h_to_h
+        if type(up) is onn.Linear and type(down) is onn.Linear and not up.reversed and not down.reversed and down.skip_bias_add:
+            from oslo_b200.ops.gemm import mlp_gelu
+
+            # both element-wise steps ride in GEMM epilogues: bias + GELU forward, GELU' in the gradient GEMM backward
+            return mlp_gelu(hidden_states, up.weight, up.bias, down.weight), down.bias
         if type(up) is onn.Linear and not up.reversed:
             from oslo_b200.ops.gemm import linear_gelu
 

@@ -19,7 +19,7 @@ import torch.nn.functional as F
 
 from . import _lib
 
-_EPI = {None: 0, "none": 0, "bias": 1, "gelu": 2}
+_EPI = {None: 0, "none": 0, "bias": 1, "gelu": 2, "gelu_grad": 3}
 
 #: use the two-CTA kernel (256 x 256 tile on a CTA pair) automatically for large products; OSLO_B200_GEMM_2CTA=0 turns it
 #: off.  Measured against the one-CTA kernel it is 7 - 12 % faster from K = 2048 up and slower at K = 256.
@@ -99,7 +99,10 @@ def gemm(
         _prof.report_gemm_flops(M, N, K, b_in * b_out)
     lib = _lib.cuda_lib()
     status = _lib.status_word(a.device)
-    use_epi = _EPI[epilogue] if (bias is not None or epilogue == "gelu") else 0
+    use_epi = _EPI[epilogue] if (bias is not None or epilogue in ("gelu", "gelu_grad")) else 0
+    if use_epi == 3:
+        # ``aux`` is an INPUT here: the product is multiplied by gelu_tanh'(aux) element by element
+        assert aux is not None and bias is None and not accumulate, "gelu_grad takes aux (the pre-activation) and nothing else"
     if two_cta is None:
         pairs = _lib.num_sms() // 2
         tiles = b_in * b_out * ((M + 255) // 256) * ((N + 255) // 256)
@@ -242,6 +245,53 @@ class _LinearGeluFn(torch.autograd.Function):
 
             gb = colsum(dpre)
         return gx, gw, gb
+
+
+class _MLPGeluFn(torch.autograd.Function):
+    """``y = gelu_tanh(x W1^T + b1) W2^T``.  Forward: bias + GELU in the first GEMM's epilogue.  Backward: the GEMM that
+    brings the gradient back through W2 multiplies by ``gelu'(pre)`` in ITS epilogue, so the activation's backward costs no
+    pass of its own over the ``[tokens, 4 hidden]`` tensor."""
+
+    @staticmethod
+    def forward(ctx, x, w1, b1, w2):
+        x2 = x.reshape(-1, x.shape[-1])
+        h, pre = gemm_bias_gelu(x2, w1, b1)
+        y = matmul_nt(h, w2)
+        ctx.save_for_backward(x2, w1, w2, pre, h)
+        ctx.has_bias = b1 is not None
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], w2.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, w1, w2, pre, h = ctx.saved_tensors
+        gy2 = gy.reshape(-1, gy.shape[-1])
+        if not gy2.is_contiguous():
+            gy2 = gy2.contiguous()
+        if supported(gy2, w2.t()) and _aligned(gy2.shape[-1], w2.shape[1], gy2.shape[0]):
+            dpre = gemm(gy2, w2.t(), epilogue="gelu_grad", aux=pre)
+        else:
+            dpre = gelu_backward(matmul_nt(gy2, w2.t()), pre)
+        gx = gw1 = gb1 = gw2 = None
+        if ctx.needs_input_grad[0]:
+            gx = matmul_nt(dpre, w1.t()).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            gw1 = matmul_nt(dpre.t(), x2.t())
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            from .activation import colsum
+
+            gb1 = colsum(dpre)
+        if ctx.needs_input_grad[3]:
+            gw2 = matmul_nt(gy2.t(), h.t())
+        return gx, gw1, gb1, gw2
+
+
+def mlp_gelu(x: torch.Tensor, w1: torch.Tensor, b1: Optional[torch.Tensor], w2: torch.Tensor) -> torch.Tensor:
+    """``gelu_tanh(F.linear(x, w1, b1)) @ w2^T`` (the second bias is left to the caller) with both element-wise steps folded
+    into GEMM epilogues, forward and backward."""
+    if b1 is not None and b1.dtype != x.dtype:
+        b1 = b1.to(x.dtype)
+    return _MLPGeluFn.apply(x, w1, b1, w2)
 
 
 def linear_gelu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -444,6 +444,30 @@ def test_flash_attention_forward_pingpong(causal, hd, dtype):
     assert frac == 0.0, ("vs two-pass", frac, worst)
 
 
+def test_mlp_gelu_epilogue_backward():
+    """gelu(x W1^T + b1) W2^T with the GELU derivative applied in the epilogue of the gradient GEMM (both the two-CTA and
+    the one-CTA kernel, chosen by K) against fp32 autograd."""
+    from oslo_b200.ops.gemm import mlp_gelu
+
+    for rows, hid, ffn in ((4096, 1024, 4096), (512, 256, 512)):
+        torch.manual_seed(81)
+        x = (torch.randn(rows, hid, device=DEV) * 0.5).to(torch.bfloat16).requires_grad_()
+        w1 = (torch.randn(ffn, hid, device=DEV) * 0.05).to(torch.bfloat16).requires_grad_()
+        b1 = (torch.randn(ffn, device=DEV) * 0.1).to(torch.bfloat16).requires_grad_()
+        w2 = (torch.randn(hid, ffn, device=DEV) * 0.05).to(torch.bfloat16).requires_grad_()
+        g = (torch.randn(rows, hid, device=DEV) * 0.5).to(torch.bfloat16)
+        y = mlp_gelu(x, w1, b1, w2)
+        y.backward(g)
+        refs = [t.detach().float().requires_grad_() for t in (x, w1, b1, w2)]
+        yr = torch.nn.functional.gelu(refs[0] @ refs[1].t() + refs[2], approximate="tanh") @ refs[3].t()
+        yr.backward(g.float())
+        frac, worst = _close(y, yr, rtol=2e-2, atol=0.02 * yr.abs().max().item())
+        assert frac == 0.0, ("y", rows, frac, worst)
+        for got, want, name in zip((x, w1, b1, w2), refs, ("dx", "dw1", "db1", "dw2")):
+            frac, worst = _close(got.grad, want.grad, rtol=3e-2, atol=0.03 * want.grad.abs().max().item())
+            assert frac < 1e-4, (name, rows, frac, worst)
+
+
 def _close(a, b, rtol, atol):
     """Per-element check ``|a - b| <= atol + rtol * |b|`` (a single large element cannot hide errors elsewhere);
     returns the fraction of elements outside the bound and the worst excess, for the assertion message."""
