@@ -268,3 +268,35 @@ def test_cli_train_validate_generate_export(tmp_path, capsys):
     out = os.path.join(tmp_path, "m.lsw")
     assert cli.main(["export", "--load", ckpt, "--out", out, "--int8"]) == 0
     assert read_header(out)[0]["quantized"]
+
+
+def test_lsflow_static_graph_matches_eager_and_reuses_memory():
+    from oslo_b200.lightseq import lsflow
+    from oslo_b200.lightseq.layers import LSLayerConfig, LSTransformerEncoderLayer
+
+    torch.manual_seed(8)
+    cfg = LSLayerConfig(max_batch_tokens=64, max_seq_len=16, hidden_size=32, intermediate_size=64, nhead=4, pre_layer_norm=True,
+                        activation_fn="gelu")
+    layers = [LSTransformerEncoderLayer(cfg).eval() for _ in range(3)]
+    ctx = lsflow.Context()
+    x = ctx.input("x", (64, 32))
+    h = x
+    for i, layer in enumerate(layers):
+        h = lsflow.encoder_layer_graph(ctx, h, layer, f"layer{i}")
+    ctx.build()
+    # lifetimes let the planner fold 27 intermediates into far fewer bytes than their sum
+    assert 0 < ctx.arena_bytes < 0.5 * ctx.naive_bytes, (ctx.arena_bytes, ctx.naive_bytes)
+    for batch, seq in ((4, 16), (2, 8)):  # the second run is smaller than the declared maximum and reuses the arena
+        inp = torch.randn(batch, seq, 32)
+        want = inp
+        with torch.no_grad():
+            for layer in layers:
+                want = layer(want)
+        ptr = ctx.arena.data_ptr()
+        (got,) = ctx.run({"x": inp.reshape(batch * seq, 32)}, [h], seq_len=seq)
+        assert ctx.arena.data_ptr() == ptr
+        assert torch.allclose(got.view(batch, seq, 32), want, atol=1e-5), (got.view(batch, seq, 32) - want).abs().max()
+    with pytest.raises(ValueError):
+        ctx.run({"x": torch.randn(65, 32)}, [h])
+    with pytest.raises(RuntimeError):
+        lsflow.AddOp(ctx, "late")(x, x)
