@@ -91,6 +91,29 @@ __global__ void moe_dispatch_kernel(const T* __restrict__ x, DestPtrs dst, const
   }
 }
 
+// The same dispatch seen from the destination side: one block per (expert, position) slot of THIS source; `inv` holds the
+// token that owns the slot or -1.  Unowned slots are written as zeros, so the destination needs no clearing pass (and no
+// barrier between that pass and the arrival of remote rows): every row of the [local expert][source][C] block that this
+// source owns is written exactly once per call.
+template <typename T>
+__global__ void moe_dispatch_rows_kernel(const T* __restrict__ x, DestPtrs dst, const int* __restrict__ inv, int E, int H, int ep_size,
+                                         int src_rank, int experts_per_rank, int C) {
+  const int sl = blockIdx.x;  // e * C + c
+  const int e = sl / C, c = sl - e * C;
+  const int dest = e / experts_per_rank, le = e - dest * experts_per_rank;
+  const size_t row = (static_cast<size_t>(le) * ep_size + src_rank) * C + c;
+  uint4* out = reinterpret_cast<uint4*>(static_cast<T*>(dst.p[dest]) + row * H);
+  const int nvec = H * sizeof(T) / 16;
+  const int tok = inv[sl];
+  if (tok >= 0) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(tok) * H);
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) out[v] = src[v];
+  } else {
+    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) out[v] = z;
+  }
+}
+
 // y[s] = sum_k w[s,k] * buf[slot[s,k]]
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ buf, const float* __restrict__ w, const int* __restrict__ slot,
@@ -271,6 +294,19 @@ extern "C" int oslo_moe_dispatch(const void* x, void* const* dst_ptrs, int ep_si
   for (int i = 0; i < 8; ++i) d.p[i] = i < ep_size ? dst_ptrs[i] : nullptr;
   OSLO_MOE_DTYPE((moe_dispatch_kernel<T><<<S, 128, 0, (cudaStream_t)stream>>>((const T*)x, d, slot, S, K, H, ep_size, src_rank,
                                                                                experts_per_rank, C)));
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// inv: [E * C] int, the token index that owns each slot of this source or -1; every slot row is written (zeros when unowned).
+extern "C" int oslo_moe_dispatch_rows(const void* x, void* const* dst_ptrs, int ep_size, const int* inv, int E, int H, int src_rank,
+                                      int experts_per_rank, int C, int dtype, void* stream) {
+  if (E <= 0 || C <= 0) return 0;
+  const int esz = dtype == 0 ? 4 : 2;
+  if ((H * esz) % 16 || ep_size > 8 || ep_size < 1) return -1;
+  DestPtrs d;
+  for (int i = 0; i < 8; ++i) d.p[i] = i < ep_size ? dst_ptrs[i] : nullptr;
+  OSLO_MOE_DTYPE((moe_dispatch_rows_kernel<T><<<E * C, 128, 0, (cudaStream_t)stream>>>((const T*)x, d, inv, E, H, ep_size, src_rank,
+                                                                                       experts_per_rank, C)));
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -27,7 +27,9 @@ def available(x: torch.Tensor, ep_size: int) -> bool:
 
 def _buffers(pc, rows: int, h: int, esz: int):
     nbytes = rows * h * esz
-    return [symm.group_buffer(pc, ParallelMode.EXPERT, key, nbytes) for key in ("moe_xin", "moe_xout", "moe_gout", "moe_gin")]
+    # the expert-input buffer holds two generations (see PeerDispatch.forward)
+    return [symm.group_buffer(pc, ParallelMode.EXPERT, key, nbytes * (2 if key == "moe_xin" else 1))
+            for key in ("moe_xin", "moe_xout", "moe_gout", "moe_gin")]
 
 
 def _view(buf, rows, h, dtype):
@@ -43,18 +45,30 @@ class PeerDispatch(torch.autograd.Function):
         S, h = tokens.shape
         rows = e_local * ep * C
         xin, _, _, gin = _buffers(pc, rows, h, tokens.element_size())
-        local = _view(xin, rows, h, tokens.dtype)
-        local.zero_()
-        xin.barrier()  # every destination buffer is cleared
-        rc = _lib.cuda_lib().oslo_moe_dispatch(_lib.ptr(tokens.contiguous()), xin.peer_array(0), ctypes.c_int(ep), _lib.ptr(slot),
-                                               ctypes.c_int(S), ctypes.c_int(slot.shape[1]), ctypes.c_int(h), ctypes.c_int(rank),
-                                               ctypes.c_int(e_local), ctypes.c_int(C), ctypes.c_int(_DT[tokens.dtype]), _lib.stream_ptr())
+        # Every source writes ALL its slot rows of every destination (zeros where no token owns the slot), so nothing is
+        # cleared beforehand, and two generations of the buffer alternate by call parity: a rank can be at most one call
+        # ahead of its peers (the barrier below), so writes of call n + 1 never land on rows that a peer still reads from
+        # call n.  One barrier per dispatch instead of a clearing pass and two barriers.
+        gen = getattr(xin, "moe_generation", 0)
+        xin.moe_generation = gen + 1
+        off = (gen & 1) * rows * h * tokens.element_size()
+        E = e_local * ep
+        flat = slot.reshape(-1)
+        owner = torch.arange(S, device=slot.device, dtype=torch.int32).repeat_interleave(slot.shape[1])
+        inv = torch.full((E * C + 1,), -1, dtype=torch.int32, device=slot.device)
+        inv.scatter_(0, torch.where(flat < 0, torch.full_like(flat, E * C), flat).long(), owner)  # dropped tokens go to the spare cell
+        rc = _lib.cuda_lib().oslo_moe_dispatch_rows(_lib.ptr(tokens.contiguous()), xin.peer_array(off), ctypes.c_int(ep), _lib.ptr(inv),
+                                                    ctypes.c_int(E), ctypes.c_int(h), ctypes.c_int(rank), ctypes.c_int(e_local),
+                                                    ctypes.c_int(C), ctypes.c_int(_DT[tokens.dtype]), _lib.stream_ptr())
         if rc:
-            raise RuntimeError(f"oslo_moe_dispatch (peer) failed ({rc})")
+            raise RuntimeError(f"oslo_moe_dispatch_rows (peer) failed ({rc})")
         xin.barrier()  # every source has delivered its rows
         ctx.save_for_backward(slot)
         ctx.meta = (pc, ep, e_local, C, rank, S, h)
-        return local.clone().view(e_local, ep * C, h)
+        nbytes = rows * h * tokens.element_size()
+        local = xin.payload(off, nbytes, tokens.dtype, (rows, h))
+        # training keeps the expert inputs for the weight gradients beyond the two calls this generation stays intact
+        return (local.clone() if torch.is_grad_enabled() else local).view(e_local, ep * C, h)
 
     @staticmethod
     def backward(ctx, g):
