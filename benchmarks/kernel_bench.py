@@ -166,12 +166,12 @@ def bench_attention(a):
     g = torch.randn_like(out)
     from oslo_b200.ops.attention import set_backward_groups
 
-    for groups in (1, 2):
-        set_backward_groups(groups)
+    for groups, dq in ((1, 1), (2, 1), (2, 2)):
+        set_backward_groups(groups, dq_groups=dq)
         ms = time_op(lambda: torch.autograd.grad(out, qkv, g, retain_graph=True), a.iters)
-        report(f"attention_bwd ({groups} element-wise group{'s' if groups > 1 else ''} in dK/dV) B{a.batch} S{a.seq} "
+        report(f"attention_bwd (element-wise groups: {groups} in dK/dV, {dq} in dQ) B{a.batch} S{a.seq} "
                f"H{a.heads}x{a.head_dim}", ms, flops=2.5 * fl)
-    set_backward_groups(2)  # the default
+    set_backward_groups(2, dq_groups=1)  # the defaults
 
 
 KERNELS = {"gemm": bench_gemm, "layernorm": bench_layernorm, "softmax": bench_softmax, "bias_gelu": bench_bias_gelu,

@@ -84,8 +84,10 @@ struct DqCfg {
   static constexpr int kSmem = 2 * kTile /*Q, dO*/ + 4 * kTile /*K x2, V x2*/ + kDs + 1024 + 256;
 };
 
-template <int HD>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+// NG element-wise warp groups: with two, each 128-key tile is split by COLUMNS (group g takes keys [64 g, 64 g + 64)), so
+// eight warps work on one tile at once and the exponentials of a tile take half as long before dQ can accumulate it.
+template <int HD, int NG>
+__global__ void __launch_bounds__(64 + 128 * NG, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                    const __grid_constant__ CUtensorMap tmDQ, const AttnBwdParams p) {
@@ -122,7 +124,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0) {
     mbar_init(qd_full, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
-    mbar_init(s_full, 1); mbar_init(s_empty, 4); mbar_init(ds_full, 4); mbar_init(ds_empty, 1); mbar_init(dq_full, 1);
+    mbar_init(s_full, 1); mbar_init(s_empty, 4 * NG); mbar_init(ds_full, 4 * NG); mbar_init(ds_empty, 1); mbar_init(dq_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -216,6 +218,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   } else {
     const int q = warp & 3;
+    const int grp = (warp - 2) >> 2;  // which 64-column half of every tile this warp handles (NG = 2), or both (NG = 1)
     const int row = q * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
     const size_t stat = (static_cast<size_t>(b) * p.heads + h) * p.seq + q0 + row;
@@ -231,7 +234,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       // two round trips to tensor memory per tile (64 columns of S and of dP each) instead of four; the accumulators go
       // back to the MMA warp as soon as the second half is in registers, before the exponentials of that half run
 #pragma unroll
-      for (int hc = 0; hc < 2; ++hc) {
+      for (int hc = (NG == 2 ? grp : 0); hc < (NG == 2 ? grp + 1 : 2); ++hc) {
         uint32_t rs[2][32], rp[2][32];
         __syncwarp();
 #pragma unroll
@@ -240,11 +243,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           tmem_ld_32x32(tm_dp + lane_base + (hc * 2 + u) * 32, rp[u]);
         }
         tmem_ld_wait();
-        if (hc == 1) {
+        if (NG == 2 || hc == 1) {  // this warp's share of the accumulators is in registers
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(s_empty);
-        } else if (!mbar_wait_bounded(ds_empty, deph ^ 1, abort_flag)) {  // dS of the previous tile has been consumed
+        }
+        if ((NG == 2 || hc == 0) && !mbar_wait_bounded(ds_empty, deph ^ 1, abort_flag)) {  // dS of the previous tile has been consumed
           ok = false;
         }
 #pragma unroll
@@ -279,7 +283,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       sph ^= 1;
       deph ^= 1;
     }
-    if (ok && mbar_wait_bounded(dq_full, 0, abort_flag)) {
+    if (grp != 0) {
+      // the first group alone writes dQ out
+    } else if (ok && mbar_wait_bounded(dq_full, 0, abort_flag)) {
       tc_fence_after();
       uint8_t* stage = sDS + q * 8192;
 #pragma unroll
@@ -595,9 +601,21 @@ static int g_dkv_groups = [] {
   return (e && e[0] == '1') ? 1 : 2;
 }();
 
+// Element-wise warp groups of the dQ kernel (1 or 2); OSLO_B200_ATTN_BWD_DQ_GROUPS sets the start value.
+static int g_dq_groups = [] {
+  const char* e = getenv("OSLO_B200_ATTN_BWD_DQ_GROUPS");
+  return (e && e[0] == '2') ? 2 : 1;
+}();
+
 extern "C" int oslo_attention_backward_set_groups(int groups) {
   if (groups != 1 && groups != 2) return -1;
   g_dkv_groups = groups;
+  return 0;
+}
+
+extern "C" int oslo_attention_backward_set_dq_groups(int groups) {
+  if (groups != 1 && groups != 2) return -1;
+  g_dq_groups = groups;
   return 0;
 }
 
@@ -633,7 +651,8 @@ extern "C" int oslo_attention_backward(const void* q, const void* k, const void*
   const int grid = batch * heads * (seq / 128);
   static bool configured = false;
   if (!configured) {
-    if (set_smem(attn_bwd_dq_kernel<128>, DqCfg<128>::kSmem) || set_smem(attn_bwd_dq_kernel<64>, DqCfg<64>::kSmem) ||
+    if (set_smem(attn_bwd_dq_kernel<128, 1>, DqCfg<128>::kSmem) || set_smem(attn_bwd_dq_kernel<64, 1>, DqCfg<64>::kSmem) ||
+        set_smem(attn_bwd_dq_kernel<128, 2>, DqCfg<128>::kSmem) || set_smem(attn_bwd_dq_kernel<64, 2>, DqCfg<64>::kSmem) ||
         set_smem(attn_bwd_dkv_kernel<128, 1>, DkvCfg<128, 1>::kSmem) || set_smem(attn_bwd_dkv_kernel<64, 1>, DkvCfg<64, 1>::kSmem) ||
         set_smem(attn_bwd_dkv_kernel<128, 2>, DkvCfg<128, 2>::kSmem) || set_smem(attn_bwd_dkv_kernel<64, 2>, DkvCfg<64, 2>::kSmem))
       return -3;
@@ -643,11 +662,13 @@ extern "C" int oslo_attention_backward(const void* q, const void* k, const void*
   if (head_dim == 128) {
     if (groups == 2) attn_bwd_dkv_kernel<128, 2><<<grid, DkvCfg<128, 2>::kThreads, DkvCfg<128, 2>::kSmem, st>>>(tq64, tk128, tv128, tdo64, tdk, tdv, p);
     else attn_bwd_dkv_kernel<128, 1><<<grid, DkvCfg<128, 1>::kThreads, DkvCfg<128, 1>::kSmem, st>>>(tq64, tk128, tv128, tdo64, tdk, tdv, p);
-    attn_bwd_dq_kernel<128><<<grid, kBwdThreads, DqCfg<128>::kSmem, st>>>(tq128, tk128, tv128, tdo128, tdq, p);
+    if (g_dq_groups == 2) attn_bwd_dq_kernel<128, 2><<<grid, 320, DqCfg<128>::kSmem, st>>>(tq128, tk128, tv128, tdo128, tdq, p);
+    else attn_bwd_dq_kernel<128, 1><<<grid, kBwdThreads, DqCfg<128>::kSmem, st>>>(tq128, tk128, tv128, tdo128, tdq, p);
   } else {
     if (groups == 2) attn_bwd_dkv_kernel<64, 2><<<grid, DkvCfg<64, 2>::kThreads, DkvCfg<64, 2>::kSmem, st>>>(tq64, tk128, tv128, tdo64, tdk, tdv, p);
     else attn_bwd_dkv_kernel<64, 1><<<grid, DkvCfg<64, 1>::kThreads, DkvCfg<64, 1>::kSmem, st>>>(tq64, tk128, tv128, tdo64, tdk, tdv, p);
-    attn_bwd_dq_kernel<64><<<grid, kBwdThreads, DqCfg<64>::kSmem, st>>>(tq128, tk128, tv128, tdo128, tdq, p);
+    if (g_dq_groups == 2) attn_bwd_dq_kernel<64, 2><<<grid, 320, DqCfg<64>::kSmem, st>>>(tq128, tk128, tv128, tdo128, tdq, p);
+    else attn_bwd_dq_kernel<64, 1><<<grid, kBwdThreads, DqCfg<64>::kSmem, st>>>(tq128, tk128, tv128, tdo128, tdq, p);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

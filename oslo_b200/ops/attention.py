@@ -218,12 +218,15 @@ def flash_attention_forward(q, k, v, causal: bool, scale: float, pingpong=None):
     return out.view(b, s, nh * hd), lse
 
 
-def set_backward_groups(groups: int) -> None:
+def set_backward_groups(groups: int, dq_groups: Optional[int] = None) -> None:
     """1 or 2 element-wise warp groups in the dK / dV kernel of the fused attention backward (2: consecutive query tiles
-    alternate between two groups of four warps and the probabilities are double-buffered)."""
+    alternate between two groups of four warps and the probabilities are double-buffered) and, with ``dq_groups``, in the
+    dQ kernel (2: the two groups split every key tile by columns)."""
     rc = _lib.cuda_lib().oslo_attention_backward_set_groups(int(groups))
     if rc:
         raise ValueError("groups must be 1 or 2")
+    if dq_groups is not None and _lib.cuda_lib().oslo_attention_backward_set_dq_groups(int(dq_groups)):
+        raise ValueError("dq_groups must be 1 or 2")
 
 
 def flash_attention_backward(q, k, v, out, d_out, lse, dq, dk, dv, causal: bool, scale: float):

@@ -557,7 +557,7 @@ def test_flash_attention_backward_two_groups(causal, hd):
     grads = {}
     try:
         for groups in (1, 2):
-            set_backward_groups(groups)
+            set_backward_groups(groups, dq_groups=groups)
             qkv = qkv0.clone().requires_grad_()
             out = attention(qkv[..., 0, :], qkv[..., 1, :], qkv[..., 2, :], causal=causal)
             out.backward(g)
@@ -565,7 +565,7 @@ def test_flash_attention_backward_two_groups(causal, hd):
             _lib.check_status()
             grads[groups] = qkv.grad.float()
     finally:
-        set_backward_groups(2)  # the default
+        set_backward_groups(2, dq_groups=1)  # the defaults
     ref_in = qkv0.float().requires_grad_()
     attention_reference(ref_in[..., 0, :], ref_in[..., 1, :], ref_in[..., 2, :], causal=causal).backward(g.float())
     tol = 0.03 * ref_in.grad.abs().max().item()
