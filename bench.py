@@ -34,6 +34,19 @@ CONFIGS = {
 }
 
 
+def _transport_note(fused, world):
+    """Which path each side of the sequence-parallel linears took in this run (for the JSON line)."""
+    if not fused:
+        return "none (single rank)" if world == 1 else "NCCL collectives + tcgen05 GEMM"
+    from oslo_b200.ops import fused_collectives
+    from oslo_b200.parallel.tensor_parallel import _ops_1d
+
+    ws = fused_collectives.runtime().ws
+    how = "copy engine" if ws.ce_transport else ("NVSwitch multicast (multimem)" if ws.mc_base else "peer stores")
+    rs = "fused GEMM -> reduce-scatter" if world <= _ops_1d.FUSED_RS_MAX_RANKS else "tcgen05 GEMM + NCCL reduce-scatter"
+    return f"all-gather -> GEMM fused in one kernel over {how}; row-parallel side: {rs}"
+
+
 def reference_arm(args):
     """Run the unmodified reference package from ``baseline/_ref`` (see ``baseline/reference_arm.py``); if that attempt
     fails, the line carries the traceback of this very attempt."""
@@ -293,6 +306,7 @@ def main():
                 "seq_len": S,
                 "parallelism": f"tp{world}" + ("+sp" if sp else ""),
                 "fused_collectives": bool(fused),
+                "collective_transport": _transport_note(fused, world),
                 "cuda_graph": graphed is not None,
                 "optimizer": "AdamW, fp32 master weights and moments",
                 "l2_policy": "inputs larger than L2: every step streams > 126 MB of weights and activations",

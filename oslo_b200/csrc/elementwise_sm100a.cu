@@ -201,6 +201,42 @@ __global__ void rope_kernel(T* __restrict__ x, const float* __restrict__ cosb, c
   }
 }
 
+// The same rotation for 2-byte types in the rotate-half ("neox") pairing, 16 bytes at a time: one thread takes eight
+// consecutive d of one (token, head, part) and the eight partners at d + rot/2.  `parts` tensors that share the token and
+// head strides and lie `ps` elements apart (q and k inside one fused QKV buffer) are rotated by one launch.
+template <typename T>
+__global__ void rope_vec_kernel(T* __restrict__ x, const float* __restrict__ cosb, const float* __restrict__ sinb,
+                                const int* __restrict__ pos, size_t tokens, int heads, int rot_dim, int seq, long long ld,
+                                long long hs, int parts, long long ps, float sign) {
+  const int half = rot_dim / 2;
+  const int chunks = half / 8;
+  const size_t total = tokens * heads * parts * chunks;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % chunks);
+    size_t r = i / chunks;
+    const int part = (int)(r % parts);
+    r /= parts;
+    const int h = (int)(r % heads);
+    const size_t t = r / heads;
+    const int p = pos ? pos[t] : (int)(t % seq);
+    const float4* cp = reinterpret_cast<const float4*>(cosb + (size_t)p * half + c * 8);
+    const float4* sp = reinterpret_cast<const float4*>(sinb + (size_t)p * half + c * 8);
+    const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+    const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    T* base = x + t * ld + h * hs + part * ps + c * 8;
+    Pack<T> a = ld_pack(base), b = ld_pack(base + half);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float av = to_f(a.v[j]), bv = to_f(b.v[j]), sj = sign * sn[j];
+      a.v[j] = from_f<T>(av * cs[j] - bv * sj);
+      b.v[j] = from_f<T>(bv * cs[j] + av * sj);
+    }
+    st_pack(base, a);
+    st_pack(base + half, b);
+  }
+}
+
 // Row softmax of scale * x (+ additive mask) with optional causal masking.  One warp per row.
 // x: [batches, sq, sk]; mask (optional): additive fp32/T-agnostic float [mask_batches, sq or 1, sk]
 // causal: key j is visible to query i iff j <= i + (sk - sq).
@@ -464,6 +500,33 @@ extern "C" int oslo_rope(void* x, const float* cosb, const float* sinb, const in
 }
 
 // x, y: [batches * sq, sk] contiguous; sk % 8 == 0 (4 for fp32).  mask: additive fp32 or null.
+// `parts` tensors `ps` elements apart (same token / head strides) in one call; the 16-byte kernel when the layout allows it.
+extern "C" int oslo_rope_parts(void* x, const float* cosb, const float* sinb, const int* pos, long long tokens, int heads,
+                               int rot_dim, int seq, long long ld, long long hs, int parts, long long ps, int neox, int backward,
+                               int dtype, int num_sms, void* stream) {
+  if (tokens <= 0 || rot_dim <= 0 || parts <= 0) return 0;
+  if (rot_dim % 2) return -1;
+  const int half = rot_dim / 2;
+  const bool vec = dtype != 0 && neox && half % 8 == 0 && ld % 8 == 0 && hs % 8 == 0 && (parts == 1 || ps % 8 == 0) &&
+                   (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(cosb) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(sinb) & 15) == 0;
+  if (!vec) {
+    const long long esz = dtype == 0 ? 4 : 2;
+    for (int part = 0; part < parts; ++part) {
+      const int rc = oslo_rope(static_cast<char*>(x) + part * ps * esz, cosb, sinb, pos, tokens, heads, rot_dim, seq, ld, hs, neox,
+                               backward, dtype, num_sms, stream);
+      if (rc) return rc;
+    }
+    return 0;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  const int g = grid_for((size_t)tokens * heads * parts * (half / 8), 256, num_sms);
+  const float sign = backward ? -1.f : 1.f;
+  if (dtype == 1) rope_vec_kernel<__half><<<g, 256, 0, st>>>((__half*)x, cosb, sinb, pos, tokens, heads, rot_dim, seq, ld, hs, parts, ps, sign);
+  else rope_vec_kernel<__nv_bfloat16><<<g, 256, 0, st>>>((__nv_bfloat16*)x, cosb, sinb, pos, tokens, heads, rot_dim, seq, ld, hs, parts, ps, sign);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
 extern "C" int oslo_softmax_forward(const void* x, void* y, const float* mask, long long rows, int sq, int sk, float scale,
                                     int causal, int heads_per_mask, int mask_rows, int dtype, int num_sms, void* stream) {
   if (rows <= 0) return 0;

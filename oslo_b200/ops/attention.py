@@ -300,8 +300,8 @@ class _QKVAttentionFn(torch.autograd.Function):
         q, k, v = _split_qkv(qkv5, layout)
         if rope is not None:
             cos, sin, rot, neox = rope
-            for t in (q, k):
-                _rope_launch(t.reshape(b * s, heads, hd) if t.is_contiguous() else _tok_view(t), cos, sin, rot, neox, None, False)
+            # q and k lie a fixed distance apart inside the fused buffer: one launch rotates both
+            _rope_launch(_tok_view(q), cos, sin, rot, neox, None, False, parts=2, part_stride=k.storage_offset() - q.storage_offset())
         if flash_supported(q, k, v):
             # fused kernel: scores never leave the SM; only the row log-sum-exp is kept for backward
             out, lse = flash_attention_forward(q, k, v, causal, scale)
@@ -338,8 +338,7 @@ class _QKVAttentionFn(torch.autograd.Function):
                                      dv, causal, scale)
             if rope is not None:
                 cos, sin, rot, neox = rope
-                for t in (dq, dk):
-                    _rope_launch(_tok_view(t), cos, sin, rot, neox, None, True)
+                _rope_launch(_tok_view(dq), cos, sin, rot, neox, None, True, parts=2, part_stride=dk.storage_offset() - dq.storage_offset())
             return dqkv, None, None, None, None, None, None
         dqkv = torch.empty_like(qkv)
         dq, dk, dv = _split_qkv(dqkv.view(shape5), layout)

@@ -131,17 +131,18 @@ def rope_reference(x, cos, sin, rot_dim, neox=True, positions=None, inverse=Fals
     return out.to(x.dtype).view(shape)
 
 
-def _rope_launch(x, cos, sin, rot_dim, neox, positions, backward):
-    # x: [tokens, heads, head_dim] view with unit stride on the last dim
+def _rope_launch(x, cos, sin, rot_dim, neox, positions, backward, parts: int = 1, part_stride: int = 0):
+    # x: [tokens, heads, head_dim] view with unit stride on the last dim; ``parts`` such tensors ``part_stride`` elements
+    # apart (q and k of one fused QKV buffer) are rotated by one launch
     tokens, heads, hd = x.shape
     pos = positions.to(torch.int32).contiguous() if positions is not None else None
-    rc = _lib.cuda_lib().oslo_rope(
+    rc = _lib.cuda_lib().oslo_rope_parts(
         _lib.ptr(x), _lib.ptr(cos), _lib.ptr(sin), _lib.ptr(pos), ctypes.c_longlong(tokens), ctypes.c_int(heads),
         ctypes.c_int(rot_dim), ctypes.c_int(cos.shape[0]), ctypes.c_longlong(x.stride(0)), ctypes.c_longlong(x.stride(1)),
-        ctypes.c_int(1 if neox else 0), ctypes.c_int(1 if backward else 0), ctypes.c_int(_DT[x.dtype]),
-        ctypes.c_int(_lib.num_sms()), _lib.stream_ptr())
+        ctypes.c_int(parts), ctypes.c_longlong(part_stride), ctypes.c_int(1 if neox else 0), ctypes.c_int(1 if backward else 0),
+        ctypes.c_int(_DT[x.dtype]), ctypes.c_int(_lib.num_sms()), _lib.stream_ptr())
     if rc:
-        raise RuntimeError(f"oslo_rope failed ({rc})")
+        raise RuntimeError(f"oslo_rope_parts failed ({rc})")
 
 
 class _RopeFn(torch.autograd.Function):
