@@ -202,3 +202,38 @@ def _tp_pp_ckpt_worker(rank, world, mode_name, tp, tmp):
 def test_tensor_x_pipeline_checkpoints(mode, tp, world):
     with tempfile.TemporaryDirectory() as tmp:
         run_dist(_tp_pp_ckpt_worker, world, mode, tp, tmp, timeout=900)
+
+
+def test_fused_reduce_scatter_policy_by_group_size(monkeypatch):
+    """The row-parallel side leaves the fused kernel above FUSED_RS_MAX_RANKS ranks; the all-gather side never does."""
+    import torch
+
+    from oslo_b200.ops import fused_collectives as fc
+    from oslo_b200.parallel.tensor_parallel import _ops_1d
+
+    class _WS:
+        def __init__(self, tp):
+            self.tp = tp
+
+        def ag_ok(self, x, w):
+            return True
+
+        def rs_ok(self, x, w, along_n=False):
+            return True
+
+    class _RT:
+        def __init__(self, tp):
+            self.ws = _WS(tp)
+
+    class _FakeCuda(torch.Tensor):
+        is_cuda = True
+
+    x = torch.zeros(4, 4).as_subclass(_FakeCuda)
+    for tp, want_rs in ((2, True), (4, True), (8, False)):
+        monkeypatch.setattr(fc, "_runtime", _RT(tp))
+        assert _ops_1d._use_fused(x, x, "rs") is want_rs, tp
+        assert _ops_1d._use_fused(x, x, "ag") is True
+    monkeypatch.setattr(_ops_1d, "FUSED_RS_MAX_RANKS", 8)
+    assert _ops_1d._use_fused(x, x, "rs") is True
+    monkeypatch.setattr(fc, "_runtime", None)
+    assert _ops_1d._use_fused(x, x, "rs") is False
