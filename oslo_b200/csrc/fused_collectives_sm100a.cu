@@ -50,7 +50,10 @@ extern "C" int oslo_ag_chunk_rows(int Tl, int tp) { return (Tl > 0 && tp > 0 && 
 extern "C" int oslo_ag_gemm(const void* x_shard, void* const* peer_xfull, const void* B, void* C, const void* bias, int T, int N,
                             int K, long long ldb, int b_mn, int is_bf16, int tp, int rank, int epoch,
                             void* const* peer_chunk_flag, int* chunk_arrive, int copy_ctas, int num_sms, int* status,
-                            void* stream_ptr, const int* epoch_ptr, void* mc_xfull, int external_push) {
+                            void* stream_ptr, const int* epoch_ptr, void* mc_xfull, int external_push,
+                            const void* gelu_grad_aux) {
+  // gelu_grad_aux: optional [T, N] pre-activation; the product is multiplied by gelu'(aux) in the epilogue (the backward of
+  // a bias-GELU linear whose incoming gradient is this product) and no bias may be given then.
   // external_push: the shards are delivered (and the chunk flags raised) by somebody else, e.g. copy-engine transfers on
   // other streams: no CTA copies, all of them multiply and take remote row chunks as their flags come up.
   // mc_xfull: the same gathered buffer through an NVSwitch multicast mapping over the group (or null): the copy CTAs then
@@ -72,8 +75,10 @@ extern "C" int oslo_ag_gemm(const void* x_shard, void* const* peer_xfull, const 
   p.M = T; p.N = N; p.K = K; p.batch = 1; p.batch_inner = 1; p.causal = 0;
   p.m_blocks = T / kBlockM;
   p.n_blocks = (N + block_n - 1) / block_n;
-  p.epilogue = bias ? 1 : 0; p.accumulate = 0; p.is_bf16 = is_bf16;
-  p.bias = bias; p.c_ptr = C; p.ldc = N; p.stride_c = 0; p.stride_c_outer = 0; p.aux_ptr = nullptr; p.status = status;
+  if (gelu_grad_aux && (bias || (reinterpret_cast<uintptr_t>(gelu_grad_aux) & 15))) return -5;
+  p.epilogue = gelu_grad_aux ? 3 : (bias ? 1 : 0); p.accumulate = 0; p.is_bf16 = is_bf16;
+  p.bias = bias; p.c_ptr = C; p.ldc = N; p.stride_c = 0; p.stride_c_outer = 0;
+  p.aux_ptr = const_cast<void*>(gelu_grad_aux); p.status = status;
   FusedParams fp;
   fp.tp = tp; fp.rank = rank; fp.shard_rows = Tl; fp.epoch = epoch; fp.copy_ctas = copy_ctas; fp.k_elems = K;
   fp.tiles_per_shard = (Tl / kBlockM) * p.n_blocks;

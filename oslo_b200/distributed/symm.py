@@ -357,7 +357,8 @@ class SymmetricWorkspace:
         return (self.supports(x, w) and t % self.tp == 0 and (t // self.tp) % 128 == 0 and t <= self.max_tokens
                 and n <= self.max_features and t * n * x.element_size() <= self.slot_bytes)
 
-    def ag_gemm(self, x_shard: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, keep: bool = True):
+    def ag_gemm(self, x_shard: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, keep: bool = True,
+                gelu_grad_of: Optional[torch.Tensor] = None):
         """Returns ``(all_gather(x_shard) @ weight^T (+ bias, added in the epilogue), all_gather(x_shard))``.
 
         The gathered activations live in the workspace's symmetric buffer of this call's parity, which the peers
@@ -376,6 +377,10 @@ class SymmetricWorkspace:
             if bias.shape != (n,):
                 raise ValueError("ag_gemm: bias must be [N]")
             bias = bias.to(x_shard.dtype).contiguous()
+        if gelu_grad_of is not None:
+            # the product is multiplied by gelu'(pre-activation) in the epilogue: [T, N], contiguous, operand dtype
+            if gelu_grad_of.shape != (t, n) or gelu_grad_of.dtype != x_shard.dtype or not gelu_grad_of.is_contiguous() or bias is not None:
+                raise ValueError("ag_gemm: gelu_grad_of must be a contiguous [T, N] tensor of the operand dtype, without bias")
         external = 0
         if self.ce_transport:
             self._ce_push_shard(x_shard, parity, tl, k)
@@ -386,7 +391,7 @@ class SymmetricWorkspace:
             ctypes.c_int(1 if self.dtype == torch.bfloat16 else 0), ctypes.c_int(self.tp), ctypes.c_int(self.rank),
             ctypes.c_int(self.epoch), self._flag_ptrs(0), self._local_ptr(1), ctypes.c_int(self.copy_ctas),
             ctypes.c_int(_lib.num_sms()), _lib.ptr(_lib.status_word(self.device)), _lib.stream_ptr(), _lib.ptr(self.epoch_dev),
-            self._mc_gathered(parity), ctypes.c_int(external))
+            self._mc_gathered(parity), ctypes.c_int(external), _lib.ptr(gelu_grad_of))
         if rc:
             raise RuntimeError(f"oslo_ag_gemm failed ({rc})")
         if external:
@@ -586,10 +591,10 @@ class _Runtime:
         # called with either a token shard (all-gather side) or full tokens (reduce-scatter side)
         return self.ws.ag_ok(x, w) or self.ws.rs_ok(x, w)
 
-    def ag_gemm(self, x_shard, weight, bias=None, keep=True):
+    def ag_gemm(self, x_shard, weight, bias=None, keep=True, gelu_grad_of=None):
         if not self.ws.ag_ok(x_shard, weight):
             raise RuntimeError("ag_gemm: operands not supported by the fused kernel")
-        return self.ws.ag_gemm(x_shard, weight, bias, keep)
+        return self.ws.ag_gemm(x_shard, weight, bias, keep, gelu_grad_of)
 
     def gemm_rs(self, x, weight, addend=None, along_n=False, pair=None):
         if not self.ws.rs_ok(x, weight, along_n):

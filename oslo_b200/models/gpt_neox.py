@@ -131,13 +131,13 @@ class GPTNeoXLayer(nn.Module):
         b2 = torch.mv(h4h.weight, ln2.bias.to(h4h.weight.dtype))
         if h4h.bias is not None:
             b2 = b2 + h4h.bias
-        qkv, h = ops.ag_linear_pair(xhat, w1, w2, pc, b1, b2, gelu2=True)
+        qkv, h, h_pre = ops.ag_linear_pair(xhat, w1, w2, pc, b1, b2, gelu2="deferred")
         d = att.query_key_value.sequence_parallel_state.dim if getattr(att.query_key_value, "sequence_parallel_state", None) else 0
         full = list(lead)
         full[d] *= tp
         qkv = qkv.view(*full, qkv.shape[-1])
         ctx = att.core(qkv, attention_mask)
-        out = ops.linear_pair_rs(ctx.reshape(-1, ctx.shape[-1]), att.dense.weight, h, mlp.dense_4h_to_h.weight, pc)
+        out = ops.linear_pair_rs(ctx.reshape(-1, ctx.shape[-1]), att.dense.weight, h, mlp.dense_4h_to_h.weight, pc, x2_pre=h_pre)
         out = out.view(*lead, hidden)
         bias = None
         for b in (att.dense.bias, mlp.dense_4h_to_h.bias):

@@ -52,11 +52,12 @@ def available(x: torch.Tensor, w: torch.Tensor, kind: str = "any") -> bool:
     return rt.supports(x, w)
 
 
-def ag_gemm(x_shard, weight, pc, bias=None, keep=True):
+def ag_gemm(x_shard, weight, pc, bias=None, keep=True, gelu_grad_of=None):
     """``(all_gather(x_shard) @ weight^T (+ bias), all_gather(x_shard))`` in one kernel.  ``keep=False`` returns the gathered
-    activations as a view of the workspace, valid until two more fused calls have been issued."""
+    activations as a view of the workspace, valid until two more fused calls have been issued.  ``gelu_grad_of`` (a ``[T, N]``
+    pre-activation) multiplies the product by ``gelu'`` of it in the epilogue."""
     with annotate("oslo.ag_gemm"):
-        return _runtime.ag_gemm(x_shard, weight, bias, keep)
+        return _runtime.ag_gemm(x_shard, weight, bias, keep, gelu_grad_of)
 
 
 def gemm_rs(x, weight, pc, addend=None, pair=None):

@@ -258,17 +258,21 @@ class _AGLinearPair(torch.autograd.Function):
             if b2 is not None:
                 y2 = y2 + b2
         ctx.save_for_backward(x_full, w1, w2, pre2)
+        if gelu2 == "deferred":
+            # the consumer of y2 applies gelu'(pre2) to the gradient it sends back (in a GEMM epilogue): hand it pre2
+            ctx.mark_non_differentiable(pre2)
+            return y1, y2, pre2
         return y1, y2
 
     @staticmethod
-    def backward(ctx, g1, g2):
+    def backward(ctx, g1, g2, *unused):
         from oslo_b200.ops.activation import colsum
         from oslo_b200.ops.gemm import gelu_backward, matmul_nt
 
         x_full, w1, w2, pre2 = ctx.saved_tensors
         pc = ctx.pc
         g1, g2 = g1.contiguous(), g2.contiguous()
-        if ctx.gelu2:
+        if ctx.gelu2 and ctx.gelu2 != "deferred":  # "deferred": g2 already is the gradient of the pre-activation
             g2 = gelu_backward(g2, pre2)
         gx = gw1 = gw2 = None
         if ctx.needs_input_grad[0]:
@@ -295,11 +299,12 @@ class _LinearPairRS(torch.autograd.Function):
     of ``dY`` backward."""
 
     @staticmethod
-    def forward(ctx, x1, w1, x2, w2, pc):
+    def forward(ctx, x1, w1, x2, w2, pc, x2_pre=None):
         from oslo_b200.ops.gemm import matmul_nt
 
         ctx.pc = pc
-        ctx.save_for_backward(x1, w1, x2, w2)
+        ctx.has_pre = x2_pre is not None
+        ctx.save_for_backward(x1, w1, x2, w2, *([x2_pre] if x2_pre is not None else []))
         if _use_fused(x2, w2, "rs"):
             from oslo_b200.ops import fused_collectives as fc
 
@@ -313,28 +318,39 @@ class _LinearPairRS(torch.autograd.Function):
     def backward(ctx, gy):
         from oslo_b200.ops.gemm import matmul_nt
 
-        x1, w1, x2, w2 = ctx.saved_tensors
+        x1, w1, x2, w2 = ctx.saved_tensors[:4]
+        pre = ctx.saved_tensors[4] if ctx.has_pre else None  # x2 = gelu(pre): the gradient returned for x2 is d(pre)
         pc = ctx.pc
         gy = gy.contiguous()
         if _use_fused(gy, w2.t(), "ag"):
             from oslo_b200.ops import fused_collectives as fc
 
-            gx2, gy_full = fc.ag_gemm(gy, w2.t(), pc, keep=False)  # consumed by the GEMMs below before two more fused calls
+            # consumed by the GEMMs below before two more fused calls; gelu'(pre) rides in this GEMM's epilogue
+            gx2, gy_full = fc.ag_gemm(gy, w2.t(), pc, keep=False, gelu_grad_of=pre)
         else:
             gy_full = comm.all_gather(gy, dim=0, parallel_context=pc, parallel_mode=_MODE)
             gx2 = matmul_nt(gy_full, w2.t())
+            if pre is not None:
+                from oslo_b200.ops.gemm import gelu_backward
+
+                gx2 = gelu_backward(gx2, pre)
         gx1 = matmul_nt(gy_full, w1.t()) if ctx.needs_input_grad[0] else None
         gw1 = matmul_nt(gy_full.t(), x1.t()) if ctx.needs_input_grad[1] else None
         gw2 = matmul_nt(gy_full.t(), x2.t()) if ctx.needs_input_grad[3] else None
-        return gx1, gw1, gx2, gw2, None
+        return gx1, gw1, gx2, gw2, None, None
 
 
 def ag_linear_pair(x, w1, w2, parallel_context, b1=None, b2=None, gelu2=False):
     """Two sequence-parallel column linears on the same input: ``[T/tp, K] -> ([T, N1/tp] (+ b1), [T, N2/tp] (+ b2))``;
-    ``gelu2`` applies the tanh GELU to the second output inside its GEMM epilogue."""
+    ``gelu2`` applies the tanh GELU to the second output inside its GEMM epilogue.  ``gelu2="deferred"`` additionally
+    returns the pre-activation as a third output and expects the gradient that comes back for the second output to be the
+    gradient of that PRE-activation: pass it to :func:`linear_pair_rs` as ``x2_pre``, whose backward applies ``gelu'`` in
+    the epilogue of its gradient GEMM."""
     return _AGLinearPair.apply(x, w1, w2, parallel_context, b1, b2, gelu2)
 
 
-def linear_pair_rs(x1, w1, x2, w2, parallel_context):
-    """Two sequence-parallel row linears summed: ``([T, K1/tp], [T, K2/tp]) -> [T/tp, N]``."""
-    return _LinearPairRS.apply(x1, w1, x2, w2, parallel_context)
+def linear_pair_rs(x1, w1, x2, w2, parallel_context, x2_pre=None):
+    """Two sequence-parallel row linears summed: ``([T, K1/tp], [T, K2/tp]) -> [T/tp, N]``.  With ``x2_pre`` (``x2`` is
+    ``gelu_tanh(x2_pre)``, produced by ``ag_linear_pair(..., gelu2="deferred")``) the gradient returned for ``x2`` is the
+    gradient of ``x2_pre``."""
+    return _LinearPairRS.apply(x1, w1, x2, w2, parallel_context, x2_pre)
