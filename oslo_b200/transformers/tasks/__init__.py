@@ -19,3 +19,4 @@ from .data_pretraining import (
     ProcessorForBertPretraining,
     ProcessorForT5Pretraining,
 )
+from .data_utils import Corpus, CorpusType, batch_iterator, load_corpora, read_sent_text, serialize_corpora, train_tokenizer

@@ -28,21 +28,49 @@ from oslo_b200.utils.logging import get_dist_logger
 
 from .trainer_callback import (CallbackHandler, PredictionOutput, TrainerCallback, TrainerControl,  # noqa: F401
                                TrainerMemoryTracker)
+from .trainer_utils import IntervalStrategy, create_optimizer, get_scheduler  # noqa: F401
 from .training_args import TrainingArguments
 
 
-def _scheduler(optimizer, kind: str, warmup: int, total: int):
-    def lr_lambda(step):
-        if warmup and step < warmup:
-            return (step + 1) / warmup
-        if kind == "constant":
-            return 1.0
-        frac = (step - warmup) / max(1, total - warmup)
-        if kind == "cosine":
-            return 0.5 * (1.0 + math.cos(math.pi * min(1.0, frac)))
-        return max(0.0, 1.0 - frac)  # linear
+def _scheduler(optimizer, kind: str, warmup: int, total: int, num_cycles: float = 0.5, power: float = 1.0):
+    return get_scheduler(kind, optimizer, warmup, total, num_cycles=num_cycles, power=power)
 
-    return torch.optim.lr_scheduler.LambdaLR(optimizer, lr_lambda)
+
+class LengthGroupedSampler(torch.utils.data.Sampler):
+    """Distributed sampler whose batches hold examples of similar length: a seeded shuffle, cut into mega-batches of
+    ``50 x batch_size x replicas`` examples that are sorted by length, then dealt to the replicas batch by batch (so every
+    replica's k-th batch comes from the same length neighbourhood and padding is short everywhere)."""
+
+    def __init__(self, dataset, batch_size: int, num_replicas: int = 1, rank: int = 0, seed: int = 0, drop_last: bool = True,
+                 lengths: Optional[List[int]] = None):
+        self.n, self.bs, self.world, self.rank, self.seed, self.epoch = len(dataset), batch_size, num_replicas, rank, seed, 0
+        if lengths is None:
+            def length(ex):
+                if isinstance(ex, dict):
+                    return int(ex["length"]) if "length" in ex else len(ex["input_ids"])
+                return len(ex)
+            lengths = [length(dataset[i]) for i in range(self.n)]
+        self.lengths = lengths
+        per = self.bs * self.world
+        self.total = (self.n // per) * per if drop_last else (self.n + per - 1) // per * per
+
+    def set_epoch(self, epoch: int):
+        self.epoch = epoch
+
+    def __len__(self):
+        return self.total // self.world
+
+    def __iter__(self):
+        g = torch.Generator().manual_seed(self.seed + self.epoch)
+        order = torch.randperm(self.n, generator=g).tolist()
+        order = (order + order[: self.total - self.n])[: self.total]
+        mega = 50 * self.bs * self.world
+        out = []
+        for s in range(0, self.total, mega):
+            chunk = sorted(order[s : s + mega], key=lambda i: -self.lengths[i])
+            for b in range(0, len(chunk), self.bs * self.world):
+                out.extend(chunk[b + self.rank * self.bs : b + (self.rank + 1) * self.bs])
+        return iter(out)
 
 
 class TrainerState:
@@ -132,11 +160,16 @@ class Trainer:
 
     def get_train_dataloader(self) -> DataLoader:
         world, rank = self._dp()
-        sampler = DistributedSampler(self.train_dataset, num_replicas=world, rank=rank, shuffle=True, seed=self.args.seed,
-                                     drop_last=self.args.dataloader_drop_last)
+        if self.args.group_by_length:
+            sampler = LengthGroupedSampler(self.train_dataset, self.args.per_device_train_batch_size, num_replicas=world, rank=rank,
+                                           seed=self.args.seed, drop_last=self.args.dataloader_drop_last)
+        else:
+            sampler = DistributedSampler(self.train_dataset, num_replicas=world, rank=rank, shuffle=True, seed=self.args.seed,
+                                         drop_last=self.args.dataloader_drop_last)
         return DataLoader(self.train_dataset, batch_size=self.args.per_device_train_batch_size, sampler=sampler,
                           collate_fn=self.data_collator, drop_last=self.args.dataloader_drop_last,
-                          num_workers=self.args.dataloader_num_workers, pin_memory=torch.cuda.is_available())
+                          num_workers=self.args.dataloader_num_workers,
+                          pin_memory=self.args.dataloader_pin_memory and torch.cuda.is_available())
 
     def get_eval_dataloader(self, dataset=None) -> DataLoader:
         dataset = dataset or self.eval_dataset
@@ -148,24 +181,10 @@ class Trainer:
     def create_optimizer(self):
         if self.optimizer is not None:
             return self.optimizer
-        from oslo_b200 import optim
-
         a = self.args
         params = [p for p in self.base_model.parameters() if p.requires_grad and p.numel() > 0]
-        kind = a.optim.lower()
-        if kind in ("adam", "adamw"):
-            opt = optim.FusedAdam(params, lr=a.learning_rate, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
-                                  weight_decay=a.weight_decay, master_weights=a.dtype != torch.float32)
-        elif kind == "lamb":
-            opt = optim.FusedLamb(params, lr=a.learning_rate, weight_decay=a.weight_decay, max_grad_norm=a.max_grad_norm)
-        elif kind == "sgd":
-            opt = optim.FusedSGD(params, lr=a.learning_rate, weight_decay=a.weight_decay)
-        elif kind == "adagrad":
-            opt = optim.FusedAdagrad(params, lr=a.learning_rate, weight_decay=a.weight_decay)
-        elif kind == "novograd":
-            opt = optim.FusedNovoGrad(params, lr=a.learning_rate, weight_decay=a.weight_decay)
-        else:
-            raise ValueError(f"unknown optimizer {a.optim}")
+        opt = create_optimizer(a.optim, params, lr=a.learning_rate, weight_decay=a.weight_decay, betas=(a.adam_beta1, a.adam_beta2),
+                               eps=a.adam_epsilon, max_grad_norm=a.max_grad_norm, master_weights=a.dtype != torch.float32)
         cfg = a.oslo_config
         dp = (cfg.data_parallelism if cfg else None) or {}
         if self.pc is not None and dp.get("zero_stage", 0) in (1, 2):
@@ -179,8 +198,44 @@ class Trainer:
         return opt
 
     # ------------------------------------------------------------- train loop
+    def _forward_keys(self):
+        """Argument names of the model's forward, or None when it takes ``**kwargs`` (then nothing is dropped)."""
+        if not hasattr(self, "_fwd_keys"):
+            import inspect
+
+            sig = inspect.signature(self.base_model.forward)
+            open_ended = any(p.kind == p.VAR_KEYWORD for p in sig.parameters.values())
+            self._fwd_keys = None if open_ended else set(sig.parameters)
+        return self._fwd_keys
+
     def _move(self, batch: Dict[str, torch.Tensor]):
+        keys = self._forward_keys() if self.args.remove_unused_columns else None
+        if keys is not None:
+            batch = {k: v for k, v in batch.items() if k in keys}
         return {k: (v.to(self.device, non_blocking=True) if torch.is_tensor(v) else v) for k, v in batch.items()}
+
+    def compute_loss(self, batch) -> torch.Tensor:
+        """The model's own loss, or, with ``label_smoothing_factor``, (1 - eps) * NLL + eps * mean over the vocabulary of
+        -log p, taken on the logits with the labels withheld from the model (decoder-only models: shifted by one)."""
+        eps = self.args.label_smoothing_factor
+        if not eps or "labels" not in batch:
+            return self.model(**batch).loss
+        labels = batch["labels"]
+        out = self.model(**{k: v for k, v in batch.items() if k != "labels"})
+        logits = out.logits if hasattr(out, "logits") else out[0]
+        if logits.dim() == 3 and logits.shape[1] == labels.shape[-1] and getattr(self.base_model, "shift_labels", self._is_causal()):
+            logits, labels = logits[:, :-1], labels[:, 1:]
+        logp = torch.log_softmax(logits.float(), dim=-1)
+        valid = labels.ne(-100)
+        safe = labels.clamp(min=0).unsqueeze(-1)
+        nll = -logp.gather(-1, safe).squeeze(-1)
+        smooth = -logp.mean(dim=-1)
+        n = valid.sum().clamp(min=1)
+        return ((1.0 - eps) * (nll * valid).sum() + eps * (smooth * valid).sum()) / n
+
+    def _is_causal(self) -> bool:
+        name = type(self.base_model).__name__
+        return "CausalLM" in name or "LMHeadModel" in name
 
     def training_step(self, batch) -> torch.Tensor:
         batch = self._move(batch)
@@ -192,7 +247,7 @@ class Trainer:
                     (out.loss / accum).backward()
                     total += out.loss.detach()
             return total
-        loss = self.model(**batch).loss / accum
+        loss = self.compute_loss(batch) / accum
         if self.zero is not None:
             self.zero.backward(loss)
         else:
@@ -215,17 +270,19 @@ class Trainer:
         inner = opt.optim if self.zero is not None else opt
         if self.lr_scheduler is None:
             warm = a.warmup_steps or int(a.warmup_ratio * max_steps)
-            self.lr_scheduler = _scheduler(inner, a.lr_scheduler_type, warm, max_steps)
+            self.lr_scheduler = _scheduler(inner, a.lr_scheduler_type, warm, max_steps, a.lr_scheduler_num_cycles, a.lr_scheduler_power)
         resume = resume_from_checkpoint or a.resume_from_checkpoint
         skip_batches = 0
         if resume:
             skip_batches = self._load_checkpoint(resume) * a.gradient_accumulation_steps
+            if a.ignore_data_skip:
+                skip_batches = 0
         self.base_model.train()
         self._memory_tracker.start("train")
         self._event("on_train_begin")
         t0 = time.time()
         tokens = 0
-        running, epoch = 0.0, int(self.state.epoch)
+        running, epoch, last_logged = 0.0, int(self.state.epoch), self.state.global_step
         done = False
         while not done:
             if hasattr(loader.sampler, "set_epoch"):
@@ -268,24 +325,42 @@ class Trainer:
                 self.state.global_step += 1
                 self.state.epoch = epoch + (i + 1) / len(loader)
                 self._event("on_step_end")
-                if (a.logging_steps and self.state.global_step % a.logging_steps == 0) or self.control.should_log:
-                    n = a.logging_steps * a.gradient_accumulation_steps
+                first = a.logging_first_step and self.state.global_step == 1
+                if (a.logging_strategy == "steps" and a.logging_steps and self.state.global_step % a.logging_steps == 0) \
+                        or first or self.control.should_log:
+                    n = max(1, self.state.global_step - last_logged) * a.gradient_accumulation_steps
+                    last_logged = self.state.global_step
                     self.log({"loss": self._mean_over_dp(running / n), "learning_rate": self.lr_scheduler.get_last_lr()[0],
                               "epoch": round(self.state.epoch, 3), "step": self.state.global_step})
                     running = 0.0
-                if self.eval_dataset is not None and ((a.eval_steps and self.state.global_step % a.eval_steps == 0)
+                if self.eval_dataset is not None and ((a.evaluation_strategy == "steps" and a.eval_steps
+                                                       and self.state.global_step % a.eval_steps == 0)
                                                       or self.control.should_evaluate):
                     self._track_best(self.evaluate())
                     self.base_model.train()
-                if (a.save_steps and self.state.global_step % a.save_steps == 0) or self.control.should_save:
+                if (a.save_strategy == "steps" and a.save_steps and self.state.global_step % a.save_steps == 0) \
+                        or self.control.should_save:
                     self.save_checkpoint()
                 if self.state.global_step >= max_steps or self.control.should_training_stop:
                     done = True
                     break
             self._event("on_epoch_end")
+            if a.logging_strategy == "epoch" and self.state.global_step > last_logged:
+                n = (self.state.global_step - last_logged) * a.gradient_accumulation_steps
+                last_logged = self.state.global_step
+                self.log({"loss": self._mean_over_dp(running / n), "learning_rate": self.lr_scheduler.get_last_lr()[0],
+                          "epoch": round(self.state.epoch, 3), "step": self.state.global_step})
+                running = 0.0
+            if a.evaluation_strategy == "epoch" and self.eval_dataset is not None:
+                self._track_best(self.evaluate())
+                self.base_model.train()
+            if a.save_strategy == "epoch":
+                self.save_checkpoint()
             if self.control.should_training_stop:
                 done = True
             epoch += 1
+        if a.load_best_model_at_end and self.state.best_model_checkpoint:
+            self._load_checkpoint(self.state.best_model_checkpoint, weights_only=True)
         elapsed = time.time() - t0
         dp_world, _ = self._dp()
         metrics = {"train_runtime": elapsed, "train_steps_per_second": self.state.global_step / max(elapsed, 1e-9),
@@ -308,6 +383,10 @@ class Trainer:
     def log(self, logs: dict):
         self.state.log_history.append(dict(logs))
         self.logger.info(json.dumps(logs), ranks=[0])
+        if self.args.logging_dir and self._rank() == 0:
+            os.makedirs(self.args.logging_dir, exist_ok=True)
+            with open(os.path.join(self.args.logging_dir, "log.jsonl"), "a") as f:
+                f.write(json.dumps(logs) + "\n")
         self._event("on_log", logs=logs)
 
     # ------------------------------------------------------------- evaluation
@@ -428,13 +507,18 @@ class Trainer:
             if full != self.state.best_model_checkpoint:
                 shutil.rmtree(full, ignore_errors=True)
 
-    def _load_checkpoint(self, path: str) -> int:
-        """Restores model shards, optimizer, scheduler, RNG and trainer state; returns the steps already done."""
+    def _load_checkpoint(self, path: str, weights_only: bool = False) -> int:
+        """Restores model shards, optimizer, scheduler, RNG and trainer state; returns the steps already done.
+        ``weights_only`` reloads the model alone (best-model reload at the end of training)."""
         rank = self._rank()
         if self.pc is not None and hasattr(self.model, "from_parallelized"):
             self.model.from_parallelized(path)
         else:
             self.base_model.load_state_dict(torch.load(os.path.join(path, "pytorch_model.bin"), map_location="cpu"))
+        if weights_only:
+            if self.zero is not None:
+                self.zero.resync_master()
+            return self.state.global_step
         opt_file = os.path.join(path, f"optimizer_{rank}.pt" if self.pc is not None else "optimizer.pt")
         if os.path.exists(opt_file):
             self.optimizer.load_state_dict(torch.load(opt_file, map_location="cpu", weights_only=False))

@@ -27,19 +27,38 @@ class TrainingArguments:
     max_grad_norm: float = 1.0
     num_train_epochs: float = 1.0
     max_steps: int = -1
-    lr_scheduler_type: str = "linear"
+    lr_scheduler_type: str = "linear"  # see trainer_utils.SchedulerType
+    lr_scheduler_num_cycles: float = 0.5  # cosine: half-waves / 2; cosine_with_restarts: number of restarts
+    lr_scheduler_power: float = 1.0  # polynomial
     warmup_ratio: float = 0.0
     warmup_steps: int = 0
+    logging_strategy: str = "steps"  # no | steps | epoch
     logging_steps: int = 10
+    logging_first_step: bool = False
+    logging_dir: Optional[str] = None  # when set, every log record is also appended to <logging_dir>/log.jsonl
+    save_strategy: str = "steps"  # no | steps | epoch
     save_steps: int = 0
     save_total_limit: Optional[int] = None
+    evaluation_strategy: str = "steps"  # no | steps | epoch
     eval_steps: int = 0
+    eval_accumulation_steps: Optional[int] = None  # predict(): move gathered outputs to the host every this many batches
+    load_best_model_at_end: bool = False
+    label_names: Optional[list] = None  # batch keys handed to compute_metrics as labels (default ["labels"])
+    label_smoothing_factor: float = 0.0
+    remove_unused_columns: bool = True  # drop batch keys the model's forward does not take
+    ignore_data_skip: bool = False  # resume: do not fast-forward the data loader to the saved step
+    group_by_length: bool = False  # batches drawn from length-sorted buckets (needs a "length" or "input_ids" column)
+    overwrite_output_dir: bool = False
+    local_rank: int = -1
+    report_to: Optional[list] = None  # "jsonl" (logging_dir) is the only built-in sink
+    disable_tqdm: bool = True
     seed: int = 42
     bf16: bool = False
     fp16: bool = False
     dataloader_drop_last: bool = True
     dataloader_num_workers: int = 0
-    optim: str = "adam"  # adam | adamw | lamb | sgd | adagrad | novograd | cpu_adam
+    dataloader_pin_memory: bool = True
+    optim: str = "adam"  # see trainer_utils.OptimizerNames
     resume_from_checkpoint: Optional[str] = None
     metric_for_best_model: Optional[str] = None
     greater_is_better: bool = False
@@ -52,8 +71,20 @@ class TrainingArguments:
     oslo_config: Any = field(default=None, repr=False)
 
     def __post_init__(self):
+        from .trainer_utils import IntervalStrategy, OptimizerNames, SchedulerType
+
         if self.bf16 and self.fp16:
             raise ValueError("choose one of bf16 / fp16")
+        SchedulerType(self.lr_scheduler_type)
+        OptimizerNames(str(self.optim).lower())
+        for name in ("logging_strategy", "save_strategy", "evaluation_strategy"):
+            setattr(self, name, IntervalStrategy(getattr(self, name)).value)
+        if self.load_best_model_at_end and self.metric_for_best_model is None:
+            self.metric_for_best_model = "eval_loss"
+        if not 0.0 <= self.label_smoothing_factor < 1.0:
+            raise ValueError("label_smoothing_factor must be in [0, 1)")
+        if self.label_names is None:
+            self.label_names = ["labels"]
         if self.oslo_config_path_or_dict is not None and self.parallel_context is None:
             from .oslo_init import OsloTrainerConfig, init_oslo_features
 

@@ -160,3 +160,107 @@ def test_trainer_callbacks_predict_and_memory_metrics():
         out = t.predict(_Toy(16))
         assert out.predictions.shape == out.label_ids.shape == (16, 16)
         assert out.metrics["test_loss"] > 0 and "test_mem_cpu_alloc_delta" in out.metrics
+
+
+def test_scheduler_types_and_optimizer_names():
+    from oslo_b200.transformers.trainer_utils import (OptimizerNames, SchedulerType, create_optimizer, get_scheduler, lr_factor,
+                                                      log_dist)
+
+    # closed forms of each schedule (warm-up 2 of 10 steps)
+    assert lr_factor("linear", 0, 2, 10) == 0.5 and lr_factor("linear", 1, 2, 10) == 1.0
+    assert abs(lr_factor("linear", 6, 2, 10) - 0.5) < 1e-12 and lr_factor("linear", 10, 2, 10) == 0.0
+    assert abs(lr_factor("cosine", 6, 2, 10) - 0.5) < 1e-12
+    assert abs(lr_factor("polynomial", 6, 2, 10, power=2.0) - 0.25) < 1e-12
+    assert lr_factor("constant", 0, 2, 10) == 1.0 and lr_factor("constant_with_warmup", 0, 2, 10) == 0.5
+    assert lr_factor("constant_with_warmup", 9, 2, 10) == 1.0
+    # two restarts: the factor returns to 1 at the middle of the decay phase
+    assert abs(lr_factor("cosine_with_restarts", 6, 2, 10, num_cycles=2) - 1.0) < 1e-12
+    assert lr_factor("cosine_with_restarts", 5, 2, 10, num_cycles=2) < 0.2
+    with pytest.raises(ValueError):
+        SchedulerType("nope")
+    assert OptimizerNames("lamb") == "lamb"
+    w = torch.nn.Parameter(torch.ones(4))
+    for name in ("adam", "adamw", "sgd", "adagrad", "adadelta", "cpu_adam", "cpu_adagrad"):
+        w.grad = torch.ones(4)
+        before = w.detach().clone()
+        opt = create_optimizer(name, [w], lr=0.1)
+        opt.step()
+        assert (w.detach() < before).all(), name
+    sched = get_scheduler("linear", torch.optim.SGD([w], lr=1.0), 0, 4)
+    seen = []
+    for _ in range(4):
+        seen.append(sched.get_last_lr()[0])
+        sched.optimizer.step()
+        sched.step()
+    assert seen == [1.0, 0.75, 0.5, 0.25]
+    assert log_dist("hello", rank=0) and not log_dist("hello", rank=3)
+
+
+def test_epoch_strategies_best_model_reload_and_log_sink():
+    from oslo_b200.transformers import Trainer, TrainingArguments
+
+    with tempfile.TemporaryDirectory() as tmp:
+        args = TrainingArguments(output_dir=tmp, per_device_train_batch_size=8, learning_rate=3e-3, num_train_epochs=2,
+                                 logging_strategy="epoch", evaluation_strategy="epoch", save_strategy="epoch",
+                                 load_best_model_at_end=True, logging_dir=os.path.join(tmp, "logs"), seed=1)
+        assert args.metric_for_best_model == "eval_loss"
+        t = Trainer(_model(), args, train_dataset=_Toy(), eval_dataset=_Toy(16))
+        t.train()
+        steps_per_epoch = len(_Toy()) // 8
+        assert os.path.isdir(os.path.join(tmp, f"checkpoint-{steps_per_epoch}"))
+        assert os.path.isdir(os.path.join(tmp, f"checkpoint-{2 * steps_per_epoch}"))
+        losses = [h for h in t.state.log_history if "loss" in h]
+        evals = [h for h in t.state.log_history if "eval_loss" in h]
+        assert len(losses) == 2 and len(evals) == 2
+        assert t.state.best_model_checkpoint is not None
+        # the reloaded weights are those of the best checkpoint
+        best = torch.load(os.path.join(t.state.best_model_checkpoint, "pytorch_model.bin"), map_location="cpu")
+        for k, v in t.base_model.state_dict().items():
+            assert torch.equal(v.cpu(), best[k]), k
+        with open(os.path.join(tmp, "logs", "log.jsonl")) as f:
+            lines = [json.loads(line) for line in f]
+        assert len(lines) == len(t.state.log_history)
+    with pytest.raises(ValueError):
+        TrainingArguments(save_strategy="sometimes")
+    with pytest.raises(ValueError):
+        TrainingArguments(optim="adamz")
+
+
+def test_label_smoothing_unused_columns_and_length_grouping():
+    from oslo_b200.transformers import Trainer, TrainingArguments
+    from oslo_b200.transformers.trainer import LengthGroupedSampler
+
+    class _Extra(_Toy):
+        def __getitem__(self, i):
+            d = super().__getitem__(i)
+            d["not_a_model_argument"] = torch.zeros(1)
+            return d
+
+    class _Strict(torch.nn.Module):
+        shift_labels = True
+
+        def __init__(self):
+            super().__init__()
+            self.inner = _model()
+
+        def forward(self, input_ids, labels=None):
+            return self.inner(input_ids=input_ids, labels=labels)
+
+    with tempfile.TemporaryDirectory() as tmp:
+        model = _Strict()
+        t = Trainer(model, TrainingArguments(output_dir=tmp, label_smoothing_factor=0.1, max_steps=1, save_steps=0), train_dataset=_Extra())
+        batch = {"input_ids": torch.arange(16).view(1, 16) % 64, "labels": torch.arange(16).view(1, 16) % 64,
+                 "not_a_model_argument": torch.zeros(1)}
+        moved = t._move(batch)
+        assert "not_a_model_argument" not in moved
+        with torch.no_grad():
+            got = t.compute_loss(moved)
+            logits = model(input_ids=moved["input_ids"]).logits[:, :-1].float()
+            want = torch.nn.functional.cross_entropy(logits.reshape(-1, 64), moved["labels"][:, 1:].reshape(-1), label_smoothing=0.1)
+        assert torch.allclose(got, want, rtol=1e-5, atol=1e-6)
+        t.train()  # the extra column does not reach the model
+    lengths = [int(x) for x in torch.randint(1, 100, (64,), generator=torch.Generator().manual_seed(0))]
+    parts = [list(LengthGroupedSampler(list(range(64)), 4, num_replicas=2, rank=r, seed=3, lengths=lengths)) for r in (0, 1)]
+    assert sorted(parts[0] + parts[1]) == list(range(64))
+    spread = [max(lengths[i] for i in parts[0][b:b + 4]) - min(lengths[i] for i in parts[0][b:b + 4]) for b in range(0, 32, 4)]
+    assert sum(spread) / len(spread) < 25  # random batches of four would spread over ~60
