@@ -103,6 +103,12 @@ def gemm(
     if use_epi == 3:
         # ``aux`` is an INPUT here: the product is multiplied by gelu_tanh'(aux) element by element
         assert aux is not None and bias is None and not accumulate, "gelu_grad takes aux (the pre-activation) and nothing else"
+    if two_cta is None and block_n == 0 and causal == 0:
+        from . import gemm_algo
+
+        tuned = gemm_algo.lookup(M, N, K, a_mn, b_mn, a.dtype, b_in * b_out)  # offline search results, when a map is loaded
+        if tuned is not None:
+            two_cta, block_n = tuned.two_cta, tuned.block_n
     if two_cta is None:
         pairs = _lib.num_sms() // 2
         tiles = b_in * b_out * ((M + 255) // 256) * ((N + 255) // 256)
