@@ -215,5 +215,38 @@ class LSBert(nn.Module):
         return torch.nn.functional.cross_entropy(logits.float(), labels), logits
 
 
-__all__ = ["LSModelConfig", "MODEL_ARCH", "get_config", "LSTransformer", "LSTransformerEncoder", "LSTransformerDecoder",
+class LSBertCrf(nn.Module):
+    """Sequence tagger: bidirectional encoder -> per-token emission scores -> linear-chain CRF (the reference's
+    ``BertCrf`` lsflow model, oslo/lightseq2/csrc/models/bert_crf.cc).  ``forward(input_ids, tags)`` returns the mean
+    negative log-likelihood per sequence, ``infer(input_ids)`` the Viterbi paths (one list of tags per sequence, padding
+    excluded)."""
+
+    get_config = staticmethod(get_config)
+
+    def __init__(self, config: LSModelConfig):
+        super().__init__()
+        from .crf import LSCRFLayer
+
+        self.config = config
+        self.encoder = LSTransformerEncoder(config, LSTransformerEmbeddingLayer(config))
+        self.emission = onn.Linear(config.hidden_size, config.num_labels)
+        self.crf = LSCRFLayer(config.num_labels)
+
+    def emissions(self, input_ids):
+        x, mask = self.encoder(input_ids)
+        return self.emission(x), (None if mask is None else ~mask)
+
+    def forward(self, input_ids, tags: Optional[torch.Tensor] = None):
+        em, keep = self.emissions(input_ids)
+        if tags is None:
+            return em
+        return self.crf(em, tags, keep, reduction="mean"), em
+
+    @torch.no_grad()
+    def infer(self, input_ids):
+        em, keep = self.emissions(input_ids)
+        return self.crf.decode(em, keep)
+
+
+__all__ = ["LSBertCrf", "LSModelConfig", "MODEL_ARCH", "get_config", "LSTransformer", "LSTransformerEncoder", "LSTransformerDecoder",
            "LSGpt", "LSBert"]

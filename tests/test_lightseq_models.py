@@ -300,3 +300,103 @@ def test_lsflow_static_graph_matches_eager_and_reuses_memory():
         ctx.run({"x": torch.randn(65, 32)}, [h])
     with pytest.raises(RuntimeError):
         lsflow.AddOp(ctx, "late")(x, x)
+
+
+def _ls_cfg(**kw):
+    from oslo_b200.lightseq import get_config
+
+    base = dict(vocab_size=97, hidden_size=32, intermediate_size=64, nhead=4, max_seq_len=48, padding_idx=0,
+                num_encoder_layer=2, num_decoder_layer=2, num_labels=5)
+    base.update(kw)
+    return get_config(**base)
+
+
+def test_lsflow_bert_and_bert_crf_match_the_eager_models_for_any_request_size():
+    from oslo_b200.lightseq import LSBert, LSBertCrf, LSFlowBert, LSFlowBertCrf
+
+    torch.manual_seed(0)
+    for pre in (True, False):  # pre- and post-LayerNorm encoders
+        model = LSBert(_ls_cfg(pre_layer_norm=pre, activation_fn="gelu")).eval()
+        flow = LSFlowBert(model, max_batch=4, max_seq=16)
+        mem = flow.memory(flow.ctx)
+        assert mem["arena_bytes"] < mem["unplanned_bytes"] and mem["cache_bytes"] == 0
+        arena = flow.ctx.arena.data_ptr()
+        for b, s in ((4, 16), (1, 5), (3, 9)):
+            ids = torch.randint(1, 97, (b, s))
+            if b == 3:
+                ids[0, 6:] = 0  # padded request
+                ids[2, 4:] = 0
+            with torch.no_grad():
+                want = model(ids)
+            got = flow.infer(ids)
+            assert got.shape == want.shape and torch.allclose(got, want, atol=2e-5, rtol=1e-4), (pre, b, s)
+        assert flow.ctx.arena.data_ptr() == arena  # no re-allocation between requests
+        with pytest.raises(ValueError):
+            flow.infer(torch.ones(5, 16, dtype=torch.long))
+    tagger = LSBertCrf(_ls_cfg()).eval()
+    # training direction: the CRF likelihood is differentiable through encoder and transitions
+    ids = torch.randint(1, 97, (3, 10))
+    ids[1, 7:] = 0
+    tags = torch.randint(0, 5, (3, 10))
+    loss, _ = tagger(ids, tags)
+    loss.backward()
+    assert tagger.crf.transitions.grad is not None and tagger.emission.weight.grad is not None
+    flow = LSFlowBertCrf(tagger, max_batch=4, max_seq=12)
+    paths = flow.infer(ids)
+    assert paths == tagger.infer(ids) and [len(p) for p in paths] == [10, 7, 10]
+
+
+def test_lsflow_gpt_decodes_incrementally_over_persistent_caches():
+    from oslo_b200.lightseq import LSFlowGpt, LSGpt, generate
+
+    torch.manual_seed(1)
+    model = LSGpt(_ls_cfg(num_decoder_layer=3)).eval()
+    flow = LSFlowGpt(model, max_batch=4, max_len=40)
+    assert flow.memory(flow.ctx)["cache_bytes"] == 3 * 2 * 4 * 4 * 40 * 8 * 4  # layers x (k, v) x batch x heads x len x hd x fp32
+    prompt = torch.randint(1, 97, (3, 7))
+    out = flow.infer(prompt, max_new_tokens=12)
+    want = generate(model, prompt, max_new_tokens=12, do_sample=False) if "do_sample" in generate.__code__.co_varnames else None
+    if want is None:
+        want = prompt
+        with torch.no_grad():
+            for _ in range(12):
+                want = torch.cat([want, model(want).logits[:, -1].argmax(-1, keepdim=True)], dim=1)
+    assert torch.equal(out, want)
+    assert flow.runs == 12  # one prompt run + eleven single-token runs
+    # the logits of an incremental run equal those of a full-prefix forward
+    flow.infer(prompt, max_new_tokens=1)
+    nxt = model(prompt).logits[:, -1].argmax(-1, keepdim=True)
+    inc = flow._step(nxt, 7)
+    with torch.no_grad():
+        full = model(torch.cat([prompt, nxt], dim=1)).logits[:, -1]
+    assert torch.allclose(inc, full, atol=2e-5, rtol=1e-4)
+    # sampling: reproducible under a seeded generator, stops at eos and pads after it
+    g = torch.Generator().manual_seed(5)
+    a = flow.infer(prompt, 10, top_k=8, top_p=0.9, temperature=0.8, generator=g)
+    g = torch.Generator().manual_seed(5)
+    b = flow.infer(prompt, 10, top_k=8, top_p=0.9, temperature=0.8, generator=g)
+    assert torch.equal(a, b) and a.shape == (3, 17)
+    eos = int(out[0, 9])
+    stopped = flow.infer(prompt, 12, eos_token_id=eos)
+    row = stopped[0, 7:].tolist()
+    assert eos in row and all(t == 0 for t in row[row.index(eos) + 1:])
+    with pytest.raises(ValueError):
+        flow.infer(prompt, max_new_tokens=40)
+
+
+def test_lsflow_transformer_translates_like_the_eager_model_greedy_and_beam():
+    from oslo_b200.lightseq import LSFlowTransformer, LSTransformer
+
+    torch.manual_seed(2)
+    model = LSTransformer(_ls_cfg(activation_fn="relu")).eval()
+    flow = LSFlowTransformer(model, max_batch=3, max_src=12, max_trg=16, max_beam=3)
+    src = torch.randint(4, 97, (3, 9))
+    src[1, 6:] = 0
+    for beams in (1, 3):
+        want = model.infer(src, max_new_tokens=10, beam_size=beams)
+        got = flow.infer(src, max_new_tokens=10, beam_size=beams)
+        assert torch.equal(got, want), beams
+    mem = flow.memory()
+    assert mem["cache_bytes"] > 0 and mem["arena_bytes"] < mem["unplanned_bytes"]
+    with pytest.raises(ValueError):
+        flow.infer(src, beam_size=4)
