@@ -47,4 +47,5 @@ from .loss import (
     VocabParallelCrossEntropyLoss2D,
     VocabParallelCrossEntropyLoss2p5D,
 )
+from .zero_linear import ZeroShardedLinear, shard_linears, zero_linear
 from .ngram_repeat_block import FusedNoRepeatNGramLogitsProcessor, NGramRepeatBlock, fused_no_repeat_ngram_logits_processor

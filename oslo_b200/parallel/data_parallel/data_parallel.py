@@ -60,7 +60,8 @@ class _DistributedDataParallel(ParallelWrapper):
     def parallelize(self):
         """Flatten gradients and install the hooks (run by ``oslo_b200.ready`` after TP / EP sharding)."""
         pc = self.parallel_context
-        skip = lambda p: getattr(p, "oslo_expert_param", False)  # expert weights are not replicated over DATA
+        # expert weights are not replicated over DATA; row-sharded (ZeRO-3 style) linears reduce their own gradients
+        skip = lambda p: getattr(p, "oslo_expert_param", False) or getattr(p, "oslo_zero_sharded", False)
         params = [p for p in self.module.parameters() if p.requires_grad and not skip(p)]
         if self.dp_world_size > 1:
             src = pc.get_ranks_in_group(self.mode)[0]

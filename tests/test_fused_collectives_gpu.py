@@ -318,3 +318,47 @@ def test_fused_2d_model_step_matches_composition(mode):
 @pytest.mark.skipif(_n_gpus() < 8, reason="needs 8 GPUs")
 def test_fused_3d_model_step_matches_composition():
     run_dist(_nd_worker, 8, "TENSOR_3D", timeout=600)
+
+
+def _zero_linear_worker(rank, world):
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    from oslo_b200 import ParallelContext, ParallelMode
+    from oslo_b200.distributed import symm
+    from oslo_b200.nn.zero_linear import ZeroShardedLinear
+    from oslo_b200.ops import _lib, fused_collectives as fc
+
+    pc = ParallelContext.from_torch(data_parallel_size=world, backend="nccl", seed=0)
+    dev = pc.device
+    torch.manual_seed(7)  # same full layer on every rank
+    full = torch.nn.Linear(256, 512).to(dev, torch.bfloat16)
+    layer = ZeroShardedLinear.from_linear(full, pc)
+    torch.manual_seed(50 + rank)  # own batch per rank
+    x = (torch.randn(4, 256, 256, device=dev) * 0.5).to(torch.bfloat16)
+    gy = (torch.randn(4, 256, 512, device=dev) * 0.1).to(torch.bfloat16)
+
+    def run():
+        xi = x.clone().requires_grad_(True)
+        layer.weight.grad = layer.bias.grad = None
+        y = layer(xi)
+        y.backward(gy)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        return y.detach().float().clone(), xi.grad.float().clone(), layer.weight.grad.float().clone(), layer.bias.grad.float().clone()
+
+    ref = run()  # collective + matmul composition: no workspace yet
+    assert symm.enable(pc, ParallelMode.DATA, max_tokens=1024, max_features=1024, multimem=False)
+    rt = fc.runtime(ParallelMode.DATA)
+    assert rt is not None and rt.ws.ag_ok(layer.weight, x.reshape(-1, 256))
+    before = rt.ws.epoch
+    got = run()
+    assert rt.ws.epoch >= before + 2, "the fused all-gather GEMM and GEMM reduce-scatter did not run"
+    for name, a, b in zip(("y", "dx", "dw", "db"), got, ref):
+        err = (a - b).abs().max().item() / (b.abs().max().item() + 1e-6)
+        assert err < 2e-2, (name, err)
+    symm.disable()
+    pc.destroy()
+
+
+@pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_zero_sharded_linear_fused_gather_gemm_matches_composition():
+    run_dist(_zero_linear_worker, 2, timeout=600)
