@@ -346,6 +346,9 @@ def _zero_linear_worker(rank, world):
         return y.detach().float().clone(), xi.grad.float().clone(), layer.weight.grad.float().clone(), layer.bias.grad.float().clone()
 
     ref = run()  # collective + matmul composition: no workspace yet
+    from oslo_b200.nn import zero_linear as zl
+
+    zl.FUSED_GATHER = True  # the fused route is opt-in (measured slower than the composition at this size)
     assert symm.enable(pc, ParallelMode.DATA, max_tokens=1024, max_features=1024, multimem=False)
     rt = fc.runtime(ParallelMode.DATA)
     assert rt is not None and rt.ws.ag_ok(layer.weight, x.reshape(-1, 256))
