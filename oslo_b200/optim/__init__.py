@@ -5,6 +5,7 @@ from .fused_adam import FusedAdam
 from .fused_lamb import FusedLamb, FusedMixedPrecisionLamb
 from .fused_novograd import FusedNovoGrad
 from .fused_sgd import FusedSGD
+from .loss_scaler import DynamicLossScaler
 
 __all__ = ["FusedAdam", "FusedSGD", "FusedAdagrad", "FusedLamb", "FusedMixedPrecisionLamb", "FusedNovoGrad", "CPUAdam",
-           "CPUAdagrad"]
+           "CPUAdagrad", "DynamicLossScaler"]

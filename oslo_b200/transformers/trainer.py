@@ -106,6 +106,7 @@ class Trainer:
             model.to(args.dtype)
         self.model = model
         self.zero = None
+        self.scaler = None  # DynamicLossScaler, built with the optimizer when fp16 is on
         if self.pc is not None:
             from .oslo_init import apply_wrappers
 
@@ -195,6 +196,11 @@ class Trainer:
             self.zero = opt = ZeroRedundancyOptimizer(inner, parallel_context=self.pc, partition_grad=dp["zero_stage"] == 2,
                                                       clip_grad_norm=a.max_grad_norm, **(dp.get("params") or {}))
         self.optimizer = opt
+        if a.fp16 and self.zero is None and self.scaler is None:
+            from oslo_b200.optim.loss_scaler import DynamicLossScaler
+
+            group = dist.group.WORLD if (self.pc is not None and dist.is_initialized()) else None
+            self.scaler = DynamicLossScaler(init_scale=a.fp16_init_scale, growth_interval=a.fp16_growth_interval, group=group)
         return opt
 
     # ------------------------------------------------------------- train loop
@@ -244,12 +250,15 @@ class Trainer:
             total = torch.zeros((), device=self.device)
             for _, out in self.model(**batch):
                 if torch.is_tensor(out.loss):
-                    (out.loss / accum).backward()
+                    part = out.loss / accum
+                    (self.scaler.scale(part) if self.scaler is not None else part).backward()
                     total += out.loss.detach()
             return total
         loss = self.compute_loss(batch) / accum
         if self.zero is not None:
-            self.zero.backward(loss)
+            self.zero.backward(loss)  # the ZeRO optimizer scales the loss itself
+        elif self.scaler is not None:
+            self.scaler.scale(loss).backward()
         else:
             loss.backward()
         return loss.detach() * accum
@@ -313,9 +322,19 @@ class Trainer:
                     tokens += batch["input_ids"].numel()
                 if not sync_now:
                     continue
-                self._clip()
-                opt.step()
-                self.lr_scheduler.step()
+                if self.scaler is not None:
+                    # fp16: un-scale, skip the update (and the schedule step) when any rank's gradients overflowed
+                    overflow = self.scaler.unscale_(opt)
+                    if not overflow:
+                        self._clip()
+                    self.scaler.step(opt)
+                    self.scaler.update()
+                    if not overflow:
+                        self.lr_scheduler.step()
+                else:
+                    self._clip()
+                    opt.step()
+                    self.lr_scheduler.step()
                 if self.zero is not None:
                     opt.zero_grad()
                 elif hasattr(self.model, "zero_grad") and hasattr(self.model, "flats"):
@@ -488,6 +507,8 @@ class Trainer:
         torch.save(rng, os.path.join(out, f"rng_state_{rank}.pth"))
         if rank == 0:
             torch.save(self.lr_scheduler.state_dict(), os.path.join(out, "scheduler.pt"))
+            if self.scaler is not None:
+                torch.save(self.scaler.state_dict(), os.path.join(out, "scaler.pt"))
             with open(os.path.join(out, "trainer_state.json"), "w") as f:
                 f.write(self.state.to_json())
             torch.save(self.args.__dict__.get("oslo_config_path_or_dict"), os.path.join(out, "training_args.bin"))
@@ -527,6 +548,9 @@ class Trainer:
         sched = os.path.join(path, "scheduler.pt")
         if os.path.exists(sched):
             self.lr_scheduler.load_state_dict(torch.load(sched))
+        scaler = os.path.join(path, "scaler.pt")
+        if self.scaler is not None and os.path.exists(scaler):
+            self.scaler.load_state_dict(torch.load(scaler))
         rng_file = os.path.join(path, f"rng_state_{rank}.pth")
         if os.path.exists(rng_file):
             rng = torch.load(rng_file, weights_only=False)

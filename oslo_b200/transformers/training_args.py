@@ -55,6 +55,8 @@ class TrainingArguments:
     seed: int = 42
     bf16: bool = False
     fp16: bool = False
+    fp16_init_scale: float = 65536.0  # dynamic loss scaling (fp16 only): initial scale ...
+    fp16_growth_interval: int = 2000  # ... doubled after this many overflow-free steps, halved on overflow
     dataloader_drop_last: bool = True
     dataloader_num_workers: int = 0
     dataloader_pin_memory: bool = True

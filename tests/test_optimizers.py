@@ -76,3 +76,42 @@ def test_fused_optimizers_torch_paths():
             opt.step()
             first = first or loss.item()
         assert torch.isfinite(w).all() and (w ** 2).sum().item() < first
+
+
+def test_dynamic_loss_scaler_skips_overflow_and_adapts_the_scale():
+    import torch
+
+    from oslo_b200.optim import DynamicLossScaler
+
+    w = torch.nn.Parameter(torch.ones(4))
+    opt = torch.optim.SGD([w], lr=0.5)
+    sc = DynamicLossScaler(init_scale=8.0, growth_interval=2)
+    # clean step: the gradient is un-scaled exactly once, the step is taken
+    sc.scale((w * torch.tensor([1.0, 2.0, 3.0, 4.0])).sum()).backward()
+    assert w.grad.tolist() == [8.0, 16.0, 24.0, 32.0]
+    assert sc.unscale_(opt) is False and sc.unscale_(opt) is False
+    assert w.grad.tolist() == [1.0, 2.0, 3.0, 4.0]
+    sc.step(opt)
+    sc.update()
+    assert w.tolist() == [0.5, 0.0, -0.5, -1.0] and sc.get_scale() == 8.0
+    # overflow: no update, scale halves, counter resets
+    opt.zero_grad()
+    before = w.detach().clone()
+    sc.scale((w * torch.tensor([1.0, float("inf"), 1.0, 1.0])).sum()).backward()
+    assert sc.step(opt) is None
+    sc.update()
+    assert torch.equal(w.detach(), before) and sc.get_scale() == 4.0 and sc.skipped_steps == 1
+    # two clean steps grow it again; the state round-trips
+    for _ in range(2):
+        opt.zero_grad()
+        sc.scale(w.sum()).backward()
+        sc.step(opt)
+        sc.update()
+    assert sc.get_scale() == 8.0
+    other = DynamicLossScaler()
+    other.load_state_dict(sc.state_dict())
+    assert other.get_scale() == 8.0 and other.skipped_steps == 1 and other.growth_interval == 2
+    off = DynamicLossScaler(enabled=False)
+    assert off.get_scale() == 1.0 and off.scale(torch.tensor(3.0)).item() == 3.0
+    with pytest.raises(ValueError):
+        DynamicLossScaler(growth_factor=1.0)

@@ -1,5 +1,6 @@
 """Trainer: loss goes down, checkpoint + resume reproduces the uninterrupted run, config validation, profiler."""
 import json
+import math
 import os
 import tempfile
 
@@ -264,3 +265,27 @@ def test_label_smoothing_unused_columns_and_length_grouping():
     assert sorted(parts[0] + parts[1]) == list(range(64))
     spread = [max(lengths[i] for i in parts[0][b:b + 4]) - min(lengths[i] for i in parts[0][b:b + 4]) for b in range(0, 32, 4)]
     assert sum(spread) / len(spread) < 25  # random batches of four would spread over ~60
+
+
+def test_fp16_training_uses_the_dynamic_loss_scaler_and_checkpoints_it():
+    from oslo_b200.transformers import Trainer, TrainingArguments
+
+    with tempfile.TemporaryDirectory() as tmp:
+        args = TrainingArguments(output_dir=tmp, per_device_train_batch_size=8, learning_rate=1e-3, max_steps=8, logging_steps=2,
+                                 save_steps=8, fp16=True, fp16_init_scale=2.0 ** 40, fp16_growth_interval=3, seed=1)
+        t = Trainer(_model(), args, train_dataset=_Toy())
+        t.train()
+        assert t.scaler is not None and next(t.base_model.parameters()).dtype == torch.float16
+        # 2^40 overflows fp16 gradients: the first steps are skipped (weights untouched) while the scale backs off
+        assert t.scaler.skipped_steps >= 1 and t.scaler.get_scale() < 2.0 ** 40
+        assert all(torch.isfinite(p).all() for p in t.base_model.parameters())
+        losses = [h["loss"] for h in t.state.log_history if "loss" in h]
+        assert all(math.isfinite(v) for v in losses)
+        saved = torch.load(os.path.join(tmp, "checkpoint-8", "scaler.pt"))
+        assert saved["scale"] == t.scaler.get_scale() and saved["skipped_steps"] == t.scaler.skipped_steps
+        # the schedule advanced only on the steps that were taken
+        assert t.lr_scheduler.last_epoch == 8 - t.scaler.skipped_steps
+        t2 = Trainer(_model(), TrainingArguments(output_dir=tmp, per_device_train_batch_size=8, max_steps=9, fp16=True, save_steps=0, seed=1),
+                     train_dataset=_Toy())
+        t2.train(resume_from_checkpoint=os.path.join(tmp, "checkpoint-8"))
+        assert t2.scaler.skipped_steps >= t.scaler.skipped_steps
