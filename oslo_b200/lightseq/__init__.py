@@ -16,5 +16,5 @@ from .memory_planner import ActivationPlan, plan
 from .quantization import QuantLinear, TensorQuantizer, quantize_int8
 from .crf import LSCRFLayer
 from .export import export_model, import_into, load_exported
-from .lsflow_models import LSFlowBert, LSFlowBertCrf, LSFlowGpt, LSFlowTransformer
-from .models import LSBert, LSBertCrf, LSGpt, LSModelConfig, LSTransformer, LSTransformerDecoder, LSTransformerEncoder, get_config
+from .lsflow_models import LSFlowBert, LSFlowBertCrf, LSFlowGpt, LSFlowTransformer, LSFlowVit
+from .models import LSBert, LSBertCrf, LSGpt, LSVit, LSModelConfig, LSTransformer, LSTransformerDecoder, LSTransformerEncoder, get_config

@@ -99,6 +99,34 @@ class LSFlowBertCrf(_FlowModel):
         return [[t for t in row if t >= 0] for row in tags]
 
 
+class LSFlowVit(_FlowModel):
+    """:class:`oslo_b200.lightseq.models.LSVit` as a planned graph: ``infer(pixels) -> logits [batch, labels]``.  The
+    patch extraction and the class-token / position add run before the graph (they are one reshape and one add); the
+    patch projection, the encoder and the head are graph nodes."""
+
+    def __init__(self, model, max_batch: int = 8):
+        super().__init__(model, max_batch, model.num_patches + 1)
+        ctx = self.ctx = lf.Context(self.device)
+        seq = model.num_patches + 1
+        x = ctx.input("tokens", (max_batch * seq, model.config.hidden_size), self.dtype)
+        for i, layer in enumerate(model.layers):
+            x = lf.encoder_layer_graph(ctx, x, layer, f"enc{i}")
+        n = model.layer_norm
+        x = lf.LayerNormOp(ctx, "ln", n.weight, n.bias, n.eps)(x)
+        cls = lf.SelectTokenOp(ctx, "cls", 0)(x)
+        self.logits = lf.LinearOp(ctx, "head", model.classifier.weight, model.classifier.bias)(cls)
+        ctx.build()
+
+    @torch.no_grad()
+    def infer(self, pixels: torch.Tensor) -> torch.Tensor:
+        if pixels.shape[0] > self.max_batch:
+            raise ValueError(f"batch {pixels.shape[0]} exceeds the planned maximum {self.max_batch}")
+        tokens = self.module.embed(pixels)
+        b, s, h = tokens.shape
+        (out,) = self.ctx.run({"tokens": tokens.reshape(b * s, h).contiguous()}, [self.logits], seq_len=s)
+        return out.clone()
+
+
 def _pick(logits: torch.Tensor, top_k: int, top_p: float, temperature: float, generator) -> torch.Tensor:
     if top_k == 1 or (top_k == 0 and top_p >= 1.0 and temperature == 0.0):
         return logits.argmax(-1, keepdim=True)
@@ -235,4 +263,4 @@ class LSFlowTransformer(_FlowModel):
         return out
 
 
-__all__ = ["LSFlowBert", "LSFlowBertCrf", "LSFlowGpt", "LSFlowTransformer"]
+__all__ = ["LSFlowBert", "LSFlowBertCrf", "LSFlowGpt", "LSFlowTransformer", "LSFlowVit"]

@@ -248,5 +248,55 @@ class LSBertCrf(nn.Module):
         return self.crf.decode(em, keep)
 
 
-__all__ = ["LSBertCrf", "LSModelConfig", "MODEL_ARCH", "get_config", "LSTransformer", "LSTransformerEncoder", "LSTransformerDecoder",
+class LSVit(nn.Module):
+    """Vision Transformer classifier on the same encoder layers: non-overlapping ``patch x patch`` patches projected by one
+    linear map (a strided convolution written as unfold + GEMM, so it runs on the tcgen05 kernel), a class token, learned
+    positions, pre-LayerNorm encoder, final LayerNorm, linear head on the class token (the reference's ``Vit`` inference
+    model, oslo/lightseq2/inference/model/vit_encoder.cc.cu)."""
+
+    get_config = staticmethod(get_config)
+
+    def __init__(self, config: LSModelConfig, image_size: int = 224, patch_size: int = 16, channels: int = 3):
+        super().__init__()
+        if image_size % patch_size:
+            raise ValueError("image_size must be a multiple of patch_size")
+        if not config.pre_layer_norm:
+            raise ValueError("the vision transformer is pre-LayerNorm")
+        self.config, self.image_size, self.patch_size, self.channels = config, image_size, patch_size, channels
+        self.num_patches = (image_size // patch_size) ** 2
+        h = config.hidden_size
+        self.patch_proj = onn.Linear(channels * patch_size * patch_size, h)
+        self.cls_token = nn.Parameter(torch.zeros(1, 1, h))
+        self.pos_embed = nn.Parameter(torch.zeros(1, self.num_patches + 1, h))
+        nn.init.trunc_normal_(self.pos_embed, std=0.02)
+        nn.init.trunc_normal_(self.cls_token, std=0.02)
+        self.layers = nn.ModuleList([LSTransformerEncoderLayer(config) for _ in range(config.num_encoder_layer)])
+        self.layer_norm = onn.FusedLayerNorm(h)
+        self.classifier = onn.Linear(h, config.num_labels)
+
+    def patches(self, pixels: torch.Tensor) -> torch.Tensor:
+        """``[b, c, H, W] -> [b, patches, c * p * p]`` (channel-major inside a patch, like a Conv2d weight flattened)."""
+        b, c, hh, ww = pixels.shape
+        p = self.patch_size
+        if (c, hh, ww) != (self.channels, self.image_size, self.image_size):
+            raise ValueError(f"expected images of {self.channels} x {self.image_size} x {self.image_size}")
+        x = pixels.view(b, c, hh // p, p, ww // p, p).permute(0, 2, 4, 1, 3, 5)
+        return x.reshape(b, self.num_patches, c * p * p)
+
+    def embed(self, pixels: torch.Tensor) -> torch.Tensor:
+        x = self.patch_proj(self.patches(pixels).to(self.patch_proj.weight.dtype))
+        x = torch.cat([self.cls_token.expand(x.shape[0], -1, -1).to(x.dtype), x], dim=1)
+        return x + self.pos_embed.to(x.dtype)
+
+    def forward(self, pixels, labels: Optional[torch.Tensor] = None):
+        x = self.embed(pixels)
+        for layer in self.layers:
+            x = layer(x)
+        logits = self.classifier(self.layer_norm(x)[:, 0])
+        if labels is None:
+            return logits
+        return torch.nn.functional.cross_entropy(logits.float(), labels), logits
+
+
+__all__ = ["LSVit", "LSBertCrf", "LSModelConfig", "MODEL_ARCH", "get_config", "LSTransformer", "LSTransformerEncoder", "LSTransformerDecoder",
            "LSGpt", "LSBert"]

@@ -400,3 +400,30 @@ def test_lsflow_transformer_translates_like_the_eager_model_greedy_and_beam():
     assert mem["cache_bytes"] > 0 and mem["arena_bytes"] < mem["unplanned_bytes"]
     with pytest.raises(ValueError):
         flow.infer(src, beam_size=4)
+
+
+def test_vit_matches_a_conv_patch_embedding_and_its_graph():
+    from oslo_b200.lightseq import LSFlowVit, LSVit
+
+    torch.manual_seed(3)
+    model = LSVit(_ls_cfg(num_labels=7, vocab_size=0), image_size=32, patch_size=8, channels=3).eval()
+    x = torch.randn(3, 3, 32, 32)
+    # the unfold + GEMM patch projection is a stride-8 convolution with the same weights
+    conv = torch.nn.Conv2d(3, 32, 8, stride=8)
+    with torch.no_grad():
+        conv.weight.copy_(model.patch_proj.weight.view(32, 3, 8, 8))
+        conv.bias.copy_(model.patch_proj.bias)
+        want = conv(x).flatten(2).transpose(1, 2)
+        got = model.patch_proj(model.patches(x))
+    assert torch.allclose(got, want, atol=1e-5)
+    with torch.no_grad():
+        logits = model(x)
+    assert logits.shape == (3, 7)
+    loss, _ = model(x, torch.tensor([1, 2, 3]))
+    loss.backward()
+    assert model.pos_embed.grad is not None and model.cls_token.grad is not None
+    flow = LSFlowVit(model, max_batch=4)
+    assert torch.allclose(flow.infer(x), logits, atol=2e-5, rtol=1e-4)
+    assert torch.allclose(flow.infer(x[:1]), logits[:1], atol=2e-5, rtol=1e-4)
+    with pytest.raises(ValueError):
+        model(torch.randn(1, 3, 16, 16))
