@@ -22,6 +22,7 @@ from .config import BartConfig, MBartConfig
 from .heads import classification_loss, qa_loss
 from .losses import token_lm_loss
 from .modeling_utils import ModelOutput, PreTrainedModel, additive_mask
+from .modeling_utils import active_seq2seq_cache, offset_causal_mask, seq2seq_generate
 
 
 def shift_tokens_right(input_ids, pad_token_id: int, decoder_start_token_id: int):
@@ -65,9 +66,23 @@ class BartAttention(nn.Module):
         b, t, _ = hidden_states.shape
         src = hidden_states if key_value_states is None else key_value_states
         q = self.q_proj(hidden_states).view(b, t, -1, self.head_dim)
-        k = self.k_proj(src).view(b, src.shape[1], -1, self.head_dim)
-        v = self.v_proj(src).view(b, src.shape[1], -1, self.head_dim)
-        return self.out_proj(OF.attention(q, k, v, causal=self.is_causal and key_value_states is None, mask=mask))
+        project = lambda: (self.k_proj(src).view(b, src.shape[1], -1, self.head_dim),  # noqa: E731
+                           self.v_proj(src).view(b, src.shape[1], -1, self.head_dim))
+        cross = key_value_states is not None
+        cache = active_seq2seq_cache() if (cross or self.is_causal) else None  # decoder modules only
+        causal = self.is_causal and not cross
+        if cache is None:
+            k, v = project()
+        elif cross:
+            k, v = cache.cross(id(self), project)  # the encoder memory is projected on the first step only
+        else:
+            k, v = cache.self_append(id(self), *project())
+            if cache.offset > 0:  # new tokens against stored ones: the triangle is offset, not square
+                causal = False
+                tri = offset_causal_mask(t, cache.offset, q.device)
+                if tri is not None:
+                    mask = tri if mask is None else mask + tri
+        return self.out_proj(OF.attention(q, k, v, causal=causal, mask=mask))
 
 
 class BartEncoderLayer(nn.Module):
@@ -182,7 +197,9 @@ class BartDecoder(nn.Module):
 
     def forward(self, input_ids, attention_mask=None, encoder_hidden_states=None, encoder_attention_mask=None):
         t = input_ids.shape[1]
-        x = self.embed_tokens(input_ids) * self.embed_scale + self.embed_positions(t, input_ids.device)
+        cache = active_seq2seq_cache()
+        past = cache.offset if cache is not None else 0
+        x = self.embed_tokens(input_ids) * self.embed_scale + self.embed_positions(t, input_ids.device, past)
         x = self.dropout(self.layernorm_embedding(x))
         self_mask = causal_additive_mask(attention_mask, t) if attention_mask is not None else None
         cross_mask = additive_mask(encoder_attention_mask, torch.float32)
@@ -260,20 +277,16 @@ class BartForConditionalGeneration(BartPreTrainedModel):
         return ModelOutput(loss=loss, logits=logits, encoder_last_hidden_state=out.encoder_last_hidden_state)
 
     @torch.no_grad()
-    def generate(self, input_ids, attention_mask=None, max_new_tokens: int = 32):
-        """Greedy decoding: the encoder runs once, the decoder re-reads its own prefix each step."""
-        enc = self.model.encoder(input_ids, attention_mask)
+    def generate(self, input_ids, attention_mask=None, max_new_tokens: int = 32, num_beams: int = 1, length_penalty: float = 1.0,
+                 use_cache: bool = True):
+        """Greedy (``num_beams = 1``) or beam-search decoding.  The encoder runs once; with ``use_cache`` every step feeds
+        the newest target token only and the attention modules keep their keys / values (``Seq2SeqCache``)."""
         cfg = self.config
-        out = torch.full((input_ids.shape[0], 1), cfg.decoder_start_token_id, dtype=torch.long, device=input_ids.device)
-        done = torch.zeros(input_ids.shape[0], dtype=torch.bool, device=input_ids.device)
-        for _ in range(max_new_tokens):
-            logits = self.forward(attention_mask=attention_mask, decoder_input_ids=out, encoder_outputs=enc).logits[:, -1]
-            nxt = logits.argmax(-1).masked_fill(done, cfg.pad_token_id)
-            out = torch.cat([out, nxt[:, None]], dim=1)
-            done |= nxt == cfg.eos_token_id
-            if bool(done.all()):
-                break
-        return out
+        return seq2seq_generate(
+            self, lambda ids, mask: self.model.encoder(ids, mask),
+            lambda enc, mask, dec: self.forward(attention_mask=mask, decoder_input_ids=dec, encoder_outputs=enc).logits[:, -1],
+            input_ids, attention_mask, max_new_tokens, num_beams, length_penalty, cfg.decoder_start_token_id, cfg.eos_token_id,
+            cfg.pad_token_id, use_cache)
 
 
 class BartClassificationHead(nn.Module):

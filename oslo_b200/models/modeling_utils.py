@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import os
 from dataclasses import dataclass
-from typing import Optional
+from typing import Dict, Optional, Tuple
 
 import torch
 import torch.nn as nn
@@ -115,3 +115,119 @@ class PreTrainedModel(nn.Module, OsloModel):
         model.load_state_dict(state, strict=False)
         model.tie_weights()
         return model
+
+
+class Seq2SeqCache:
+    """Decoder state of an encoder-decoder model during incremental generation: per attention module the keys / values
+    of the target tokens seen so far (self-attention, grown by one position per step) and the projected encoder memory
+    (cross-attention, computed on the first step only).  ``offset`` is the number of target tokens already stored; the
+    decoders add it to their positions / relative-position biases.  The reference keeps the same buffers in its decoder
+    (oslo/lightseq2/inference/model/decoder.cc.cu: self key / value caches per layer, encoder key / value projected once)."""
+
+    def __init__(self):
+        self.self_kv: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
+        self.cross_kv: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
+        self.offset = 0
+
+    def self_append(self, key: int, k: torch.Tensor, v: torch.Tensor):
+        """``k`` / ``v``: ``[batch, new tokens, heads, head_dim]``; returns everything stored for ``key`` so far."""
+        if key in self.self_kv:
+            pk, pv = self.self_kv[key]
+            k, v = torch.cat([pk, k], dim=1), torch.cat([pv, v], dim=1)
+        self.self_kv[key] = (k, v)
+        return k, v
+
+    def cross(self, key: int, make):
+        if key not in self.cross_kv:
+            self.cross_kv[key] = make()
+        return self.cross_kv[key]
+
+    def advance(self, n: int):
+        self.offset += n
+
+    def reorder(self, index: torch.Tensor):
+        """Beam search: hypothesis ``i`` continues hypothesis ``index[i]``."""
+        self.self_kv = {k: (a.index_select(0, index), b.index_select(0, index)) for k, (a, b) in self.self_kv.items()}
+        self.cross_kv = {k: (a.index_select(0, index), b.index_select(0, index)) for k, (a, b) in self.cross_kv.items()}
+
+
+_S2S_CACHE: Optional[Seq2SeqCache] = None
+
+
+class seq2seq_cache:
+    """Context manager that makes ``cache`` the active :class:`Seq2SeqCache` (inference only)."""
+
+    def __init__(self, cache: Seq2SeqCache):
+        self.cache = cache
+
+    def __enter__(self):
+        global _S2S_CACHE
+        self.prev, _S2S_CACHE = _S2S_CACHE, self.cache
+        return self.cache
+
+    def __exit__(self, *exc):
+        global _S2S_CACHE
+        _S2S_CACHE = self.prev
+
+
+def active_seq2seq_cache() -> Optional[Seq2SeqCache]:
+    return _S2S_CACHE
+
+
+def offset_causal_mask(new: int, past: int, device, dtype=torch.float32) -> Optional[torch.Tensor]:
+    """Additive ``[new, past + new]`` mask: new token ``i`` sees stored positions ``<= past + i``.  ``None`` when a single
+    token is fed (it sees everything)."""
+    if new == 1:
+        return None
+    return torch.full((new, past + new), torch.finfo(dtype).min, device=device, dtype=dtype).triu(past + 1)
+
+
+@torch.no_grad()
+def seq2seq_generate(model, encode, decode_logits, input_ids, attention_mask, max_new_tokens: int, num_beams: int,
+                     length_penalty: float, start_id: int, eos_id: int, pad_id: int, use_cache: bool = True):
+    """Greedy / beam-search decoding shared by the encoder-decoder models.  ``encode(ids, mask)`` returns the encoder
+    output; ``decode_logits(enc, mask, decoder_ids)`` the logits of the LAST fed position.  With ``use_cache`` each step
+    feeds only the newest token and the attention modules read their :class:`Seq2SeqCache`."""
+    b = input_ids.shape[0]
+    dev = input_ids.device
+    enc = encode(input_ids, attention_mask)
+    if num_beams > 1:
+        enc = enc.repeat_interleave(num_beams, dim=0)
+        attention_mask = attention_mask.repeat_interleave(num_beams, dim=0) if attention_mask is not None else None
+    n = b * num_beams
+    out = torch.full((n, 1), start_id, dtype=torch.long, device=dev)
+    done = torch.zeros(n, dtype=torch.bool, device=dev)
+    scores = torch.zeros(b, num_beams, device=dev)
+    if num_beams > 1:
+        scores[:, 1:] = -1e9  # the beams start identical: only the first may spawn children at step 0
+    cache = Seq2SeqCache() if use_cache else None
+    for _ in range(max_new_tokens):
+        if cache is not None:
+            feed = out[:, cache.offset:]
+            with seq2seq_cache(cache):
+                logits = decode_logits(enc, attention_mask, feed)
+            cache.advance(feed.shape[1])
+        else:
+            logits = decode_logits(enc, attention_mask, out)
+        if num_beams == 1:
+            nxt = logits.argmax(-1).masked_fill(done, pad_id)
+        else:
+            logp = torch.log_softmax(logits.float(), dim=-1)
+            logp[done] = -1e9
+            logp[done, pad_id] = 0.0  # finished hypotheses extend with padding at no cost
+            v = logp.shape[-1]
+            scores, idx = (scores.view(-1, 1) + logp).view(b, num_beams * v).topk(num_beams, dim=-1)
+            parent = (idx // v + torch.arange(b, device=dev).unsqueeze(1) * num_beams).view(-1)
+            nxt = (idx % v).view(-1)
+            out, done = out[parent], done[parent]
+            if cache is not None:
+                cache.reorder(parent)
+        out = torch.cat([out, nxt[:, None]], dim=1)
+        done = done | (nxt == eos_id)
+        if bool(done.all()):
+            break
+    if num_beams > 1:
+        lengths = (out != pad_id).sum(-1).view(b, num_beams).float()
+        best = (scores / lengths.pow(length_penalty)).argmax(-1)
+        out = out.view(b, num_beams, -1)[torch.arange(b, device=dev), best]
+    return out

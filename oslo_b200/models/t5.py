@@ -22,6 +22,7 @@ from oslo_b200.ops.activation import act_reference
 from .config import MT5Config, T5Config
 from .losses import token_lm_loss
 from .modeling_utils import ModelOutput, PreTrainedModel, additive_mask
+from .modeling_utils import active_seq2seq_cache, offset_causal_mask, seq2seq_generate
 
 
 class T5LayerNorm(onn.FusedRMSNorm):
@@ -110,8 +111,14 @@ class T5Attention(nn.Module):
         src = x if key_value_states is None else key_value_states
         hd = self.key_value_proj_dim
         q = self.q(x).view(b, t, -1, hd)
-        k = self.k(src).view(b, src.shape[1], -1, hd)
-        v = self.v(src).view(b, src.shape[1], -1, hd)
+        project = lambda: (self.k(src).view(b, src.shape[1], -1, hd), self.v(src).view(b, src.shape[1], -1, hd))  # noqa: E731
+        cache = active_seq2seq_cache() if self.is_decoder else None
+        if cache is None:
+            k, v = project()
+        elif key_value_states is None:
+            k, v = cache.self_append(id(self), *project())  # keys / values of every target token so far
+        else:
+            k, v = cache.cross(id(self), project)  # the encoder memory is projected on the first step only
         return self.o(OF.attention(q, k, v, causal=False, scale=1.0, mask=position_bias))
 
 
@@ -168,9 +175,13 @@ class T5Stack(nn.Module):
     def forward(self, input_ids, attention_mask=None, encoder_hidden_states=None, encoder_attention_mask=None):
         b, t = input_ids.shape
         x = self.dropout(self.embed_tokens(input_ids))
-        bias = self.block[0].layer[0].SelfAttention.compute_bias(t, t, input_ids.device).float()
+        cache = active_seq2seq_cache() if self.is_decoder else None
+        past = cache.offset if cache is not None else 0
+        bias = self.block[0].layer[0].SelfAttention.compute_bias(past + t, past + t, input_ids.device).float()[:, :, past:]
         if self.is_decoder:
-            bias = bias + torch.full((t, t), torch.finfo(torch.float32).min, device=input_ids.device).triu(1)
+            tri = offset_causal_mask(t, past, input_ids.device)
+            if tri is not None:
+                bias = bias + tri
         if attention_mask is not None:
             bias = bias + additive_mask(attention_mask, torch.float32)
         cross_mask = additive_mask(encoder_attention_mask, torch.float32)
@@ -275,20 +286,16 @@ class T5ForConditionalGeneration(T5Model):
         return ModelOutput(loss=loss, logits=logits, encoder_last_hidden_state=out.encoder_last_hidden_state)
 
     @torch.no_grad()
-    def generate(self, input_ids, attention_mask=None, max_new_tokens: int = 32):
-        """Greedy decoding: the encoder runs once, the decoder re-reads its own prefix each step."""
-        enc = self.encoder(input_ids, attention_mask)
+    def generate(self, input_ids, attention_mask=None, max_new_tokens: int = 32, num_beams: int = 1, length_penalty: float = 1.0,
+                 use_cache: bool = True):
+        """Greedy (``num_beams = 1``) or beam-search decoding.  The encoder runs once; with ``use_cache`` every step feeds
+        the newest target token only and the attention modules keep their keys / values (``Seq2SeqCache``)."""
         cfg = self.config
-        out = torch.full((input_ids.shape[0], 1), cfg.decoder_start_token_id, dtype=torch.long, device=input_ids.device)
-        done = torch.zeros(input_ids.shape[0], dtype=torch.bool, device=input_ids.device)
-        for _ in range(max_new_tokens):
-            logits = self.forward(attention_mask=attention_mask, decoder_input_ids=out, encoder_outputs=enc).logits[:, -1]
-            nxt = logits.argmax(-1).masked_fill(done, cfg.pad_token_id)
-            out = torch.cat([out, nxt[:, None]], dim=1)
-            done |= nxt == cfg.eos_token_id
-            if bool(done.all()):
-                break
-        return out
+        return seq2seq_generate(
+            self, lambda ids, mask: self.encoder(ids, mask),
+            lambda enc, mask, dec: self.forward(attention_mask=mask, decoder_input_ids=dec, encoder_outputs=enc).logits[:, -1],
+            input_ids, attention_mask, max_new_tokens, num_beams, length_penalty, cfg.decoder_start_token_id, cfg.eos_token_id,
+            cfg.pad_token_id, use_cache)
 
 
 class MT5PreTrainedModel(T5PreTrainedModel):

@@ -123,6 +123,25 @@ def test_seq2seq_family_matches_hugging_face(module, name, cfg, kw):
         _compare(ours, theirs, ("logits",), tol=1e-4, input_ids=ids, attention_mask=m, labels=dec)  # decoder inputs from labels
     out = ours.generate(ids[:2], max_new_tokens=4)
     assert out.shape[0] == 2 and 2 <= out.shape[1] <= 5
+    # incremental decoding over the key / value cache gives the tokens of full-prefix decoding, greedy and beam, with and
+    # without source padding; and the greedy tokens are Hugging Face's
+    ours.config.eos_token_id = theirs.config.eos_token_id = -1  # random weights: never stop early, compare every step
+    ours.double()  # random weights give near-tied beam candidates: keep cached-vs-full rounding far below the gaps
+    for m in (None, mask):
+        for beams in (1, 3):
+            cached = ours.generate(ids, m, max_new_tokens=7, num_beams=beams, use_cache=True)
+            full = ours.generate(ids, m, max_new_tokens=7, num_beams=beams, use_cache=False)
+            assert torch.equal(cached, full), (name, beams, m is not None)
+    ours.float()
+    from oslo_b200.models.modeling_utils import Seq2SeqCache, active_seq2seq_cache
+
+    assert active_seq2seq_cache() is None  # the cache does not outlive generate()
+    cache = Seq2SeqCache()
+    assert cache.offset == 0 and not cache.self_kv
+    if name in ("BartForConditionalGeneration", "T5ForConditionalGeneration"):  # (mBART's generation config forces other tokens)
+        hf = theirs.generate(input_ids=ids, attention_mask=mask, max_new_tokens=7, num_beams=1, do_sample=False, min_length=0)
+        mine = ours.generate(ids, mask, max_new_tokens=7)
+        assert torch.equal(mine[:, : hf.shape[1]], hf[:, : mine.shape[1]]), name
 
 
 def test_bart_heads_match_hugging_face():
