@@ -157,6 +157,13 @@ class GPT2LMHeadModel(PreTrainedModel):
 
     def forward(self, input_ids=None, attention_mask=None, position_ids=None, labels=None, **kwargs):
         hidden = self.transformer(input_ids, attention_mask, position_ids)
+        chunk = getattr(self.config, "chunked_head_loss", 0)
+        if labels is not None and chunk:  # config.chunked_head_loss = tokens per chunk: the logits are never materialised
+            from .losses import chunked_head_loss
+
+            loss = chunked_head_loss(self, hidden, self.lm_head, labels, chunk)
+            if loss is not None:
+                return CausalLMOutput(loss=loss, logits=None)
         logits = self.lm_head(hidden)
         loss = None
         if labels is not None:

@@ -247,6 +247,13 @@ class GPTNeoXForCausalLM(PreTrainedModel):
 
     def forward(self, input_ids=None, attention_mask=None, labels=None, **kwargs):
         hidden = self.gpt_neox(input_ids, attention_mask)
+        chunk = getattr(self.config, "chunked_head_loss", 0)
+        if labels is not None and chunk:  # config.chunked_head_loss = tokens per chunk: the logits are never materialised
+            from .losses import chunked_head_loss
+
+            loss = chunked_head_loss(self, hidden, self.embed_out, labels, chunk)
+            if loss is not None:
+                return CausalLMOutput(loss=loss, logits=None)
         logits = self.embed_out(hidden)
         loss = None
         if labels is not None:

@@ -161,6 +161,13 @@ class LlamaForCausalLM(PreTrainedModel):
 
     def forward(self, input_ids=None, attention_mask=None, labels=None, **kwargs):
         hidden = self.model(input_ids, attention_mask)
+        chunk = getattr(self.config, "chunked_head_loss", 0)
+        if labels is not None and chunk:  # config.chunked_head_loss = tokens per chunk: the logits are never materialised
+            from .losses import chunked_head_loss
+
+            loss = chunked_head_loss(self, hidden, self.lm_head, labels, chunk)
+            if loss is not None:
+                return CausalLMOutput(loss=loss, logits=None)
         logits = self.lm_head(hidden)
         loss = None
         if labels is not None:

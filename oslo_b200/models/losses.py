@@ -55,3 +55,18 @@ def token_lm_loss(model, logits, targets, ignore_index: int = -100) -> LossResul
     fn = onn.VocabParallelCrossEntropyLoss1D(parallel_context=None, ignore_index=ignore_index)
     fn.orig_vocab_size = orig_vocab
     return LossResult(fn(logits, targets), logits.is_cuda)
+
+
+def chunked_head_loss(model, hidden, head, labels, chunk_size: int, ignore_index: int = -100):
+    """Next-token loss straight from the final hidden states: LM head and cross-entropy run chunk by chunk
+    (:func:`oslo_b200.ops.linear_cross_entropy.linear_cross_entropy`), the ``[tokens, vocab]`` logits never exist.  Returns
+    ``None`` when the head is not a plain (unsharded, bias-free) linear, in which case the caller takes the usual path."""
+    if type(head) not in (torch.nn.Linear, onn.Linear) or getattr(head, "bias", None) is not None:
+        return None
+    pc = getattr(model, "parallel_context", None)
+    if pc is not None and pc.tensor_parallel_size > 1:
+        return None
+    from oslo_b200.ops.linear_cross_entropy import linear_cross_entropy
+
+    return linear_cross_entropy(hidden, head.weight, shift_labels(labels, ignore_index), chunk_size, ignore_index,
+                                orig_vocab_size=model.config.vocab_size)

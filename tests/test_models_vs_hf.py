@@ -56,3 +56,35 @@ def test_gpt2_matches_hugging_face():
     kw = dict(vocab_size=100, n_positions=32, n_embd=64, n_layer=2, n_head=4, resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
     theirs = HM(HC(**kw)).eval()
     _check(GPT2LMHeadModel(GPT2Config(**kw)).eval(), theirs, 100)
+
+
+def test_chunked_head_loss_equals_the_materialised_head_for_the_causal_models():
+    from oslo_b200 import models
+    from oslo_b200.models.config import GPTNeoXConfig
+    from oslo_b200.models.gpt_neox import GPTNeoXForCausalLM
+
+    torch.manual_seed(0)
+    cases = [
+        (GPTNeoXForCausalLM, GPTNeoXConfig(vocab_size=101, hidden_size=32, num_hidden_layers=2, num_attention_heads=4,
+                                           intermediate_size=64, max_position_embeddings=32)),
+        (models.GPT2LMHeadModel, models.GPT2Config(vocab_size=101, n_positions=32, n_embd=32, n_layer=2, n_head=4, resid_pdrop=0.0,
+                                                   embd_pdrop=0.0, attn_pdrop=0.0, tie_word_embeddings=False)),
+        (models.LlamaForCausalLM, models.LlamaConfig(vocab_size=101, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                                                     num_attention_heads=4, max_position_embeddings=32)),
+    ]
+    ids = torch.randint(0, 101, (3, 17))
+    labels = ids.clone()
+    labels[1, :4] = -100
+    for cls, cfg in cases:
+        model = cls(cfg)
+        ref = model(input_ids=ids, labels=labels).loss
+        ref.backward()
+        want = {n: p.grad.clone() for n, p in model.named_parameters() if p.grad is not None}
+        model.zero_grad()
+        model.config.chunked_head_loss = 8
+        out = model(input_ids=ids, labels=labels)
+        assert out.logits is None and torch.allclose(out.loss, ref, atol=1e-5), cls.__name__
+        out.loss.backward()
+        for n, p in model.named_parameters():
+            if n in want:
+                assert torch.allclose(p.grad, want[n], atol=2e-5), (cls.__name__, n)

@@ -90,3 +90,30 @@ def _p2p_worker(rank, world):
 
 def test_object_p2p_and_gather_dim():
     run_dist(_p2p_worker, 2)
+
+
+def test_linear_cross_entropy_chunks_match_the_materialised_head():
+    import torch
+    import torch.nn.functional as F
+
+    from oslo_b200.ops.linear_cross_entropy import linear_cross_entropy
+
+    torch.manual_seed(0)
+    T, H, V = 37, 16, 50
+    hidden = torch.randn(3, T, H, requires_grad=True)
+    weight = torch.randn(V, H, requires_grad=True)
+    targets = torch.randint(0, V - 4, (3, T))
+    targets[0, :5] = -100
+    for chunk, valid in ((8, None), (1000, None), (16, V - 4)):
+        hidden.grad = weight.grad = None
+        loss = linear_cross_entropy(hidden, weight, targets, chunk_size=chunk, orig_vocab_size=valid)
+        (loss * 2.0).backward()
+        gh, gw = hidden.grad.clone(), weight.grad.clone()
+        hidden.grad = weight.grad = None
+        logits = hidden.reshape(-1, H) @ weight.t()
+        if valid is not None:
+            logits = logits[:, :valid]
+        ref = F.cross_entropy(logits, targets.reshape(-1), ignore_index=-100)
+        (ref * 2.0).backward()
+        assert torch.allclose(loss, ref, atol=1e-5), (chunk, float(loss), float(ref))
+        assert torch.allclose(gh, hidden.grad, atol=1e-5) and torch.allclose(gw, weight.grad, atol=1e-5), chunk
