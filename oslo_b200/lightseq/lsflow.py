@@ -79,6 +79,22 @@ class Operator:
     def run(self, lead: int):
         raise NotImplementedError
 
+    def native_record(self, slot):
+        """Record of this node for the host executor (``csrc/cpu/graph_exec.cpp``): a dict of the record's fields, with
+        tensors / variables given through ``slot(obj)`` (an index into the pointer table), or ``None`` when the executor has
+        no such operator (the context then keeps running node by node)."""
+        return None
+
+
+_ACT_CODE = {None: -1, "tanh": 0, "relu": 1, "gelu": 2}
+_ROWS = {"tokens": 0, "batch": 1}
+
+
+def _f64_bits(x: float) -> int:
+    import struct
+
+    return struct.unpack("<q", struct.pack("<d", float(x)))[0]
+
 
 class LinearOp(Operator):
     """``out = act(x @ W^T + b)``; ``act`` in {None, "gelu", "relu"} (GELU rides in the GEMM epilogue on CUDA)."""
@@ -91,6 +107,12 @@ class LinearOp(Operator):
         out = Variable(self.ctx, self.name + ".out", (x.max_shape[0], self.weight.shape[0]), x.dtype, lead=x.lead)
         self._register([x], [out])
         return out
+
+    def native_record(self, slot):
+        if self.act not in _ACT_CODE:
+            return None
+        return dict(op=1, in0=slot(self.inputs[0]), out=slot(self.outputs[0]), w=slot(self.weight), b=slot(self.bias),
+                    rows=_ROWS[self.outputs[0].lead], d0=self.weight.shape[1], d1=self.weight.shape[0], d2=_ACT_CODE[self.act])
 
     def run(self, lead):
         from oslo_b200.ops.gemm import gemm, supported
@@ -121,6 +143,10 @@ class LayerNormOp(Operator):
         self._register([x], [out])
         return out
 
+    def native_record(self, slot):
+        return dict(op=2, in0=slot(self.inputs[0]), out=slot(self.outputs[0]), w=slot(self.weight), b=slot(self.bias),
+                    rows=_ROWS[self.outputs[0].lead], d0=self.inputs[0].max_shape[-1], scalar=_f64_bits(self.eps))
+
     def run(self, lead):
         from oslo_b200.ops.norm import layer_norm
 
@@ -135,6 +161,10 @@ class AddOp(Operator):
         out = Variable(self.ctx, self.name + ".out", a.max_shape, a.dtype, lead=a.lead)
         self._register([a, b], [out])
         return out
+
+    def native_record(self, slot):
+        return dict(op=3, in0=slot(self.inputs[0]), in1=slot(self.inputs[1]), out=slot(self.outputs[0]),
+                    rows=_ROWS[self.outputs[0].lead], d0=math.prod(self.inputs[0].max_shape[1:]))
 
     def run(self, lead):
         torch.add(self.inputs[0].value, self.inputs[1].value, out=self.outputs[0].value)
@@ -152,6 +182,11 @@ class AttentionOp(Operator):
         out = Variable(self.ctx, self.name + ".out", (qkv.max_shape[0], qkv.max_shape[1] // 3), qkv.dtype)
         self._register([qkv], [out])
         return out
+
+    def native_record(self, slot):
+        hidden = self.inputs[0].max_shape[1] // 3
+        return dict(op=4, in0=slot(self.inputs[0]), out=slot(self.outputs[0]), d1=self.heads, d2=hidden // self.heads,
+                    flags=1 if self.causal else 0)
 
     def run(self, lead):
         from oslo_b200.ops.attention import qkv_attention
@@ -180,6 +215,13 @@ class EmbeddingOp(Operator):
         self._register([ids], [out])
         return out
 
+    def native_record(self, slot):
+        pos = self.positions
+        if pos.dtype != self.weight.dtype or pos.device != self.weight.device:
+            pos = self.positions = pos.to(device=self.weight.device, dtype=self.weight.dtype)
+        return dict(op=5, in0=slot(self.inputs[0]), out=slot(self.outputs[0]), w=slot(self.weight), x0=slot(pos),
+                    d0=self.weight.shape[1], d2=self.padding_idx, scalar=_f64_bits(self.scale))
+
     def run(self, lead):
         from .kernels import ls_embedding
 
@@ -207,6 +249,10 @@ class CachedAttentionOp(Operator):
         out = Variable(self.ctx, self.name + ".out", (qkv.max_shape[0], qkv.max_shape[1] // 3), qkv.dtype)
         self._register([qkv], [out])
         return out
+
+    def native_record(self, slot):
+        return dict(op=8, in0=slot(self.inputs[0]), out=slot(self.outputs[0]), d1=self.heads, d2=self.head_dim,
+                    x0=slot(("buffer", self.k_name)), x1=slot(("buffer", self.v_name)), max_len=self.max_len)
 
     def run(self, lead):
         ctx = self.ctx
@@ -292,6 +338,9 @@ class SelectTokenOp(Operator):
         self._register([x], [out])
         return out
 
+    def native_record(self, slot):
+        return dict(op=6, in0=slot(self.inputs[0]), out=slot(self.outputs[0]), rows=1, d0=self.inputs[0].max_shape[-1], d2=self.which)
+
     def run(self, lead):
         seq = self.ctx.seq_len
         x = self.inputs[0].value.view(lead // seq, seq, -1)
@@ -311,6 +360,10 @@ class ActivationOp(Operator):
         out = Variable(self.ctx, self.name + ".out", x.max_shape, x.dtype, lead=x.lead)
         self._register([x], [out])
         return out
+
+    def native_record(self, slot):
+        return dict(op=7, in0=slot(self.inputs[0]), out=slot(self.outputs[0]), rows=_ROWS[self.outputs[0].lead],
+                    d0=math.prod(self.inputs[0].max_shape[1:]), d2=_ACT_CODE[self.kind])
 
     def run(self, lead):
         self.outputs[0].value.copy_(self._FN[self.kind](self.inputs[0].value))
@@ -394,6 +447,84 @@ class Context:
         self.built = True
         return self
 
+    # ---------------------------------------------------------------- native program
+    _FIELDS = ("op", "in0", "in1", "out", "w", "b", "rows", "d0", "d1", "d2", "flags", "scalar", "x0", "x1", "max_len", "reserved")
+
+    def compile_native(self) -> bool:
+        """Translate the graph into a program for the host executor (``csrc/cpu/graph_exec.cpp``): afterwards a run is
+        one native call instead of one Python dispatch per node.  Possible when the graph lives on the CPU in fp32 and every
+        node has a native operator; returns whether it was (the node-by-node path stays available either way)."""
+        if not self.built:
+            raise RuntimeError("call build() first")
+        self._native = None
+        if self.device.type != "cpu":
+            return False
+        if any(v.dtype not in (torch.float32, torch.int64) for v in self._variables):
+            return False
+        items: List[object] = []
+        index: Dict[object, int] = {}
+
+        def slot(obj) -> int:
+            if obj is None:
+                return -1
+            key = obj if isinstance(obj, tuple) else id(obj)
+            if key not in index:
+                if torch.is_tensor(obj) and (obj.dtype != torch.float32 or not obj.is_contiguous() or obj.device.type != "cpu"):
+                    raise TypeError("native programs take contiguous fp32 host tensors")
+                index[key] = len(items)
+                items.append(obj)
+            return index[key]
+
+        records = []
+        try:
+            for node in self._nodes:
+                rec = node.native_record(slot)
+                if rec is None:
+                    return False
+                row = [-1 if f in ("in0", "in1", "out", "w", "b", "x0", "x1") else 0 for f in self._FIELDS]
+                for k, v in rec.items():
+                    row[self._FIELDS.index(k)] = int(v)
+                records.append(row)
+        except TypeError:
+            return False
+        import ctypes
+
+        from oslo_b200.ops import _lib
+
+        lib = _lib.cpu_lib()
+        if lib.oslo_cpu_graph_record_size() != len(self._FIELDS):
+            return False
+        lib.oslo_cpu_graph_run.restype = ctypes.c_int
+        self._native = {"lib": lib, "prog": torch.tensor(records, dtype=torch.int64).contiguous(), "items": items,
+                        "ptrs": (ctypes.c_void_p * max(len(items), 1))()}
+        return True
+
+    def _run_native(self, lead: int) -> None:
+        import ctypes
+
+        nat = self._native
+        ptrs = nat["ptrs"]
+        for i, obj in enumerate(nat["items"]):
+            if isinstance(obj, Variable):
+                t = obj.value
+                if not t.is_contiguous():
+                    t = obj.value = t.contiguous()
+            elif isinstance(obj, tuple):
+                t = self.buffers[obj[1]]
+            else:
+                t = obj
+            ptrs[i] = t.data_ptr()
+        pad = self.padding_mask
+        pad_t = None
+        if pad is not None:
+            pad_t = pad.to(torch.uint8).contiguous()
+        rc = nat["lib"].oslo_cpu_graph_run(
+            ctypes.c_void_p(nat["prog"].data_ptr()), ctypes.c_int(nat["prog"].shape[0]), ptrs, ctypes.c_longlong(lead),
+            ctypes.c_longlong(self.seq_len), ctypes.c_longlong(self.step), ctypes.c_void_p(pad_t.data_ptr() if pad_t is not None else None))
+        if rc != 0:
+            node = self._nodes[-rc - 1].name if -len(self._nodes) <= rc < 0 else "?"
+            raise RuntimeError(f"the host graph executor stopped at node {node!r} (code {rc})")
+
     # ------------------------------------------------------------------------ run
     def run(self, feed: Dict[str, torch.Tensor], outputs: Sequence[Variable], seq_len: Optional[int] = None, step: int = 0,
             padding_mask: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, ...]:
@@ -428,8 +559,11 @@ class Context:
             if not v.external:
                 v.value = v.view(lead if v.lead == "tokens" else batch)
         with torch.no_grad():
-            for node in self._nodes:
-                node.run(lead)
+            if getattr(self, "_native", None) is not None:
+                self._run_native(lead)
+            else:
+                for node in self._nodes:
+                    node.run(lead)
         return tuple(v.value for v in outputs)
 
 

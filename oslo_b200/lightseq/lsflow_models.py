@@ -68,6 +68,7 @@ class LSFlowBert(_FlowModel):
         pooled = lf.ActivationOp(ctx, "pool.tanh", "tanh")(lf.SelectTokenOp(ctx, "pool", 0)(x))
         self.logits = lf.LinearOp(ctx, "classifier", model.classifier.weight, model.classifier.bias)(pooled)
         ctx.build()
+        self.native = ctx.compile_native()  # host fp32 graphs run as one call into the C++ executor
 
     @torch.no_grad()
     def infer(self, input_ids: torch.Tensor) -> torch.Tensor:
@@ -116,6 +117,7 @@ class LSFlowVit(_FlowModel):
         cls = lf.SelectTokenOp(ctx, "cls", 0)(x)
         self.logits = lf.LinearOp(ctx, "head", model.classifier.weight, model.classifier.bias)(cls)
         ctx.build()
+        self.native = ctx.compile_native()
 
     @torch.no_grad()
     def infer(self, pixels: torch.Tensor) -> torch.Tensor:
@@ -153,6 +155,7 @@ class LSFlowGpt(_FlowModel):
         last = lf.SelectTokenOp(ctx, "last", -1)(x)
         self.logits = lf.LinearOp(ctx, "lm_head", model.lm_head.weight, None)(last)
         ctx.build()
+        self.native = ctx.compile_native()  # host fp32 graphs run as one call into the C++ executor
         self.runs = 0
 
     def _step(self, ids: torch.Tensor, step: int) -> torch.Tensor:
@@ -194,6 +197,7 @@ class LSFlowTransformer(_FlowModel):
         enc = self.enc_ctx = lf.Context(self.device)
         _, self.enc_out = _encoder_graph(enc, model.encoder, max_batch * max_src)
         enc.build()
+        self.native = enc.compile_native()  # the encoder; the decoder's memory attention stays node by node
         rows = max_batch * max_beam
         dec = self.dec_ctx = lf.Context(self.device)
         ids = dec.input("ids", (rows * max_trg,), torch.int64)

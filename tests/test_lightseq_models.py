@@ -427,3 +427,48 @@ def test_vit_matches_a_conv_patch_embedding_and_its_graph():
     assert torch.allclose(flow.infer(x[:1]), logits[:1], atol=2e-5, rtol=1e-4)
     with pytest.raises(ValueError):
         model(torch.randn(1, 3, 16, 16))
+
+
+def test_host_graph_executor_runs_the_same_graphs_in_one_native_call():
+    """On the CPU the BERT / GPT / ViT graphs compile to a program for the C++ executor; results equal the node-by-node
+    path and the eager models, including padding, incremental decoding and requests smaller than the plan."""
+    from oslo_b200.lightseq import LSBert, LSFlowBert, LSFlowGpt, LSFlowVit, LSGpt, LSVit
+    from oslo_b200.lightseq import lsflow as lf
+
+    torch.manual_seed(4)
+    bert = LSBert(_ls_cfg(pre_layer_norm=False)).eval()
+    flow = LSFlowBert(bert, max_batch=4, max_seq=16)
+    assert flow.native and flow.ctx._native is not None
+    ids = torch.randint(1, 97, (3, 11))
+    ids[1, 5:] = 0
+    native = flow.infer(ids)
+    flow.ctx._native = None  # node-by-node
+    assert torch.allclose(native, flow.infer(ids), atol=1e-5)
+    with torch.no_grad():
+        assert torch.allclose(native, bert(ids), atol=2e-5, rtol=1e-4)
+
+    gpt = LSGpt(_ls_cfg(num_decoder_layer=2)).eval()
+    gflow = LSFlowGpt(gpt, max_batch=4, max_len=32)
+    assert gflow.native
+    prompt = torch.randint(1, 97, (2, 6))
+    out = gflow.infer(prompt, max_new_tokens=9)
+    want = prompt
+    with torch.no_grad():
+        for _ in range(9):
+            want = torch.cat([want, gpt(want).logits[:, -1].argmax(-1, keepdim=True)], dim=1)
+    assert torch.equal(out, want)
+
+    vit = LSVit(_ls_cfg(num_labels=3, vocab_size=0), image_size=16, patch_size=8).eval()
+    vflow = LSFlowVit(vit, max_batch=2)
+    x = torch.randn(2, 3, 16, 16)
+    with torch.no_grad():
+        assert vflow.native and torch.allclose(vflow.infer(x), vit(x), atol=2e-5, rtol=1e-4)
+
+    # a graph with an operator the executor does not have keeps the node-by-node path
+    from oslo_b200.lightseq import LSBertCrf, LSFlowBertCrf
+
+    crf = LSFlowBertCrf(LSBertCrf(_ls_cfg()).eval(), max_batch=2, max_seq=8)
+    assert crf.ctx.compile_native() is False and crf.infer(torch.randint(1, 97, (2, 8)))
+    # errors come back as the failing node: a decoding step beyond the cache length
+    with pytest.raises(RuntimeError, match="attn"):
+        gflow.ctx.run({"ids": prompt.reshape(-1)}, [gflow.logits], seq_len=6, step=30)
