@@ -6,7 +6,12 @@ FastAPI application:
 
 * ``POST /generate``  ``{"input_ids": [[...]], "max_new_tokens": 32, "do_sample": false, ...}`` or ``{"text": "..."}`` when a
   tokenizer was given; answers ``{"output_ids": [[...]], "text": [...]?, "batched_with": n}``;
-* ``GET /health``, ``GET /metrics`` (Prometheus text: requests, batches, batch-size histogram, latency).
+* ``GET /health``, ``GET /metrics`` (Prometheus text: requests, batches, batch-size histogram, latency);
+* the inference protocol that Triton clients speak (KServe "v2" REST): ``GET /v2``, ``/v2/health/live``,
+  ``/v2/health/ready``, ``/v2/models/{name}``, ``/v2/models/{name}/ready`` and ``POST /v2/models/{name}/infer`` with an
+  ``input_ids`` INT64 tensor ``[batch, seq]`` (flat or nested ``data``) and generation settings under ``parameters``; the answer
+  carries an ``output_ids`` INT64 tensor padded to the longest row.  So a client written against the reference's Triton
+  back end needs a URL change only.
 
 Requests wait in a queue; a single worker takes up to ``max_batch`` requests that arrive within ``max_wait_ms`` of the
 first one and runs those with the same prompt length and sampling settings as one batch (prompts of other lengths in the
@@ -101,7 +106,8 @@ class DynamicBatcher:
                     r.future.set_exception(e)
 
 
-def create_app(model, tokenizer=None, device=None, max_batch: int = 8, max_wait_ms: float = 5.0):
+def create_app(model, tokenizer=None, device=None, max_batch: int = 8, max_wait_ms: float = 5.0, model_name: str = "oslo_b200",
+               model_version: str = "1"):
     """Build the FastAPI application serving ``model`` (any causal LM accepted by ``generate``)."""
     from fastapi import FastAPI, HTTPException
     from fastapi.responses import PlainTextResponse
@@ -141,6 +147,70 @@ def create_app(model, tokenizer=None, device=None, max_batch: int = 8, max_wait_
         if tokenizer is not None and hasattr(tokenizer, "decode"):
             out["text"] = [tokenizer.decode(r[0]) for r in results]
         return out
+
+    # ------------------------------------------------------------- KServe v2 ("Triton") protocol
+    def _known(name: str, version: Optional[str] = None):
+        if name != model_name or (version is not None and version != model_version):
+            raise HTTPException(status_code=404, detail=f"unknown model {name!r}" + (f" version {version!r}" if version else ""))
+
+    @app.get("/v2")
+    async def _v2_server():
+        return {"name": "oslo_b200", "version": model_version, "extensions": ["generate_parameters"]}
+
+    @app.get("/v2/health/live")
+    async def _v2_live():
+        return {"live": True}
+
+    @app.get("/v2/health/ready")
+    async def _v2_ready():
+        return {"ready": True}
+
+    @app.get("/v2/models/{name}")
+    async def _v2_model(name: str):
+        _known(name)
+        return {"name": model_name, "versions": [model_version], "platform": "oslo_b200",
+                "inputs": [{"name": "input_ids", "datatype": "INT64", "shape": [-1, -1]}],
+                "outputs": [{"name": "output_ids", "datatype": "INT64", "shape": [-1, -1]}]}
+
+    @app.get("/v2/models/{name}/ready")
+    async def _v2_model_ready(name: str):
+        _known(name)
+        return {"ready": True}
+
+    async def _v2_infer_impl(name: str, body: Dict[str, Any], version: Optional[str] = None):
+        _known(name, version)
+        tensors = {t.get("name"): t for t in body.get("inputs", [])}
+        t = tensors.get("input_ids")
+        if t is None:
+            raise HTTPException(status_code=400, detail="the request needs an input tensor named input_ids")
+        if t.get("datatype", "INT64") not in ("INT64", "INT32"):
+            raise HTTPException(status_code=400, detail="input_ids must be INT64 or INT32")
+        shape, data = t.get("shape"), t.get("data")
+        if not isinstance(shape, list) or len(shape) != 2 or data is None:
+            raise HTTPException(status_code=400, detail="input_ids needs shape [batch, seq] and data")
+        flat = [x for row in data for x in row] if data and isinstance(data[0], list) else list(data)
+        b, sl = int(shape[0]), int(shape[1])
+        if b <= 0 or sl <= 0 or len(flat) != b * sl:
+            raise HTTPException(status_code=400, detail=f"data holds {len(flat)} elements, shape says {b} x {sl}")
+        params = {k: v for k, v in (body.get("parameters") or {}).items() if k in allowed}
+        pad = int((body.get("parameters") or {}).get("pad_token_id", 0))
+        try:
+            results = await asyncio.gather(*[batcher.submit([int(x) for x in flat[i * sl : (i + 1) * sl]], **params) for i in range(b)])
+        except Exception as e:  # noqa: BLE001
+            raise HTTPException(status_code=500, detail=repr(e))
+        rows = [r[0] for r in results]
+        width = max(len(r) for r in rows)
+        out = [x for r in rows for x in (r + [pad] * (width - len(r)))]
+        return {"model_name": model_name, "model_version": model_version, "id": body.get("id", ""),
+                "outputs": [{"name": "output_ids", "datatype": "INT64", "shape": [b, width], "data": out}]}
+
+    @app.post("/v2/models/{name}/infer")
+    async def _v2_infer(name: str, body: Dict[str, Any]):
+        return await _v2_infer_impl(name, body)
+
+    @app.post("/v2/models/{name}/versions/{version}/infer")
+    async def _v2_infer_version(name: str, version: str, body: Dict[str, Any]):
+        return await _v2_infer_impl(name, body, version)
 
     @app.get("/health")
     async def _health():

@@ -179,6 +179,23 @@ def test_http_server_generates():
         assert r.json()["output_ids"] == want
         assert client.post("/generate", json={"max_new_tokens": 3}).status_code == 422
         assert "oslo_requests_total 2" in client.get("/metrics").text
+        # the inference protocol of Triton clients (KServe v2)
+        assert client.get("/v2/health/ready").json() == {"ready": True} and client.get("/v2").json()["name"] == "oslo_b200"
+        meta = client.get("/v2/models/oslo_b200").json()
+        assert meta["inputs"][0] == {"name": "input_ids", "datatype": "INT64", "shape": [-1, -1]}
+        assert client.get("/v2/models/other").status_code == 404
+        body = {"id": "req-7", "inputs": [{"name": "input_ids", "datatype": "INT64", "shape": [2, 3], "data": [5, 6, 7, 8, 9, 10]}],
+                "parameters": {"max_new_tokens": 3}}
+        r = client.post("/v2/models/oslo_b200/infer", json=body)
+        assert r.status_code == 200, r.text
+        out = r.json()["outputs"][0]
+        assert r.json()["id"] == "req-7" and out["shape"] == [2, 6] and out["data"] == [x for row in want for x in row]
+        body["inputs"][0]["data"] = [[5, 6, 7], [8, 9, 10]]  # nested data is accepted too
+        assert client.post("/v2/models/oslo_b200/versions/1/infer", json=body).json()["outputs"][0]["data"] == out["data"]
+        assert client.post("/v2/models/oslo_b200/versions/2/infer", json=body).status_code == 404
+        body["inputs"][0]["shape"] = [2, 4]
+        assert client.post("/v2/models/oslo_b200/infer", json=body).status_code == 400
+        assert client.post("/v2/models/oslo_b200/infer", json={"inputs": []}).status_code == 400
 
 
 def test_cpu_gemms_match_torch():
