@@ -83,8 +83,17 @@ class ParallelContext:
         seed: int = 42,
         **kwargs,
     ) -> "ParallelContext":
-        """Build from the environment written by ``torchrun`` / ``torch.distributed.run``."""
+        """Build from the environment written by ``torchrun`` / ``torch.distributed.run``.  A plain ``python script.py``
+        (no ``RANK`` / ``WORLD_SIZE``) is a job of one process on a free local port."""
         env = os.environ
+        if "RANK" not in env and "WORLD_SIZE" not in env:
+            import socket
+
+            with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as sock:
+                sock.bind(("127.0.0.1", 0))
+                free = sock.getsockname()[1]
+            env = {"RANK": "0", "WORLD_SIZE": "1", "LOCAL_RANK": "0", "LOCAL_WORLD_SIZE": "1", "MASTER_ADDR": "127.0.0.1",
+                   "MASTER_PORT": env.get("MASTER_PORT", str(free))}
         return cls(
             rank=int(env["RANK"]),
             local_rank=int(env.get("LOCAL_RANK", env["RANK"])),
