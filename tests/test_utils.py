@@ -117,3 +117,30 @@ def test_linear_cross_entropy_chunks_match_the_materialised_head():
         (ref * 2.0).backward()
         assert torch.allclose(loss, ref, atol=1e-5), (chunk, float(loss), float(ref))
         assert torch.allclose(gh, hidden.grad, atol=1e-5) and torch.allclose(gw, weight.grad, atol=1e-5), chunk
+
+
+def test_documentation_names_exist():
+    """Every ``oslo_b200...`` dotted name and every repository path quoted in the docs resolves (documentation that
+    drifts from the code fails here)."""
+    import importlib
+    import os
+    import re
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    docs = []
+    for base, _, files in os.walk(os.path.join(root, "docs")):
+        docs += [os.path.join(base, f) for f in files if f.endswith(".md")]
+    assert len(docs) >= 10
+    text = "\n".join(open(d, encoding="utf-8").read() for d in docs)
+    for stmt in set(re.findall(r"^from (oslo_b200[\w.]*) import ([\w, ]+)$", text, flags=re.M)):
+        mod = importlib.import_module(stmt[0])
+        for name in stmt[1].split(","):
+            name = name.strip().split(" as ")[0]
+            if not hasattr(mod, name):
+                importlib.import_module(f"{stmt[0]}.{name}")  # a submodule: ``from package import module``
+    for path in set(re.findall(r"`((?:oslo_b200|examples|benchmarks|tests|profiles)/[\w/.{},*-]+\.(?:py|cu|cuh|cpp|md))`", text)):
+        if any(c in path for c in "{*"):
+            continue
+        assert os.path.exists(os.path.join(root, path)), path
+    for link in set(re.findall(r"\]\(([\w/._-]+\.md)\)", text)):
+        assert any(os.path.exists(os.path.join(os.path.dirname(d), link)) for d in docs), link
