@@ -119,10 +119,12 @@ def gather_sequence_1d(x, dim, parallel_context):
 
 # ----------------------------------------------------------- sequence-parallel linears
 #: Largest tensor-parallel size at which the row-parallel side (GEMM -> reduce-scatter) uses the fused kernel.  Measured
-#: back to back on 8 x B200 (tokens 16384, hidden 2048): the fused reduce-scatter kernels take 0.26 - 0.34 ms per layer
-#: product against 0.20 - 0.28 ms for the tcgen05 GEMM followed by NCCL's in-switch reduce-scatter, while at 2 ranks the
-#: fused kernel is ahead (0.32 vs 0.41 ms); the all-gather side is ahead at every size and is always fused.
-FUSED_RS_MAX_RANKS = int(__import__("os").environ.get("OSLO_B200_FUSED_RS_MAX_RANKS", "4"))
+#: back to back as isolated calls on 8 x B200 (tokens 16384, hidden 2048): the fused reduce-scatter kernels take 0.26 - 0.34 ms
+#: per layer product against 0.20 - 0.28 ms for the tcgen05 GEMM followed by NCCL's in-switch reduce-scatter, while at 2 ranks
+#: the fused kernel is ahead (0.32 vs 0.41 ms).  The whole 1.3B step, however, has only been measured with both sides fused
+#: (47.3 ms at 8 ranks), so that stays the default; OSLO_B200_FUSED_RS_MAX_RANKS=4 moves the row-parallel side to GEMM + NCCL
+#: reduce-scatter above four ranks.  The all-gather side is ahead at every size and is always fused.
+FUSED_RS_MAX_RANKS = int(__import__("os").environ.get("OSLO_B200_FUSED_RS_MAX_RANKS", "8"))
 
 
 def _use_fused(x, weight, kind) -> bool:

@@ -229,6 +229,8 @@ def test_fused_reduce_scatter_policy_by_group_size(monkeypatch):
         is_cuda = True
 
     x = torch.zeros(4, 4).as_subclass(_FakeCuda)
+    assert _ops_1d.FUSED_RS_MAX_RANKS == 8  # default: fused at every size of one node (the configuration measured end to end)
+    monkeypatch.setattr(_ops_1d, "FUSED_RS_MAX_RANKS", 4)
     for tp, want_rs in ((2, True), (4, True), (8, False)):
         monkeypatch.setattr(fc, "_runtime", _RT(tp))
         assert _ops_1d._use_fused(x, x, "rs") is want_rs, tp
