@@ -61,6 +61,10 @@ def get_args(description: str, training: bool = True):
         ap.add_argument("--zero_stage", type=int, default=0, choices=[0, 1, 2])
         ap.add_argument("--text-file", default=None, help="train on this text (byte-level) instead of synthetic tokens")
         ap.add_argument("--merge", action="store_true", help="also write the merged single-file checkpoint")
+        ap.add_argument("--check_parity", action="store_true",
+                        help="train an unsharded twin on the same global batches (every rank, fp32 recommended) and fail if the "
+                             "losses drift apart by more than --parity_tol")
+        ap.add_argument("--parity_tol", type=float, default=2e-3)
     return ap
 
 

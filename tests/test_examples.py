@@ -27,7 +27,9 @@ def test_train_merge_and_infer_examples(tmp_path):
     ckpt = str(tmp_path / "ckpt")
     common = ["--model", "gpt-neox-tiny", "--cpu", "--sequence_length", "16", "--save_dir", ckpt]
     out = _run("train.py", *common, "--tensor_parallel_size", "2", "--data_parallel_size", "2", "--train_step", "30", "--lr", "3e-3",
-               "--merge", nproc=4, port=29713)
+               "--merge", "--check_parity", nproc=4, port=29713)
+    parity = [line for line in out.splitlines() if line.startswith("parity:")]
+    assert parity and float(parity[0].split("=")[1].split()[0]) < 2e-3, parity  # sharded run tracks the unsharded twin
     losses = [float(line.split()[-1]) for line in out.splitlines() if line.startswith("step")]
     assert len(losses) >= 3 and losses[-1] < losses[0] - 0.3, losses
     assert os.path.exists(os.path.join(ckpt, "pytorch_model_tp_0_pp_0_ep_0.bin")) and os.path.exists(os.path.join(ckpt, "pytorch_model_tp_1_pp_0_ep_0.bin"))
