@@ -191,8 +191,8 @@ class TensorParallel(ParallelWrapper):
         module = self.module
         div = self.get_divisible_by(self.parallel_context)
         emb = module.get_input_embeddings() if hasattr(module, "get_input_embeddings") else None
-        if emb is None:
-            return None, None
+        if emb is None or not isinstance(getattr(emb, "weight", None), torch.Tensor) or emb.weight.dim() != 2:
+            return None, None  # no token table (e.g. a vision model's patch projection): nothing to pad
         head = module.get_output_embeddings() if hasattr(module, "get_output_embeddings") else None
         tied = head is not None and head.weight is emb.weight
         orig = emb.weight.shape[0]

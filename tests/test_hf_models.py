@@ -63,7 +63,52 @@ def _build(kind):
 
         return OPTForCausalLM(OPTConfig(vocab_size=100, hidden_size=32, ffn_dim=64, num_hidden_layers=2, num_attention_heads=4,
                                         max_position_embeddings=32, word_embed_proj_dim=32, dropout=0.0)).eval()
+    if kind == "gptj":
+        from transformers import GPTJConfig, GPTJForCausalLM
+
+        return GPTJForCausalLM(GPTJConfig(vocab_size=100, n_positions=32, n_embd=32, n_layer=2, n_head=4, rotary_dim=4, resid_pdrop=0.0,
+                                          embd_pdrop=0.0, attn_pdrop=0.0)).eval()
+    if kind == "gpt_neo":
+        from transformers import GPTNeoConfig, GPTNeoForCausalLM
+
+        return GPTNeoForCausalLM(GPTNeoConfig(vocab_size=100, max_position_embeddings=32, hidden_size=32, num_layers=2, num_heads=4,
+                                              attention_types=[[["global", "local"], 1]], window_size=8, resid_dropout=0.0,
+                                              embed_dropout=0.0, attention_dropout=0.0)).eval()
+    if kind == "t5":
+        from transformers import T5Config, T5ForConditionalGeneration
+
+        return T5ForConditionalGeneration(T5Config(vocab_size=100, d_model=32, d_kv=8, d_ff=64, num_layers=2, num_decoder_layers=2,
+                                                   num_heads=4, dropout_rate=0.0, decoder_start_token_id=0)).eval()
+    if kind == "bart":
+        from transformers import BartConfig, BartForConditionalGeneration
+
+        return BartForConditionalGeneration(BartConfig(vocab_size=100, d_model=32, encoder_layers=2, decoder_layers=2,
+                                                       encoder_attention_heads=4, decoder_attention_heads=4, encoder_ffn_dim=64,
+                                                       decoder_ffn_dim=64, max_position_embeddings=32, dropout=0.0,
+                                                       attention_dropout=0.0, activation_dropout=0.0)).eval()
+    if kind == "blenderbot":
+        from transformers import BlenderbotConfig, BlenderbotForConditionalGeneration
+
+        return BlenderbotForConditionalGeneration(BlenderbotConfig(
+            vocab_size=100, d_model=32, encoder_layers=2, decoder_layers=2, encoder_attention_heads=4, decoder_attention_heads=4,
+            encoder_ffn_dim=64, decoder_ffn_dim=64, max_position_embeddings=32, dropout=0.0, attention_dropout=0.0,
+            activation_dropout=0.0)).eval()
+    if kind == "vit":
+        from transformers import ViTConfig, ViTForImageClassification
+
+        return ViTForImageClassification(ViTConfig(hidden_size=32, num_hidden_layers=2, num_attention_heads=4, intermediate_size=64,
+                                                   image_size=16, patch_size=8, num_labels=6, hidden_dropout_prob=0.0,
+                                                   attention_probs_dropout_prob=0.0)).eval()
     raise KeyError(kind)
+
+
+def _inputs(kind):
+    ids = torch.randint(0, 100, (2, 12), generator=torch.Generator().manual_seed(1))
+    if kind == "vit":
+        return {"pixel_values": torch.randn(2, 3, 16, 16, generator=torch.Generator().manual_seed(1))}
+    if kind in ("t5", "bart", "blenderbot"):
+        return {"input_ids": ids, "decoder_input_ids": ids[:, :7].contiguous()}
+    return {"input_ids": ids}
 
 
 def _worker(rank, world, kind, tmp):
@@ -77,10 +122,10 @@ def _worker(rank, world, kind, tmp):
     state = {k: v.clone() for k, v in ref.state_dict().items()}
     wrapped = TensorParallel(model, pc)
     oslo_b200.ready(wrapped, pc)
-    ids = torch.randint(0, 100, (2, 12), generator=torch.Generator().manual_seed(1))
+    feed = _inputs(kind)
     with torch.no_grad():
-        want = ref(input_ids=ids).logits
-        got = wrapped(input_ids=ids).logits
+        want = ref(**feed).logits
+        got = wrapped(**feed).logits
     assert got.shape == want.shape, (got.shape, want.shape)
     assert torch.allclose(got, want, rtol=1e-4, atol=1e-5), (got - want).abs().max()
     sharded = [n for n, p in model.named_parameters() if hasattr(p, "oslo_shard")]
@@ -94,7 +139,8 @@ def _worker(rank, world, kind, tmp):
     pc.destroy()
 
 
-@pytest.mark.parametrize("kind", ["gpt2", "bert", "gpt_neox", "roberta", "distilbert", "electra", "albert", "llama", "opt"])
+@pytest.mark.parametrize("kind", ["gpt2", "bert", "gpt_neox", "roberta", "distilbert", "electra", "albert", "llama", "opt", "gptj",
+                                  "gpt_neo", "t5", "bart", "blenderbot", "vit"])
 def test_hf_model_tensor_parallel_1d(kind):
     with tempfile.TemporaryDirectory() as tmp:
         run_dist(_worker, 2, kind, tmp, timeout=600)
