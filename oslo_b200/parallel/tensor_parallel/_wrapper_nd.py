@@ -116,7 +116,8 @@ class _Plan:
 
 def parallelize_nd(tp):
     """Shard ``tp.module`` for the context's N-D mode (called by ``TensorParallel.parallelize``)."""
-    from .tensor_parallel import _NORM_NAMES, _RMS_NAMES, _bare, _is_conv1d, _is_linear_like, _set_child, onn_marker
+    from .tensor_parallel import (_NORM_NAMES, _RMS_NAMES, _bare, _embedding_aliases, _is_conv1d, _is_linear_like,
+                                  _keep_custom_embedding, _set_child, onn_marker)
 
     pc = tp.parallel_context
     module = tp.module
@@ -136,6 +137,10 @@ def parallelize_nd(tp):
     else:
         dims["cubic_dim"] = pc.cubic_dim
         feature_div = pc.cubic_dim
+
+    cfg = getattr(module, "config", None)
+    hidden_size = next((getattr(cfg, k) for k in ("hidden_size", "d_model", "n_embd", "dim") if isinstance(getattr(cfg, k, None), int)), None)
+    feature_div_sq = feature_div * feature_div
 
     for attr in mapping.update_attrs(module):
         for m in module.modules():
@@ -185,7 +190,11 @@ def parallelize_nd(tp):
                 new.vocab_per_input = per
                 new.vocab_start_index, new.vocab_end_index = r * per, (r + 1) * per
             new.weight = w
+            new = _keep_custom_embedding(child, cls, new)
+            aliases = _embedding_aliases(module, child)
             _set_child(module, name, new)
+            for alias in aliases:
+                _set_child(module, alias, new)  # encoder / decoder copies of the shared table
             continue
         if isinstance(child, nn.Embedding):
             if mapping.is_other(module, name):
@@ -195,7 +204,7 @@ def parallelize_nd(tp):
                             sparse=False, parallel_context=pc, **dims)
                 new.weight = w
                 sync(w, "other_embedding")
-                _set_child(module, name, new)
+                _set_child(module, name, _keep_custom_embedding(child, plan.other_embedding_cls(), new))
             continue
         cname = child.__class__.__name__
         if cname in _NORM_NAMES + _RMS_NAMES:
@@ -219,7 +228,13 @@ def parallelize_nd(tp):
         if not _is_linear_like(child):
             continue
         if not (mapping.is_column_parallel(module, name) or mapping.is_row_parallel(module, name)):
-            continue
+            # In the N-D layouts every activation between layers is sharded over features, so a linear the mapping does
+            # not name (e.g. the transform in front of a masked-LM head) still has to take a feature shard.  It becomes an
+            # N-D linear when it maps hidden -> hidden-like sizes that the grid divides; anything else is left alone.
+            conv = _is_conv1d(child)
+            o, i = (child.weight.shape[1], child.weight.shape[0]) if conv else child.weight.shape
+            if hidden_size is None or i != hidden_size or o % feature_div_sq or i % feature_div_sq:
+                continue
         conv = _is_conv1d(child)
         out_dim, in_dim = (1, 0) if conv else (0, 1)
         parts = mapping.get_combined_qkv_degree(child.weight) if mapping.is_combined_qkv_param(module, name) else 1
@@ -230,8 +245,9 @@ def parallelize_nd(tp):
             sync(b, "bias")
         if mode == M.TENSOR_2P5D:
             sync(w, "weight")
-        gather = mapping.is_gather_output(module, name) and not is_oslo_model
-        _set_child(module, name, make_linear(child, name, w, b, gather))
+        # between layers the N-D layouts keep activations sharded (the next norm / linear takes a shard), so the mapping's
+        # gather_output, which in 1-D returns a column-parallel output to replicated form, only applies to heads
+        _set_child(module, name, make_linear(child, name, w, b, False))
 
     if head is not None:
         name = next(n for n, m in module.named_modules() if m is head)
@@ -253,6 +269,48 @@ def parallelize_nd(tp):
         gather = (mapping.is_gather_output(module, name) and not is_oslo_model) or mode == M.TENSOR_3D
         new = make_linear(head, name, w, b, gather)
         new.orig_num_classes = head.orig_num_classes
+        _set_child(module, name, new)
+    if emb is None:
+        # No token table (vision models): the module that builds the first hidden state from pixels produces it whole, so
+        # its output is cut to this rank's feature shard before the first sharded layer sees it.
+        entry = next((m for n, m in module.named_modules() if n.split(".")[-1] == "embeddings"), None)
+        if entry is not None:
+            feature_mode = plan.row if mode in (M.TENSOR_2D, M.TENSOR_2P5D) else M.TENSOR_3D_OUTPUT
+
+            def to_feature_shard(mod, inputs, output):
+                if torch.is_tensor(output):
+                    return comm.scatter(output, dim=-1, parallel_context=pc, parallel_mode=feature_mode)
+                return output
+
+            tp._entry_hooks = getattr(tp, "_entry_hooks", []) + [entry.register_forward_hook(to_feature_shard)]
+
+    # task heads other than the vocabulary head (classifier, qa_outputs, seq_relationship, ...): they read the sharded hidden
+    # state like any other linear; their few output classes are padded to what the grid divides, gathered, and cropped
+    from ._sharding import pad_dim
+
+    div = tp.get_divisible_by(pc)
+    for name, child in list(module.named_modules()):
+        if name == "" or child is head or not _is_linear_like(child) or not mapping.is_head(module, name):
+            continue
+        if isinstance(child, (onn.Linear2D, onn.Linear2p5D, onn.Linear3D)):
+            continue
+        conv = _is_conv1d(child)
+        out_dim, in_dim = (1, 0) if conv else (0, 1)
+        if child.weight.shape[in_dim] % feature_div_sq:
+            continue
+        classes = child.weight.shape[out_dim]
+        full = list(child.weight.shape)
+        child.weight.data = pad_dim(child.weight.data, out_dim, div)
+        w = tp._shard_param(child.weight, ShardSpec(plan.linear_weight(out_dim, in_dim, 1)), full)
+        b = None
+        if getattr(child, "bias", None) is not None:
+            child.bias.data = pad_dim(child.bias.data, 0, div)
+            b = tp._shard_param(child.bias, ShardSpec(plan.linear_bias(1)), (classes,))
+            sync(b, "bias")
+        if mode == M.TENSOR_2P5D:
+            sync(w, "weight")
+        new = make_linear(child, name, w, b, True)
+        new.orig_num_classes = classes
         _set_child(module, name, new)
     if mode == M.TENSOR_2P5D:
         # every parameter is replicated along the depth dimension

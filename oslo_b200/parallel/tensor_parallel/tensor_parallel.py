@@ -44,11 +44,42 @@ def _is_conv1d(m) -> bool:
 
 
 def _set_child(root: nn.Module, dotted: str, new: nn.Module):
+    """Put ``new`` where ``dotted`` is, and everywhere else the same module object is registered (a table shared by an
+    encoder and a decoder is one object under several names; ``named_modules`` reports only the first)."""
     parent = root
     parts = dotted.split(".")
     for p in parts[:-1]:
         parent = getattr(parent, p)
+    old = getattr(parent, parts[-1], None)
     setattr(parent, parts[-1], new)
+    if isinstance(old, nn.Module):
+        for m in root.modules():
+            for key, sub in m._modules.items():
+                if sub is old:
+                    m._modules[key] = new
+
+
+def _embedding_aliases(root: nn.Module, emb: nn.Module):
+    """Names of the OTHER embedding modules that hold ``emb``'s weight parameter (libraries that give an encoder and a
+    decoder their own ``nn.Embedding`` tied to the shared table): they must become the same sharded module."""
+    w = getattr(emb, "weight", None)
+    return [n for n, m in root.named_modules() if m is not emb and isinstance(m, nn.Embedding) and getattr(m, "weight", None) is w]
+
+
+def _keep_custom_embedding(child: nn.Module, parallel_cls, new: nn.Module) -> nn.Module:
+    """Libraries subclass ``nn.Embedding`` to do something around the lookup (scale the result, turn a shape or a mask into
+    position ids, add an offset) and then call ``super().forward(ids)``.  Swapping such a module for a plain parallel
+    embedding would drop that behaviour, so the replacement's class becomes ``(original subclass, parallel class)``: the
+    original ``forward`` still runs and its ``super().forward`` now reaches the parallel lookup.  Plain attributes of the
+    original (scale factors, offsets) are carried over."""
+    cls = type(child)
+    if cls is nn.Embedding or not isinstance(child, nn.Embedding) or cls.forward is nn.Embedding.forward:
+        return new
+    new.__class__ = type(f"{parallel_cls.__name__}For{cls.__name__}", (cls, parallel_cls), {})
+    for key, value in child.__dict__.items():
+        if key not in new.__dict__ and not key.startswith("_"):
+            new.__dict__[key] = value
+    return new
 
 
 def _bare(cls, **attrs):
@@ -262,6 +293,9 @@ class TensorParallel(ParallelWrapper):
                             vocab_start_index=rank * (full[0] // tp), vocab_end_index=(rank + 1) * (full[0] // tp),
                             sequence_parallel_state=self.sp_state)
                 new.weight = w
+                new = _keep_custom_embedding(child, onn.VocabParallelEmbedding1D, new)
+                for alias in _embedding_aliases(module, child):
+                    _set_child(module, alias, new)  # other modules built around the same table (encoder / decoder copies)
                 _set_child(module, name, new)
                 continue
             if head is not None and child is head:
@@ -419,6 +453,9 @@ class TensorParallel(ParallelWrapper):
         module = self.module
         if pc.tensor_parallel_size == 1:
             return
+        for handle in getattr(self, "_entry_hooks", []):
+            handle.remove()
+        self._entry_hooks = []
         merged = {}
         for name, child in list(module.named_modules()):
             if name == "":

@@ -99,6 +99,13 @@ def _build(kind):
         return ViTForImageClassification(ViTConfig(hidden_size=32, num_hidden_layers=2, num_attention_heads=4, intermediate_size=64,
                                                    image_size=16, patch_size=8, num_labels=6, hidden_dropout_prob=0.0,
                                                    attention_probs_dropout_prob=0.0)).eval()
+    if kind in ("bert_cls", "bert_qa"):
+        from transformers import BertConfig, BertForQuestionAnswering, BertForSequenceClassification
+
+        cfg = BertConfig(vocab_size=100, hidden_size=32, num_hidden_layers=2, num_attention_heads=4, intermediate_size=64,
+                         max_position_embeddings=32, hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0,
+                         num_labels=3 if kind == "bert_cls" else 2)
+        return (BertForSequenceClassification if kind == "bert_cls" else BertForQuestionAnswering)(cfg).eval()
     raise KeyError(kind)
 
 
@@ -144,6 +151,43 @@ def _worker(rank, world, kind, tmp):
 def test_hf_model_tensor_parallel_1d(kind):
     with tempfile.TemporaryDirectory() as tmp:
         run_dist(_worker, 2, kind, tmp, timeout=600)
+
+
+def _nd_worker(rank, world, kind, mode, depth):
+    """Stock Hugging Face models under the 2-D / 2.5-D / 3-D layouts: same outputs as the unsharded model.  Exercises what
+    the 1-D layout never needs: tables shared by an encoder and a decoder under several names, embedding subclasses with
+    their own forward (scaled words, learned positions), linears the mapping does not name, task heads with a handful of
+    classes, and models whose first hidden state does not come from a token table."""
+    import oslo_b200
+    from oslo_b200 import ParallelContext, ParallelMode
+    from oslo_b200.parallel import TensorParallel
+
+    layout = {"2d": ParallelMode.TENSOR_2D, "2.5d": ParallelMode.TENSOR_2P5D, "3d": ParallelMode.TENSOR_3D}[mode]
+    pc = ParallelContext.from_torch(tensor_parallel_size=world, tensor_parallel_mode=layout, tensor_parallel_depth=depth,
+                                    backend="gloo", seed=0)
+    ref = _build(kind)
+    model = _build(kind)
+    wrapped = TensorParallel(model, pc)
+    oslo_b200.ready(wrapped, pc)
+    feed = {k: torch.cat([v, v]) for k, v in _inputs("bert" if kind.startswith("bert_") else kind).items()}  # batch 4
+    with torch.no_grad():
+        a, b = ref(**feed), wrapped(**feed)
+    for key in ("logits", "start_logits", "end_logits"):
+        if hasattr(a, key) and getattr(a, key) is not None:
+            want, got = getattr(a, key), getattr(b, key)
+            assert got.shape == want.shape, (key, got.shape, want.shape)
+            assert torch.allclose(got, want, rtol=1e-4, atol=1e-5), (key, (got - want).abs().max())
+    pc.destroy()
+
+
+ND_CASES = [(k, "2d", 4, None) for k in ("gpt2", "bert", "roberta", "albert", "t5", "bart", "opt", "blenderbot", "vit", "bert_cls",
+                                          "bert_qa")]
+ND_CASES += [("bart", "2.5d", 8, 2), ("t5", "3d", 8, None), ("vit", "3d", 8, None), ("bert_cls", "3d", 8, None)]
+
+
+@pytest.mark.parametrize("kind,mode,world,depth", ND_CASES, ids=[f"{c[0]}-{c[1]}" for c in ND_CASES])
+def test_hf_model_tensor_parallel_nd(kind, mode, world, depth):
+    run_dist(_nd_worker, world, kind, mode, depth, timeout=600)
 
 
 def _pp_worker(rank, world, kind):
