@@ -197,6 +197,16 @@ class ExpertParallelFrontBlock(nn.Module):
             w = next(residual.parameters())
             self.residual_mix = nn.Linear(gate.wg.weight.shape[1], 2, dtype=w.dtype, device=w.device)
 
+    # Libraries peek at ``module.weight`` / ``module.bias`` of the linear this block replaced (dtype checks before a cast):
+    # answer with the experts' tensors.
+    @property
+    def weight(self):
+        return self.experts.weight
+
+    @property
+    def bias(self):
+        return self.experts.bias
+
     def forward(self, x):
         link = self.link
         link.in_shape = x.shape
@@ -237,6 +247,16 @@ class ExpertParallelBehindBlock(nn.Module):
         self.ep_size, self.num_local_experts = ep_size, num_local_experts
         self.skip_bias_add = skip_bias_add
         self.residual = residual  # dense copy of the replaced linear (Residual-MoE)
+
+    # Libraries peek at ``module.weight`` / ``module.bias`` of the linear this block replaced (dtype checks before a cast):
+    # answer with the experts' tensors.
+    @property
+    def weight(self):
+        return self.experts.weight
+
+    @property
+    def bias(self):
+        return self.experts.bias
 
     def forward(self, x):  # x: [E_local, ep * C, ffn]  (+ the dense rows behind it under Residual-MoE)
         link = self.link

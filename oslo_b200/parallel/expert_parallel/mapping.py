@@ -44,7 +44,25 @@ class ExpertParallelMapping:
                Behind("DenseReluDense.wo", layer="block", enc_name="encoder", dec_name="decoder")],
         "Bart": [Front("fc1", layer="layers", enc_name="encoder", dec_name="decoder"),
                  Behind("fc2", layer="layers", enc_name="encoder", dec_name="decoder")],
+        "Blenderbot": [Front("fc1", layer="layers", enc_name="encoder", dec_name="decoder"),
+                       Behind("fc2", layer="layers", enc_name="encoder", dec_name="decoder")],
+        "Electra": [Front("intermediate.dense", layer="electra.encoder.layer", enc_name="encoder"),
+                    Behind("output.dense", layer="electra.encoder.layer", enc_name="encoder")],
+        "DistilBert": [Front("ffn.lin1", layer="distilbert.transformer.layer", enc_name="transformer"),
+                       Behind("ffn.lin2", layer="distilbert.transformer.layer", enc_name="transformer")],
+        "GPTNeo": [Front("mlp.c_fc", layer="transformer.h", dec_name="transformer"),
+                   Behind("mlp.c_proj", layer="transformer.h", dec_name="transformer")],
+        "GPTJ": [Front("mlp.fc_in", layer="transformer.h", dec_name="transformer"),
+                 Behind("mlp.fc_out", layer="transformer.h", dec_name="transformer")],
+        "OPT": [Front("fc1", layer="model.decoder.layers", dec_name="decoder"),
+                Behind("fc2", layer="model.decoder.layers", dec_name="decoder")],
+        "ViT": [Front("intermediate.dense", layer="vit.encoder.layer", enc_name="encoder"),
+                Behind("output.dense", layer="vit.encoder.layer", enc_name="encoder")],
     }
+    # families that share a table
+    __MAPPING__["BlenderbotSmall"] = __MAPPING__["Blenderbot"]
+    __MAPPING__["MBart"] = __MAPPING__["Bart"]
+    __MAPPING__["MT5"] = __MAPPING__["T5"]
 
     def __init__(self, mapping: Optional[dict] = None):
         self._table = dict(self.__MAPPING__)
@@ -69,14 +87,12 @@ class ExpertParallelMapping:
             for n in info.name:
                 if module_name.endswith("." + n) or module_name == n:
                     prefix = module_name[: -len(n)].rstrip(".")
-                    idx = None
                     parts = prefix.split(".")
-                    for i in range(len(parts) - 1, -1, -1):
-                        if parts[i].isdigit():
-                            idx = int(parts[i])
-                            break
-                    if idx is None:
+                    # the name must be everything after the layer index: ``layer.3.output.dense`` is the feed-forward
+                    # output, ``layer.3.attention.output.dense`` (same suffix) is not
+                    if not parts or not parts[-1].isdigit():
                         continue
+                    idx = int(parts[-1])
                     stack = "dec"
                     if info.enc_name and info.enc_name in module_name.split("."):
                         stack = "enc"

@@ -286,3 +286,44 @@ def test_kernel_fusion_surgery_keeps_hf_outputs(kind):
         want = ref(input_ids=ids).logits
         got = model(input_ids=ids).logits
     assert torch.allclose(got, want, rtol=1e-4, atol=1e-5), (got - want).abs().max()
+
+
+def _ep_worker(rank, world, kind):
+    """Stock Hugging Face models under expert parallelism: the mapped feed-forward linears (and only those: an attention
+    output projection with the same name suffix stays dense) become router + experts, the experts are spread over the
+    group, forward / backward run and every expert parameter receives a gradient."""
+    import oslo_b200
+    from oslo_b200 import ParallelContext
+    from oslo_b200.parallel import ExpertParallel
+    from oslo_b200.parallel.expert_parallel.layers import ExpertParallelBehindBlock, ExpertParallelFrontBlock
+
+    pc = ParallelContext.from_torch(expert_parallel_size=world, backend="gloo", seed=0)
+    model = _build(kind).train()
+    encoder_only = kind in ("bert", "roberta", "albert", "electra", "distilbert", "vit")
+    both = kind in ("t5", "bart", "blenderbot")
+    kw = dict(top_k=2, capacity_factor_train=4.0, aux_loss_coef=0.01)
+    if encoder_only or both:
+        kw["num_enc_experts"] = 4
+    if not encoder_only:
+        kw["num_dec_experts"] = 4
+    wrapped = ExpertParallel(model, pc, **kw)
+    oslo_b200.ready(wrapped, pc)
+    fronts = [n for n, m in model.named_modules() if isinstance(m, ExpertParallelFrontBlock)]
+    behinds = [n for n, m in model.named_modules() if isinstance(m, ExpertParallelBehindBlock)]
+    assert len(fronts) == len(behinds) >= 2 and not any("attention" in n or "attn" in n.split(".")[-2] for n in behinds), (fronts, behinds)
+    feed = _inputs(kind)
+    if kind == "vit":
+        feed["labels"] = torch.tensor([1, 2])
+    else:
+        feed["labels"] = feed.pop("decoder_input_ids", feed["input_ids"]).clone() if both else feed["input_ids"].clone()
+    out = wrapped(**feed)
+    assert torch.isfinite(out.loss)
+    out.loss.backward()
+    experts = [(n, p) for n, p in model.named_parameters() if getattr(p, "oslo_expert_param", False)]
+    assert experts and all(p.shape[0] == 4 // world and p.grad is not None and torch.isfinite(p.grad).all() for _, p in experts)
+    pc.destroy()
+
+
+@pytest.mark.parametrize("kind", ["bert", "t5", "bart", "gptj", "vit", "distilbert"])
+def test_hf_model_expert_parallel(kind):
+    run_dist(_ep_worker, 2, kind, timeout=600)
