@@ -276,6 +276,77 @@ class BartForConditionalGeneration(BartPreTrainedModel):
             loss, logits = res.value, (None if res.consumed_logits else logits)
         return ModelOutput(loss=loss, logits=logits, encoder_last_hidden_state=out.encoder_last_hidden_state)
 
+    def pipeline_units(self):
+        """Encoder embedding, one unit per encoder layer, the hand-over (encoder output norm + decoder embedding), one unit
+        per decoder layer, head + loss.  One activation crosses a stage boundary, so from the hand-over on it is the encoder
+        output and the decoder state concatenated along the sequence (``[b, s_enc + s_dec, d]``): every decoder unit splits it,
+        runs its layer with the encoder part as memory and joins it again, and the gradient of both parts flows back through
+        the same tensor."""
+        from oslo_b200.parallel.pipeline_parallel.partitioner import PipeUnit
+
+        enc, dec = self.model.encoder, self.model.decoder
+
+        def dec_ids(state):
+            ids = state.get("decoder_input_ids")
+            return ids if ids is not None else self._shift(state["labels"] if state.get("labels") is not None else state["input_ids"])
+
+        def enc_embed(state):
+            ids = state["input_ids"]
+            x = enc.embed_tokens(ids) * enc.embed_scale + enc.embed_positions(ids.shape[1], ids.device)
+            state["hidden"] = enc.dropout(enc.layernorm_embedding(x))
+            return state
+
+        def make_enc(layer):
+            def run(state):
+                state["hidden"] = layer(state["hidden"], additive_mask(state.get("attention_mask"), torch.float32))
+                return state
+
+            return run
+
+        def hand_over(state):
+            memory = enc.layer_norm(state["hidden"]) if enc.final_norm else state["hidden"]
+            ids = dec_ids(state)
+            y = dec.embed_tokens(ids) * dec.embed_scale + dec.embed_positions(ids.shape[1], ids.device)
+            y = dec.dropout(dec.layernorm_embedding(y))
+            state["hidden"] = torch.cat([memory, y], dim=1)
+            return state
+
+        def make_dec(layer):
+            def run(state):
+                s_enc = state["input_ids"].shape[1]
+                memory, y = state["hidden"][:, :s_enc], state["hidden"][:, s_enc:]
+                dmask = state.get("decoder_attention_mask")
+                self_mask = causal_additive_mask(dmask, y.shape[1]) if dmask is not None else None
+                y = layer(y, self_mask, memory, additive_mask(state.get("attention_mask"), torch.float32))
+                state["hidden"] = torch.cat([memory, y], dim=1)
+                return state
+
+            return run
+
+        def head(state):
+            y = state["hidden"][:, state["input_ids"].shape[1]:]
+            if dec.final_norm:
+                y = dec.layer_norm(y)
+            logits = self.lm_head(y)
+            if self.final_logits_bias.shape[-1] == logits.shape[-1] and bool(self.final_logits_bias.any()):
+                logits = logits + self.final_logits_bias.to(logits.dtype)
+            state["logits"] = logits
+            if state.get("labels") is not None:
+                res = token_lm_loss(self, logits, state["labels"])
+                state["loss"] = res.value
+                if res.consumed_logits:
+                    state["logits"] = None
+            return state
+
+        shared = self.model.shared
+        units = [PipeUnit("encoder.embed", [shared, enc.embed_positions, enc.layernorm_embedding], enc_embed)]
+        units += [PipeUnit(f"encoder.layers.{i}", [l], make_enc(l)) for i, l in enumerate(enc.layers)]
+        units.append(PipeUnit("decoder.embed", ([enc.layer_norm] if enc.final_norm else [])
+                              + [shared, dec.embed_positions, dec.layernorm_embedding], hand_over))
+        units += [PipeUnit(f"decoder.layers.{i}", [l], make_dec(l)) for i, l in enumerate(dec.layers)]
+        units.append(PipeUnit("head", ([dec.layer_norm] if dec.final_norm else []) + [self.lm_head], head))
+        return units
+
     @torch.no_grad()
     def generate(self, input_ids, attention_mask=None, max_new_tokens: int = 32, num_beams: int = 1, length_penalty: float = 1.0,
                  use_cache: bool = True):

@@ -285,6 +285,81 @@ class T5ForConditionalGeneration(T5Model):
             loss, logits = res.value, (None if res.consumed_logits else logits)
         return ModelOutput(loss=loss, logits=logits, encoder_last_hidden_state=out.encoder_last_hidden_state)
 
+    def pipeline_units(self):
+        """Same plan as BART's: encoder embedding, encoder blocks, hand-over (encoder final norm + decoder embedding with the
+        two activations joined along the sequence), decoder blocks, head + loss.  The relative-position bias table lives in
+        the first block of each stack and is used by all of them: it is listed in every block unit, so each stage that owns
+        a block keeps a copy and the copies' gradients are summed after the backward pass."""
+        from oslo_b200.parallel.pipeline_parallel.partitioner import PipeUnit
+
+        enc, dec = self.encoder, self.decoder
+        enc_rel = enc.block[0].layer[0].SelfAttention
+        dec_rel = dec.block[0].layer[0].SelfAttention
+
+        def dec_ids(state):
+            ids = state.get("decoder_input_ids")
+            return ids if ids is not None else self._shift_right(state["labels"])
+
+        def enc_embed(state):
+            state["hidden"] = enc.dropout(enc.embed_tokens(state["input_ids"]))
+            return state
+
+        def enc_bias(state):
+            s = state["input_ids"].shape[1]
+            bias = enc_rel.compute_bias(s, s, state["input_ids"].device).float()
+            if state.get("attention_mask") is not None:
+                bias = bias + additive_mask(state["attention_mask"], torch.float32)
+            return bias
+
+        def make_enc(blk):
+            def run(state):
+                state["hidden"] = blk(state["hidden"], enc_bias(state))
+                return state
+
+            return run
+
+        def hand_over(state):
+            memory = enc.dropout(enc.final_layer_norm(state["hidden"]))
+            y = dec.dropout(dec.embed_tokens(dec_ids(state)))
+            state["hidden"] = torch.cat([memory, y], dim=1)
+            return state
+
+        def make_dec(blk):
+            def run(state):
+                s_enc = state["input_ids"].shape[1]
+                memory, y = state["hidden"][:, :s_enc], state["hidden"][:, s_enc:]
+                t = y.shape[1]
+                bias = dec_rel.compute_bias(t, t, y.device).float()
+                bias = bias + torch.full((t, t), torch.finfo(torch.float32).min, device=y.device).triu(1)
+                if state.get("decoder_attention_mask") is not None:
+                    bias = bias + additive_mask(state["decoder_attention_mask"], torch.float32)
+                y = blk(y, bias, memory, additive_mask(state.get("attention_mask"), torch.float32))
+                state["hidden"] = torch.cat([memory, y], dim=1)
+                return state
+
+            return run
+
+        def head(state):
+            y = dec.dropout(dec.final_layer_norm(state["hidden"][:, state["input_ids"].shape[1]:]))
+            if getattr(self.config, "tie_word_embeddings", True):
+                y = y * (self.config.d_model ** -0.5)
+            logits = self.lm_head(y)
+            state["logits"] = logits
+            if state.get("labels") is not None:
+                res = token_lm_loss(self, logits, state["labels"])
+                state["loss"] = res.value
+                if res.consumed_logits:
+                    state["logits"] = None
+            return state
+
+        enc_table, dec_table = enc_rel.relative_attention_bias, dec_rel.relative_attention_bias
+        units = [PipeUnit("encoder.embed", [self.shared], enc_embed)]
+        units += [PipeUnit(f"encoder.block.{i}", [b, enc_table], make_enc(b)) for i, b in enumerate(enc.block)]
+        units.append(PipeUnit("decoder.embed", [enc.final_layer_norm, self.shared], hand_over))
+        units += [PipeUnit(f"decoder.block.{i}", [b, dec_table], make_dec(b)) for i, b in enumerate(dec.block)]
+        units.append(PipeUnit("head", [dec.final_layer_norm, self.lm_head], head))
+        return units
+
     @torch.no_grad()
     def generate(self, input_ids, attention_mask=None, max_new_tokens: int = 32, num_beams: int = 1, length_penalty: float = 1.0,
                  use_cache: bool = True):

@@ -107,3 +107,60 @@ def _pp_tp2d_worker(rank, world):
 
 def test_pipeline_with_2d_tensor_parallel():
     run_dist(_pp_tp2d_worker, 8, timeout=900)
+
+
+def _seq2seq(kind):
+    from oslo_b200 import models
+
+    torch.manual_seed(0)
+    if kind == "t5":
+        return models.T5ForConditionalGeneration(models.T5Config(vocab_size=96, d_model=32, d_kv=8, d_ff=64, num_layers=3,
+                                                                 num_decoder_layers=3, num_heads=4, dropout_rate=0.0))
+    return models.BartForConditionalGeneration(models.BartConfig(
+        vocab_size=96, d_model=32, encoder_layers=3, decoder_layers=3, encoder_attention_heads=4, decoder_attention_heads=4,
+        encoder_ffn_dim=64, decoder_ffn_dim=64, max_position_embeddings=32, dropout=0.0, attention_dropout=0.0,
+        activation_dropout=0.0))
+
+
+def _seq2seq_worker(rank, world, kind):
+    """Encoder-decoder models through the pipeline: the encoder output and the decoder state travel as one activation, the
+    loss and every gradient (including parameters kept on several stages: the shared embedding, T5's relative-position
+    tables) equal those of the unsplit model."""
+    import oslo_b200
+    from oslo_b200 import ParallelContext
+    from oslo_b200.parallel import PipelineParallel
+
+    pc = ParallelContext.from_torch(pipeline_parallel_size=world, backend="gloo", seed=0)
+    ref, model = _seq2seq(kind), _seq2seq(kind)
+    wrapped = PipelineParallel(model, pc, num_micro_batches=2)
+    oslo_b200.ready(wrapped, pc)
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(3, 96, (4, 11), generator=g)
+    labels = torch.randint(3, 96, (4, 7), generator=g)
+    mask = torch.ones_like(ids)
+    mask[1, 8:] = 0
+    ref_loss = sum(ref(input_ids=i, attention_mask=m, labels=l).loss for i, m, l in zip(ids.chunk(2), mask.chunk(2), labels.chunk(2))) / 2
+    ref_loss.backward()
+    total = 0.0
+    for _, out in wrapped(input_ids=ids, attention_mask=mask, labels=labels):
+        out.loss.backward()
+        if wrapped.stage == world - 1:
+            total += out.loss.item()
+    if wrapped.stage == world - 1:
+        assert abs(total - ref_loss.item()) < 1e-4, (total, ref_loss.item())
+    ref_grads = {n: p.grad for n, p in ref.named_parameters()}
+    checked = 0
+    for n, p in model.named_parameters():
+        if getattr(p, "oslo_pipeline_released", False) or p.grad is None:
+            continue
+        assert torch.allclose(p.grad, ref_grads[n], rtol=1e-3, atol=1e-5), (kind, n, (p.grad - ref_grads[n]).abs().max().item())
+        checked += 1
+    assert checked > 5
+    released = [n for n, p in model.named_parameters() if getattr(p, "oslo_pipeline_released", False)]
+    assert released, "every stage still holds the whole model"
+    pc.destroy()
+
+
+@pytest.mark.parametrize("kind,world", [("bart", 2), ("t5", 2), ("t5", 4)])
+def test_pipeline_encoder_decoder_models(kind, world):
+    run_dist(_seq2seq_worker, world, kind)
