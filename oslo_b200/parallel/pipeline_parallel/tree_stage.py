@@ -63,8 +63,19 @@ class TreeStage:
         pos = names.index(self.block_name)
         order = {n: i for i, n in enumerate(names)}
         leaves = _leaf_modules_with_params(model, self.blocks)
-        self.head = [(n, m) for n, m in leaves if order[n] < pos]
-        self.tail = [(n, m) for n, m in leaves if order[n] > pos]
+        # Registration order decides, with one correction: some models register the norm that runs AFTER the blocks before
+        # the block list (OPT's ``final_layer_norm``).  A normalisation that is a sibling of the block list and is named as a
+        # closing norm belongs to the tail; embedding norms (``layernorm_embedding``, ``embeddings.LayerNorm``) do not match.
+        parent = self.block_name.rsplit(".", 1)[0] if "." in self.block_name else ""
+
+        def closing_norm(name: str, mod: nn.Module) -> bool:
+            leaf = name.rsplit(".", 1)[-1]
+            sibling = (name.rsplit(".", 1)[0] if "." in name else "") == parent
+            is_norm = "norm" in type(mod).__name__.lower()
+            return sibling and is_norm and ("final" in leaf or leaf in ("ln_f", "norm", "layer_norm")) and "embed" not in leaf
+
+        self.head = [(n, m) for n, m in leaves if order[n] < pos and not closing_norm(n, m)]
+        self.tail = [(n, m) for n, m in leaves if order[n] > pos or (order[n] < pos and closing_norm(n, m))]
         self._inject: Optional[torch.Tensor] = None
         self._captured: Optional[torch.Tensor] = None
         self._orig_forward: Dict[int, object] = {}

@@ -226,7 +226,7 @@ def _pp_worker(rank, world, kind):
     pc.destroy()
 
 
-@pytest.mark.parametrize("kind", ["gpt2", "gpt_neox"])
+@pytest.mark.parametrize("kind", ["gpt2", "gpt_neox", "bert", "llama", "opt"])  # opt registers its closing norm BEFORE the blocks
 def test_hf_model_pipeline_parallel_from_module_tree(kind):
     run_dist(_pp_worker, 2, kind, timeout=600)
 
