@@ -31,15 +31,20 @@ from .partitioner import PipeUnit
 
 
 def find_block_list(model: nn.Module) -> Tuple[str, nn.ModuleList]:
-    best, best_params = None, -1
+    lists = []
     for name, m in model.named_modules():
         if isinstance(m, nn.ModuleList) and len(m) >= 2 and len({type(c) for c in m}) == 1:
-            n = sum(p.numel() for p in m.parameters())
-            if n > best_params:
-                best, best_params = (name, m), n
-    if best is None:
+            lists.append((sum(p.numel() for p in m.parameters()), name, m))
+    if not lists:
         raise TypeError(f"{type(model).__name__}: no list of repeated blocks found; define pipeline_units() instead")
-    return best
+    lists.sort(key=lambda t: -t[0])
+    top = [(n, m) for _, n, m in lists if not any(n.startswith(o + ".") for _, o, _ in lists if o != n)]  # outermost lists only
+    if len(top) >= 2 and {"encoder", "decoder"} <= {part for n, _ in top for part in n.split(".")}:
+        raise TypeError(
+            f"{type(model).__name__} has an encoder stack and a decoder stack ({', '.join(n for n, _ in top[:2])}); one "
+            "activation crosses a stage boundary, which a model's own forward cannot express for two stacks.  The in-tree "
+            "oslo_b200.models BART / mBART / T5 / mT5 classes load the same checkpoints and define pipeline_units().")
+    return lists[0][1], lists[0][2]
 
 
 def _leaf_modules_with_params(model: nn.Module, exclude: nn.Module) -> List[Tuple[str, nn.Module]]:
