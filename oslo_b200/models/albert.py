@@ -33,7 +33,7 @@ class AlbertAttention(nn.Module):
 
     def forward(self, x, mask=None):
         b, s, _ = x.shape
-        q, k, v = (lin(x).view(b, s, -1, self.attention_head_size) for lin in (self.query, self.key, self.value))
+        q, k, v = (lin(x).unflatten(-1, (-1, self.attention_head_size)) for lin in (self.query, self.key, self.value))
         h, bias = self.dense(OF.attention(q, k, v, causal=False, mask=mask))
         return self.LayerNorm(OF.bias_dropout_add(h, bias, x, self.p, self.training))
 

@@ -65,9 +65,9 @@ class BartAttention(nn.Module):
     def forward(self, hidden_states, key_value_states=None, mask=None):
         b, t, _ = hidden_states.shape
         src = hidden_states if key_value_states is None else key_value_states
-        q = self.q_proj(hidden_states).view(b, t, -1, self.head_dim)
-        project = lambda: (self.k_proj(src).view(b, src.shape[1], -1, self.head_dim),  # noqa: E731
-                           self.v_proj(src).view(b, src.shape[1], -1, self.head_dim))
+        q = self.q_proj(hidden_states).unflatten(-1, (-1, self.head_dim))
+        project = lambda: (self.k_proj(src).unflatten(-1, (-1, self.head_dim)),  # noqa: E731
+                           self.v_proj(src).unflatten(-1, (-1, self.head_dim)))
         cross = key_value_states is not None
         cache = active_seq2seq_cache() if (cross or self.is_causal) else None  # decoder modules only
         causal = self.is_causal and not cross

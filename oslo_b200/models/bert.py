@@ -65,7 +65,7 @@ class BertSelfAttention(nn.Module):
     def forward(self, hidden_states, mask=None):
         b, s, _ = hidden_states.shape
         hd = self.attention_head_size
-        q, k, v = (lin(hidden_states).view(b, s, -1, hd) for lin in (self.query, self.key, self.value))
+        q, k, v = (lin(hidden_states).unflatten(-1, (-1, hd)) for lin in (self.query, self.key, self.value))
         return OF.attention(q, k, v, causal=False, mask=mask)
 
 

@@ -44,7 +44,7 @@ class MultiHeadSelfAttention(nn.Module):
 
     def forward(self, x, mask=None):
         b, s, _ = x.shape
-        q, k, v = (lin(x).view(b, s, -1, self.head_dim) for lin in (self.q_lin, self.k_lin, self.v_lin))
+        q, k, v = (lin(x).unflatten(-1, (-1, self.head_dim)) for lin in (self.q_lin, self.k_lin, self.v_lin))
         return self.out_lin(OF.attention(q, k, v, causal=False, mask=mask))
 
 

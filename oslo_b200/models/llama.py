@@ -39,10 +39,10 @@ class LlamaAttention(nn.Module):
         return self._rope[0][:seq], self._rope[1][:seq]
 
     def forward(self, x, attention_mask=None):
-        b, s = x.shape[0], x.shape[1]
         q = self.q_proj(x)
         k = self.k_proj(x)
         v = self.v_proj(x)
+        b, s = q.shape[0], q.shape[1]  # from the projection: under sequence parallelism it has gathered the token shards
         hq, hkv = q.shape[-1] // self.head_dim, k.shape[-1] // self.head_dim
         q, k, v = q.view(b, s, hq, self.head_dim), k.view(b, s, hkv, self.head_dim), v.view(b, s, hkv, self.head_dim)
         from oslo_b200.ops.attention import decode_offset

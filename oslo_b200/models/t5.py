@@ -110,8 +110,8 @@ class T5Attention(nn.Module):
         b, t, _ = x.shape
         src = x if key_value_states is None else key_value_states
         hd = self.key_value_proj_dim
-        q = self.q(x).view(b, t, -1, hd)
-        project = lambda: (self.k(src).view(b, src.shape[1], -1, hd), self.v(src).view(b, src.shape[1], -1, hd))  # noqa: E731
+        q = self.q(x).unflatten(-1, (-1, hd))
+        project = lambda: (self.k(src).unflatten(-1, (-1, hd)), self.v(src).unflatten(-1, (-1, hd)))  # noqa: E731
         cache = active_seq2seq_cache() if self.is_decoder else None
         if cache is None:
             k, v = project()

@@ -100,6 +100,7 @@ class SequenceParallelState:
 
     def configure(self, batch: int, seq: int):
         tp = self.pc.get_world_size(ParallelMode.TENSOR_1D)
+        self.full = (batch, seq)
         if batch % tp == 0:
             self.dim = 0
         elif batch == 1 and seq % tp == 0:
@@ -111,6 +112,16 @@ class SequenceParallelState:
 
     def shard(self, t):
         return comm.scatter(t, dim=self.dim, parallel_context=self.pc, parallel_mode=ParallelMode.TENSOR_1D)
+
+    def shard_if_full(self, t):
+        """Cut ``t`` to this rank's share when it still spans the whole batch / sequence along the sharded dimension (a
+        size-1 dimension that broadcasts against the shard is left alone)."""
+        full = getattr(self, "full", None)
+        if full is None or not torch.is_tensor(t) or t.dim() <= self.dim or t.shape[self.dim] != full[self.dim]:
+            return t
+        if self.pc.get_world_size(ParallelMode.TENSOR_1D) == 1:
+            return t
+        return self.shard(t)
 
 
 class TensorParallel(ParallelWrapper):
@@ -132,6 +143,15 @@ class TensorParallel(ParallelWrapper):
         mode = self.parallel_context.tensor_parallel_mode
         if sequence_parallel and mode != ParallelMode.TENSOR_1D:
             raise ValueError("sequence_parallel=True is only defined for 1D tensor parallelism")
+        if sequence_parallel and type(module).__module__.startswith("transformers.") \
+                and not type(module).__name__.startswith(("GPT2", "GPTJ")):
+            # Between blocks the activations are token shards and the column-parallel projections return the gathered
+            # sequence.  Most Hugging Face attention modules take (batch, seq) from their INPUT and reshape the projections
+            # with it, which silently folds tokens into heads; GPT-2 and GPT-J take the shape from the projections.
+            raise NotImplementedError(
+                f"sequence_parallel=True is not supported for transformers' {type(module).__name__}: its attention reshapes "
+                "the projections with the input's sequence length.  Use the in-tree model of the same family "
+                "(oslo_b200.models; it loads the same checkpoint) or sequence_parallel=False.")
         self.sp_state = SequenceParallelState(self.parallel_context) if sequence_parallel else None
         self._sp_params = []
         self._sp_callback_queued = False
@@ -312,6 +332,12 @@ class TensorParallel(ParallelWrapper):
                     _set_child(module, name, new)
                 elif isinstance(child, nn.Embedding) and mapping.is_other(module, name) and sp:
                     self._mark_sp(child)
+                    if not isinstance(module, onn_marker()) or getattr(module, "sequence_parallel_shards_other_embeddings", True):
+                        # position / token-type tables are looked up for the whole batch; what is added to the token-sharded
+                        # word embeddings must be this rank's share
+                        state = self.sp_state
+                        handle = child.register_forward_hook(lambda mod, inputs, out, state=state: state.shard_if_full(out))
+                        self._entry_hooks = getattr(self, "_entry_hooks", []) + [handle]  # removed by deparallelize()
                 elif child.__class__.__name__ in _NORM_NAMES + _RMS_NAMES:
                     if sp:
                         self._mark_sp(child)
@@ -320,6 +346,13 @@ class TensorParallel(ParallelWrapper):
             out_dim, in_dim = (1, 0) if conv else (0, 1)
             has_bias = getattr(child, "bias", None) is not None
             skip = getattr(child, "skip_bias_add", False)
+            if sp and mapping.is_column_parallel(module, name) and mapping.is_gather_output(module, name):
+                # A column-parallel linear whose output is gathered again computes, in the end, the whole product on every
+                # rank.  Under sequence parallelism its input is a token shard, so the same result per token comes from
+                # simply keeping the layer whole and applying it to the shard: the activation stays token-sharded for
+                # whatever follows (norm, head), and nothing is gathered twice.  Its gradients are partial sums over tokens.
+                self._mark_sp(child)
+                continue
             if mapping.is_column_parallel(module, name):
                 parts = mapping.get_combined_qkv_degree(child.weight) if mapping.is_combined_qkv_param(module, name) else 1
                 w = self._shard_param(child.weight, ShardSpec([Split(M1, out_dim, parts)]))
