@@ -537,8 +537,17 @@ def _restore_plain(child: nn.Module, params: dict) -> nn.Module:
     w = params.get("weight")
     b = params.get("bias")
     if isinstance(child, nn.Embedding):
-        new = _bare(nn.Embedding, num_embeddings=w.shape[0], embedding_dim=w.shape[1], padding_idx=None, max_norm=None,
-                    norm_type=2.0, scale_grad_by_freq=False, sparse=False)
+        # an embedding subclass with its own forward (see _keep_custom_embedding) gets that class back
+        custom = next((c for c in type(child).__mro__[1:] if issubclass(c, nn.Embedding) and c is not nn.Embedding
+                       and not c.__module__.startswith("oslo_b200.nn")), nn.Embedding)
+        new = _bare(custom, num_embeddings=w.shape[0], embedding_dim=w.shape[1], padding_idx=getattr(child, "padding_idx", None),
+                    max_norm=None, norm_type=2.0, scale_grad_by_freq=False, sparse=False)
+        if custom is not nn.Embedding:
+            for key, value in child.__dict__.items():
+                if key not in new.__dict__ and not key.startswith("_") and key not in (
+                        "parallel_context", "vocab_start_index", "vocab_end_index", "world_size", "sequence_parallel",
+                        "sequence_parallel_state", "summa_dim", "tesseract_dim", "tesseract_dep", "cubic_dim", "vocab_per_input"):
+                    new.__dict__[key] = value
         new.weight = w
         return new
     if isinstance(child, nn.Linear):
@@ -548,6 +557,11 @@ def _restore_plain(child: nn.Module, params: dict) -> nn.Module:
             new = _bare(onn.Linear, in_features=w.shape[1], out_features=w.shape[0],
                         skip_bias_add=getattr(child, "skip_bias_add", False))
         new.weight, new.bias = w, b
+        return new
+    if child.__class__.__name__.startswith("LayerNorm") and getattr(child, "rms", False):
+        new = _bare(onn.FusedRMSNorm, normalized_shape=(w.shape[0],), eps=getattr(child, "variance_epsilon", 1e-6),
+                    elementwise_affine=True)
+        new.weight = w
         return new
     if child.__class__.__name__.startswith("LayerNorm"):
         new = _bare(onn.FusedLayerNorm, normalized_shape=(w.shape[0],), eps=getattr(child, "variance_epsilon", 1e-5),

@@ -327,3 +327,32 @@ def _ep_worker(rank, world, kind):
 @pytest.mark.parametrize("kind", ["bert", "t5", "bart", "gptj", "vit", "distilbert"])
 def test_hf_model_expert_parallel(kind):
     run_dist(_ep_worker, 2, kind, timeout=600)
+
+
+def _deparallel_worker(rank, world, kind):
+    """Shard a stock model over a 2-D grid and merge it back in memory: same state dict, same outputs, and the layers that
+    were swapped for parallel ones are the library's own classes again (scaled / learned-position embeddings, RMS norms)."""
+    import oslo_b200
+    from oslo_b200 import ParallelContext, ParallelMode
+    from oslo_b200.parallel import TensorParallel
+
+    pc = ParallelContext.from_torch(tensor_parallel_size=world, tensor_parallel_mode=ParallelMode.TENSOR_2D, backend="gloo", seed=0)
+    ref, model = _build(kind), _build(kind)
+    classes = {n: type(m).__name__ for n, m in ref.named_modules(remove_duplicate=False) if isinstance(m, torch.nn.Embedding)}
+    wrapped = TensorParallel(model, pc)
+    oslo_b200.ready(wrapped, pc)
+    wrapped.deparallelize()
+    state, ref_state = model.state_dict(), ref.state_dict()
+    assert set(state) == set(ref_state) and all(torch.equal(state[k], v) for k, v in ref_state.items())
+    # (tables that were separate modules around one tied weight come back as one module under all their names)
+    after = {n: type(m).__name__ for n, m in model.named_modules(remove_duplicate=False) if isinstance(m, torch.nn.Embedding)}
+    assert after == classes, (after, classes)
+    feed = {k: torch.cat([v, v]) for k, v in _inputs(kind).items()}
+    with torch.no_grad():
+        assert torch.allclose(model(**feed).logits, ref(**feed).logits, rtol=1e-4, atol=1e-5)
+    pc.destroy()
+
+
+@pytest.mark.parametrize("kind", ["bart", "t5", "opt"])
+def test_hf_model_deparallelize_after_2d(kind):
+    run_dist(_deparallel_worker, 4, kind, timeout=600)
