@@ -104,17 +104,22 @@ class HeteroDataParallel(ParallelWrapper):
                 continue
             chunks = self.manager.chunks_of(own)
             self._hooks.append(m.register_forward_pre_hook(lambda mod, inp, c=chunks: self.manager.access(c)))
-            self._hooks.append(m.register_forward_hook(lambda mod, inp, out, c=chunks: self._after_forward(c)))
+            self._hooks.append(m.register_forward_hook(lambda mod, inp, out, c=chunks: self._after_forward(c, mod, out)))
             self._hooks.append(m.register_full_backward_pre_hook(lambda mod, gout, c=chunks: self.manager.access(c)))
         for p in params:
             p.register_post_accumulate_grad_hook(self._grad_ready)
         for c in self.manager.chunks:
             c.pending_grads = len(c.params)
 
-    def _after_forward(self, chunks):
-        # a chunk shared with a module that runs later stays; modules re-gather on demand, so releasing is always safe
-        if not torch.is_grad_enabled() or True:
-            self.manager.release(chunks)
+    def _after_forward(self, chunks, mod=None, out=None):
+        """Release the module's chunks (modules re-gather on demand, so releasing is always safe).  A parameter that the
+        module hands to its caller (``skip_bias_add`` layers return ``(output, bias)`` and the bias is added later, fused
+        with dropout and the residual) must outlive the release: the caller gets a differentiable copy instead."""
+        replaced = None
+        if isinstance(out, tuple) and any(isinstance(o, nn.Parameter) for o in out):
+            replaced = tuple(o.clone() if isinstance(o, nn.Parameter) else o for o in out)
+        self.manager.release(chunks)
+        return replaced
 
     def _grad_ready(self, p):
         c = self.manager.param_to_chunk[id(p)]

@@ -106,6 +106,7 @@ class Trainer:
             model.to(args.dtype)
         self.model = model
         self.zero = None
+        self.hetero = None
         self.scaler = None  # DynamicLossScaler, built with the optimizer when fp16 is on
         if self.pc is not None:
             from .oslo_init import apply_wrappers
@@ -114,6 +115,16 @@ class Trainer:
             cfg = args.oslo_config
             dp = cfg.data_parallelism if cfg else None
             stage = (dp or {}).get("zero_stage", 0)
+            self.hetero = None
+            if stage == 3:
+                # chunked ZeRO-3: parameters live in chunks sharded over the DATA group and are gathered around each module
+                from oslo_b200.parallel.data_parallel.zero.hetero import HeteroDataParallel
+
+                params = {k: v for k, v in ((dp or {}).get("params") or {}).items()
+                          if k in ("placement_policy", "chunk_size_mb", "pin_memory", "min_free_fraction", "device_budget_bytes")}
+                if (dp or {}).get("params", {}).get("cpu_offload"):
+                    params.setdefault("placement_policy", "cpu")
+                self.hetero = self.model = HeteroDataParallel(self.model, self.pc, **params)
             if self.pc.data_parallel_size > 1 and stage == 0:
                 from oslo_b200.parallel import DistributedDataParallel
 
@@ -183,8 +194,8 @@ class Trainer:
         if self.optimizer is not None:
             return self.optimizer
         a = self.args
-        params = [p for p in self.base_model.parameters() if p.requires_grad and p.numel() > 0]
-        opt = create_optimizer(a.optim, params, lr=a.learning_rate, weight_decay=a.weight_decay, betas=(a.adam_beta1, a.adam_beta2),
+        params = [p for p in self.base_model.parameters() if p.requires_grad and (p.numel() > 0 or self.hetero is not None)]
+        opt = None if self.hetero is not None else create_optimizer(a.optim, params, lr=a.learning_rate, weight_decay=a.weight_decay, betas=(a.adam_beta1, a.adam_beta2),
                                eps=a.adam_epsilon, max_grad_norm=a.max_grad_norm, master_weights=a.dtype != torch.float32)
         cfg = a.oslo_config
         dp = (cfg.data_parallelism if cfg else None) or {}
@@ -195,6 +206,12 @@ class Trainer:
                                       weight_decay=a.weight_decay)
             self.zero = opt = ZeroRedundancyOptimizer(inner, parallel_context=self.pc, partition_grad=dp["zero_stage"] == 2,
                                                       clip_grad_norm=a.max_grad_norm, **(dp.get("params") or {}))
+        if self.hetero is not None:
+            from oslo_b200.parallel.data_parallel.zero.hetero import HeteroOptimizer
+
+            inner = torch.optim.AdamW(params, lr=a.learning_rate, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
+                                      weight_decay=a.weight_decay)
+            self.zero = opt = HeteroOptimizer(self.hetero, inner, clip_grad_norm=a.max_grad_norm)
         self.optimizer = opt
         if a.fp16 and self.zero is None and self.scaler is None:
             from oslo_b200.optim.loss_scaler import DynamicLossScaler
@@ -253,7 +270,7 @@ class Trainer:
                     part = out.loss / accum
                     (self.scaler.scale(part) if self.scaler is not None else part).backward()
                     total += out.loss.detach()
-            return total
+            return self._from_last_stage(total)
         loss = self.compute_loss(batch) / accum
         if self.zero is not None:
             self.zero.backward(loss)  # the ZeRO optimizer scales the loss itself
@@ -262,6 +279,15 @@ class Trainer:
         else:
             loss.backward()
         return loss.detach() * accum
+
+    def _from_last_stage(self, value) -> torch.Tensor:
+        """Under pipeline parallelism only the last stage computes the loss: hand it to every stage (the others add
+        zero), so logs, best-model tracking and early stopping see the same number on all ranks."""
+        t = torch.zeros((), device=self.device) if value is None else value.detach().float().to(self.device).reshape(())
+        if self.pc is not None and self.pc.pipeline_parallel_size > 1:
+            t = t.clone()
+            dist.all_reduce(t, group=self.pc.get_group(ParallelMode.PIPELINE))
+        return t
 
     def _clip(self):
         if self.zero is not None or not self.args.max_grad_norm:
@@ -283,7 +309,10 @@ class Trainer:
         resume = resume_from_checkpoint or a.resume_from_checkpoint
         skip_batches = 0
         if resume:
-            skip_batches = self._load_checkpoint(resume) * a.gradient_accumulation_steps
+            done_steps = self._load_checkpoint(resume)
+            # the loop restarts in the epoch the checkpoint was taken in: skip only what that epoch had already consumed
+            self.state.epoch = float(done_steps // steps_per_epoch)
+            skip_batches = (done_steps % steps_per_epoch) * a.gradient_accumulation_steps
             if a.ignore_data_skip:
                 skip_batches = 0
         self.base_model.train()
@@ -312,7 +341,7 @@ class Trainer:
                     self.profiler = FlopsProfiler(self.base_model)
                     self.profiler.start_profile()
                 ctx = self.model.no_sync() if (not sync_now and hasattr(self.model, "no_sync")) else _null()
-                zctx = self.zero.no_sync() if (not sync_now and self.zero is not None) else _null()
+                zctx = self.zero.no_sync() if (not sync_now and self.zero is not None and hasattr(self.zero, "no_sync")) else _null()
                 with ctx, zctx:
                     running += float(self.training_step(batch))
                 if profile:
@@ -421,8 +450,7 @@ class Trainer:
                 for _, out in self.model(**batch):
                     if torch.is_tensor(out.loss):
                         total = out.loss if total is None else total + out.loss
-                if total is not None:
-                    losses.append(float(total))
+                losses.append(float(self._from_last_stage(total)))
             else:
                 losses.append(float(self.model(**batch).loss))
         loss = self._mean_over_dp(sum(losses) / max(1, len(losses)))
@@ -449,8 +477,7 @@ class Trainer:
                 for _, out in self.model(**batch):
                     if torch.is_tensor(out.loss):
                         total = out.loss if total is None else total + out.loss
-                if total is not None:
-                    losses.append(float(total))
+                losses.append(float(self._from_last_stage(total)))
                 continue
             out = self.model(**batch)
             if getattr(out, "loss", None) is not None:
@@ -494,7 +521,11 @@ class Trainer:
         a = self.args
         out = os.path.join(a.output_dir, f"checkpoint-{self.state.global_step}")
         os.makedirs(out, exist_ok=True)
-        if hasattr(self.model, "save_pretrained") and self.pc is not None:
+        if self.hetero is not None:
+            full = self.hetero.state_dict()  # collective: every chunk is gathered
+            if self._rank() == 0:
+                torch.save(full, os.path.join(out, "pytorch_model.bin"))
+        elif hasattr(self.model, "save_pretrained") and self.pc is not None:
             self.model.save_pretrained(out)
         elif self._rank() == 0:
             self.base_model.save_pretrained(out) if hasattr(self.base_model, "save_pretrained") else torch.save(
@@ -532,18 +563,22 @@ class Trainer:
         """Restores model shards, optimizer, scheduler, RNG and trainer state; returns the steps already done.
         ``weights_only`` reloads the model alone (best-model reload at the end of training)."""
         rank = self._rank()
-        if self.pc is not None and hasattr(self.model, "from_parallelized"):
+        if self.hetero is not None:
+            self.hetero.load_state_dict(torch.load(os.path.join(path, "pytorch_model.bin"), map_location="cpu"))
+            if self.zero is not None:
+                self.zero._built = False  # the fp32 masters are rebuilt from the loaded shards
+        elif self.pc is not None and hasattr(self.model, "from_parallelized"):
             self.model.from_parallelized(path)
         else:
             self.base_model.load_state_dict(torch.load(os.path.join(path, "pytorch_model.bin"), map_location="cpu"))
         if weights_only:
-            if self.zero is not None:
+            if self.zero is not None and hasattr(self.zero, "resync_master"):
                 self.zero.resync_master()
             return self.state.global_step
         opt_file = os.path.join(path, f"optimizer_{rank}.pt" if self.pc is not None else "optimizer.pt")
         if os.path.exists(opt_file):
             self.optimizer.load_state_dict(torch.load(opt_file, map_location="cpu", weights_only=False))
-        elif self.zero is not None:
+        elif self.zero is not None and hasattr(self.zero, "resync_master"):
             self.zero.resync_master()  # the fp32 master shards must follow the weights that were just loaded
         sched = os.path.join(path, "scheduler.pt")
         if os.path.exists(sched):

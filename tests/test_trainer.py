@@ -289,3 +289,54 @@ def test_fp16_training_uses_the_dynamic_loss_scaler_and_checkpoints_it():
                      train_dataset=_Toy())
         t2.train(resume_from_checkpoint=os.path.join(tmp, "checkpoint-8"))
         assert t2.scaler.skipped_steps >= t.scaler.skipped_steps
+
+
+_DIST_CONFIGS = {
+    "tp1d_sp": (2, {"tensor_parallelism": {"parallel_size": 2, "parallel_mode": "1d", "sequence_parallel": True}}),
+    "zero2": (2, {"data_parallelism": {"parallel_size": 2, "zero_stage": 2}}),
+    "zero3": (2, {"data_parallelism": {"parallel_size": 2, "zero_stage": 3}}),
+    "pp": (2, {"pipeline_parallelism": {"parallel_size": 2, "params": {"num_micro_batches": 2}}}),
+    "tp2d": (4, {"tensor_parallelism": {"parallel_size": 4, "parallel_mode": "2d"}}),
+    "tp_dp_ckpt": (4, {"tensor_parallelism": {"parallel_size": 2, "parallel_mode": "1d"},
+                       "data_parallelism": {"parallel_size": 2, "zero_stage": 1},
+                       "activation_checkpointing": {"partitioned": True}}),
+}
+
+
+def _dist_trainer_worker(rank, world, name, tmp):
+    """``Trainer`` driven by a configuration dict on CPU ranks: trains, logs the same finite loss on every rank (under
+    pipeline parallelism too, where only the last stage computes it), evaluates, checkpoints, and a second trainer resumed
+    from the mid-run checkpoint ends with the same loss."""
+    import torch.distributed as dist
+
+    from oslo_b200.transformers import Trainer, TrainingArguments
+
+    cfg = dict(_DIST_CONFIGS[name][1], backend={"name": "gloo"})
+    common = dict(output_dir=tmp, per_device_train_batch_size=8, learning_rate=3e-3, logging_steps=2, seed=1)
+    args = TrainingArguments(max_steps=6, save_steps=4, oslo_config_path_or_dict=cfg, **common)
+    t = Trainer(_model(), args, train_dataset=_Toy(), eval_dataset=_Toy(16))
+    t.train()
+    losses = [h["loss"] for h in t.state.log_history if "loss" in h]
+    assert len(losses) == 3 and all(math.isfinite(v) and v > 0 for v in losses), (name, losses)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, losses)
+    dp = cfg.get("data_parallelism", {}).get("parallel_size", 1)
+    assert all(max(abs(a - b) for a, b in zip(g, gathered[0])) < 1e-5 for g in gathered) or dp > 1, gathered
+    ev = t.evaluate()
+    assert math.isfinite(ev["eval_loss"]) and ev["eval_loss"] > 0
+    assert os.path.isdir(os.path.join(tmp, "checkpoint-4"))
+    dist.barrier()
+    args2 = TrainingArguments(max_steps=6, save_steps=0, parallel_context=args.parallel_context, wrapper_recipes=args.wrapper_recipes,
+                              oslo_config=args.oslo_config, **common)
+    t2 = Trainer(_model(), args2, train_dataset=_Toy())
+    t2.train(resume_from_checkpoint=os.path.join(tmp, "checkpoint-4"))
+    resumed = [h["loss"] for h in t2.state.log_history if "loss" in h]
+    assert abs(resumed[-1] - losses[-1]) < 2e-4, (name, resumed, losses)
+
+
+@pytest.mark.parametrize("name", list(_DIST_CONFIGS))
+def test_trainer_under_parallel_configurations(name):
+    from dist_utils import run_dist
+
+    with tempfile.TemporaryDirectory() as tmp:
+        run_dist(_dist_trainer_worker, _DIST_CONFIGS[name][0], name, tmp, timeout=600)
