@@ -176,7 +176,7 @@ def main(argv=None) -> int:
     s.add_argument("--port", type=int, default=8000)
     s.add_argument("--max-batch", type=int, default=8)
     s.set_defaults(fn=cmd_serve)
-    for p in (t, v, g, s):
+    for p in (t, v, g, e, s):  # (export always works on the host copy; it takes the flag so scripts can pass one set of options)
         p.add_argument("--device", default=dev)
     a = ap.parse_args(argv)
     return a.fn(a)

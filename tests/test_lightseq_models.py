@@ -489,3 +489,36 @@ def test_host_graph_executor_runs_the_same_graphs_in_one_native_call():
     # errors come back as the failing node: a decoding step beyond the cache length
     with pytest.raises(RuntimeError, match="attn"):
         gflow.ctx.run({"ids": prompt.reshape(-1)}, [gflow.logits], seq_len=6, step=30)
+
+
+def test_command_line_train_validate_generate_export(tmp_path, capsys):
+    """The command-line workflow end to end on a toy reversal task: train, score, translate with beam search, export to
+    int8 and read the export back."""
+    import random
+
+    from oslo_b200.lightseq import load_exported
+    from oslo_b200.lightseq.cli import main
+
+    rng = random.Random(0)
+    data = tmp_path / "train.txt"
+    with open(data, "w") as f:
+        for _ in range(96):
+            src = [rng.randint(4, 30) for _ in range(rng.randint(3, 6))]
+            f.write(" ".join(map(str, src)) + "\t" + " ".join(map(str, reversed(src))) + "\n")
+    model = str(tmp_path / "m.pt")
+    common = ["--device", "cpu"]
+    assert main(["train", "--data", str(data), "--save", model, "--epochs", "3", "--batch-size", "16", "--lr", "3e-3", "--vocab-size", "32",
+                 "--hidden", "32", "--heads", "4", "--layers", "1", "--max-len", "12", *common]) == 0
+    losses = [float(line.split()[-1]) for line in capsys.readouterr().out.splitlines() if line.startswith("epoch")]
+    assert len(losses) == 3 and losses[-1] < losses[0]
+    assert main(["validate", "--load", model, "--data", str(data), *common]) == 0
+    assert "perplexity" in capsys.readouterr().out
+    src = tmp_path / "in.txt"
+    src.write_text("5 6 7\n8 9 10 11\n")
+    assert main(["generate", "--load", model, "--input", str(src), "--beam", "2", "--max-new-tokens", "6", *common]) == 0
+    lines = capsys.readouterr().out.splitlines()  # one line per source sentence (empty when the model stops at once)
+    assert len(lines) == 2 and all(tok.isdigit() for line in lines for tok in line.split())
+    out = str(tmp_path / "m.osl")
+    assert main(["export", "--load", model, "--out", out, "--int8", *common]) == 0
+    state, header = load_exported(out)
+    assert header["quantized"] and len(state) == len(header["tensors"]) > 5
