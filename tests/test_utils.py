@@ -144,3 +144,35 @@ def test_documentation_names_exist():
         assert os.path.exists(os.path.join(root, path)), path
     for link in set(re.findall(r"\]\(([\w/._-]+\.md)\)", text)):
         assert any(os.path.exists(os.path.join(os.path.dirname(d), link)) for d in docs), link
+
+
+def _launcher_worker(rank, world, kind, port):
+    import os
+
+    import torch
+    import torch.distributed as dist
+
+    from oslo_b200 import ParallelContext, ParallelMode
+
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "LOCAL_WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT"):
+        os.environ.pop(k, None)  # only the scheduler's own variables may be read
+    if kind == "slurm":
+        os.environ.update(SLURM_PROCID=str(rank), SLURM_NPROCS=str(world), SLURM_GPUS_ON_NODE=str(world))
+        pc = ParallelContext.from_slurm("127.0.0.1", port, data_parallel_size=1, tensor_parallel_size=world, backend="gloo")
+    else:
+        os.environ.update(OMPI_COMM_WORLD_RANK=str(rank), OMPI_COMM_WORLD_LOCAL_RANK=str(rank), OMPI_COMM_WORLD_SIZE=str(world),
+                          OMPI_COMM_WORLD_LOCAL_SIZE=str(world))
+        pc = ParallelContext.from_openmpi("127.0.0.1", port, data_parallel_size=1, tensor_parallel_size=world, backend="gloo")
+    assert pc.get_global_rank() == rank and pc.get_world_size(ParallelMode.GLOBAL) == world
+    assert pc.get_world_size(ParallelMode.TENSOR) == world and pc.get_local_rank(ParallelMode.TENSOR) == rank
+    t = torch.tensor([float(rank + 1)])
+    dist.all_reduce(t, group=pc.get_group(ParallelMode.TENSOR))
+    assert float(t) == world * (world + 1) / 2
+    pc.destroy()
+
+
+def test_parallel_context_from_slurm_and_openmpi_variables():
+    from dist_utils import free_port, run_dist
+
+    for kind in ("slurm", "openmpi"):
+        run_dist(_launcher_worker, 2, kind, free_port())
