@@ -117,7 +117,10 @@ class SequenceParallelState:
         """Cut ``t`` to this rank's share when it still spans the whole batch / sequence along the sharded dimension (a
         size-1 dimension that broadcasts against the shard is left alone)."""
         full = getattr(self, "full", None)
-        if full is None or not torch.is_tensor(t) or t.dim() <= self.dim or t.shape[self.dim] != full[self.dim]:
+        if full is None or not torch.is_tensor(t) or t.dim() <= self.dim:
+            return t
+        size = t.shape[self.dim]
+        if size != full[self.dim] and not (self.dim == 1 and size in getattr(self, "other_lengths", ())):
             return t
         if self.pc.get_world_size(ParallelMode.TENSOR_1D) == 1:
             return t
@@ -166,6 +169,9 @@ class TensorParallel(ParallelWrapper):
             ids = kwargs.get("input_ids", args[0] if args else None)
             if ids is not None and ids.dim() >= 2:
                 self.sp_state.configure(ids.shape[0], ids.shape[1])
+                # a decoder runs on its own sequence length: position tables looked up for it are cut the same way
+                other = kwargs.get("decoder_input_ids", kwargs.get("labels"))
+                self.sp_state.other_lengths = {other.shape[1]} if other is not None and other.dim() >= 2 else set()
         elif getattr(self, "_parallelized", False) and mode != ParallelMode.TENSOR_1D and pc.tensor_parallel_size > 1:
             from ._wrapper_nd import scatter_batch_inputs
 

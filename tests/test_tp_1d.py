@@ -149,6 +149,7 @@ def test_sequence_parallel_in_tree_families(kind):
 def test_sequence_parallel_over_the_sequence_dimension_and_foreign_models():
     run_dist(_sp_family_worker, 2, "neox", 1)  # batch 1: the 12 tokens are what is split
     run_dist(_sp_family_worker, 2, "bert", 1)
+    run_dist(_sp_family_worker, 2, "bart", 1)  # the decoder's positions follow its own (shorter) sequence
     # stock transformers attention modules reshape with the input's length: refused with an explanation, except GPT-2 / GPT-J
     transformers = pytest.importorskip("transformers")
     from oslo_b200.parallel import TensorParallel
