@@ -190,9 +190,19 @@ def _placeholder_forward(module: nn.Module):
     matters (the stage's real input arrives from its neighbour), so it only has to have the right shape and dtype."""
     dtype = next(module.parameters()).dtype
     if isinstance(module, nn.Embedding):
-        dim = module.embedding_dim
+        dim = module.embedding_dim  # (the weight itself may already have been released on this stage)
+        kind = type(module).__name__
+        if "VocabParallel" not in kind:
+            # the 2-D / 2.5-D position-style tables store h / q^2 columns and gather them to the h / q of the activations
+            if "Embedding2D" in kind:
+                dim *= module.summa_dim
+            elif "Embedding2p5D" in kind:
+                dim *= module.tesseract_dim
 
         def fwd(ids, *a, **k):
+            if not torch.is_tensor(ids):  # position tables that take a shape (batch, seq) instead of ids
+                shape, device = tuple(ids), module.weight.device
+                return torch.zeros((), dtype=dtype, device=device).expand(*shape, dim)
             return torch.zeros((), dtype=dtype, device=ids.device).expand(*ids.shape, dim)
 
         return fwd

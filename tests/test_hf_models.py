@@ -356,3 +356,33 @@ def _deparallel_worker(rank, world, kind):
 @pytest.mark.parametrize("kind", ["bart", "t5", "opt"])
 def test_hf_model_deparallelize_after_2d(kind):
     run_dist(_deparallel_worker, 4, kind, timeout=600)
+
+
+def _tp_pp_worker(rank, world, kind):
+    """Stock model, 2-D tensor parallel inside each of two pipeline stages cut from the module tree: the stage that does
+    not own the embeddings stands in for them with placeholders of the sharded width."""
+    import oslo_b200
+    from oslo_b200 import ParallelContext, ParallelMode
+    from oslo_b200.parallel import PipelineParallel, TensorParallel
+
+    pc = ParallelContext.from_torch(tensor_parallel_size=4, pipeline_parallel_size=2, tensor_parallel_mode=ParallelMode.TENSOR_2D,
+                                    backend="gloo", seed=0)
+    ref, model = _build(kind).train(), _build(kind).train()
+    TensorParallel(model, pc)
+    wrapped = PipelineParallel(model, pc, num_micro_batches=2)
+    oslo_b200.ready(wrapped, pc)
+    ids = torch.randint(0, 100, (8, 12), generator=torch.Generator().manual_seed(1))
+    ref_loss = sum(ref(input_ids=c, labels=c).loss for c in ids.chunk(2)) / 2
+    total = 0.0
+    for _, out in wrapped(input_ids=ids, labels=ids):
+        if out.loss is not None:
+            out.loss.backward()
+            if wrapped.stage == 1:
+                total += out.loss.item()
+    if wrapped.stage == 1:
+        assert abs(total - ref_loss.item()) < 1e-4, (total, ref_loss.item())
+    pc.destroy()
+
+
+def test_hf_model_2d_tensor_parallel_inside_pipeline_stages():
+    run_dist(_tp_pp_worker, 8, "gpt2", timeout=900)
