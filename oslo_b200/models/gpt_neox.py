@@ -70,6 +70,10 @@ _DEFER_GELU_GRAD = __import__("os").environ.get("OSLO_B200_DEFER_GELU", "0") == 
 
 
 class GPTNeoXMLP(nn.Module):
+    #: the forward hands its linears' weights to one fused op instead of calling the linears: engines that materialise
+    #: parameters per module call (chunked ZeRO-3) must treat this module's whole subtree as one unit
+    reads_descendant_parameters = True
+
     def __init__(self, config):
         super().__init__()
         self.dense_h_to_4h = onn.Linear(config.hidden_size, config.intermediate_size, skip_bias_add=True)
@@ -93,6 +97,8 @@ class GPTNeoXMLP(nn.Module):
 
 
 class GPTNeoXLayer(nn.Module):
+    reads_descendant_parameters = True  # the paired (parallel-residual) path reads attention and MLP weights directly
+
     def __init__(self, config):
         super().__init__()
         self.use_parallel_residual = config.use_parallel_residual

@@ -98,8 +98,16 @@ class HeteroDataParallel(ParallelWrapper):
             self.memory_manager = MemoryManager(self.manager.chunks, dev, self.device_budget_bytes, self.memory_probe,
                                                 self.mem_stats, self.warmup_steps)
             self.manager.before_access = self.memory_manager.adjust_layout
+        covered = set()  # modules inside a subtree that is gathered as one unit
         for m in self.module.modules():
-            own = [p for p in m.parameters(recurse=False) if id(p) in self.manager.param_to_chunk]
+            if id(m) in covered:
+                continue
+            subtree = getattr(m, "reads_descendant_parameters", False)
+            if subtree:
+                # the module's forward reads its descendants' parameters without calling them (fused ops over several
+                # layers' weights): gather / release everything below it around ITS forward and backward
+                covered.update(id(d) for d in m.modules() if d is not m)
+            own = [p for p in m.parameters(recurse=subtree) if id(p) in self.manager.param_to_chunk]
             if not own:
                 continue
             chunks = self.manager.chunks_of(own)

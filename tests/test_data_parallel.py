@@ -2,6 +2,8 @@
 the full batch."""
 import copy
 
+import os
+
 import pytest
 import torch
 import torch.nn as nn
@@ -235,3 +237,49 @@ def _zero_linear_worker(rank, world):
 
 def test_zero_sharded_linear_matches_unsharded_model():
     run_dist(_zero_linear_worker, 2)
+
+
+def _hetero_family_worker(rank, world, kind):
+    """Chunked ZeRO-3 on the in-tree models that stress its per-module gathering: layers that return a bias to their caller
+    (fused bias + dropout + residual) and layers whose forward reads their children's weights directly (fused MLP,
+    parallel-residual block).  Three optimizer steps track an unsharded AdamW run on the whole batch."""
+    import sys
+
+    import torch
+
+    import oslo_b200
+    from oslo_b200 import ParallelContext
+    from oslo_b200.parallel.data_parallel.zero.hetero import HeteroDataParallel, HeteroOptimizer
+
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from test_tp_1d import _family
+
+    pc = ParallelContext.from_torch(data_parallel_size=world, backend="gloo", seed=0)
+    ref, model = _family(kind).train(), _family(kind).train()
+    wrapped = HeteroDataParallel(model, pc, placement_policy="cuda")
+    oslo_b200.ready(wrapped, pc)
+    opt = HeteroOptimizer(wrapped, torch.optim.AdamW(model.parameters(), lr=1e-2, weight_decay=0.0))
+    ref_opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.0)
+    ids_all = torch.randint(0, 100, (4, 12), generator=torch.Generator().manual_seed(1))
+    ids = ids_all.chunk(world)[rank]
+    feed = (lambda i: {"input_ids": i, "labels": i[:, :8].contiguous()}) if kind in ("t5", "bart") else (lambda i: {"input_ids": i, "labels": i})
+    for _ in range(3):
+        opt.zero_grad()
+        ref_opt.zero_grad()
+        loss = wrapped(**feed(ids)).loss
+        opt.backward(loss)
+        opt.step()
+        ref_loss = ref(**feed(ids_all)).loss
+        ref_loss.backward()
+        ref_opt.step()
+        mean = loss.detach().clone()
+        torch.distributed.all_reduce(mean)
+        assert abs(float(mean) / world - float(ref_loss)) < 2e-4, (kind, float(mean) / world, float(ref_loss))
+    full, want = wrapped.state_dict(), ref.state_dict()
+    assert all(torch.allclose(full[k].float(), v.float(), atol=2e-4) for k, v in want.items() if k in full)
+    pc.destroy()
+
+
+@pytest.mark.parametrize("kind", ["neox", "gpt2", "t5"])
+def test_hetero_zero3_on_in_tree_families(kind):
+    run_dist(_hetero_family_worker, 2, kind)
