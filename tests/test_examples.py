@@ -58,5 +58,12 @@ def test_pipeline_and_zero_example_runs(tmp_path):
                "--save_dir", str(tmp_path / "z"), "--data_parallel_size", "2", "--zero_stage", "2", "--train_step", "6", nproc=2, port=29721)
     assert "saved shards" in out
     out = _run("train.py", "--model", "t5-tiny", "--task", "seq2seq", "--cpu", "--sequence_length", "16", "--save_dir", str(tmp_path / "t5"),
-               "--train_step", "4")
+               "--train_step", "4", "--merge")
     assert "saved shards" in out
+    out = _run("inference.py", "--model", "t5-tiny", "--task", "seq2seq", "--cpu", "--sequence_length", "16", "--load", str(tmp_path / "t5_merged"))
+    assert "output [[" in out
+    _run("train.py", "--model", "bert-tiny", "--task", "sequence-classification", "--cpu", "--sequence_length", "16", "--save_dir",
+         str(tmp_path / "cls"), "--train_step", "3", "--merge")
+    out = _run("inference.py", "--model", "bert-tiny", "--task", "sequence-classification", "--cpu", "--sequence_length", "16", "--load",
+               str(tmp_path / "cls_merged"))
+    assert "class [" in out
