@@ -88,3 +88,32 @@ def test_chunked_head_loss_equals_the_materialised_head_for_the_causal_models():
         for n, p in model.named_parameters():
             if n in want:
                 assert torch.allclose(p.grad, want[n], atol=2e-5), (cls.__name__, n)
+
+
+def test_in_tree_checkpoints_load_in_transformers(tmp_path):
+    """``save_pretrained`` of an in-tree model writes a directory that the Hugging Face class of the same name loads as is
+    (config and state-dict names), and the two give the same logits: moving between the frameworks needs no conversion."""
+    transformers = pytest.importorskip("transformers")
+    from oslo_b200 import models
+
+    torch.manual_seed(0)
+    cases = [
+        ("GPT2LMHeadModel", models.GPT2LMHeadModel(models.GPT2Config(vocab_size=100, n_positions=32, n_embd=32, n_layer=2, n_head=4))),
+        ("BertForMaskedLM", models.BertForMaskedLM(models.BertConfig(vocab_size=100, hidden_size=32, num_hidden_layers=2,
+                                                                      num_attention_heads=4, intermediate_size=64,
+                                                                      max_position_embeddings=32))),
+        ("T5ForConditionalGeneration", models.T5ForConditionalGeneration(models.T5Config(
+            vocab_size=100, d_model=32, d_kv=8, d_ff=64, num_layers=2, num_decoder_layers=2, num_heads=4))),
+        ("LlamaForCausalLM", models.LlamaForCausalLM(models.LlamaConfig(vocab_size=100, hidden_size=32, intermediate_size=64,
+                                                                        num_hidden_layers=2, num_attention_heads=4,
+                                                                        max_position_embeddings=32))),
+    ]
+    ids = torch.randint(0, 100, (2, 10))
+    for name, ours in cases:
+        ours.eval()
+        path = str(tmp_path / name)
+        ours.save_pretrained(path)
+        theirs = getattr(transformers, name).from_pretrained(path).eval()
+        extra = {"decoder_input_ids": ids[:, :5]} if "T5" in name else {}
+        with torch.no_grad():
+            assert torch.allclose(ours(input_ids=ids, **extra).logits, theirs(input_ids=ids, **extra).logits, atol=1e-4), name
