@@ -193,6 +193,14 @@ class TensorParallel(ParallelWrapper):
 
         kwargs = dict(kwargs)
         labels = kwargs.pop("labels")
+        if getattr(getattr(self.module, "config", None), "is_encoder_decoder", False) and kwargs.get("decoder_input_ids") is None \
+                and kwargs.get("decoder_inputs_embeds") is None:
+            # the model would have derived the decoder inputs from the labels it no longer receives
+            make = getattr(self.module, "prepare_decoder_input_ids_from_labels", None) or getattr(self.module, "_shift_right", None) \
+                or getattr(self.module, "_shift", None)
+            if make is None:
+                raise ValueError("give decoder_input_ids: this model cannot derive them from labels")
+            kwargs["decoder_input_ids"] = make(labels)
         out = self.module(*args, **kwargs)
         logits = out.logits if hasattr(out, "logits") else out[0]
         name = type(self.module).__name__
@@ -397,6 +405,15 @@ class TensorParallel(ParallelWrapper):
             gather = mapping.is_gather_output(module, name) and not is_oslo_model
             if self.vocab_parallel_loss and head is getattr(module, "get_output_embeddings", lambda: None)():
                 gather = False  # the loss consumes the vocabulary shards directly
+                flb = getattr(module, "final_logits_bias", None)
+                if torch.is_tensor(flb) and flb.shape[-1] == head.orig_num_classes:
+                    # a per-token bias added to the logits (BART): this rank adds its slice to its slice of the logits
+                    self._saved_buffers = getattr(self, "_saved_buffers", []) + [(module, "final_logits_bias", flb)]
+                    per = w.shape[out_dim]
+                    padded = torch.zeros(*flb.shape[:-1], per * tp, dtype=flb.dtype, device=flb.device)
+                    padded[..., : flb.shape[-1]] = flb
+                    rank_ = pc.get_local_rank(M1)
+                    module.final_logits_bias = padded[..., rank_ * per : (rank_ + 1) * per].clone()
             new = _bare(onn.ColLinear1D, in_features=w.shape[in_dim], out_features=w.shape[out_dim],
                         skip_bias_add=False, gather_output=gather, parallel_context=pc, sequence_parallel=sp,
                         world_size=tp, reversed=conv, sequence_parallel_state=self.sp_state)
@@ -495,6 +512,9 @@ class TensorParallel(ParallelWrapper):
         for handle in getattr(self, "_entry_hooks", []):
             handle.remove()
         self._entry_hooks = []
+        for owner, name, value in getattr(self, "_saved_buffers", []):
+            setattr(owner, name, value)
+        self._saved_buffers = []
         merged = {}
         for name, child in list(module.named_modules()):
             if name == "":

@@ -385,3 +385,36 @@ def _tp_pp_worker(rank, world, kind):
 
 def test_hf_model_2d_tensor_parallel_inside_pipeline_stages():
     run_dist(_tp_pp_worker, 8, "gpt2", timeout=900)
+
+
+def _vp_loss_other_worker(rank, world, kind):
+    """``vocab_parallel_loss=True`` beyond causal models: masked-LM labels are used as they are, encoder-decoder models
+    get the decoder inputs the library would have derived from the labels, and BART's per-token logits bias is added
+    slice by slice; the loss equals the unsharded model's and gradients flow."""
+    import oslo_b200
+    from oslo_b200 import ParallelContext
+    from oslo_b200.parallel import TensorParallel
+
+    pc = ParallelContext.from_torch(tensor_parallel_size=world, backend="gloo", seed=0)
+    ref, model = _build(kind), _build(kind)
+    if kind == "bart":
+        with torch.no_grad():
+            bias = torch.randn(1, 100, generator=torch.Generator().manual_seed(3))
+            ref.final_logits_bias.copy_(bias)
+            model.final_logits_bias.copy_(bias)
+    wrapped = TensorParallel(model, pc, vocab_parallel_loss=True)
+    oslo_b200.ready(wrapped, pc)
+    feed = _inputs(kind)
+    labels = feed.pop("decoder_input_ids", feed["input_ids"]).clone()
+    labels[0, :2] = -100
+    want = ref(**feed, labels=labels).loss
+    out = wrapped(**feed, labels=labels)
+    assert torch.allclose(out.loss, want, atol=1e-5), (kind, float(out.loss), float(want))
+    assert out.logits.shape[-1] == 100 // world  # the head's output stays sharded
+    out.loss.backward()
+    pc.destroy()
+
+
+@pytest.mark.parametrize("kind", ["bert", "t5", "bart"])
+def test_hf_vocab_parallel_loss_masked_and_encoder_decoder(kind):
+    run_dist(_vp_loss_other_worker, 2, kind, timeout=600)
