@@ -28,7 +28,37 @@ def _logits(model, ids, cache: Optional[DecodeCache] = None):
             out = model(input_ids=new)
         cache.advance(new.shape[1])
     logits = out.logits if hasattr(out, "logits") else out[0]
-    return logits[:, -1, :].float()
+    return _whole_logits(model, logits[:, -1, :]).float()
+
+
+def _whole_logits(model, last: torch.Tensor) -> torch.Tensor:
+    """Tensor-parallel models whose head keeps the vocabulary sharded (for the vocab-parallel loss) return a slice of the
+    logits; picking the next token needs all of them.  ``last``: ``[batch, vocab or a shard of it]``."""
+    pc = getattr(model, "parallel_context", None)
+    if pc is None or getattr(pc, "tensor_parallel_size", 1) == 1:
+        return last
+    base = getattr(model, "module", model)
+    vocab = getattr(base, "orig_vocab_size", None) or base.config.vocab_size
+    if last.shape[-1] >= vocab:
+        return last[..., :vocab]
+    from oslo_b200.distributed import ParallelMode, comm
+
+    mode = pc.tensor_parallel_mode
+    if mode == ParallelMode.TENSOR_1D:
+        full = comm.all_gather(last.contiguous(), dim=-1, parallel_context=pc, parallel_mode=ParallelMode.TENSOR_1D)
+    elif mode == ParallelMode.TENSOR_2D:
+        from oslo_b200.parallel.tensor_parallel._ops_2d import gather_output_2d
+
+        full = gather_output_2d(last.contiguous(), pc)
+    elif mode == ParallelMode.TENSOR_2P5D:
+        from oslo_b200.parallel.tensor_parallel._ops_2p5d import gather_output_2p5d
+
+        full = gather_output_2p5d(last.contiguous(), pc)
+    else:
+        from oslo_b200.parallel.tensor_parallel._ops_3d import gather_output_3d
+
+        full = gather_output_3d(last.contiguous(), pc)
+    return full[..., :vocab]
 
 
 def _filter(logits, top_k: int, top_p: float):
@@ -52,6 +82,14 @@ def generate(model, input_ids: torch.Tensor, max_new_tokens: int = 32, do_sample
     """Returns ``[batch, prompt + new]`` token ids (best beam when ``num_beams > 1``).  ``use_cache=False`` re-runs the
     whole prefix every step (the reference behaviour for models whose attention does not go through ``oslo_b200.ops``)."""
     model.eval()
+    pc = getattr(model, "parallel_context", None)
+    if num_beams > 1 and use_cache and pc is not None and getattr(pc, "tensor_parallel_size", 1) > 1:
+        from oslo_b200.distributed import ParallelMode as _PM
+
+        if pc.tensor_parallel_mode != _PM.TENSOR_1D:
+            # the N-D layouts split the batch over ranks, so a beam's parent may be cached on another rank: beams re-run
+            # their prefix instead of reordering caches
+            use_cache = False
     if num_beams > 1:
         return _beam_search(model, input_ids, max_new_tokens, num_beams, no_repeat_ngram_size, eos_token_id, length_penalty,
                             use_cache)

@@ -163,3 +163,30 @@ def test_sequence_parallel_over_the_sequence_dimension_and_foreign_models():
                                                                  num_attention_heads=2, intermediate_size=32))
     with pytest.raises(NotImplementedError, match="in-tree"):
         TensorParallel(model, _PC(), sequence_parallel=True)
+
+
+def _generate_worker(rank, world, kind, two_d):
+    """Generation through a tensor-parallel model: the in-tree heads return vocabulary shards, which are gathered before a
+    token is chosen; greedy and beam search give the unsharded model's tokens (1-D with the key / value cache, 2-D with
+    the batch split over ranks)."""
+    import oslo_b200
+    from oslo_b200 import ParallelContext, ParallelMode
+    from oslo_b200.lightseq import generate
+    from oslo_b200.parallel import TensorParallel
+
+    pc = ParallelContext.from_torch(tensor_parallel_size=world, backend="gloo", seed=0,
+                                    tensor_parallel_mode=ParallelMode.TENSOR_2D if two_d else ParallelMode.TENSOR_1D)
+    ref, model = _family(kind), _family(kind)
+    wrapped = TensorParallel(model, pc)
+    oslo_b200.ready(wrapped, pc)
+    prompt = torch.randint(1, 100, (2, 5), generator=torch.Generator().manual_seed(1))
+    for beams in (1, 2):
+        want = generate(ref, prompt, max_new_tokens=6, num_beams=beams)
+        got = generate(wrapped, prompt, max_new_tokens=6, num_beams=beams)
+        assert torch.equal(got, want), (kind, beams, got.tolist(), want.tolist())
+    pc.destroy()
+
+
+@pytest.mark.parametrize("kind,world,two_d", [("neox", 2, False), ("llama", 2, False), ("neox", 4, True)])
+def test_generation_through_tensor_parallel_models(kind, world, two_d):
+    run_dist(_generate_worker, world, kind, two_d)
