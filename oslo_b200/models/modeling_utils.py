@@ -209,6 +209,10 @@ def seq2seq_generate(model, encode, decode_logits, input_ids, attention_mask, ma
             cache.advance(feed.shape[1])
         else:
             logits = decode_logits(enc, attention_mask, out)
+        if getattr(model, "parallel_context", None) is not None:
+            from oslo_b200.lightseq.inference import _whole_logits
+
+            logits = _whole_logits(model, logits)  # tensor-parallel heads return a vocabulary shard
         if num_beams == 1:
             nxt = logits.argmax(-1).masked_fill(done, pad_id)
         else:

@@ -190,3 +190,24 @@ def _generate_worker(rank, world, kind, two_d):
 @pytest.mark.parametrize("kind,world,two_d", [("neox", 2, False), ("llama", 2, False), ("neox", 4, True)])
 def test_generation_through_tensor_parallel_models(kind, world, two_d):
     run_dist(_generate_worker, world, kind, two_d)
+
+
+def _seq2seq_generate_worker(rank, world, kind):
+    import oslo_b200
+    from oslo_b200 import ParallelContext
+    from oslo_b200.parallel import TensorParallel
+
+    pc = ParallelContext.from_torch(tensor_parallel_size=world, backend="gloo", seed=0)
+    ref, model = _family(kind), _family(kind)
+    ref.config.eos_token_id = model.config.eos_token_id = -1  # random weights: compare every step
+    oslo_b200.ready(TensorParallel(model, pc), pc)
+    ids = torch.randint(3, 100, (2, 7), generator=torch.Generator().manual_seed(1))
+    for beams in (1, 2):
+        assert torch.equal(model.generate(ids, None, max_new_tokens=5, num_beams=beams),
+                           ref.generate(ids, None, max_new_tokens=5, num_beams=beams)), (kind, beams)
+    pc.destroy()
+
+
+@pytest.mark.parametrize("kind", ["t5", "bart"])
+def test_encoder_decoder_generation_through_tensor_parallel_models(kind):
+    run_dist(_seq2seq_generate_worker, 2, kind)
