@@ -486,6 +486,12 @@ class Trainer:
             if logits is None and "labels" in batch:  # the fused loss consumed the logits: run once more without labels
                 logits = self.model(**{k: v for k, v in batch.items() if k != "labels"}).logits
             if logits is not None:
+                if self.pc is not None and self.pc.tensor_parallel_size > 1 and logits.dim() >= 2:
+                    # tensor-parallel heads may return a vocabulary (and, in the N-D layouts, batch) shard
+                    from oslo_b200.lightseq.inference import _whole_logits
+
+                    flat = _whole_logits(self.model, logits.reshape(-1, logits.shape[-1]))
+                    logits = flat.reshape(-1, *logits.shape[1:-1], flat.shape[-1]) if logits.dim() > 2 else flat
                 preds.append(logits.argmax(-1).cpu())
             if "labels" in batch:
                 labels.append(batch["labels"].cpu())

@@ -340,3 +340,25 @@ def test_trainer_under_parallel_configurations(name):
 
     with tempfile.TemporaryDirectory() as tmp:
         run_dist(_dist_trainer_worker, _DIST_CONFIGS[name][0], name, tmp, timeout=600)
+
+
+def _predict_tp_worker(rank, world, mode, tmp):
+    from oslo_b200.transformers import Trainer, TrainingArguments
+
+    cfg = {"tensor_parallelism": {"parallel_size": world, "parallel_mode": mode}, "backend": {"name": "gloo"}}
+    args = TrainingArguments(output_dir=tmp, per_device_eval_batch_size=8, oslo_config_path_or_dict=cfg)
+    ref = _model().eval()
+    out = Trainer(_model(), args, eval_dataset=_Toy(16)).predict(_Toy(16))
+    data = _Toy(16)
+    ids = torch.stack([data[i]["input_ids"] for i in range(16)])
+    with torch.no_grad():
+        want = ref(input_ids=ids).logits.argmax(-1)
+    assert out.predictions.shape == want.shape and torch.equal(out.predictions, want)  # not the argmax of a vocabulary shard
+
+
+@pytest.mark.parametrize("mode,world", [("1d", 2), ("2d", 4)])
+def test_predict_under_tensor_parallelism_sees_whole_logits(mode, world):
+    from dist_utils import run_dist
+
+    with tempfile.TemporaryDirectory() as tmp:
+        run_dist(_predict_tp_worker, world, mode, tmp, timeout=600)
