@@ -92,6 +92,13 @@ class TrainingArguments:
 
             self.oslo_config = OsloTrainerConfig(self.oslo_config_path_or_dict)
             self.parallel_context, self.wrapper_recipes = init_oslo_features(self.oslo_config)
+        mp = getattr(self.oslo_config, "mixed_precision", None) if self.oslo_config is not None else None
+        if mp and mp.get("enable", True):
+            # the configuration's mixed_precision section selects the compute dtype like the bf16 / fp16 flags do
+            want = mp.get("dtype", "bf16")
+            if (want == "bf16" and self.fp16) or (want == "fp16" and self.bf16):
+                raise ValueError(f"mixed_precision.dtype={want} contradicts the bf16 / fp16 flags")
+            self.bf16, self.fp16 = want == "bf16", want == "fp16"
 
     @property
     def dtype(self):

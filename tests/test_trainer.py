@@ -362,3 +362,21 @@ def test_predict_under_tensor_parallelism_sees_whole_logits(mode, world):
 
     with tempfile.TemporaryDirectory() as tmp:
         run_dist(_predict_tp_worker, world, mode, tmp, timeout=600)
+
+
+def test_mixed_precision_section_selects_the_compute_dtype(monkeypatch):
+    from oslo_b200.transformers import TrainingArguments
+
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
+        monkeypatch.delenv(k, raising=False)
+    cfg = {"mixed_precision": {"enable": True, "dtype": "bf16"}, "backend": {"name": "gloo"}}
+    args = TrainingArguments(output_dir="unused", oslo_config_path_or_dict=cfg)
+    try:
+        assert args.bf16 and not args.fp16 and args.dtype == torch.bfloat16
+        with pytest.raises(ValueError):
+            TrainingArguments(output_dir="unused", fp16=True, oslo_config=args.oslo_config, parallel_context=args.parallel_context)
+        off = TrainingArguments(output_dir="unused", parallel_context=args.parallel_context,
+                                oslo_config=type(args.oslo_config)({"mixed_precision": {"enable": False, "dtype": "bf16"}}))
+        assert off.dtype == torch.float32
+    finally:
+        args.parallel_context.destroy()
