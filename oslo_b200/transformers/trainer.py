@@ -204,8 +204,9 @@ class Trainer:
 
             inner = torch.optim.AdamW(params, lr=a.learning_rate, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
                                       weight_decay=a.weight_decay)
+            scaling = dict(initial_scale=a.fp16_init_scale, growth_interval=a.fp16_growth_interval) if a.fp16 else {}
             self.zero = opt = ZeroRedundancyOptimizer(inner, parallel_context=self.pc, partition_grad=dp["zero_stage"] == 2,
-                                                      clip_grad_norm=a.max_grad_norm, **(dp.get("params") or {}))
+                                                      clip_grad_norm=a.max_grad_norm, **scaling, **(dp.get("params") or {}))
         if self.hetero is not None:
             from oslo_b200.parallel.data_parallel.zero.hetero import HeteroOptimizer
 
