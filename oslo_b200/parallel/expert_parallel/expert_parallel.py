@@ -35,7 +35,9 @@ def _is_conv1d(m):
 
 
 class ExpertParallel(ParallelWrapper):
-    parallelism_priority = 1
+    #: before the tensor-parallel wrapper (priority 0): experts are built from the whole feed-forward linears, and the
+    #: tensor-parallel wrapper then leaves everything inside an expert block alone
+    parallelism_priority = -1
 
     def __init__(self, module: nn.Module, parallel_context=None, num_enc_experts: Union[int, dict, None] = None,
                  num_dec_experts: Union[int, dict, None] = None, top_k: int = 2, capacity_factor_train: float = 1.0,

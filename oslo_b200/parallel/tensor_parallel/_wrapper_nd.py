@@ -170,8 +170,11 @@ def parallelize_nd(tp):
             new.col_rank = pc.get_local_rank(M.TENSOR_2D_ROW)
         return new
 
+    from .tensor_parallel import _modules_inside_expert_blocks
+
+    inside_experts = _modules_inside_expert_blocks(module)
     for name, child in list(module.named_modules()):
-        if name == "" or (head is not None and child is head):
+        if name == "" or (head is not None and child is head) or id(child) in inside_experts:
             continue
         if emb is not None and child is emb:
             full = child.weight.shape

@@ -59,6 +59,21 @@ def _set_child(root: nn.Module, dotted: str, new: nn.Module):
                     m._modules[key] = new
 
 
+def _modules_inside_expert_blocks(root: nn.Module) -> set:
+    """Routers and experts of a mixture-of-experts layer are placed by the expert-parallel wrapper; the tensor-parallel
+    wrapper leaves everything inside such a block alone (a router called ``...c_fc.gate.wg`` is not the ``c_fc`` linear the
+    mapping names)."""
+    try:
+        from oslo_b200.parallel.expert_parallel.layers import ExpertParallelBehindBlock, ExpertParallelFrontBlock
+    except ImportError:
+        return set()
+    out = set()
+    for m in root.modules():
+        if isinstance(m, (ExpertParallelFrontBlock, ExpertParallelBehindBlock)):
+            out.update(id(d) for d in m.modules())
+    return out
+
+
 def _embedding_aliases(root: nn.Module, emb: nn.Module):
     """Names of the OTHER embedding modules that hold ``emb``'s weight parameter (libraries that give an encoder and a
     decoder their own ``nn.Embedding`` tied to the shared table): they must become the same sharded module."""
@@ -312,8 +327,9 @@ class TensorParallel(ParallelWrapper):
                         self._divided_attrs.append((m, attr, v))  # rolled back by deparallelize()
                         setattr(m, attr, v // tp)
 
+        inside_experts = _modules_inside_expert_blocks(module)
         for name, child in list(module.named_modules()):
-            if name == "":
+            if name == "" or id(child) in inside_experts:
                 continue
             if emb is not None and child is emb:
                 full = child.weight.shape

@@ -131,3 +131,39 @@ def test_gate_capacity_and_aux_loss():
     assert l_aux.item() > 0
     kept = slot[slot >= 0]
     assert kept.unique().numel() == kept.numel()  # no two tokens share a buffer row
+
+
+def _ep_tp_worker(rank, world, kind):
+    """Expert x tensor parallelism (2 x 2 ranks): the experts are built from the whole feed-forward linears before the
+    tensor-parallel wrapper shards the rest, which leaves routers and experts alone; the loss equals the expert-parallel-only
+    model's."""
+    import os
+    import sys
+
+    import oslo_b200
+    from oslo_b200 import ParallelContext
+    from oslo_b200.parallel import ExpertParallel, TensorParallel
+
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from test_tp_1d import _family
+
+    pc = ParallelContext.from_torch(data_parallel_size=2, tensor_parallel_size=2, expert_parallel_size=2, backend="gloo", seed=0)
+    model = _family(kind).train()
+    ExpertParallel(model, pc, num_dec_experts=4, top_k=2, capacity_factor_train=4.0)
+    TensorParallel(model, pc)
+    oslo_b200.ready(model, pc)
+    sharded = [n for n, p in model.named_parameters() if hasattr(p, "oslo_shard")]
+    assert sharded and not any("gate" in n or "experts" in n for n in sharded), sharded
+    ids = torch.randint(1, 100, (2, 12), generator=torch.Generator().manual_seed(1))
+    out = model(input_ids=ids, labels=ids)
+    out.loss.backward()
+    ref = _family(kind).train()
+    ExpertParallel(ref, pc, num_dec_experts=4, top_k=2, capacity_factor_train=4.0).parallelize()
+    want = ref(input_ids=ids, labels=ids).loss
+    assert abs(float(out.loss) - float(want)) < 1e-4, (kind, float(out.loss), float(want))
+    pc.destroy()
+
+
+@pytest.mark.parametrize("kind", ["gpt2", "neox"])
+def test_expert_parallel_with_tensor_parallel(kind):
+    run_dist(_ep_tp_worker, 4, kind)
