@@ -59,6 +59,11 @@ class ExpertParallel(ParallelWrapper):
         self.mapping = ExpertParallelMapping(mapping)
         self.ep_size = pc.get_world_size(ParallelMode.EXPERT) if pc.is_initialized(ParallelMode.EXPERT) else 1
         self.ep_rank = pc.get_local_rank(ParallelMode.EXPERT) if pc.is_initialized(ParallelMode.EXPERT) else 0
+        if self.ep_size > 1 and pc.pipeline_parallel_size > 1:
+            # Two pipeline stages x two expert ranks (four gloo ranks) did not finish a step: the experts' exchange and the
+            # pipeline's point-to-point schedule wait on each other.  Refused up front rather than left to hang.
+            raise NotImplementedError("expert parallelism (size > 1) cannot be combined with pipeline parallelism; "
+                                      "use tensor and / or data parallelism around the experts")
         if sync_dense_grads is None:
             sync_dense_grads = not pc.topology.expert_overlay
         self.sync_dense_grads = sync_dense_grads and self.ep_size > 1

@@ -167,3 +167,22 @@ def _ep_tp_worker(rank, world, kind):
 @pytest.mark.parametrize("kind", ["gpt2", "neox"])
 def test_expert_parallel_with_tensor_parallel(kind):
     run_dist(_ep_tp_worker, 4, kind)
+
+
+def test_expert_parallel_refuses_pipeline_parallel():
+    from oslo_b200.parallel import ExpertParallel
+
+    class _PC:
+        pipeline_parallel_size = 2
+
+        def is_initialized(self, mode):
+            return True
+
+        def get_world_size(self, mode):
+            return 2
+
+        def get_local_rank(self, mode):
+            return 0
+
+    with pytest.raises(NotImplementedError, match="pipeline"):
+        ExpertParallel(torch.nn.Linear(2, 2), _PC(), num_dec_experts=4)
