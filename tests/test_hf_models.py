@@ -418,3 +418,36 @@ def _vp_loss_other_worker(rank, world, kind):
 @pytest.mark.parametrize("kind", ["bert", "t5", "bart"])
 def test_hf_vocab_parallel_loss_masked_and_encoder_decoder(kind):
     run_dist(_vp_loss_other_worker, 2, kind, timeout=600)
+
+
+def _reload_worker(rank, world, kind, two_d, tmp):
+    """Per-rank shards written by ``save_pretrained`` load back into a freshly sharded copy with other weights
+    (``from_parallelized``), including tables that several modules share."""
+    import oslo_b200
+    from oslo_b200 import ParallelContext, ParallelMode
+    from oslo_b200.parallel import TensorParallel
+
+    pc = ParallelContext.from_torch(tensor_parallel_size=world, backend="gloo", seed=0,
+                                    tensor_parallel_mode=ParallelMode.TENSOR_2D if two_d else ParallelMode.TENSOR_1D)
+    ref, first = _build(kind), _build(kind)
+    saved = TensorParallel(first, pc)
+    oslo_b200.ready(saved, pc)
+    saved.save_pretrained(tmp)
+    torch.distributed.barrier()
+    other = _build(kind)
+    with torch.no_grad():
+        for p in other.parameters():
+            p.mul_(0.5)
+    loaded = TensorParallel(other, pc)
+    oslo_b200.ready(loaded, pc)
+    loaded.from_parallelized(tmp)
+    feed = {k: torch.cat([v, v]) for k, v in _inputs(kind).items()}
+    with torch.no_grad():
+        assert torch.allclose(loaded(**feed).logits, ref(**feed).logits, rtol=1e-4, atol=1e-5)
+    pc.destroy()
+
+
+@pytest.mark.parametrize("kind,world,two_d", [("bart", 2, False), ("t5", 4, True)])
+def test_hf_model_sharded_checkpoint_reload(kind, world, two_d):
+    with tempfile.TemporaryDirectory() as tmp:
+        run_dist(_reload_worker, world, kind, two_d, tmp, timeout=600)
