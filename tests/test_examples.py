@@ -9,7 +9,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 EX = os.path.join(ROOT, "examples")
 
 
-def _run(script, *args, nproc=1, port=29711):
+def _run(script, *args, nproc=1, port=None):
+    from dist_utils import free_port
+
+    port = free_port()  # (the argument is kept for readability of the call sites; a free port is always taken)
     env = dict(os.environ, OMP_NUM_THREADS="1", PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
     if nproc == 1:
         cmd = [sys.executable, os.path.join(EX, script), *args]
